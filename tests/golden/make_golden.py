@@ -1,0 +1,84 @@
+"""Generates tests/golden/*.npz from the REFERENCE's own code (oracle/_ref/libizb_ref.so, built by oracle/Makefile from
+the reference sources in place).  Run where the reference sources exist:  python tests/golden/make_golden.py
+
+What is stored (all inputs seeded; every array small):
+  quantize.npz   x -> aq, asc, absum from quantize_act_cpu (src/quants.h:626), incl. zero blocks, ties and denormals
+  decode.npz     random Q4_K / Q8_0 superblocks -> decode_sb fields (src/quants.h:89) and dequant_row (:519)
+  fp16.npz       fp16_to_f32 over every 16-bit pattern, f32_to_fp16 over a seeded sample (src/quants.h:17-52)
+  forward.npz    tools/ref_forward.cpp:251 matmul() outputs (REF_Q=all REF_QB=32) on small Q4_K / Q8_0 tensors
+  rawsb.npz      gpu_raw_sb (src/quants.h:728) of Q8_0 superblocks: the regrouped form the weight loader must make
+"""
+import os
+import sys
+import tempfile
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from arcinferzero_b200 import synth as S  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def main():
+    O.build(ref=True)
+    assert O.ref() is not None, "oracle/_ref/libizb_ref.so missing: the reference sources are needed"
+    rng = np.random.default_rng(20261125)
+
+    # ---- quantize
+    x = rng.standard_normal((9, 768), dtype=np.float32)
+    x[1, 32:64] = 0.0                      # an all-zero block: scale 0, inv 0
+    x[2, 0:32] = 0.5                       # all equal: every value -> 127
+    x[3, 64:96] = np.linspace(-1, 1, 32)   # symmetric ramp
+    x[4, 0:32] = (np.arange(32) - 15.5) * (1.0 / 127.0) * 15.5  # products near .5 ties
+    x[5, :] *= 1e-30                       # tiny values (scale near denormal range)
+    x[6, :] *= 1e30                        # huge values
+    x[7, 96:128] = np.float32(1e-42)       # denormal inputs
+    x[8, 0:32] = np.where(np.arange(32) % 2 == 0, 1.0, -1.0) * 3.0
+    aq, asc, absum = O.ref_quantize_act(x)
+    np.savez_compressed(os.path.join(OUT, "quantize.npz"), x=x, aq=aq, asc=asc, absum=absum)
+
+    # ---- decode / dequant
+    w4 = S.make_weight(S.GGML_Q4_K, 6, 512, 11)
+    w8 = S.make_weight(S.GGML_Q8_0, 6, 512, 12)
+    w4[0, 0:4] = 0                         # d = dmin = 0
+    w4[1, 0:2] = np.array([1, 0], np.uint8)  # fp16 subnormal d
+    w4[2, 4:16] = 0xFF                     # every scale / min = 63
+    w8[0, 0:2] = 0
+    w8[1, 2:34] = np.array([-128] * 32, np.int8).view(np.uint8)
+    d4 = [O.ref_decode_sb(12, w4[n, 144 * s:144 * (s + 1)]) for n in range(6) for s in range(2)]
+    d8 = [O.ref_decode_sb(8, w8[n, 272 * s:272 * (s + 1)]) for n in range(6) for s in range(2)]
+    np.savez_compressed(
+        os.path.join(OUT, "decode.npz"), w4=w4, w8=w8,
+        q4_d=np.array([t[0] for t in d4], np.float32), q4_dmin=np.array([t[1] for t in d4], np.float32),
+        q4_sc=np.stack([t[2] for t in d4]), q4_mn=np.stack([t[3] for t in d4]), q4_q=np.stack([t[4] for t in d4]),
+        q8_d=np.stack([t[5] for t in d8]), q8_q=np.stack([t[4] for t in d8]),
+        deq4=O.ref_dequant_rows(12, w4, 512), deq8=O.ref_dequant_rows(8, w8, 512))
+
+    # ---- fp16
+    allh = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    f = np.array([O.ref().ref_fp16_to_f32(int(h)) for h in allh], np.float32)
+    xs = np.concatenate([rng.standard_normal(2000).astype(np.float32) * np.float32(10.0) ** rng.integers(-9, 6, 2000),
+                         np.array([0, -0.0, 65504, 65520, 1e-8, 6e-8, 5.96e-8, 2.98e-8, np.inf, -np.inf], np.float32)])
+    h = np.array([O.ref().ref_f32_to_fp16(float(v)) for v in xs], np.uint16)
+    np.savez_compressed(os.path.join(OUT, "fp16.npz"), to_f32=f.view(np.uint32), xs=xs, to_f16=h)
+
+    # ---- ref_forward matmul
+    xa = rng.standard_normal((5, 512), dtype=np.float32)
+    with tempfile.TemporaryDirectory() as d:
+        p = os.path.join(d, "t.gguf")
+        S.write_gguf(p, {"q4": (12, w4, 6, 512), "q8": (8, w8, 6, 512)})
+        y4 = O.ref_forward_matmul(p, "q4", xa, 6)
+        y8 = O.ref_forward_matmul(p, "q8", xa, 6)
+    np.savez_compressed(os.path.join(OUT, "forward.npz"), x=xa, y4=y4, y8=y8)
+
+    # ---- reference GPU raw form of Q8_0
+    raw = np.stack([O.ref_gpu_raw_sb(8, w8[n, 272 * s:272 * (s + 1)]) for n in range(6) for s in range(2)])
+    np.savez_compressed(os.path.join(OUT, "rawsb.npz"), raw8=raw)
+    print("golden vectors written to", OUT)
+
+
+if __name__ == "__main__":
+    main()

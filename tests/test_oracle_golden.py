@@ -1,0 +1,150 @@
+"""The CPU oracle (oracle/izb_oracle.c) against vectors produced by the reference's own code (tests/golden/, made by
+tests/golden/make_golden.py) and, when oracle/_ref is present, against that code live."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from arcinferzero_b200 import synth as S
+from oracle import oracle as O
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def test_quantize_matches_reference_vectors(golden_dir):
+    g = np.load(os.path.join(golden_dir, "quantize.npz"))
+    aq, asc, absum = O.quantize_act(g["x"])
+    assert (aq == g["aq"]).all()
+    assert (bits(asc) == bits(g["asc"])).all()
+    assert (absum == g["absum"]).all()
+
+
+def test_quantize_padding_rows_are_zero(golden_dir):
+    g = np.load(os.path.join(golden_dir, "quantize.npz"))
+    aq, asc, absum = O.quantize_act(g["x"], Mp=16)
+    assert (aq[:9] == g["aq"]).all() and (aq[9:] == 0).all()
+    assert (bits(asc[:, :9]) == bits(g["asc"])).all() and (asc[:, 9:] == 0).all()
+    assert (absum[:, 9:] == 0).all()
+
+
+def test_decode_and_dequant_match_reference_vectors(golden_dir):
+    g = np.load(os.path.join(golden_dir, "decode.npz"))
+    i = 0
+    for n in range(6):
+        for s in range(2):
+            d, dmin, sc, mn, q = O.decode_q4k_sb(g["w4"][n, 144 * s:144 * (s + 1)])
+            assert np.float32(d) == g["q4_d"][i] and np.float32(dmin) == g["q4_dmin"][i]
+            assert (sc == g["q4_sc"][i]).all() and (mn == g["q4_mn"][i]).all() and (q == g["q4_q"][i]).all()
+            d8, q8 = O.decode_q8_0_sb(g["w8"][n, 272 * s:272 * (s + 1)])
+            assert (bits(d8) == bits(g["q8_d"][i])).all() and (q8 == g["q8_q"][i]).all()
+            i += 1
+    assert (bits(O.dequant_rows(12, g["w4"], 512)) == bits(g["deq4"])).all()
+    assert (bits(O.dequant_rows(8, g["w8"], 512)) == bits(g["deq8"])).all()
+
+
+def test_fp16_conversions_match_reference_vectors(golden_dir):
+    g = np.load(os.path.join(golden_dir, "fp16.npz"))
+    L = O.lib()
+    got = np.array([L.orc_fp16_to_f32(h) for h in range(65536)], np.float32)
+    same = bits(got) == g["to_f32"]
+    nan = np.isnan(got)
+    assert (same | nan).all() and (np.isnan(g["to_f32"].view(np.float32)) == nan).all()
+    assert (np.array([L.orc_f32_to_fp16(float(v)) for v in g["xs"]], np.uint16) == g["to_f16"]).all()
+    # numpy's float16 agrees with the reference's conversion (the generator relies on it)
+    assert (g["xs"].astype(np.float16).view(np.uint16) == g["to_f16"]).all()
+    assert (bits(np.arange(65536, dtype=np.uint32).astype(np.uint16).view(np.float16).astype(np.float32))[~nan]
+            == g["to_f32"][~nan]).all()
+
+
+def test_f64_order_is_ref_forward_matmul(golden_dir):
+    """orc_matmul_f64 == tools/ref_forward.cpp matmul() bit for bit; the two kernel orders agree with it to ~1e-7."""
+    g = np.load(os.path.join(golden_dir, "forward.npz"))
+    d = np.load(os.path.join(golden_dir, "decode.npz"))
+    aq, asc, _ = O.quantize_act(g["x"])
+    for qt, w, y in ((12, d["w4"], g["y4"]), (8, d["w8"], g["y8"])):
+        assert (bits(O.matmul(qt, w, 512, aq, asc, 5, "f64")) == bits(y)).all()
+        for order in ("gemm", "gemv"):
+            err = np.abs(O.matmul(qt, w, 512, aq, asc, 5, order) - y).max() / np.abs(y).max()
+            assert err < 1e-6, (qt, order, err)
+
+
+def test_pack_q4k_round_trip():
+    rng = np.random.default_rng(7)
+    R = 64
+    d = rng.uniform(0, 0.01, R).astype(np.float16)
+    dmin = rng.uniform(0, 0.01, R).astype(np.float16)
+    sc = rng.integers(0, 64, (R, 8), dtype=np.uint8)
+    mn = rng.integers(0, 64, (R, 8), dtype=np.uint8)
+    q = rng.integers(0, 16, (R, 256), dtype=np.uint8)
+    p = S.pack_q4k(d, dmin, sc, mn, q)
+    for r in range(R):
+        dd, dm, s2, m2, q2 = O.decode_q4k_sb(p[r])
+        assert np.float32(dd) == np.float32(d[r]) and np.float32(dm) == np.float32(dmin[r])
+        assert (s2 == sc[r]).all() and (m2 == mn[r]).all() and (q2 == q[r]).all()
+        out = np.zeros(144, np.uint8)
+        O.lib().orc_q4k_pack_sb(int(d[r:r + 1].view(np.uint16)[0]), int(dmin[r:r + 1].view(np.uint16)[0]),
+                                sc[r].ctypes.data, mn[r].ctypes.data, q[r].ctypes.data, out.ctypes.data)
+        assert (out == p[r]).all()
+
+
+def test_block_dots_are_the_sum_of_products():
+    x = S.make_act(3, 512, 21)
+    aq, asc, absum = O.quantize_act(x)
+    for qt in (12, 8):
+        w = S.make_weight(qt, 5, 512, 22 + qt)
+        dots, asum = O.block_dots(qt, w, 512, aq)
+        for n in range(5):
+            qs = []
+            for s in range(2):
+                qs.append(O.decode_q4k_sb(w[n, 144 * s:144 * s + 144])[4] if qt == 12 else O.decode_q8_0_sb(w[n, 272 * s:272 * s + 272])[1])
+            qv = np.concatenate(qs).astype(np.int64)
+            want = (aq.astype(np.int64) * qv[None, :]).reshape(3, 16, 32).sum(-1)
+            assert (dots[:, n, :] == want).all()
+        assert (asum == aq.astype(np.int64).reshape(3, 16, 32).sum(-1)).all()
+        assert (absum.astype(np.int64).reshape(16, 2, 3).sum(1).T == asum).all()
+
+
+@pytest.mark.skipif(O.ref() is None, reason="oracle/_ref not built (reference sources absent)")
+def test_live_reference_agrees_on_fresh_inputs():
+    x = S.make_act(11, 1024, 99)
+    aq, asc, absum = O.quantize_act(x)
+    raq, rasc, rab = O.ref_quantize_act(x)
+    assert (aq == raq).all() and (bits(asc) == bits(rasc)).all() and (absum == rab).all()
+    for qt in (12, 8):
+        w = S.make_weight(qt, 17, 1024, 100 + qt)
+        assert (bits(O.dequant_rows(qt, w, 1024)) == bits(O.ref_dequant_rows(qt, w, 1024))).all()
+        with tempfile.TemporaryDirectory() as d:
+            p = os.path.join(d, "t.gguf")
+            S.write_gguf(p, {"w": (qt, w, 17, 1024)})
+            y = O.ref_forward_matmul(p, "w", x, 17)
+        assert (bits(O.matmul(qt, w, 1024, aq, asc, 11, "f64")) == bits(y)).all()
+
+
+def test_store_modes():
+    x = S.make_act(4, 256, 5)
+    aq, asc, _ = O.quantize_act(x)
+    w = S.make_weight(12, 8, 256, 6)
+    base = O.matmul(12, w, 256, aq, asc, 4, "gemm")
+    c0 = np.random.default_rng(1).standard_normal((4, 20)).astype(np.float32)
+    add = O.matmul(12, w, 256, aq, asc, 4, "gemm", C_in=c0, ldc=20, c_off=3, acc=1)
+    assert (bits(add[:, 3:11]) == bits(base + c0[:, 3:11])).all()
+    assert (bits(add[:, :3]) == bits(c0[:, :3])).all() and (bits(add[:, 11:]) == bits(c0[:, 11:])).all()
+    sw = O.matmul(12, w, 256, aq, asc, 4, "gemm", C_in=c0, ldc=20, c_off=3, acc=2)
+    g = c0[:, 3:11]
+    want = base * (g / (np.float32(1) + np.exp(-g, dtype=np.float32)))
+    assert np.abs(sw[:, 3:11] - want).max() <= 1e-5 * np.abs(want).max()
+
+
+def test_tp_range_properties():
+    for total, unit in ((17408, 256), (8, 1), (151936, 16), (5120, 256)):
+        for N in (1, 2, 3, 4, 8):
+            rs = [O.tp_range(total, unit, N, r) for r in range(N)]
+            assert rs[0][0] == 0 and rs[-1][1] == total // unit * unit
+            for a, b in zip(rs, rs[1:]):
+                assert a[1] == b[0]
+            sizes = [e - b for b, e in rs]
+            assert all(s % unit == 0 for s in sizes) and sizes == sorted(sizes, reverse=True)
+            assert max(sizes) - min(sizes) <= unit

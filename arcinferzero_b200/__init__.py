@@ -1,0 +1,290 @@
+"""arcinferzero_b200: the B200 (sm_100a) implementation of inferzero's quantised matrix product.
+
+The product is the CUDA library `libizb200.so` behind the C ABI of include/izb200.h (built in-tree by
+arcinferzero_b200/build.py).  This module is the thin ctypes binding the tests and the benchmark use: it passes raw
+device pointers of torch tensors (torch is only the owner of device memory and streams here) and raises on any non-zero
+status.  There is no CPU path: importing works without a GPU, every call needs one.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libizb200.so")
+
+Q8_0, Q4_K = 8, 12
+GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
+
+# every symbol include/izb200.h declares (tests check the library exports each of them)
+SYMBOLS = [
+    "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status",
+    "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
+    "izb_quantize_act", "izb_swiglu_quant",
+    "izb_matmul", "izb_gemv", "izb_gemm", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
+    "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
+    "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_destroy", "izb_tp_allreduce_rows",
+    "izb_tp_reduce_quant_gather",
+]
+
+
+class IzbError(RuntimeError):
+    def __init__(self, status: int, detail: str):
+        super().__init__(f"izb200 status {status}: {detail}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it was never built: there is nothing to fall back to."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m arcinferzero_b200.build` "
+                              "(this package has no CPU or PyTorch fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.izb_status_string.restype = C.c_char_p
+        _lib.izb_last_error.restype = C.c_char_p
+        _lib.izb_launch_count.restype = C.c_uint64
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        L = lib()
+        raise IzbError(rc, f"{L.izb_status_string(rc).decode()}: {L.izb_last_error().decode()}")
+
+
+def _p(t) -> C.c_void_p:
+    """Device (or pinned host) pointer of a torch tensor / numpy array, or NULL."""
+    if t is None:
+        return C.c_void_p(0)
+    if isinstance(t, np.ndarray):
+        return C.c_void_p(t.ctypes.data)
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream() -> C.c_void_p:
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def launch_count() -> int:
+    return int(lib().izb_launch_count())
+
+
+def pad_rows(M: int) -> int:
+    """Row padding of the reference engine (zero/engine.h:521-522): multiples of 128 from 128 rows on, else of 16."""
+    return (M + 127) // 128 * 128 if M >= 128 else (M + 15) // 16 * 16
+
+
+class Weight:
+    """Device weight handle (izb_weight): a matrix or a stack of n_mats matrices in GGUF block form."""
+
+    def __init__(self, qtype: int, rows: np.ndarray, N: int, K: int, n_mats: int = 1, device: int = 0,
+                 row_range: tuple[int, int] | None = None, col_range: tuple[int, int] | None = None):
+        rows = np.ascontiguousarray(rows, np.uint8)
+        self.handle = C.c_void_p(0)
+        n0, n1 = row_range or (0, N)
+        k0, k1 = col_range or (0, K)
+        _check(lib().izb_weight_create_slice(qtype, _p(rows), n_mats, N, K, n0, n1, k0, k1, device, C.byref(self.handle)))
+        self.qtype, self.N, self.K, self.n_mats, self.device = qtype, n1 - n0, k1 - k0, n_mats, device
+
+    @property
+    def nbytes(self) -> int:
+        b = C.c_size_t(0)
+        _check(lib().izb_weight_info(self.handle, None, None, None, None, C.byref(b)))
+        return b.value
+
+    def close(self):
+        if self.handle:
+            lib().izb_weight_destroy(self.handle)
+            self.handle = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def quantize_act(x, Mp: int | None = None, want_absum: bool = False, out=None):
+    """x: [M, K] f32 cuda tensor (row stride may exceed K) -> aq [Mp, K] int8, asc [K/32, Mp] f32, absum or None."""
+    import torch
+    M, K = x.shape
+    Mp = Mp or pad_rows(M)
+    if out is None:
+        aq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
+        asc = torch.empty((K // 32, Mp), dtype=torch.float32, device=x.device)
+        absum = torch.empty((K // 16, Mp), dtype=torch.int16, device=x.device) if want_absum else None
+    else:
+        aq, asc, absum = out
+    _check(lib().izb_quantize_act(_p(x), x.stride(0), M, Mp, K, _p(aq), _p(asc), _p(absum), _stream()))
+    return aq, asc, absum
+
+
+def swiglu_quant(gu, F: int, Mp: int | None = None, want_h: bool = False):
+    """gu: [M, 2F] f32 (gate | up) -> quantised h = silu(gate) * up; optionally h itself."""
+    import torch
+    M = gu.shape[0]
+    Mp = Mp or pad_rows(M)
+    aq = torch.empty((Mp, F), dtype=torch.int8, device=gu.device)
+    asc = torch.empty((F // 32, Mp), dtype=torch.float32, device=gu.device)
+    h = torch.empty((M, F), dtype=torch.float32, device=gu.device) if want_h else None
+    _check(lib().izb_swiglu_quant(_p(gu), gu.stride(0), 1, M, Mp, F, _p(h), _p(aq), _p(asc), None, _stream()))
+    return aq, asc, h
+
+
+def matmul(w: Weight, aq, asc, T: int, out=None, c_off: int = 0, acc: int = 0, mat: int = 0):
+    """Engine::matmul dispatch: T == 1 GEMV, 2..8 few-row GEMV, else GEMM.  out: [rows, ldc] f32 (default [Mp, N])."""
+    import torch
+    Mp = asc.shape[1]
+    if out is None:
+        out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
+    _check(lib().izb_matmul(w.handle, mat, _p(aq), _p(asc), None, T, Mp, _p(out), out.stride(0), c_off, acc, _stream()))
+    return out
+
+
+def gemv(w: Weight, aq, asc, T: int, out=None, c_off: int = 0, acc: int = 0, mat: int = 0):
+    import torch
+    Mp = asc.shape[1]
+    if out is None:
+        out = torch.empty((T, w.N), dtype=torch.float32, device=aq.device)
+    _check(lib().izb_gemv(w.handle, mat, _p(aq), _p(asc), T, Mp, _p(out), out.stride(0), c_off, acc, _stream()))
+    return out
+
+
+def gemm(w: Weight, aq, asc, M: int | None = None, out=None, c_off: int = 0, acc: int = 0, impl: int = GEMM_AUTO,
+         mat: int = 0):
+    import torch
+    Mp = asc.shape[1]
+    M = M or Mp
+    if out is None:
+        out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
+    _check(lib().izb_gemm(w.handle, mat, _p(aq), _p(asc), M, Mp, _p(out), out.stride(0), c_off, acc, impl, _stream()))
+    return out
+
+
+def block_dots(w: Weight, aq, M: int, impl: int = GEMM_CORE, mat: int = 0):
+    import torch
+    dots = torch.empty((M, w.N, w.K // 32), dtype=torch.int32, device=aq.device)
+    _check(lib().izb_block_dots(w.handle, mat, _p(aq), M, _p(dots), impl, _stream()))
+    return dots
+
+
+def selfcheck(device: int = 0) -> None:
+    _check(lib().izb_selfcheck(device))
+
+
+def device_status(device: int = 0) -> int:
+    w = C.c_uint32(0)
+    rc = lib().izb_device_status(device, C.byref(w))
+    if rc not in (0, -7):
+        _check(rc)
+    return w.value
+
+
+def matmul_host(w: Weight, x_host, out_host, mat: int = 0) -> None:
+    """The host-buffer call: x_host [M, K] f32 and out_host [M, N] f32 live in (ideally pinned) host memory."""
+    M = x_host.shape[0]
+    _check(lib().izb_matmul_host(w.handle, mat, _p(x_host), M, _p(out_host), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------- mixture of experts
+def moe_route(logits, NU: int):
+    import torch
+    T, NE = logits.shape
+    ids = torch.empty((T, NU), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, NU), dtype=torch.float32, device=logits.device)
+    counts = torch.empty((NE,), dtype=torch.int32, device=logits.device)
+    _check(lib().izb_moe_route(_p(logits), logits.stride(0), T, NE, NU, _p(ids), _p(wts), _p(counts), _stream()))
+    return ids, wts, counts
+
+
+def moe_sort(ids, wts, counts, TM: int):
+    import torch
+    T, NU = ids.shape
+    NE = counts.shape[0]
+    dev = ids.device
+    max_tiles = (T * NU + TM - 1) // TM + NE
+    offs = torch.empty((NE + 1,), dtype=torch.int32, device=dev)
+    tiles = torch.zeros((1 + 3 * max_tiles,), dtype=torch.int32, device=dev)
+    stok = torch.empty((T * NU,), dtype=torch.int32, device=dev)
+    swt = torch.empty((T * NU,), dtype=torch.float32, device=dev)
+    inv = torch.empty((T * NU,), dtype=torch.int32, device=dev)
+    _check(lib().izb_moe_sort(_p(ids), _p(wts), _p(counts), T, NE, NU, TM, _p(offs), _p(tiles), max_tiles, _p(stok), _p(swt),
+                              _p(inv), _stream()))
+    return offs, tiles, max_tiles, stok, swt, inv
+
+
+def moe_gateup(wg: Weight, wu: Weight, aq, asc, tiles, max_tiles: int, TM: int, stok, S: int):
+    import torch
+    h = torch.empty((S, wg.N), dtype=torch.float32, device=aq.device)
+    _check(lib().izb_moe_gateup(wg.handle, wu.handle, _p(aq), _p(asc), asc.shape[1], _p(tiles), max_tiles, TM, _p(stok), _p(h),
+                                _stream()))
+    return h
+
+
+def moe_down(wd: Weight, hq, hsc, tiles, max_tiles: int, TM: int, swt, S: int):
+    import torch
+    y = torch.empty((S, wd.N), dtype=torch.float32, device=hq.device)
+    _check(lib().izb_moe_down(wd.handle, _p(hq), _p(hsc), hsc.shape[1], _p(tiles), max_tiles, TM, _p(swt), _p(y), _stream()))
+    return y
+
+
+def moe_combine(x, y, inv, NU: int):
+    T, E = x.shape
+    _check(lib().izb_moe_combine(_p(x), _p(y), _p(inv), T, NU, E, _stream()))
+    return x
+
+
+# ---------------------------------------------------------------------------------------------- tensor parallel
+def tp_range(total: int, unit: int, nranks: int, rank: int) -> tuple[int, int]:
+    b, e = C.c_int64(0), C.c_int64(0)
+    _check(lib().izb_tp_range(C.c_int64(total), C.c_int64(unit), nranks, rank, C.byref(b), C.byref(e)))
+    return b.value, e.value
+
+
+def tp_add(x, parts):
+    n = x.numel()
+    _check(lib().izb_tp_add(_p(x), _p(parts), C.c_size_t(n), parts.shape[0], C.c_size_t(n), _stream()))
+    return x
+
+
+class TpComm:
+    """NCCL communicator of the library (izb_tp); the 128-byte id travels through torch.distributed."""
+
+    def __init__(self, nranks: int, rank: int, device: int):
+        import torch
+        import torch.distributed as dist
+        idbuf = (C.c_char * 128)()
+        if nranks > 1:
+            if rank == 0:
+                _check(lib().izb_tp_unique_id(idbuf))
+            t = torch.frombuffer(bytearray(idbuf.raw), dtype=torch.uint8).clone()
+            if dist.get_backend() == "nccl":
+                t = t.cuda(device)
+            dist.broadcast(t, src=0)
+            idbuf = (C.c_char * 128).from_buffer_copy(bytes(t.cpu().numpy().tobytes()))
+        self.handle = C.c_void_p(0)
+        _check(lib().izb_tp_create(nranks, rank, idbuf, device, C.byref(self.handle)))
+        self.nranks, self.rank, self.device = nranks, rank, device
+
+    def allreduce_rows(self, x, part):
+        rows, E = part.shape
+        _check(lib().izb_tp_allreduce_rows(self.handle, _p(x), _p(part), rows, E, _stream()))
+        return x
+
+    def reduce_quant_gather(self, x, part, aq, asc, xsum=None):
+        rows, E = part.shape
+        _check(lib().izb_tp_reduce_quant_gather(self.handle, _p(x), _p(part), rows, E, _p(xsum), _p(aq), _p(asc), _stream()))
+        return aq, asc
+
+    def close(self):
+        if self.handle:
+            lib().izb_tp_destroy(self.handle)
+            self.handle = C.c_void_p(0)

@@ -1,0 +1,340 @@
+// C ABI of the library: weight handles, the row-count dispatch of Engine::matmul (zero/engine.h:1147-1251), the
+// verification entry points and the host-buffer convenience call.
+#include <cuda.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
+#include "izb_common.cuh"
+
+std::atomic<uint64_t> g_izb_launches{0};
+
+// kernels of the other translation units
+int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C,
+                         int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st);
+// returns IZB_OK, an error, or +1 when the tensor-core kernel does not take this shape
+int izb_gemm_tc_launch(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int M, int Mp, float* C, int ldc,
+                       int c_off, int acc, int32_t* dots, cudaStream_t st);
+int izb_make_raw_tensor_map(izb_weight* w);
+
+// ---------------------------------------------------------------------------------------------- errors
+static thread_local char t_err[512] = "";
+
+void izb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err, sizeof t_err, fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* izb_last_error(void) { return t_err; }
+extern "C" uint64_t izb_launch_count(void) { return g_izb_launches.load(); }
+
+extern "C" const char* izb_status_string(int s) {
+  switch (s) {
+    case IZB_OK: return "ok";
+    case IZB_ERR_ARG: return "bad argument";
+    case IZB_ERR_SHAPE: return "bad shape";
+    case IZB_ERR_TYPE: return "unsupported weight type";
+    case IZB_ERR_ALIGN: return "misaligned pointer or stride";
+    case IZB_ERR_CUDA: return "CUDA error";
+    case IZB_ERR_NCCL: return "NCCL error";
+    case IZB_ERR_TIMEOUT: return "device-side wait timed out";
+    case IZB_ERR_NOMEM: return "out of memory";
+    case IZB_ERR_SELFCHECK: return "self-check failed";
+    case IZB_ERR_LIMIT: return "capacity exceeded";
+    default: return "unknown status";
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- per-device state
+namespace {
+constexpr int kMaxDev = 16;
+struct DevState {
+  std::mutex mu;
+  uint32_t* err_word = nullptr;
+  void* ws[4] = {nullptr, nullptr, nullptr, nullptr};  // scratch arenas by user (izb_common.cuh: kWs*)
+  size_t ws_bytes[4] = {0, 0, 0, 0};
+  void* stage = nullptr;  // staging of the host-buffer call
+  size_t stage_bytes = 0;
+  int tc_ok = -1;  // -1 unknown, 0 self-check failed, 1 passed
+};
+DevState g_dev[kMaxDev];
+
+int check_device(int device) {
+  if (device < 0 || device >= kMaxDev) IZB_FAIL(IZB_ERR_ARG, "device %d out of range", device);
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device >= n) IZB_FAIL(IZB_ERR_CUDA, "no CUDA device %d (this library has no CPU path)", device);
+  cudaDeviceProp p;
+  IZB_CUDA(cudaGetDeviceProperties(&p, device));
+  if (p.major != 10) IZB_FAIL(IZB_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, p.major, p.minor);
+  return IZB_OK;
+}
+}  // namespace
+
+uint32_t* izb_device_error_word(int device) {
+  DevState& d = g_dev[device];
+  std::lock_guard<std::mutex> lk(d.mu);
+  if (!d.err_word) {
+    if (cudaMalloc(&d.err_word, 256) != cudaSuccess) return nullptr;
+    cudaMemset(d.err_word, 0, 256);
+  }
+  return d.err_word;
+}
+
+int izb_workspace(int device, int slot, size_t bytes, void** out) {
+  DevState& d = g_dev[device];
+  std::lock_guard<std::mutex> lk(d.mu);
+  if (bytes > d.ws_bytes[slot]) {
+    if (d.ws[slot]) {
+      IZB_CUDA(cudaDeviceSynchronize());
+      IZB_CUDA(cudaFree(d.ws[slot]));
+      d.ws[slot] = nullptr;
+      d.ws_bytes[slot] = 0;
+    }
+    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    if (cudaMalloc(&d.ws[slot], want) != cudaSuccess) {
+      cudaGetLastError();
+      IZB_FAIL(IZB_ERR_NOMEM, "workspace of %zu bytes on device %d", want, device);
+    }
+    d.ws_bytes[slot] = want;
+  }
+  *out = d.ws[slot];
+  return IZB_OK;
+}
+
+extern "C" int izb_device_status(int device, uint32_t* word) {
+  if (!word) IZB_FAIL(IZB_ERR_ARG, "device_status: null pointer");
+  if (int rc = check_device(device)) return rc;
+  uint32_t* p = izb_device_error_word(device);
+  if (!p) IZB_FAIL(IZB_ERR_NOMEM, "device_status: cannot allocate the error word");
+  IZB_CUDA(cudaDeviceSynchronize());
+  IZB_CUDA(cudaMemcpy(word, p, 4, cudaMemcpyDeviceToHost));
+  IZB_CUDA(cudaMemset(p, 0, 4));
+  return *word ? IZB_ERR_TIMEOUT : IZB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- weights
+namespace {
+// GGUF Q8_0 (34-byte blocks: fp16 d, 32 int8) -> per 256 values: 8 fp16 scales then 8 x 32 int8 (272 bytes, the same
+// count).  One thread per (superblock, 16-byte output piece); 17 pieces per superblock.
+__global__ void regroup_q8_0_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t n_sb) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_sb * 17) return;
+  const size_t sb = i / 17;
+  const int pc = (int)(i % 17);
+  const uint8_t* s = src + sb * 272;
+  uint8_t* d = dst + sb * 272 + pc * 16;
+  if (pc == 0) {
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      d[2 * b] = s[34 * b];
+      d[2 * b + 1] = s[34 * b + 1];
+    }
+  } else {
+    const int b = (pc - 1) >> 1, h = (pc - 1) & 1;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) d[k] = s[34 * b + 2 + 16 * h + k];
+  }
+}
+}  // namespace
+
+extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats, int N, int K, int n0, int n1, int k0, int k1,
+                                       int device, izb_weight** out) {
+  if (!h_rows || !out) IZB_FAIL(IZB_ERR_ARG, "weight_create: null pointer");
+  *out = nullptr;
+  if (type != IZB_Q8_0 && type != IZB_Q4_K) IZB_FAIL(IZB_ERR_TYPE, "weight_create: ggml type %d (only Q8_0 = 8 and Q4_K = 12)", type);
+  if (n_mats < 1 || N < 1 || K < 256 || K % 256) IZB_FAIL(IZB_ERR_SHAPE, "weight_create: %d x [%d x %d] (K must be a multiple of 256)", n_mats, N, K);
+  if (n0 < 0 || n1 > N || n0 >= n1 || k0 < 0 || k1 > K || k0 >= k1 || k0 % 256 || k1 % 256)
+    IZB_FAIL(IZB_ERR_SHAPE, "weight_create: slice rows [%d,%d) cols [%d,%d) of %d x %d (columns in whole superblocks)", n0, n1, k0, k1, N, K);
+  if (int rc = check_device(device)) return rc;
+  IZB_CUDA(cudaSetDevice(device));
+  izb_weight* w = new izb_weight;
+  w->type = type;
+  w->n_mats = n_mats;
+  w->N = n1 - n0;
+  w->K = k1 - k0;
+  w->device = device;
+  w->sb_bytes = type == IZB_Q4_K ? 144 : 272;
+  w->row_bytes = (size_t)(w->K / 256) * w->sb_bytes;
+  w->bytes = (size_t)n_mats * w->N * w->row_bytes;
+  const size_t src_row = (size_t)(K / 256) * w->sb_bytes;  // the GGUF bytes of 256 values are 144 / 8*34 = 272 as well
+  if (cudaMalloc(&w->raw, w->bytes + kRawSlack) != cudaSuccess) {
+    cudaGetLastError();
+    delete w;
+    IZB_FAIL(IZB_ERR_NOMEM, "weight_create: %zu bytes on device %d", w->bytes + kRawSlack, device);
+  }
+  cudaError_t e = cudaMemset(w->raw + w->bytes, 0, kRawSlack);
+  uint8_t* upload = w->raw;
+  uint8_t* tmp = nullptr;
+  if (e == cudaSuccess && type == IZB_Q8_0) {
+    e = cudaMalloc(&tmp, w->bytes);
+    upload = tmp;
+  }
+  if (e == cudaSuccess) {
+    const uint8_t* src = (const uint8_t*)h_rows + (size_t)n0 * src_row + (size_t)(k0 / 256) * w->sb_bytes;
+    if (n0 == 0 && n1 == N && k0 == 0 && k1 == K) {
+      e = cudaMemcpy(upload, src, w->bytes, cudaMemcpyHostToDevice);
+    } else {
+      for (int m = 0; m < n_mats && e == cudaSuccess; ++m)
+        e = cudaMemcpy2D(upload + (size_t)m * w->N * w->row_bytes, w->row_bytes, src + (size_t)m * N * src_row, src_row,
+                         w->row_bytes, w->N, cudaMemcpyHostToDevice);
+    }
+  }
+  if (e == cudaSuccess && type == IZB_Q8_0) {
+    const size_t n_sb = w->bytes / 272, items = n_sb * 17;
+    regroup_q8_0_kernel<<<(unsigned)((items + 255) / 256), 256>>>(tmp, w->raw, n_sb);
+    g_izb_launches.fetch_add(1);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  }
+  if (tmp) cudaFree(tmp);
+  if (e != cudaSuccess) {
+    cudaFree(w->raw);
+    delete w;
+    IZB_FAIL(IZB_ERR_CUDA, "weight_create: upload failed: %s", cudaGetErrorString(e));
+  }
+  w->has_tmap = izb_make_raw_tensor_map(w) == IZB_OK;
+  *out = w;
+  return IZB_OK;
+}
+
+extern "C" int izb_weight_create(int type, const void* h_rows, int n_mats, int N, int K, int device, izb_weight** out) {
+  return izb_weight_create_slice(type, h_rows, n_mats, N, K, 0, N, 0, K, device, out);
+}
+
+extern "C" void izb_weight_destroy(izb_weight* w) {
+  if (!w) return;
+  cudaSetDevice(w->device);
+  cudaFree(w->raw);
+  delete w;
+}
+
+extern "C" int izb_weight_info(const izb_weight* w, int* type, int* n_mats, int* N, int* K, size_t* bytes) {
+  if (!w) IZB_FAIL(IZB_ERR_ARG, "weight_info: null handle");
+  if (type) *type = w->type;
+  if (n_mats) *n_mats = w->n_mats;
+  if (N) *N = w->N;
+  if (K) *K = w->K;
+  if (bytes) *bytes = w->bytes + kRawSlack;
+  return IZB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- matmul
+static int check_gemm_args(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int M, int Mp, const void* C,
+                           int ldc, int c_off, int acc) {
+  if (!w || !aq || !asc || !C) IZB_FAIL(IZB_ERR_ARG, "gemm: null pointer");
+  if (mat < 0 || mat >= w->n_mats) IZB_FAIL(IZB_ERR_ARG, "gemm: matrix %d of %d", mat, w->n_mats);
+  if (acc < 0 || acc > 2) IZB_FAIL(IZB_ERR_ARG, "gemm: store mode %d", acc);
+  // the reference's shape rule (zero/engine.h:1233): Mp % 16, N % 16, K % 256
+  if (Mp % 16 || w->N % 16 || w->K % 256) IZB_FAIL(IZB_ERR_SHAPE, "gemm: bad shape Mp=%d N=%d K=%d (need Mp%%16, N%%16, K%%256)", Mp, w->N, w->K);
+  if (M < 1 || M > Mp) IZB_FAIL(IZB_ERR_SHAPE, "gemm: %d rows of Mp = %d", M, Mp);
+  if (c_off < 0 || ldc < c_off + w->N) IZB_FAIL(IZB_ERR_SHAPE, "gemm: ldc = %d < c_off + N = %d", ldc, c_off + w->N);
+  if (!izb_aligned(aq, 16) || !izb_aligned(asc, 16) || !izb_aligned(C, 16) || ldc % 4 || c_off % 4)
+    IZB_FAIL(IZB_ERR_ALIGN, "gemm: aq, asc, C must be 16-byte aligned, ldc and c_off multiples of 4");
+  return IZB_OK;
+}
+
+extern "C" int izb_gemm(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int M, int Mp, float* d_C, int ldc,
+                        int c_off, int acc, int impl, void* stream) {
+  if (int rc = check_gemm_args(w, mat, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == IZB_GEMM_AUTO || impl == IZB_GEMM_TC) {
+    const bool allowed = impl == IZB_GEMM_TC || g_dev[w->device].tc_ok != 0;
+    if (allowed) {
+      const int rc = izb_gemm_tc_launch(w, mat, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc, nullptr, st);
+      if (rc <= 0) return rc;
+    }
+    if (impl == IZB_GEMM_TC) IZB_FAIL(IZB_ERR_SHAPE, "gemm: the tensor-core kernel does not take M=%d Mp=%d N=%d K=%d", M, Mp, w->N, w->K);
+  } else if (impl != IZB_GEMM_CORE) {
+    IZB_FAIL(IZB_ERR_ARG, "gemm: impl %d", impl);
+  }
+  return izb_gemm_core_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc, nullptr, st);
+}
+
+extern "C" int izb_block_dots(const izb_weight* w, int mat, const int8_t* d_aq, int M, int32_t* d_dots, int impl, void* stream) {
+  if (!w || !d_aq || !d_dots) IZB_FAIL(IZB_ERR_ARG, "block_dots: null pointer");
+  if (mat < 0 || mat >= w->n_mats) IZB_FAIL(IZB_ERR_ARG, "block_dots: matrix %d of %d", mat, w->n_mats);
+  if (M < 1) IZB_FAIL(IZB_ERR_SHAPE, "block_dots: M = %d", M);
+  if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "block_dots: aq not 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == IZB_GEMM_TC) {
+    const int rc = izb_gemm_tc_launch(w, mat, d_aq, nullptr, M, M, nullptr, 0, 0, 0, d_dots, st);
+    if (rc > 0) IZB_FAIL(IZB_ERR_SHAPE, "block_dots: the tensor-core kernel does not take M=%d N=%d K=%d", M, w->N, w->K);
+    return rc;
+  }
+  if (impl != IZB_GEMM_CORE) IZB_FAIL(IZB_ERR_ARG, "block_dots: impl %d", impl);
+  // (dots mode: no scales are read; rows past M are not touched since Mp = M)
+  return izb_gemm_core_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, nullptr, M, M, nullptr, 0, 0, 0, d_dots, st);
+}
+
+extern "C" int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, const int16_t* d_absum, int T,
+                          int Mp, float* d_C, int ldc, int c_off, int acc, void* stream) {
+  (void)d_absum;  // the kernels recompute the block sums they need from aq
+  if (!w) IZB_FAIL(IZB_ERR_ARG, "matmul: null weight");
+  if (T < 1) IZB_FAIL(IZB_ERR_SHAPE, "matmul: T = %d", T);
+  if (T <= 8) {
+    if (acc == 2) IZB_FAIL(IZB_ERR_ARG, "matmul: store mode 2 (fused SwiGLU) exists for the GEMM only (T > 8)");
+    return izb_gemv(w, mat, d_aq, d_asc, T, Mp, d_C, ldc, c_off, acc, stream);
+  }
+  return izb_gemm(w, mat, d_aq, d_asc, Mp, Mp, d_C, ldc, c_off, acc, IZB_GEMM_AUTO, stream);
+}
+
+// records the verdict of the start-up check (izb_selfcheck lives with the tensor-core kernel)
+void izb_set_tc_ok(int device, int ok) { g_dev[device].tc_ok = ok; }
+int izb_get_tc_ok(int device) { return g_dev[device].tc_ok; }
+
+// ---------------------------------------------------------------------------------------------- host-buffer call
+extern "C" int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, int M, float* h_C, void* stream) {
+  if (!w || !h_x || !h_C) IZB_FAIL(IZB_ERR_ARG, "matmul_host: null pointer");
+  if (M < 1) IZB_FAIL(IZB_ERR_SHAPE, "matmul_host: M = %d", M);
+  IZB_CUDA(cudaSetDevice(w->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int K = w->K, N = w->N;
+  const int Mp = M <= 8 ? 16 : (M >= 128 ? (M + 127) / 128 * 128 : (M + 15) / 16 * 16);  // zero/engine.h:521-522
+  const size_t bx = (size_t)M * K * 4, baq = (size_t)Mp * K, basc = (size_t)(K / 32) * Mp * 4, bc = (size_t)Mp * N * 4;
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t total = up(bx) + up(baq) + up(basc) + up(bc);
+  DevState& d = g_dev[w->device];
+  {
+    std::lock_guard<std::mutex> lk(d.mu);
+    if (total > d.stage_bytes) {
+      if (d.stage) {
+        IZB_CUDA(cudaDeviceSynchronize());
+        IZB_CUDA(cudaFree(d.stage));
+        d.stage = nullptr;
+        d.stage_bytes = 0;
+      }
+      if (cudaMalloc(&d.stage, total) != cudaSuccess) {
+        cudaGetLastError();
+        IZB_FAIL(IZB_ERR_NOMEM, "matmul_host: %zu staging bytes", total);
+      }
+      d.stage_bytes = total;
+    }
+  }
+  uint8_t* p = (uint8_t*)d.stage;
+  float* dx = (float*)p;
+  int8_t* daq = (int8_t*)(p + up(bx));
+  float* dasc = (float*)(p + up(bx) + up(baq));
+  float* dC = (float*)(p + up(bx) + up(baq) + up(basc));
+  IZB_CUDA(cudaMemcpyAsync(dx, h_x, bx, cudaMemcpyHostToDevice, st));
+  if (int rc = izb_quantize_act(dx, K, M, Mp, K, daq, dasc, nullptr, st)) return rc;
+  if (int rc = izb_matmul(w, mat, daq, dasc, nullptr, M, Mp, dC, N, 0, 0, st)) return rc;
+  IZB_CUDA(cudaMemcpyAsync(h_C, dC, (size_t)M * N * 4, cudaMemcpyDeviceToHost, st));
+  IZB_CUDA(cudaStreamSynchronize(st));
+  return IZB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- tensor-parallel helpers
+extern "C" int izb_tp_range(int64_t total, int64_t unit, int nranks, int rank, int64_t* begin, int64_t* end) {
+  if (!begin || !end) IZB_FAIL(IZB_ERR_ARG, "tp_range: null pointer");
+  if (unit < 1 || nranks < 1 || rank < 0 || rank >= nranks || total < 0) IZB_FAIL(IZB_ERR_ARG, "tp_range: total %lld unit %lld rank %d of %d", (long long)total, (long long)unit, rank, nranks);
+  // zero/mgpu/engine_tp_shard.h:68-72: the first units % nranks ranks hold one unit more
+  const int64_t units = total / unit, base = units / nranks, extra = units % nranks;
+  const int64_t b = rank * base + (rank < extra ? rank : extra), e = b + base + (rank < extra ? 1 : 0);
+  *begin = b * unit;
+  *end = e * unit;
+  return IZB_OK;
+}

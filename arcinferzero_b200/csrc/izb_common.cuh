@@ -1,0 +1,97 @@
+// Shared declarations of the izb200 library: the weight handle, error plumbing and small device helpers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <atomic>
+
+#include "../../include/izb200.h"
+
+// ---------------------------------------------------------------------------------------------- weight handle
+// Device form of a weight (or of a stack of n_mats equal matrices): rows of K/256 superblocks.
+//   Q4_K: the 144-byte GGUF superblock unchanged: fp16 d | fp16 dmin | 12 B packed 6-bit scales/mins | 128 B nibbles
+//   Q8_0: 272 bytes per 256 values: fp16 d[8] | int8 q[8][32]
+// Both are multiples of 16 bytes, so every superblock starts on a 16-byte boundary (128-bit loads, TMA boxes).
+struct izb_weight {
+  int type = 0, n_mats = 0, N = 0, K = 0, device = 0;
+  int sb_bytes = 0;      // 144 or 272
+  size_t row_bytes = 0;  // K/256 * sb_bytes
+  size_t bytes = 0;      // n_mats * N * row_bytes (without the slack)
+  uint8_t* raw = nullptr;
+  alignas(64) unsigned char tmap_raw[128];  // CUtensorMap over raw: [n_mats*N rows][row_bytes/4 uint32]
+  bool has_tmap = false;
+};
+
+static constexpr size_t kRawSlack = 1024;  // zero bytes after the last row (zero/engine_load.h:79-84)
+
+// ---------------------------------------------------------------------------------------------- errors
+void izb_set_error(const char* fmt, ...);
+extern std::atomic<uint64_t> g_izb_launches;
+
+#define IZB_FAIL(code, ...)     \
+  do {                          \
+    izb_set_error(__VA_ARGS__); \
+    return (code);              \
+  } while (0)
+
+#define IZB_CUDA(call)                                                                              \
+  do {                                                                                              \
+    cudaError_t e__ = (call);                                                                       \
+    if (e__ != cudaSuccess) {                                                                       \
+      izb_set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, __LINE__);   \
+      return IZB_ERR_CUDA;                                                                          \
+    }                                                                                               \
+  } while (0)
+
+// after a kernel launch: count it and pick up launch-configuration errors
+#define IZB_LAUNCHED()                                                                                    \
+  do {                                                                                                    \
+    g_izb_launches.fetch_add(1, std::memory_order_relaxed);                                               \
+    cudaError_t e__ = cudaGetLastError();                                                                 \
+    if (e__ != cudaSuccess) {                                                                             \
+      izb_set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e__), __FILE__, __LINE__);     \
+      return IZB_ERR_CUDA;                                                                                \
+    }                                                                                                     \
+  } while (0)
+
+static inline bool izb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Device-side error word (one per device, in managed-free plain device memory): kernels that give up on a bounded
+// wait OR a code into it; izb_device_status reads and clears it.
+uint32_t* izb_device_error_word(int device);
+
+// Per-device scratch arenas, one per user so that independent users never share bytes; each is grown on demand
+// (cudaMalloc only when a call needs more than any call before it).  Calls that use the same arena must be ordered on
+// one stream.
+enum { kWsGemm = 0, kWsTp = 1, kWsMoe = 2, kWsCheck = 3 };
+int izb_workspace(int device, int slot, size_t bytes, void** out);
+
+// ---------------------------------------------------------------------------------------------- device helpers
+#ifdef __CUDACC__
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float half_bits_to_float(uint32_t h16) { return __half2float(__ushort_as_half((unsigned short)h16)); }
+
+// Q4_K: 6-bit scale and min of sub-block j (0..7) from the 12 packed bytes held as three little-endian words
+// (get_scale_min_k4, src/quants.h:61-69)
+__device__ __forceinline__ void q4k_scale_min(const uint32_t s[3], int j, int& sc, int& mn) {
+  auto byte = [&](int i) -> uint32_t { return (s[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+  if (j < 4) {
+    sc = byte(j) & 63;
+    mn = byte(j + 4) & 63;
+  } else {
+    sc = (byte(j + 4) & 0xF) | ((byte(j - 4) >> 6) << 4);
+    mn = (byte(j + 4) >> 4) | ((byte(j) >> 6) << 4);
+  }
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+#endif

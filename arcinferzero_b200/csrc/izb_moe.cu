@@ -1,0 +1,303 @@
+// Mixture-of-experts around the quantised matmul: routing, the counting sort of (token, choice) pairs into expert
+// slots, the per-tile expert kernels on raw GGUF rows, and the combine.
+//   moe_route    zero/kernels/moe.cl:50-89     softmax numerators of the NU largest logits, ties -> lower expert id
+//   moe_sort     zero/kernels/moe.cl:141-179   exclusive scan of the counts, tile list, scatter (here deterministic)
+//   moe_gateup   zero/kernels/decode_moe.cl:92-260   h = silu(x Wg^T) * (x Wu^T) per tile of <= TM slots of one expert
+//   moe_down     zero/kernels/decode_moe.cl:269-449  y = swt * (hq Wd^T)
+//   moe_combine  zero/kernels/moe.cl:344-352   x[t] += sum_k y[inv[t*NU+k]] in choice order
+// The per-tile kernels run the few-row GEMV loop (izb_gemv_body.cuh) over the rows of the tile's expert, with the
+// activation rows gathered through the slot -> token map, as the reference's moe_gateup_q / moe_down_q do.
+#include "izb_gemv_body.cuh"
+
+namespace {
+using namespace izb_gemvk;
+
+constexpr int kMaxPerLane = 16;  // experts per lane: NE <= 512
+
+__global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int ldl, int T, int NE, int NU,
+                                                        int32_t* __restrict__ ids, float* __restrict__ wts,
+                                                        int32_t* __restrict__ counts) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* lg = logits + (size_t)t * ldl;
+  const int per = (NE + 31) / 32;
+  float v[kMaxPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = (i < per && e < NE) ? lg[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+  float sum = 0.0f, my_p = 0.0f;
+  int my_sel = 0;
+  for (int k = 0; k < NU; ++k) {
+    float bv = -INFINITY;
+    int bi = NE;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (v[i] > bv) { bv = v[i]; bi = i * 32 + lane; }
+    float gv = bv;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gv = fmaxf(gv, __shfl_xor_sync(0xFFFFFFFFu, gv, o));
+    int gi = bv == gv ? bi : NE;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gi = min(gi, __shfl_xor_sync(0xFFFFFFFFu, gi, o));
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if (i * 32 + lane == gi) v[i] = -INFINITY;
+    const int sel = min(gi, NE - 1);
+    const float p = expf(gv - mx);
+    sum += p;
+    if (lane == k) { my_p = p; my_sel = sel; }
+  }
+  if (lane < NU) {
+    ids[t * NU + lane] = my_sel;
+    wts[t * NU + lane] = __fdiv_rn(my_p, sum);
+    atomicAdd(&counts[my_sel], 1);
+  }
+}
+
+// One thread per expert: offsets (exclusive scan, serial: NE is a few hundred) and the expert's tiles.
+__global__ void moe_scan_kernel(const int32_t* __restrict__ counts, int NE, int TM, int32_t* __restrict__ offs,
+                                int32_t* __restrict__ tiles, int max_tiles) {
+  const int e = threadIdx.x;
+  int off = 0, toff = 0;
+  for (int i = 0; i < e && i < NE; ++i) {
+    off += counts[i];
+    toff += (counts[i] + TM - 1) / TM;
+  }
+  if (e < NE) {
+    const int c = counts[e], nt = (c + TM - 1) / TM;
+    offs[e] = off;
+    for (int i = 0; i < nt; ++i) {
+      if (toff + i >= max_tiles) break;
+      int32_t* tp = tiles + 1 + 3 * (toff + i);
+      tp[0] = e;
+      tp[1] = off + i * TM;
+      tp[2] = min(TM, c - i * TM);
+    }
+    if (e == NE - 1) {
+      offs[NE] = off + c;
+      tiles[0] = min(toff + nt, max_tiles);
+    }
+  }
+}
+
+// One CTA per expert: its pairs in increasing pair index take consecutive slots (a deterministic atomic_inc order).
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, int n,
+                                                          int NU, const int32_t* __restrict__ offs, int32_t* __restrict__ stok,
+                                                          float* __restrict__ swt, int32_t* __restrict__ inv) {
+  __shared__ int s_warp[8];
+  __shared__ int s_base;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_base = offs[e];
+  __syncthreads();
+  for (int i0 = 0; i0 < n; i0 += 256) {
+    const int i = i0 + threadIdx.x;
+    const bool mine = i < n && ids[i] == e;
+    const unsigned bal = __ballot_sync(0xFFFFFFFFu, mine);
+    if (lane == 0) s_warp[warp] = __popc(bal);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) before += s_warp[w];
+      total += s_warp[w];
+    }
+    if (mine) {
+      const int s = s_base + before + __popc(bal & ((1u << lane) - 1));
+      stok[s] = i / NU;
+      swt[s] = wts[i];
+      inv[i] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += total;
+    __syncthreads();
+  }
+}
+
+template <int QT>
+__global__ void __launch_bounds__(kWarps * 32) moe_gateup_kernel(const uint8_t* __restrict__ rg, const uint8_t* __restrict__ ru,
+                                                                 int F, int K, size_t mat_bytes, const int8_t* __restrict__ aq,
+                                                                 const float* __restrict__ asc, int Mp,
+                                                                 const int32_t* __restrict__ tiles,
+                                                                 const int32_t* __restrict__ stok, float* __restrict__ h, int spc) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int tok[8];
+  const int ti = blockIdx.y;
+  if (ti >= tiles[0]) return;  // uniform over the CTA
+  const int e = tiles[1 + 3 * ti], r0 = tiles[2 + 3 * ti], nr = tiles[3 + 3 * ti];
+  if (threadIdx.x < 8) tok[threadIdx.x] = stok[r0 + min((int)threadIdx.x, nr - 1)];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row0 = (blockIdx.x * kWarps + warp) * kRows;
+  float ag[kRows][8], au[kRows][8];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) ag[r][t] = au[r][t] = 0.0f;
+  gemv_body<QT, 8>(smem, rg + (size_t)e * mat_bytes, F, K, aq, asc, Mp, tok, row0, spc, ag);
+  gemv_body<QT, 8>(smem, ru + (size_t)e * mat_bytes, F, K, aq, asc, Mp, tok, row0, spc, au);
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const float g = warp_sum(ag[r][t]), u = warp_sum(au[r][t]);
+      const int n = row0 + r;
+      if (lane == 0 && n < F && t < nr) h[(size_t)(r0 + t) * F + n] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+    }
+}
+
+template <int QT>
+__global__ void __launch_bounds__(kWarps * 32) moe_down_kernel(const uint8_t* __restrict__ rd, int E, int F, size_t mat_bytes,
+                                                               const int8_t* __restrict__ hq, const float* __restrict__ hsc,
+                                                               int Sp, const int32_t* __restrict__ tiles,
+                                                               const float* __restrict__ swt, float* __restrict__ y, int spc) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int tok[8];
+  const int ti = blockIdx.y;
+  if (ti >= tiles[0]) return;
+  const int e = tiles[1 + 3 * ti], r0 = tiles[2 + 3 * ti], nr = tiles[3 + 3 * ti];
+  if (threadIdx.x < 8) tok[threadIdx.x] = r0 + min((int)threadIdx.x, nr - 1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row0 = (blockIdx.x * kWarps + warp) * kRows;
+  float a[kRows][8];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) a[r][t] = 0.0f;
+  gemv_body<QT, 8>(smem, rd + (size_t)e * mat_bytes, E, F, hq, hsc, Sp, tok, row0, spc, a);
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const float v = warp_sum(a[r][t]);
+      const int n = row0 + r;
+      if (lane == 0 && n < E && t < nr) y[(size_t)(r0 + t) * E + n] = __fmul_rn(swt[r0 + t], v);
+    }
+}
+
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ inv, int T,
+                                   int NU, int E) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4, t = blockIdx.y;
+  if (c >= E) return;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = 0; k < NU; ++k) {
+    const float4 a = *reinterpret_cast<const float4*>(y + (size_t)inv[t * NU + k] * E + c);
+    v.x = __fadd_rn(v.x, a.x); v.y = __fadd_rn(v.y, a.y); v.z = __fadd_rn(v.z, a.z); v.w = __fadd_rn(v.w, a.w);
+  }
+  float4* px = reinterpret_cast<float4*>(x + (size_t)t * E + c);
+  float4 o = *px;
+  o.x = __fadd_rn(o.x, v.x); o.y = __fadd_rn(o.y, v.y); o.z = __fadd_rn(o.z, v.z); o.w = __fadd_rn(o.w, v.w);
+  *px = o;
+}
+
+}  // namespace
+
+extern "C" int izb_moe_route(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts,
+                             int32_t* d_counts, void* stream) {
+  if (!d_logits || !d_ids || !d_wts || !d_counts) IZB_FAIL(IZB_ERR_ARG, "moe_route: null pointer");
+  if (T < 1 || NE < 1 || NE > 32 * kMaxPerLane || NU < 1 || NU > 32 || NU > NE || ldl < NE)
+    IZB_FAIL(IZB_ERR_SHAPE, "moe_route: T=%d NE=%d NU=%d ldl=%d (NE <= 512, NU <= 32)", T, NE, NU, ldl);
+  cudaStream_t st = (cudaStream_t)stream;
+  IZB_CUDA(cudaMemsetAsync(d_counts, 0, (size_t)NE * 4, st));
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(d_logits, ldl, T, NE, NU, d_ids, d_wts, d_counts);
+  IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+extern "C" int izb_moe_sort(const int32_t* d_ids, const float* d_wts, const int32_t* d_counts, int T, int NE, int NU, int TM,
+                            int32_t* d_offs, int32_t* d_tiles, int max_tiles, int32_t* d_stok, float* d_swt, int32_t* d_inv,
+                            void* stream) {
+  if (!d_ids || !d_wts || !d_counts || !d_offs || !d_tiles || !d_stok || !d_swt || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_sort: null pointer");
+  if (T < 1 || NE < 1 || NE > 1024 || NU < 1 || TM < 1) IZB_FAIL(IZB_ERR_SHAPE, "moe_sort: T=%d NE=%d NU=%d TM=%d", T, NE, NU, TM);
+  if (max_tiles < (T * NU + TM - 1) / TM + NE) IZB_FAIL(IZB_ERR_LIMIT, "moe_sort: max_tiles = %d < %d (pairs/TM + NE)", max_tiles, (T * NU + TM - 1) / TM + NE);
+  cudaStream_t st = (cudaStream_t)stream;
+  moe_scan_kernel<<<1, 1024, 0, st>>>(d_counts, NE, TM, d_offs, d_tiles, max_tiles);
+  IZB_LAUNCHED();
+  moe_scatter_kernel<<<NE, 256, 0, st>>>(d_ids, d_wts, T * NU, NU, d_offs, d_stok, d_swt, d_inv);
+  IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+int izb_moe_gateup_tiles(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
+                         const int32_t* d_tiles, int max_tiles, const int32_t* d_stok, float* d_h, cudaStream_t st) {
+  const int F = wg->N, K = wg->K;
+  size_t smem = 0;
+  const int spc = steps_per_chunk(wg->type, K, 8, &smem);
+  dim3 grid((F + kWarps * kRows - 1) / (kWarps * kRows), max_tiles);
+  const size_t mat_bytes = (size_t)F * wg->row_bytes;
+  if (wg->type == IZB_Q4_K) {
+    IZB_CUDA(cudaFuncSetAttribute(moe_gateup_kernel<IZB_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    moe_gateup_kernel<IZB_Q4_K><<<grid, kWarps * 32, smem, st>>>(wg->raw, wu->raw, F, K, mat_bytes, d_aq, d_asc, Mp, d_tiles, d_stok, d_h, spc);
+  } else {
+    IZB_CUDA(cudaFuncSetAttribute(moe_gateup_kernel<IZB_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    moe_gateup_kernel<IZB_Q8_0><<<grid, kWarps * 32, smem, st>>>(wg->raw, wu->raw, F, K, mat_bytes, d_aq, d_asc, Mp, d_tiles, d_stok, d_h, spc);
+  }
+  IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+int izb_moe_down_tiles(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles,
+                       int max_tiles, const float* d_swt, float* d_y, cudaStream_t st) {
+  const int E = wd->N, F = wd->K;
+  size_t smem = 0;
+  const int spc = steps_per_chunk(wd->type, F, 8, &smem);
+  dim3 grid((E + kWarps * kRows - 1) / (kWarps * kRows), max_tiles);
+  const size_t mat_bytes = (size_t)E * wd->row_bytes;
+  if (wd->type == IZB_Q4_K) {
+    IZB_CUDA(cudaFuncSetAttribute(moe_down_kernel<IZB_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    moe_down_kernel<IZB_Q4_K><<<grid, kWarps * 32, smem, st>>>(wd->raw, E, F, mat_bytes, d_hq, d_hsc, Sp, d_tiles, d_swt, d_y, spc);
+  } else {
+    IZB_CUDA(cudaFuncSetAttribute(moe_down_kernel<IZB_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    moe_down_kernel<IZB_Q8_0><<<grid, kWarps * 32, smem, st>>>(wd->raw, E, F, mat_bytes, d_hq, d_hsc, Sp, d_tiles, d_swt, d_y, spc);
+  }
+  IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+extern "C" int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, void* stream) {
+  if (!d_x || !d_y || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_combine: null pointer");
+  if (T < 1 || NU < 1 || E < 4 || E % 4) IZB_FAIL(IZB_ERR_SHAPE, "moe_combine: T=%d NU=%d E=%d (E %% 4 == 0)", T, NU, E);
+  if (!izb_aligned(d_x, 16) || !izb_aligned(d_y, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_combine: x, y must be 16-byte aligned");
+  dim3 grid((E / 4 + 127) / 128, T);
+  moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(d_x, d_y, d_inv, T, NU, E);
+  IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+// grouped tensor-core path (izb_gemm_tc.cu): tiles of up to 128 slots; +1 = shape not taken
+int izb_moe_gateup_tc(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
+                      const int32_t* d_tiles, int max_tiles, const int32_t* d_stok, float* d_h, cudaStream_t st);
+int izb_moe_down_tc(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles, int max_tiles,
+                    const float* d_swt, float* d_y, cudaStream_t st);
+
+extern "C" int izb_moe_gateup(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
+                              const int32_t* d_tiles, int max_tiles, int TM, const int32_t* d_stok, float* d_h, void* stream) {
+  if (!wg || !wu || !d_aq || !d_asc || !d_tiles || !d_stok || !d_h) IZB_FAIL(IZB_ERR_ARG, "moe_gateup: null pointer");
+  if (wg->type != wu->type || wg->N != wu->N || wg->K != wu->K || wg->n_mats != wu->n_mats)
+    IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: gate and up stacks differ");
+  if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_gateup: max_tiles = %d (1..65535)", max_tiles);
+  if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_gateup: aq not 16-byte aligned");
+  if (TM >= 1 && TM <= 8) return izb_moe_gateup_tiles(wg, wu, d_aq, d_asc, Mp, d_tiles, max_tiles, d_stok, d_h, (cudaStream_t)stream);
+  if (TM == 128) {
+    const int rc = izb_moe_gateup_tc(wg, wu, d_aq, d_asc, Mp, d_tiles, max_tiles, d_stok, d_h, (cudaStream_t)stream);
+    if (rc <= 0) return rc;
+  }
+  IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: tiles of %d slots (1..8: per-tile GEMV kernels; 128: grouped tensor-core GEMM)", TM);
+}
+
+extern "C" int izb_moe_down(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles,
+                            int max_tiles, int TM, const float* d_swt, float* d_y, void* stream) {
+  if (!wd || !d_hq || !d_hsc || !d_tiles || !d_swt || !d_y) IZB_FAIL(IZB_ERR_ARG, "moe_down: null pointer");
+  if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_down: max_tiles = %d (1..65535)", max_tiles);
+  if (!izb_aligned(d_hq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_down: hq not 16-byte aligned");
+  if (TM >= 1 && TM <= 8) return izb_moe_down_tiles(wd, d_hq, d_hsc, Sp, d_tiles, max_tiles, d_swt, d_y, (cudaStream_t)stream);
+  if (TM == 128) {
+    const int rc = izb_moe_down_tc(wd, d_hq, d_hsc, Sp, d_tiles, max_tiles, d_swt, d_y, (cudaStream_t)stream);
+    if (rc <= 0) return rc;
+  }
+  IZB_FAIL(IZB_ERR_SHAPE, "moe_down: tiles of %d slots (1..8: per-tile GEMV kernels; 128: grouped tensor-core GEMM)", TM);
+}

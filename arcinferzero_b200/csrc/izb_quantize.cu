@@ -1,0 +1,122 @@
+// Activation quantiser: f32 rows -> int8 per 32-block + f32 scale (+ int16 sums per 16), HBM-bound.
+// Arithmetic of quantize_act_cpu (src/quants.h:626-643) = quant_store16 (zero/kernels/ops.cl:38-72), bit for bit:
+//   amax = max|x|;  inv = amax > 0 ? 127.0f / amax : 0;  q = rint(x * inv);  scale = amax / 127.0f
+// The divisions and the product are written with the round-to-nearest intrinsics so no contraction or reciprocal
+// approximation can change a bit.
+//
+// One CTA covers 32 token rows x 256 columns: every lane owns 8 consecutive values (two 128-bit loads), four lanes make
+// a 32-block.  The int8 row stores are 256 contiguous bytes per warp; the scales, whose layout is block-major
+// ([K/32][Mp]), go through shared memory so that each block's 32 token scales leave as one 128-byte line.
+#include "izb_common.cuh"
+
+namespace {
+
+template <bool kSwiglu>
+__global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restrict__ x, int ldx, int M, int Mp, int K,
+                                                           int8_t* __restrict__ aq, float* __restrict__ asc,
+                                                           int16_t* __restrict__ absum, float* __restrict__ hout,
+                                                           int F /* kSwiglu: up projection at column offset F */) {
+  __shared__ float s_sc[8][33];
+  __shared__ int16_t s_sum[16][34];
+  const int sb = blockIdx.x, m0 = blockIdx.y * 32, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = sb * 256 + lane * 8;
+  float v[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + warp + 8 * i;
+    if (m < M) {
+      const float4* p = reinterpret_cast<const float4*>(x + (size_t)m * ldx + col);
+      const float4 a = __ldcs(p), b = __ldcs(p + 1);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+      v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+      if (kSwiglu) {  // v holds the gate g: h = g / (1 + exp(-g)) * u   (zero/kernels/ops.cl:272-315)
+        const float4* pu = reinterpret_cast<const float4*>(x + (size_t)m * ldx + F + col);
+        const float4 c = __ldcs(pu), d = __ldcs(pu + 1);
+        const float u[8] = {c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[i][k] = __fmul_rn(__fdiv_rn(v[i][k], __fadd_rn(1.0f, expf(-v[i][k]))), u[k]);
+        if (hout) {
+          float4* ph = reinterpret_cast<float4*>(hout + (size_t)m * F + col);
+          ph[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          ph[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[i][k] = 0.0f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = warp + 8 * i, m = m0 + r;
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[i][k]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    int q[8], s8 = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      // lrintf's x86 result for products outside the int range or NaN (only when amax is so small that 127 / amax
+      // overflows): INT_MIN, whose low byte is 0
+      const float p = __fmul_rn(v[i][k], inv);
+      q[k] = fabsf(p) <= 2147483520.0f ? __float2int_rn(p) : 0;
+      s8 += q[k];
+    }
+    const int s16 = s8 + __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
+    if (m < Mp) {
+      uint2 pk;
+      pk.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+      pk.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+      *reinterpret_cast<uint2*>(aq + (size_t)m * K + col) = pk;
+    }
+    if ((lane & 3) == 0) s_sc[lane >> 2][r] = __fdiv_rn(amax, 127.0f);
+    if ((lane & 1) == 0) s_sum[lane >> 1][r] = (int16_t)s16;
+  }
+  __syncthreads();
+  {
+    const int b = threadIdx.x >> 5, r = threadIdx.x & 31;
+    if (m0 + r < Mp) {
+      asc[(size_t)(sb * 8 + b) * Mp + m0 + r] = s_sc[b][r];
+      if (absum) {
+        absum[(size_t)(sb * 16 + b) * Mp + m0 + r] = s_sum[b][r];
+        absum[(size_t)(sb * 16 + 8 + b) * Mp + m0 + r] = s_sum[8 + b][r];
+      }
+    }
+  }
+}
+
+int check_quant_args(const float* x, int ldx, int M, int Mp, int K, const int8_t* aq, const float* asc, int width_needed) {
+  if (!x || !aq || !asc) IZB_FAIL(IZB_ERR_ARG, "quantize: null pointer");
+  if (K <= 0 || K % 256) IZB_FAIL(IZB_ERR_SHAPE, "quantize: K = %d is not a positive multiple of 256", K);
+  if (Mp <= 0 || Mp % 16 || M < 0 || M > Mp) IZB_FAIL(IZB_ERR_SHAPE, "quantize: rows %d of Mp = %d (Mp must be a multiple of 16)", M, Mp);
+  if (ldx < width_needed) IZB_FAIL(IZB_ERR_SHAPE, "quantize: row stride %d shorter than the row (%d)", ldx, width_needed);
+  if (ldx % 4 || !izb_aligned(x, 16)) IZB_FAIL(IZB_ERR_ALIGN, "quantize: input rows must be 16-byte aligned (ldx %% 4 == 0)");
+  if (!izb_aligned(aq, 16) || !izb_aligned(asc, 4)) IZB_FAIL(IZB_ERR_ALIGN, "quantize: outputs not aligned");
+  return IZB_OK;
+}
+
+}  // namespace
+
+extern "C" int izb_quantize_act(const float* d_x, int ldx, int M_valid, int Mp, int K, int8_t* d_aq, float* d_asc,
+                                int16_t* d_absum, void* stream) {
+  if (int rc = check_quant_args(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, K)) return rc;
+  dim3 grid(K / 256, (Mp + 31) / 32);
+  quantize_act_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0);
+  IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+extern "C" int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_valid, int Mp, int F, float* d_h, int8_t* d_aq,
+                                float* d_asc, int16_t* d_absum, void* stream) {
+  if (int rc = check_quant_args(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, split ? 2 * F : F)) return rc;
+  if (d_h && !izb_aligned(d_h, 16)) IZB_FAIL(IZB_ERR_ALIGN, "swiglu_quant: h not 16-byte aligned");
+  dim3 grid(F / 256, (Mp + 31) / 32);
+  if (split)
+    quantize_act_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F);
+  else
+    quantize_act_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0);
+  IZB_LAUNCHED();
+  return IZB_OK;
+}

@@ -1,0 +1,166 @@
+/* izb200 -- B200 (sm_100a) implementation of inferzero's quantised matrix product, behind a C ABI.
+ *
+ * The path: int8 activations (one f32 scale per 32 values) x GGUF block-quantised weights (Q8_0, Q4_K), integer dot
+ * products per 32-block, f32 combine.  Activation quantiser, prefill GEMM, decode GEMV (1..8 rows), MoE grouped
+ * expert GEMM, tensor-parallel split + sum.  CUDA only: there is no CPU fallback; every entry point returns an error
+ * when no sm_100 device is present.
+ *
+ * Conventions
+ *   - every function returns an int status (IZB_OK = 0, errors < 0) and never throws; izb_last_error() gives the detail
+ *     of the calling thread's last failure;
+ *   - shapes and alignment are validated before anything is launched (the reference throws std::runtime_error at the
+ *     same place, zero/engine.h:1233-1235);
+ *   - pointers named d_* are device pointers owned by the caller; h_* are host pointers; izb_weight is library-owned and
+ *     immutable after creation;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream); calls are asynchronous on it unless
+ *     stated otherwise (the *_create calls and the *_host convenience calls synchronise);
+ *   - one izb_weight may be used from several threads; concurrent calls must use different streams and outputs.
+ *
+ * Buffer layouts are the reference engine's (zero/engine_alloc.h:10,39,41):
+ *   aq     int8  [Mp][K]      quantised activations, row-major
+ *   asc    f32   [K/32][Mp]   one scale per 32-block, block-major / token-minor
+ *   absum  int16 [K/16][Mp]   sums of 16 quantised values (optional everywhere: kernels recompute what they need)
+ *   C      f32   [rows][ldc]  outputs, written at column offset c_off
+ */
+#ifndef IZB200_H
+#define IZB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IZB_OK 0
+#define IZB_ERR_ARG (-1)       /* null pointer, bad enum */
+#define IZB_ERR_SHAPE (-2)     /* K not a multiple of 256, Mp not a multiple of 16, N out of range ... */
+#define IZB_ERR_TYPE (-3)      /* ggml type other than Q8_0 (8) / Q4_K (12) */
+#define IZB_ERR_ALIGN (-4)     /* pointer or leading dimension not aligned as documented */
+#define IZB_ERR_CUDA (-5)      /* a CUDA runtime / driver call failed, or no sm_100 device */
+#define IZB_ERR_NCCL (-6)
+#define IZB_ERR_TIMEOUT (-7)   /* a bounded device-side wait gave up (see izb_device_status) */
+#define IZB_ERR_NOMEM (-8)
+#define IZB_ERR_SELFCHECK (-9) /* tensor-core kernel disagreed with the CUDA-core kernel at start-up */
+#define IZB_ERR_LIMIT (-10)    /* a fixed capacity of the called entry point was exceeded */
+
+#define IZB_Q8_0 8  /* ggml type ids, src/gguf.h */
+#define IZB_Q4_K 12
+
+/* izb_gemm `impl` */
+#define IZB_GEMM_AUTO 0 /* tensor-core kernel when the shape allows it, else the CUDA-core kernel */
+#define IZB_GEMM_CORE 1 /* CUDA-core dp4a kernel, f32 combine in the reference's order (zero/kernels/gemm.cl:441-487) */
+#define IZB_GEMM_TC 2   /* tcgen05 kernel (TMEM accumulators), error if the shape is not taken */
+
+typedef struct izb_weight izb_weight;
+typedef struct izb_tp izb_tp;
+
+const char* izb_status_string(int status);
+const char* izb_last_error(void);
+/* number of kernels this library has launched in the calling process (benchmark bookkeeping) */
+uint64_t izb_launch_count(void);
+/* Reads and clears the device-side error word of `device`: non-zero when a kernel gave up on a bounded wait
+ * (value = where).  Synchronises the device. */
+int izb_device_status(int device, uint32_t* word);
+
+/* ------------------------------------------------------------------------------------------------ weights
+ * Replaces Engine::make_weight / upload_padded (zero/engine_load.h:85-196) and the GpuWeight handle
+ * (zero/engine.h:27-34).  h_gguf_rows: n_mats matrices of N rows of K values in GGUF block form (Q8_0: 34-byte blocks,
+ * Q4_K: 144-byte superblocks), matrix-major, as in the file (MoE stacks are [NE][N][K], zero/engine_stream.h:285-306).
+ * The device copy keeps Q4_K superblocks as they are and regroups Q8_0 per 256 values (8 fp16 scales, then 8 x 32
+ * int8: the reference's gpu_raw_sb form, src/quants.h:728-751), followed by 1024 zero bytes of slack.  Synchronous. */
+int izb_weight_create(int ggml_type, const void* h_gguf_rows, int n_mats, int N, int K, int device, izb_weight** out);
+/* Tensor-parallel shard of a matrix (Engine::tp_slice, zero/mgpu/engine_tp_shard.h:202-234): rows [n0, n1) and input
+ * columns [k0, k1) of every matrix; k0, k1 multiples of 256. */
+int izb_weight_create_slice(int ggml_type, const void* h_gguf_rows, int n_mats, int N, int K, int n0, int n1, int k0, int k1,
+                            int device, izb_weight** out);
+void izb_weight_destroy(izb_weight* w);
+int izb_weight_info(const izb_weight* w, int* ggml_type, int* n_mats, int* N, int* K, size_t* device_bytes);
+
+/* ------------------------------------------------------------------------------------------------ activations
+ * Replaces Engine::quant_rows (zero/engine.h:1445) = ops.cl quant_store16 (zero/kernels/ops.cl:38-72); bit-exact with
+ * quantize_act_cpu (src/quants.h:626-643).  d_x: [M_valid][ldx] f32; rows M_valid..Mp-1 of the outputs are written as
+ * zeros with scale 0 (zero/kernels/ops.cl:132-135).  K % 256 == 0, Mp % 16 == 0, Mp >= M_valid.  d_absum may be NULL. */
+int izb_quantize_act(const float* d_x, int ldx, int M_valid, int Mp, int K, int8_t* d_aq, float* d_asc, int16_t* d_absum,
+                     void* stream);
+/* SwiGLU then quantise (ops.cl swiglu_quant, zero/kernels/ops.cl:272-315): h = g/(1+exp(-g)) * u; d_gu: [M_valid][2F]
+ * with gate in columns [0,F) and up in [F,2F) when `split` != 0, or d_gu = gate-times-up product already ([M][F],
+ * split == 0: plain quantise).  d_h (may be NULL) receives h as f32 [M_valid][F]. */
+int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_valid, int Mp, int F, float* d_h, int8_t* d_aq,
+                     float* d_asc, int16_t* d_absum, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ matmul
+ * Replaces Engine::matmul / matmul1 (zero/engine.h:1080,1147-1251): C[t][c_off + n] (op)= sum_k A[t][k] W[n][k] for
+ * the T valid rows, dispatching on T as the reference does: T == 1 -> GEMV (decode.cl gemv, :913), 2..8 -> few-row
+ * GEMV reading the weights once (gemv_mt, :1581), T > 8 -> GEMM over Mp padded rows (gemm.cl gemm, :163; needs
+ * Mp % 16 == 0, N % 16 == 0).  acc: 0 store, 1 add to C, 2 C = result * silu(C) (fused SwiGLU, gemm.cl:562-565; GEMM
+ * only, as in the reference).  `mat` selects the matrix of a stack (0 for a dense weight). */
+int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, const int16_t* d_absum, int T, int Mp,
+               float* d_C, int ldc, int c_off, int acc, void* stream);
+/* The two kernels behind izb_matmul, callable directly (kernel ABIs of zero/kernels/decode.cl:913-915,1581-1583 and
+ * zero/kernels/gemm.cl:163-166). */
+int izb_gemv(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int T, int Mp, float* d_C, int ldc,
+             int c_off, int acc, void* stream);
+int izb_gemm(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int M_rows, int Mp, float* d_C, int ldc,
+             int c_off, int acc, int impl, void* stream);
+/* Verification mode (the reference's xmx_check idea, zero/engine_setup.h:424): the per-32-block integer dot products
+ * themselves, d_dots int32 [M][N][K/32], from the CUDA-core kernel (impl = IZB_GEMM_CORE) or from the tensor-core
+ * kernel's accumulators before any scaling (impl = IZB_GEMM_TC).  Both must equal the CPU values bit for bit. */
+int izb_block_dots(const izb_weight* w, int mat, const int8_t* d_aq, int M, int32_t* d_dots, int impl, void* stream);
+/* Start-up check in the manner of Engine::xmx_check: runs the tensor-core kernel and the CUDA-core kernel on seeded
+ * data for both weight types and all store modes and compares (dots bit for bit, outputs within 1e-5 of max|ref|).
+ * Synchronous.  IZB_ERR_SELFCHECK on disagreement; izb_matmul then keeps to the CUDA-core kernel on that device. */
+int izb_selfcheck(int device);
+
+/* Host-buffer convenience call = what a caller without device code does per projection: copies h_x [M][K] to the
+ * device, quantises, multiplies, copies C [M][N] back, synchronises.  Uses library-owned staging buffers per device. */
+int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, int M, float* h_C, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ mixture of experts
+ * moe_route (zero/kernels/moe.cl:50-89): per token softmax numerators of the NU largest of NE logits (ties: lower
+ * expert id), weights renormalised over the selection.  d_ids, d_wts: [T][NU]; d_counts: [NE] (overwritten). */
+int izb_moe_route(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts, int32_t* d_counts,
+                  void* stream);
+/* moe_scan + moe_scatter (zero/kernels/moe.cl:141-179), deterministic: slots of an expert in increasing (token, choice)
+ * order.  d_offs [NE+1]; d_tiles [1 + 3*max_tiles] = count, then (expert, first slot, rows <= TM); d_stok, d_swt, d_inv
+ * [T*NU]. */
+int izb_moe_sort(const int32_t* d_ids, const float* d_wts, const int32_t* d_counts, int T, int NE, int NU, int TM,
+                 int32_t* d_offs, int32_t* d_tiles, int max_tiles, int32_t* d_stok, float* d_swt, int32_t* d_inv,
+                 void* stream);
+/* moe_gateup_q (zero/kernels/decode_moe.cl:92-260): d_h[slot][F] = silu(x_tok Wg_e^T) * (x_tok Wu_e^T) for every tile
+ * of d_tiles (made by izb_moe_sort with the same TM); wg, wu are stacks [NE][F][K]; the activations are token rows
+ * (d_aq [Mp][K], d_asc [K/32][Mp]) gathered through d_stok.  TM 1..8: per-tile kernels on the raw rows, as the
+ * reference; TM = 128: grouped tensor-core GEMM.  The grid is sized by max_tiles; tiles past d_tiles[0] return. */
+int izb_moe_gateup(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
+                   const int32_t* d_tiles, int max_tiles, int TM, const int32_t* d_stok, float* d_h, void* stream);
+/* moe_down_q (zero/kernels/decode_moe.cl:269-449): d_y[slot][E] = swt[slot] * (hq[slot] Wd_e^T); d_hq [Sp][F],
+ * d_hsc [F/32][Sp] from izb_quantize_act over the slot rows of d_h. */
+int izb_moe_down(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles, int max_tiles,
+                 int TM, const float* d_swt, float* d_y, void* stream);
+/* moe_combine (zero/kernels/moe.cl:344-352, no shared expert): x[t] += sum_k y[inv[t*NU+k]] in choice order. */
+int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, void* stream);
+
+/* ------------------------------------------------------------------------------------------------ tensor parallel
+ * tp_range (zero/mgpu/engine_tp_shard.h:68-72): rank r's [begin, end) of `total` in whole `unit`s. */
+int izb_tp_range(int64_t total, int64_t unit, int nranks, int rank, int64_t* begin, int64_t* end);
+/* tp_add (zero/kernels/tp.cl:5-11): x[i] += part_0[i] + ... + part_{np-1}[i], rank order. */
+int izb_tp_add(float* d_x, const float* d_parts, size_t n, int np, size_t stride, void* stream);
+/* Communicator over NCCL (replaces TpComm, zero/mgpu/engine_tp.h:36-124).  id: 128 bytes from izb_tp_unique_id on rank
+ * 0, distributed by the caller. */
+int izb_tp_unique_id(void* id128);
+int izb_tp_create(int nranks, int rank, const void* id128, int device, izb_tp** out);
+void izb_tp_destroy(izb_tp* tp);
+/* tp_out's sum (zero/mgpu/engine_tp_shard.h:318-325, tp_reduce_at zero/mgpu/engine_tp.h:272): d_x[rows][E] += sum over
+ * ranks of d_part (f32 all-reduce over NVLink; d_part is overwritten with the sum). */
+int izb_tp_allreduce_rows(izb_tp* tp, float* d_x, float* d_part, int rows, int E, void* stream);
+/* Same sum where the next step quantises anyway: reduce-scatter the f32 partials by token rows, add this rank's rows
+ * of d_x, quantise them, all-gather int8 + scales.  Every element is summed on one rank only, so all ranks end with
+ * identical int8 rows (the reference's bit-identical-residual property, zero/kernels/tp.cl:3-4).  rows % (16*nranks)
+ * == 0.  d_xsum (may be NULL) receives this rank's summed f32 rows [rows/nranks][E]. */
+int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d_part, int rows, int E, float* d_xsum, int8_t* d_aq,
+                               float* d_asc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IZB200_H */

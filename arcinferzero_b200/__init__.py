@@ -20,7 +20,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 
 # every symbol include/izb200.h declares (tests check the library exports each of them)
 SYMBOLS = [
-    "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status",
+    "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
     "izb_quantize_act", "izb_swiglu_quant",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
@@ -75,6 +75,18 @@ def _stream() -> C.c_void_p:
 
 def launch_count() -> int:
     return int(lib().izb_launch_count())
+
+
+def profile_start() -> None:
+    _check(lib().izb_profile_start())
+
+
+def profile_stop() -> dict:
+    """Per-kernel {"launches", "ms"} of every library launch since profile_start (synchronises)."""
+    import json
+    buf = C.create_string_buffer(8192)
+    _check(lib().izb_profile_stop(buf, C.c_size_t(8192)))
+    return json.loads(buf.value.decode())
 
 
 def pad_rows(M: int) -> int:

@@ -49,6 +49,70 @@ extern "C" const char* izb_status_string(int s) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------- per-kernel timing
+namespace {
+struct ProfRec { const char* name; cudaEvent_t a, b; };
+std::atomic<int> g_prof_on{0};
+std::mutex g_prof_mu;
+std::vector<ProfRec> g_prof;
+std::vector<cudaEvent_t> g_prof_pool;
+cudaEvent_t prof_event() {
+  if (!g_prof_pool.empty()) { cudaEvent_t e = g_prof_pool.back(); g_prof_pool.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+}  // namespace
+
+void izb_prof_begin(const char* name, cudaStream_t st) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  ProfRec r{name, prof_event(), prof_event()};
+  cudaEventRecord(r.a, st);
+  g_prof.push_back(r);
+}
+void izb_prof_end(cudaStream_t st) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (!g_prof.empty()) cudaEventRecord(g_prof.back().b, st);
+}
+
+extern "C" int izb_profile_start(void) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) { g_prof_pool.push_back(r.a); g_prof_pool.push_back(r.b); }
+  g_prof.clear();
+  g_prof_on.store(1);
+  return IZB_OK;
+}
+
+extern "C" int izb_profile_stop(char* json, size_t cap) {
+  g_prof_on.store(0);
+  if (!json || cap < 64) IZB_FAIL(IZB_ERR_ARG, "profile_stop: buffer too small");
+  IZB_CUDA(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  struct Agg { const char* name; int n; double ms; };
+  std::vector<Agg> agg;
+  for (auto& r : g_prof) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, r.a, r.b) != cudaSuccess) { cudaGetLastError(); ms = 0.0f; }
+    size_t i = 0;
+    for (; i < agg.size(); ++i)
+      if (!strcmp(agg[i].name, r.name)) break;
+    if (i == agg.size()) agg.push_back({r.name, 0, 0.0});
+    agg[i].n++;
+    agg[i].ms += ms;
+    g_prof_pool.push_back(r.a);
+    g_prof_pool.push_back(r.b);
+  }
+  g_prof.clear();
+  size_t off = 0;
+  off += snprintf(json + off, cap - off, "{");
+  for (size_t i = 0; i < agg.size() && off + 96 < cap; ++i)
+    off += snprintf(json + off, cap - off, "%s\"%s\": {\"launches\": %d, \"ms\": %.6f}", i ? ", " : "", agg[i].name, agg[i].n, agg[i].ms);
+  snprintf(json + off, cap - off, "}");
+  return IZB_OK;
+}
+
 // ---------------------------------------------------------------------------------------------- per-device state
 namespace {
 constexpr int kMaxDev = 16;

@@ -56,6 +56,18 @@ extern std::atomic<uint64_t> g_izb_launches;
     }                                                                                                     \
   } while (0)
 
+// Optional per-kernel timing (izb_profile_start / izb_profile_stop): when on, every launch is bracketed by two event
+// records on its stream; off by default (one relaxed atomic load per launch).
+void izb_prof_begin(const char* name, cudaStream_t st);
+void izb_prof_end(cudaStream_t st);
+#define IZB_LAUNCH(name, st, ...) \
+  do {                            \
+    izb_prof_begin(name, st);     \
+    __VA_ARGS__;                  \
+    izb_prof_end(st);             \
+    IZB_LAUNCHED();               \
+  } while (0)
+
 static inline bool izb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 // Device-side error word (one per device, in managed-free plain device memory): kernels that give up on a bounded

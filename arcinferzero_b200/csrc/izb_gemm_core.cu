@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(256) gemm_core_kernel(const uint8_t* __restric
 int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C,
                          int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st) {
   dim3 grid((w->N + TN - 1) / TN, (M + TM - 1) / TM);
+  izb_prof_begin(dots ? "gemm_core_dots" : "gemm_core", st);
   if (w->type == IZB_Q4_K) {
     if (dots) gemm_core_kernel<IZB_Q4_K, true><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots);
     else gemm_core_kernel<IZB_Q4_K, false><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots);
@@ -201,6 +202,7 @@ int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* 
     if (dots) gemm_core_kernel<IZB_Q8_0, true><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots);
     else gemm_core_kernel<IZB_Q8_0, false><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots);
   }
+  izb_prof_end(st);
   IZB_LAUNCHED();
   return IZB_OK;
 }

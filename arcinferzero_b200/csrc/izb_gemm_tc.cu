@@ -1,7 +1,832 @@
-// placeholder until the tcgen05 kernel lands
+// Prefill GEMM on the 5th-generation tensor cores (tcgen05, TMEM accumulators), exact per-32-block semantics.
+//
+// Problem: C[m][n] = sum over 32-blocks b of asc[m][b] * wscale[n][b] * dot_b[m][n]  (- the Q4_K min term), where dot_b
+// is an exact integer.  Both operands carry a scale per block, so a block's dot product must leave the tensor core
+// before the next one is added: the f32 combine on the CUDA cores (M*N*K/32 fused multiply-adds), not the MMA, bounds
+// the kernel.  The design therefore minimises CUDA-core work per (m, n, block) to ONE fma:
+//   * operands are fed as fp16 holding exact integers: activations a in [-127,127]; Q4_K weights as sc*q in [0,945]
+//     (the 6-bit sub-block scale folded in, exactly representable), Q8_0 weights q in [-128,127].  tcgen05.mma
+//     kind::f16 then leaves (float)(sc*dot) in TMEM: every product and every partial sum is an integer below 2^24,
+//     so the f32 accumulator holds it exactly (the verification mode reads these accumulators back and the tests
+//     compare them bit for bit with the CPU's int32 dots).  A kind::i8 accumulator would need an int->float
+//     conversion and a second multiply per element, which costs more than the slower fp16 MMA rate saves.
+//   * Q4_K:  tq += asc[m][b] * D_b   per block;   res = fma(d[n], tq, fma(-dmin[n], tmn, res))   per superblock
+//     with tmn = sum_b (asc*asum)[m][b] * mn[n][b] computed on the tensor cores too (kind::f16, bf16 operands: the f32
+//     activation factor split into three bf16 terms, mn exact in bf16), one K=32 MMA pair per superblock.
+//   * Q8_0:  res += (asc[m][b] * d[n][b]) * D_b.
+//
+// CTA = one 128 (tokens, TMEM lanes) x 128 (weight rows, TMEM columns) output tile, 16 warps:
+//   warp 0      activation producer: cp.async.bulk of pre-swizzled fp16 tiles (made by act_prepare_kernel) into a
+//               5-deep ring;
+//   warp 3      weight producer: TMA (cp.async.bulk.tensor.2d) of the raw GGUF superblocks of 128 rows, double-buffered;
+//   warps 4-7   dequantisers: one thread per weight row, nibbles -> fp16 sc*q written in the 128-byte-swizzled K-major
+//               operand layout (3-deep ring), block scales / mins to shared memory;
+//   warp 2      builds the bf16 operand of the min-term MMA;
+//   warp 1      issues tcgen05.mma (one thread) into a ring of three 128-column accumulators + one for the min term;
+//   warps 8-15  combine: tcgen05.ld, one fma per element, final store with the reference's store modes.
+// All waits are bounded: a wait that gives up sets a CTA-wide abort flag and a device error word, the CTA drains and
+// returns without storing (izb_device_status reports it).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <string.h>
+
 #include "izb_common.cuh"
-int izb_make_raw_tensor_map(izb_weight*) { return IZB_ERR_CUDA; }
-int izb_gemm_tc_launch(const izb_weight*, int, const int8_t*, const float*, int, int, float*, int, int, int, int32_t*, cudaStream_t) { return 1; }
-int izb_moe_gateup_tc(const izb_weight*, const izb_weight*, const int8_t*, const float*, int, const int32_t*, int, const int32_t*, float*, cudaStream_t) { return 1; }
-int izb_moe_down_tc(const izb_weight*, const int8_t*, const float*, int, const int32_t*, int, const float*, float*, cudaStream_t) { return 1; }
-extern "C" int izb_selfcheck(int) { return IZB_OK; }
+
+void izb_set_tc_ok(int device, int ok);
+int izb_get_tc_ok(int device);
+int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C,
+                         int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st);
+
+namespace {
+
+constexpr int BM = 128, BN = 128, KS = 64;
+constexpr int NA = 5, NB = 3, ND1 = 3;
+constexpr int STAGE_BYTES = BM * KS * 2;  // 16 KB: 128 rows x 128 B
+constexpr int kThreads = 512;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+// shared memory map (bytes from a 1024-aligned base)
+constexpr int OFF_A = 0;
+constexpr int OFF_B = OFF_A + NA * STAGE_BYTES;       // 81920
+constexpr int OFF_X = OFF_B + NB * STAGE_BYTES;       // 131072: Q4_K: A2 pair tile, B2 pair tile, raw[2], vsum[2], d/dmin ring
+constexpr int RAW_Q4 = 128 * 144, RAW_Q8 = 128 * 272;  // 18432, 34816
+constexpr int OFF_A2 = OFF_X, OFF_B2 = OFF_X + STAGE_BYTES;
+constexpr int OFF_RAW_Q4 = OFF_X + 2 * STAGE_BYTES;   // 163840
+constexpr int OFF_VS = OFF_RAW_Q4 + 2 * RAW_Q4;       // 200704
+constexpr int OFF_DM = OFF_VS + 2 * 4096;             // 208896: 4 x [2][128] f32
+constexpr int OFF_RAW_Q8 = OFF_X;                     // 131072
+constexpr int OFF_D8 = OFF_RAW_Q8 + 2 * RAW_Q8;       // 200704: 4 x [8][128] f32
+constexpr int OFF_BAR = 217088;                       // after the larger of the two maps
+constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;      // barriers + alignment slack
+
+enum Bar {  // 8-byte mbarriers
+  A_FULL = 0, A_EMPTY = A_FULL + NA, B_FULL = A_EMPTY + NA, B_EMPTY = B_FULL + NB, RAW_FULL = B_EMPTY + NB,
+  RAW_EMPTY = RAW_FULL + 2, D1_FULL = RAW_EMPTY + 2, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1, D2_EMPTY,
+  AB2_FULL, MINS_DONE = AB2_FULL + 2, NUM_BARS = MINS_DONE + 2
+};
+static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
+
+// error-word codes (which wait gave up)
+enum : uint32_t { E_APROD = 1, E_WPROD = 2, E_DEQ = 4, E_PREP = 8, E_MMA = 16, E_EPI = 32 };
+
+struct TcParams {
+  const uint16_t* aimg;   // [tiles][K/64][128][64] fp16, rows 128-byte swizzled
+  const float* vsum;      // [tiles][K/32][128] f32 = asc * asum (Q4_K)
+  const float* asc;       // [K/32][lda]
+  int lda;                // Mp (or Sp)
+  const int32_t* tiles;   // grouped: [1 + 3*max_tiles]; dense: null
+  const int32_t* rowmap;  // grouped gather of activation rows (slot -> token) or null
+  const float* rowscale;  // per output row factor or null
+  int M;                  // dense: rows to store
+  int N, K;               // per matrix
+  int mat;                // dense: matrix of the stack
+  float* C;
+  int ldc, c_off, acc;
+  int32_t* dots;          // verification mode output or null
+  uint32_t* err;
+};
+
+// ---------------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  false = gave up (or another thread did): the caller leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
+                                          uint32_t code) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicOr(err, code);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(tmap), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart (tcgen05 shared-memory
+// descriptor: start address >> 4, stride byte offset >> 4 at bit 32, descriptor version 1 at bit 46, swizzle mode 2
+// (128 B) at bit 61; the leading byte offset is not used when the MMA's K extent lies inside one swizzled row).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// instruction descriptor, kind::f16: D = f32 (bit 4), A/B format at bits 7 / 10 (0 fp16, 1 bf16), both K-major,
+// N >> 3 at bit 17, M >> 4 at bit 24
+constexpr uint32_t kIdescF16 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t kIdescBF16 = kIdescF16 | (1u << 7) | (1u << 10);
+
+// position p (0..7) inside a 16-byte chunk of the Q4_K operand row holds element perm8[p] of that group of eight:
+// the order in which the dequantiser's two-nibbles-per-word extraction delivers them
+__device__ __forceinline__ int q4k_perm8(int p) { return (p & 4) | ((p & 1) << 1) | ((p >> 1) & 1); }
+
+// ---------------------------------------------------------------------------------------------- activation pre-pass
+// Per 128-row tile: fp16 operand images (one 16 KB swizzled stage per 64 elements of K) and, for Q4_K, the min-term
+// factor vsum[b][r] = asc * (float)asum.  One thread per (row, 16-byte output chunk).
+template <int QT>
+__global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asc, int lda,
+                                                          int K, int rows_total, const int32_t* __restrict__ tiles,
+                                                          const int32_t* __restrict__ rowmap, uint16_t* __restrict__ aimg,
+                                                          float* __restrict__ vsum, int want_vsum) {
+  const int tile = blockIdx.y;
+  int r0, nr;
+  if (tiles) {
+    if (tile >= tiles[0]) return;
+    r0 = tiles[2 + 3 * tile];
+    nr = tiles[3 + 3 * tile];
+  } else {
+    r0 = tile * BM;
+    nr = min(BM, rows_total - r0);
+  }
+  const int nchunk = K / 8;                      // 16-byte output chunks per row
+  const int idx = blockIdx.x * 256 + threadIdx.x;  // over 128 rows x nchunk, chunk fastest
+  if (idx >= BM * nchunk) return;
+  const int r = idx / nchunk, ch = idx % nchunk;
+  const int stage = ch >> 3, c = ch & 7;
+  int src = -1;
+  if (r < nr) src = rowmap ? rowmap[r0 + r] : r0 + r;
+  uint2 v = make_uint2(0, 0);
+  if (src >= 0) v = *reinterpret_cast<const uint2*>(aq + (size_t)src * K + (size_t)ch * 8);
+  int a[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    a[i] = (int)(int8_t)(v.x >> (8 * i));
+    a[4 + i] = (int)(int8_t)(v.y >> (8 * i));
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e0 = QT == IZB_Q4_K ? q4k_perm8(2 * i) : 2 * i, e1 = QT == IZB_Q4_K ? q4k_perm8(2 * i + 1) : 2 * i + 1;
+    const __half2 h = __floats2half2_rn((float)a[e0], (float)a[e1]);
+    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const size_t nstages = K / KS;
+  uint8_t* dst = reinterpret_cast<uint8_t*>(aimg) + ((size_t)tile * nstages + stage) * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+  *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+  if (QT == IZB_Q4_K && want_vsum) {
+    int s = a[0] + a[1] + a[2] + a[3] + a[4] + a[5] + a[6] + a[7];
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);  // the four chunks of a 32-block are four consecutive threads of one row
+    if ((ch & 3) == 0) {
+      const int b = ch >> 2;
+      const float sc = src >= 0 ? asc[(size_t)b * lda + src] : 0.0f;
+      vsum[((size_t)tile * (K / 32) + b) * BM + r] = __fmul_rn(sc, (float)s);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- the GEMM kernel
+template <int QT, bool kDots>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NUM_BARS * 8);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + NUM_BARS * 8 + 4);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) -> uint32_t { return bar0 + 8u * (uint32_t)i; };
+
+  // ---- which tile
+  int tile, expert, r0, nr;
+  if (p.tiles) {
+    tile = blockIdx.y;
+    if (tile >= p.tiles[0]) return;  // uniform over the CTA, before any barrier or TMEM use
+    expert = p.tiles[1 + 3 * tile];
+    r0 = p.tiles[2 + 3 * tile];
+    nr = p.tiles[3 + 3 * tile];
+  } else {
+    tile = blockIdx.y;
+    expert = p.mat;
+    r0 = tile * BM;
+    nr = min(BM, p.M - r0);
+  }
+  const int n0 = blockIdx.x * BN;
+  const int nsb = p.K >> 8, nb = p.K >> 5, nstages = p.K / KS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int SBB = QT == IZB_Q4_K ? 144 : 272;
+  constexpr int RAW = QT == IZB_Q4_K ? RAW_Q4 : RAW_Q8;
+  constexpr int OFF_RAW = QT == IZB_Q4_K ? OFF_RAW_Q4 : OFF_RAW_Q8;
+  constexpr bool kMins = QT == IZB_Q4_K && !kDots;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NA; ++i) { mbar_init(bar(A_FULL + i), 1); mbar_init(bar(A_EMPTY + i), 1); }
+    for (int i = 0; i < NB; ++i) { mbar_init(bar(B_FULL + i), 4); mbar_init(bar(B_EMPTY + i), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(RAW_FULL + i), 1);
+      mbar_init(bar(RAW_EMPTY + i), kMins ? 5 : 4);
+      mbar_init(bar(AB2_FULL + i), 5);
+      mbar_init(bar(MINS_DONE + i), 1);
+    }
+    for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 8); }
+    mbar_init(bar(D2_FULL), 1);
+    mbar_init(bar(D2_EMPTY), 8);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (kMins) {  // the padding chunks of the min-term operands stay zero for the whole kernel
+    for (int i = threadIdx.x; i < 2 * STAGE_BYTES / 16; i += kThreads) reinterpret_cast<uint4*>(smem + OFF_A2)[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      // ================= activation producer
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
+      for (int g = 0; g < nstages; ++g) {
+        const int sa = g % NA;
+        if (!mbar_wait(bar(A_EMPTY + sa), ((g / NA) & 1) ^ 1, abort_flag, p.err, E_APROD)) break;
+        mbar_expect_tx(bar(A_FULL + sa), STAGE_BYTES);
+        bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(A_FULL + sa));
+      }
+    } else if (warp == 3 && lane == 0) {
+      // ================= weight producer
+      const int wrow = expert * p.N + n0;
+      for (int s = 0; s < nsb; ++s) {
+        const int rb = s & 1;
+        if (!mbar_wait(bar(RAW_EMPTY + rb), ((s >> 1) & 1) ^ 1, abort_flag, p.err, E_WPROD)) break;
+        mbar_expect_tx(bar(RAW_FULL + rb), RAW + (kMins ? 4096 : 0));
+        tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
+        if (kMins)
+          bulk_g2s(smem_u32(smem + OFF_VS + rb * 4096), p.vsum + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(RAW_FULL + rb));
+      }
+    } else if (warp == 2 && kMins) {
+      // ================= min-term activation operand: vsum (f32) -> three bf16 terms, swizzled K-major half tile
+      for (int s = 0; s < nsb; ++s) {
+        const int rb = s & 1, h = s & 1, u = s >> 1;
+        if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_PREP)) break;
+        if (!mbar_wait(bar(MINS_DONE + h), (u & 1) ^ 1, abort_flag, p.err, E_PREP)) break;
+        const float* vs = reinterpret_cast<const float*>(smem + OFF_VS + rb * 4096);
+#pragma unroll 1
+        for (int i = 0; i < 4; ++i) {
+          const int r = lane + 32 * i;
+          uint32_t hi[4], mid[4], lo[4];
+#pragma unroll
+          for (int b2 = 0; b2 < 4; ++b2) {
+            uint32_t w3[3] = {0, 0, 0};
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const float v = vs[(2 * b2 + k) * BM + r];
+              const __nv_bfloat16 h1 = __float2bfloat16_rn(v);
+              const float r1 = __fsub_rn(v, __bfloat162float(h1));
+              const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+              const float r2 = __fsub_rn(r1, __bfloat162float(h2));
+              const __nv_bfloat16 h3 = __float2bfloat16_rn(r2);
+              w3[0] |= (uint32_t)__bfloat16_as_ushort(h1) << (16 * k);
+              w3[1] |= (uint32_t)__bfloat16_as_ushort(h2) << (16 * k);
+              w3[2] |= (uint32_t)__bfloat16_as_ushort(h3) << (16 * k);
+            }
+            hi[b2] = w3[0]; mid[b2] = w3[1]; lo[b2] = w3[2];
+          }
+          unsigned char* row = smem + OFF_A2 + r * 128;
+          *reinterpret_cast<uint4*>(row + (((4 * h + 0) ^ (r & 7)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(row + (((4 * h + 1) ^ (r & 7)) << 4)) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
+          *reinterpret_cast<uint4*>(row + (((4 * h + 2) ^ (r & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(AB2_FULL + h));
+          mbar_arrive(bar(RAW_EMPTY + rb));
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ================= MMA issuer
+      bool ok = true;
+      int j = 0;  // block counter -> accumulator ring
+      for (int g = 0; g < nstages && ok; ++g) {
+        const int sa = g % NA, sbq = g % NB;
+        ok = mbar_wait(bar(A_FULL + sa), (g / NA) & 1, abort_flag, p.err, E_MMA) &&
+             mbar_wait(bar(B_FULL + sbq), (g / NB) & 1, abort_flag, p.err, E_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sbq * STAGE_BYTES);
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk, ++j) {
+          const int d = j % ND1;
+          if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t dt = tmem_base + (uint32_t)(d * BN);
+#pragma unroll
+          for (int k16 = 0; k16 < 2; ++k16)
+            tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
+          tc_commit(bar(D1_FULL + d));
+        }
+        if (!ok) break;
+        tc_commit(bar(A_EMPTY + sa));
+        tc_commit(bar(B_EMPTY + sbq));
+        if (kMins && (g & 3) == 3) {
+          const int s = g >> 2, h = s & 1, u = s >> 1;
+          ok = mbar_wait(bar(AB2_FULL + h), u & 1, abort_flag, p.err, E_MMA) &&
+               mbar_wait(bar(D2_EMPTY), (s & 1) ^ 1, abort_flag, p.err, E_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a2 = smem_u32(smem + OFF_A2) + 64 * h, b2 = smem_u32(smem + OFF_B2) + 64 * h;
+#pragma unroll
+          for (int k16 = 0; k16 < 2; ++k16)
+            tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a2 + k16 * 32), umma_desc(b2 + k16 * 32), kIdescBF16, k16);
+          tc_commit(bar(D2_FULL));
+          tc_commit(bar(MINS_DONE + h));
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ================= dequantisers: thread t <-> weight row n0 + t
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    const int t = threadIdx.x - 128;
+    bool ok = true;
+    for (int s = 0; s < nsb && ok; ++s) {
+      const int rb = s & 1, u = s >> 1;
+      if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_DEQ)) break;
+      const unsigned char* rrow = smem + OFF_RAW + rb * RAW + t * SBB;
+      const uint4 hdr = *reinterpret_cast<const uint4*>(rrow);
+      const uint32_t s3[3] = {hdr.y, hdr.z, hdr.w};
+      if (QT == IZB_Q4_K) {
+        if (kMins) {
+          float* dm = reinterpret_cast<float*>(smem + OFF_DM + (s & 3) * 1024);
+          dm[t] = half_bits_to_float(hdr.x & 0xFFFFu);
+          dm[128 + t] = half_bits_to_float(hdr.x >> 16);
+          const int h = s & 1;
+          if (!mbar_wait(bar(MINS_DONE + h), (u & 1) ^ 1, abort_flag, p.err, E_DEQ)) break;
+          uint32_t m4[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            int sc0, mn0, sc1, mn1;
+            q4k_scale_min(s3, 2 * k, sc0, mn0);
+            q4k_scale_min(s3, 2 * k + 1, sc1, mn1);
+            m4[k] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)mn0)) |
+                    ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)mn1)) << 16);
+          }
+          unsigned char* row = smem + OFF_B2 + t * 128;
+#pragma unroll
+          for (int k = 0; k < 3; ++k) *reinterpret_cast<uint4*>(row + (((4 * h + k) ^ (t & 7)) << 4)) = make_uint4(m4[0], m4[1], m4[2], m4[3]);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(AB2_FULL + h));
+        }
+      } else {
+        float* d8 = reinterpret_cast<float*>(smem + OFF_D8 + (s & 3) * 4096);
+        const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
+#pragma unroll
+        for (int b = 0; b < 8; ++b) d8[b * 128 + t] = half_bits_to_float((b & 1) ? hw[b >> 1] >> 16 : hw[b >> 1] & 0xFFFFu);
+      }
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        const int g = 4 * s + c, sbq = g % NB;
+        if (!mbar_wait(bar(B_EMPTY + sbq), ((g / NB) & 1) ^ 1, abort_flag, p.err, E_DEQ)) { ok = false; break; }
+        unsigned char* orow = smem + OFF_B + sbq * STAGE_BYTES + t * 128;
+        if (QT == IZB_Q4_K) {
+          const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c), q1 = *reinterpret_cast<const uint4*>(rrow + 32 + 32 * c);
+          const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          int sc_lo = 1, sc_hi = 1, mn_unused;
+          if (!kDots) {
+            q4k_scale_min(s3, 2 * c, sc_lo, mn_unused);
+            q4k_scale_min(s3, 2 * c + 1, sc_hi, mn_unused);
+          }
+          const __half2 slo = __half2half2(__int2half_rn(sc_lo)), shi = __half2half2(__int2half_rn(sc_hi));
+          const __half2 nlo = __half2half2(__int2half_rn(-1024 * sc_lo)), nhi = __half2half2(__int2half_rn(-1024 * sc_hi));
+          auto cvt = [](uint32_t word, int sh, __half2 scale, __half2 neg) -> uint32_t {
+            const uint32_t bitsv = ((word >> sh) & 0x000F000Fu) | 0x64006400u;  // (1024 + q) in both halves
+            const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&bitsv), scale, neg);  // = sc * q exactly
+            return *reinterpret_cast<const uint32_t*>(&r);
+          };
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const uint32_t w0 = w[2 * jj], w1 = w[2 * jj + 1];
+            *reinterpret_cast<uint4*>(orow + ((jj ^ (t & 7)) << 4)) =
+                make_uint4(cvt(w0, 0, slo, nlo), cvt(w0, 8, slo, nlo), cvt(w1, 0, slo, nlo), cvt(w1, 8, slo, nlo));
+            *reinterpret_cast<uint4*>(orow + (((4 + jj) ^ (t & 7)) << 4)) =
+                make_uint4(cvt(w0, 4, shi, nhi), cvt(w0, 12, shi, nhi), cvt(w1, 4, shi, nhi), cvt(w1, 12, shi, nhi));
+          }
+        } else {
+          const __half2 bias = __half2half2(__int2half_rn(1152));
+          auto cvt = [&](uint32_t x, uint32_t sel) -> uint32_t {
+            const uint32_t bitsv = __byte_perm(x, 0x64646464u, sel);  // (1024 + (q + 128)) in both halves
+            const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&bitsv), bias);
+            return *reinterpret_cast<const uint32_t*>(&r);
+          };
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const uint4 q = *reinterpret_cast<const uint4*>(rrow + 16 + 64 * c + 16 * jj);
+            const uint32_t x0 = q.x ^ 0x80808080u, x1 = q.y ^ 0x80808080u, x2 = q.z ^ 0x80808080u, x3 = q.w ^ 0x80808080u;
+            *reinterpret_cast<uint4*>(orow + (((2 * jj) ^ (t & 7)) << 4)) =
+                make_uint4(cvt(x0, 0x4140), cvt(x0, 0x4342), cvt(x1, 0x4140), cvt(x1, 0x4342));
+            *reinterpret_cast<uint4*>(orow + (((2 * jj + 1) ^ (t & 7)) << 4)) =
+                make_uint4(cvt(x2, 0x4140), cvt(x2, 0x4342), cvt(x3, 0x4140), cvt(x3, 0x4342));
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_FULL + sbq));
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(RAW_EMPTY + rb));
+    }
+  } else {
+    // ================= combine: thread <-> TMEM lane (token row) 32*(warp%4) + lane, 64 of the 128 columns
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int q = warp & 3, half = (warp - 8) >> 2;
+    const int r = 32 * q + lane;
+    const bool row_ok = r < nr;
+    const int out_row = r0 + r;
+    int arow = -1;
+    if (row_ok) arow = p.rowmap ? p.rowmap[out_row] : out_row;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(half * 64);
+    float res[64], tq[64];
+#pragma unroll
+    for (int c = 0; c < 64; ++c) res[c] = tq[c] = 0.0f;
+    float a_cur[8];  // this row's activation scales, fetched one superblock (8 blocks) ahead of their use
+#pragma unroll
+    for (int b = 0; b < 8; ++b) a_cur[b] = (!kDots && arow >= 0) ? p.asc[(size_t)b * p.lda + arow] : 0.0f;
+    bool ok = true;
+    int j = 0;
+    for (int s = 0; s < nsb && ok; ++s) {
+#pragma unroll
+      for (int b = 0; b < 8; ++b, ++j) {
+        const int d = j % ND1;
+        if (!mbar_wait(bar(D1_FULL + d), (j / ND1) & 1, abort_flag, p.err, E_EPI)) { ok = false; break; }
+        tc_fence_after();
+        const float a = a_cur[b];
+        a_cur[b] = (!kDots && arow >= 0 && s + 1 < nsb) ? p.asc[(size_t)(8 * (s + 1) + b) * p.lda + arow] : 0.0f;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {  // the thread's 64 columns in two passes of 32 (registers)
+          uint32_t v[32];
+          tc_ld32(t_lane + (uint32_t)(d * BN + 32 * hh), v);
+          tc_wait_ld();
+          if (hh == 1) {  // both halves read: the accumulator buffer may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(D1_EMPTY + d));
+          }
+          if (kDots) {
+            if (row_ok) {
+              int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64 + 32 * hh) * nb + 8 * s + b;
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[(size_t)c * nb] = __float2int_rn(__uint_as_float(v[c]));
+            }
+          } else if (QT == IZB_Q4_K) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) tq[32 * hh + c] = fmaf(a, __uint_as_float(v[c]), tq[32 * hh + c]);
+          } else {
+            const float4* d8 = reinterpret_cast<const float4*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256 + hh * 128);
+#pragma unroll
+            for (int c4 = 0; c4 < 8; ++c4) {
+              const float4 dd = d8[c4];
+              res[32 * hh + 4 * c4 + 0] = fmaf(__fmul_rn(a, dd.x), __uint_as_float(v[4 * c4 + 0]), res[32 * hh + 4 * c4 + 0]);
+              res[32 * hh + 4 * c4 + 1] = fmaf(__fmul_rn(a, dd.y), __uint_as_float(v[4 * c4 + 1]), res[32 * hh + 4 * c4 + 1]);
+              res[32 * hh + 4 * c4 + 2] = fmaf(__fmul_rn(a, dd.z), __uint_as_float(v[4 * c4 + 2]), res[32 * hh + 4 * c4 + 2]);
+              res[32 * hh + 4 * c4 + 3] = fmaf(__fmul_rn(a, dd.w), __uint_as_float(v[4 * c4 + 3]), res[32 * hh + 4 * c4 + 3]);
+            }
+          }
+        }
+      }
+      if (!ok) break;
+      if (kMins) {
+        if (!mbar_wait(bar(D2_FULL), s & 1, abort_flag, p.err, E_EPI)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t v[32];
+          tc_ld32(t_lane + (uint32_t)(ND1 * BN + 32 * hh), v);
+          tc_wait_ld();
+          if (hh == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(D2_EMPTY));
+          }
+          const float4* dv = reinterpret_cast<const float4*>(smem + OFF_DM + (s & 3) * 1024 + half * 256 + hh * 128);
+          const float4* mv = reinterpret_cast<const float4*>(smem + OFF_DM + (s & 3) * 1024 + 512 + half * 256 + hh * 128);
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 dd = dv[c4], mm = mv[c4];
+            const int c = 32 * hh + 4 * c4;
+            res[c + 0] = fmaf(dd.x, tq[c + 0], fmaf(-mm.x, __uint_as_float(v[4 * c4 + 0]), res[c + 0]));
+            res[c + 1] = fmaf(dd.y, tq[c + 1], fmaf(-mm.y, __uint_as_float(v[4 * c4 + 1]), res[c + 1]));
+            res[c + 2] = fmaf(dd.z, tq[c + 2], fmaf(-mm.z, __uint_as_float(v[4 * c4 + 2]), res[c + 2]));
+            res[c + 3] = fmaf(dd.w, tq[c + 3], fmaf(-mm.w, __uint_as_float(v[4 * c4 + 3]), res[c + 3]));
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 64; ++c) tq[c] = 0.0f;
+      }
+    }
+    if (ok && !kDots && row_ok && !*abort_flag) {
+      float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + n0 + half * 64;
+      const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
+#pragma unroll
+      for (int c4 = 0; c4 < 16; ++c4) {
+        float4 v = make_float4(res[4 * c4], res[4 * c4 + 1], res[4 * c4 + 2], res[4 * c4 + 3]);
+        if (p.rowscale) { v.x = __fmul_rn(rs, v.x); v.y = __fmul_rn(rs, v.y); v.z = __fmul_rn(rs, v.z); v.w = __fmul_rn(rs, v.w); }
+        float4* dst = reinterpret_cast<float4*>(cp) + c4;
+        if (p.acc == 1) {
+          const float4 o = *dst;
+          v.x = __fadd_rn(v.x, o.x); v.y = __fadd_rn(v.y, o.y); v.z = __fadd_rn(v.z, o.z); v.w = __fadd_rn(v.w, o.w);
+        } else if (p.acc == 2) {  // C holds the gate projection: C = v * silu(C)   (zero/kernels/gemm.cl:562-565)
+          const float4 o = *dst;
+          v.x = __fmul_rn(v.x, __fdiv_rn(o.x, __fadd_rn(1.0f, expf(-o.x))));
+          v.y = __fmul_rn(v.y, __fdiv_rn(o.y, __fadd_rn(1.0f, expf(-o.y))));
+          v.z = __fmul_rn(v.z, __fdiv_rn(o.z, __fadd_rn(1.0f, expf(-o.z))));
+          v.w = __fmul_rn(v.w, __fdiv_rn(o.w, __fadd_rn(1.0f, expf(-o.w))));
+        }
+        *dst = v;
+      }
+    }
+  }
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up: let copies and MMAs still in flight land before shared memory and TMEM are released
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+template <int QT, bool kDots>
+int launch_tc(const izb_weight* w, const TcParams& p, dim3 grid, cudaStream_t st) {
+  static bool attr = false;
+  if (!attr) {
+    IZB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<QT, kDots>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr = true;
+  }
+  CUtensorMap tm;
+  memcpy(&tm, w->tmap_raw, sizeof tm);
+  IZB_LAUNCH("gemm_tc", st, gemm_tc_kernel<QT, kDots><<<grid, kThreads, SMEM_BYTES, st>>>(tm, p));
+  return IZB_OK;
+}
+
+// the activation pre-pass + the GEMM for one tile set
+int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int lda, int rows_total, const int32_t* tiles,
+           int n_tiles_grid, const int32_t* rowmap, const float* rowscale, int M_store, float* C, int ldc, int c_off, int acc,
+           int32_t* dots, int ws_slot, cudaStream_t st) {
+  if (!w->has_tmap) return 1;
+  if (w->N % BN || w->K % 256) return 1;
+  const int K = w->K, nb = K / 32, nstages = K / KS;
+  const size_t img_bytes = (size_t)n_tiles_grid * nstages * STAGE_BYTES;
+  const size_t vs_bytes = w->type == IZB_Q4_K ? (size_t)n_tiles_grid * nb * BM * 4 : 0;
+  void* ws = nullptr;
+  if (int rc = izb_workspace(w->device, ws_slot, img_bytes + vs_bytes, &ws)) return rc;
+  uint16_t* aimg = (uint16_t*)ws;
+  float* vsum = (float*)((unsigned char*)ws + img_bytes);
+  dim3 pg((BM * (K / 8) + 255) / 256, n_tiles_grid);
+  const int want_vs = (w->type == IZB_Q4_K && !dots) ? 1 : 0;
+  if (w->type == IZB_Q4_K)
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, want_vs));
+  else
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, 0));
+  TcParams p;
+  p.aimg = aimg;
+  p.vsum = vsum;
+  p.asc = asc;
+  p.lda = lda;
+  p.tiles = tiles;
+  p.rowmap = rowmap;
+  p.rowscale = rowscale;
+  p.M = M_store;
+  p.N = w->N;
+  p.K = K;
+  p.mat = mat;
+  p.C = C;
+  p.ldc = ldc;
+  p.c_off = c_off;
+  p.acc = acc;
+  p.dots = dots;
+  p.err = izb_device_error_word(w->device);
+  if (!p.err) IZB_FAIL(IZB_ERR_NOMEM, "gemm: no device error word");
+  dim3 grid(w->N / BN, n_tiles_grid);
+  if (w->type == IZB_Q4_K) return dots ? launch_tc<IZB_Q4_K, true>(w, p, grid, st) : launch_tc<IZB_Q4_K, false>(w, p, grid, st);
+  return dots ? launch_tc<IZB_Q8_0, true>(w, p, grid, st) : launch_tc<IZB_Q8_0, false>(w, p, grid, st);
+}
+
+}  // namespace
+
+int izb_make_raw_tensor_map(izb_weight* w) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return IZB_ERR_CUDA;
+  const cuuint64_t rows = (cuuint64_t)w->n_mats * w->N;
+  if (rows < 1 || w->row_bytes % 16) return IZB_ERR_ALIGN;
+  cuuint64_t dims[2] = {(cuuint64_t)(w->row_bytes / 4), rows};
+  cuuint64_t strides[1] = {(cuuint64_t)w->row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(w->sb_bytes / 4), (cuuint32_t)BN};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap tm;
+  const CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w->raw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return IZB_ERR_CUDA;
+  memcpy(w->tmap_raw, &tm, sizeof tm);
+  return IZB_OK;
+}
+
+int izb_gemm_tc_launch(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int M, int Mp, float* C, int ldc, int c_off,
+                       int acc, int32_t* dots, cudaStream_t st) {
+  const int n_tiles = (M + BM - 1) / BM;
+  if (n_tiles > 65535) return 1;
+  return run_tc(w, mat, aq, asc, Mp, Mp, nullptr, n_tiles, nullptr, nullptr, M, C, ldc, c_off, acc, dots, kWsGemm, st);
+}
+
+// MoE on the tensor cores: the slots of each expert are tiles of up to 128 rows (izb_moe_sort with TM = 128); gate then up
+// with the fused-SwiGLU store mode (h = up * silu(gate)), down with the routing weight as row scale.
+int izb_moe_gateup_tc(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
+                      const int32_t* d_tiles, int max_tiles, const int32_t* d_stok, float* d_h, cudaStream_t st) {
+  const int F = wg->N;
+  int rc = run_tc(wg, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, F, 0, 0, nullptr, kWsMoe, st);
+  if (rc != 0) return rc;
+  return run_tc(wu, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, F, 0, 2, nullptr, kWsMoe, st);
+}
+
+int izb_moe_down_tc(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles, int max_tiles,
+                    const float* d_swt, float* d_y, cudaStream_t st) {
+  return run_tc(wd, 0, d_hq, d_hsc, Sp, 0, d_tiles, max_tiles, nullptr, d_swt, 0, d_y, wd->N, 0, 0, nullptr, kWsMoe, st);
+}
+
+// ---------------------------------------------------------------------------------------------- start-up check
+// Seeded data, both weight types, all store modes: tensor-core dots == CUDA-core dots bit for bit, outputs within 1e-5
+// of max|ref| (Engine::xmx_check, zero/engine_setup.h:424-622, does the same for its XMX kernel against DP4a).
+namespace {
+__global__ void fill_kernel(uint8_t* p, size_t n, uint32_t seed, int mode) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t x = (uint32_t)i * 2654435761u + seed;
+  x ^= x >> 15; x *= 2246822519u; x ^= x >> 13; x *= 3266489917u; x ^= x >> 16;
+  p[i] = mode == 0 ? (uint8_t)x : (uint8_t)(int8_t)((int)(x % 255u) - 127);
+}
+__global__ void fix_q4k_headers(uint8_t* w, size_t n_sb, uint32_t seed) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_sb) return;
+  uint32_t x = (uint32_t)i * 747796405u + seed;
+  x ^= x >> 16; x *= 2246822519u; x ^= x >> 13;
+  const __half d = __float2half(0.0001f + (float)(x & 0xFFFF) * (0.0099f / 65535.0f));
+  const __half m = __float2half(0.0001f + (float)(x >> 16) * (0.0099f / 65535.0f));
+  *reinterpret_cast<__half*>(w + i * 144) = d;
+  *reinterpret_cast<__half*>(w + i * 144 + 2) = m;
+}
+__global__ void fix_q8_headers(uint8_t* w, size_t n_sb, uint32_t seed) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_sb * 8) return;
+  uint32_t x = (uint32_t)i * 747796405u + seed;
+  x ^= x >> 16; x *= 2246822519u; x ^= x >> 13;
+  *reinterpret_cast<__half*>(w + (i / 8) * 272 + 2 * (i % 8)) = __float2half(0.001f + (float)(x & 0xFFFF) * (0.019f / 65535.0f));
+}
+__global__ void fill_scales(float* p, size_t n, uint32_t seed) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t x = (uint32_t)i * 2654435761u + seed;
+  x ^= x >> 15; x *= 2246822519u; x ^= x >> 13;
+  p[i] = 0.005f + (float)(x & 0xFFFF) * (0.03f / 65535.0f);
+}
+// out[0] = count of differing ints, out[1] = max|a-b| bits, out[2] = max|b| bits
+__global__ void compare_kernel(const float* a, const float* b, size_t n, int as_int, unsigned int* out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (as_int) {
+    if (reinterpret_cast<const int*>(a)[i] != reinterpret_cast<const int*>(b)[i]) atomicAdd(&out[0], 1u);
+  } else {
+    const float d = fabsf(a[i] - b[i]);
+    if (!(d == d)) atomicAdd(&out[0], 1u);
+    atomicMax(&out[1], __float_as_uint(d == d ? d : 0.0f));
+    atomicMax(&out[2], __float_as_uint(fabsf(b[i])));
+  }
+}
+}  // namespace
+
+extern "C" int izb_selfcheck(int device) {
+  if (izb_get_tc_ok(device) == 1) return IZB_OK;
+  IZB_CUDA(cudaSetDevice(device));
+  const int M = 200, Mp = 256, N = 256, K = 1024, nb = K / 32;
+  int verdict = IZB_OK;
+  for (int type : {IZB_Q4_K, IZB_Q8_0}) {
+    izb_weight w;
+    w.type = type; w.n_mats = 1; w.N = N; w.K = K; w.device = device;
+    w.sb_bytes = type == IZB_Q4_K ? 144 : 272;
+    w.row_bytes = (size_t)(K / 256) * w.sb_bytes;
+    w.bytes = (size_t)N * w.row_bytes;
+    const size_t n_out = (size_t)Mp * N, n_dots = (size_t)M * N * nb;
+    void* ws = nullptr;
+    const size_t need = w.bytes + kRawSlack + (size_t)Mp * K + (size_t)nb * Mp * 4 + 2 * n_out * 4 + 2 * n_dots * 4 + 4096;
+    if (int rc = izb_workspace(device, kWsCheck, need, &ws)) return rc;
+    uint8_t* base = (uint8_t*)ws;
+    w.raw = base; base += (w.bytes + kRawSlack + 255) & ~size_t(255);
+    int8_t* aq = (int8_t*)base; base += (size_t)Mp * K;
+    float* asc = (float*)base; base += (size_t)nb * Mp * 4;
+    float* c_tc = (float*)base; base += n_out * 4;
+    float* c_core = (float*)base; base += n_out * 4;
+    int32_t* d_tc = (int32_t*)base; base += n_dots * 4;
+    int32_t* d_core = (int32_t*)base; base += n_dots * 4;
+    unsigned int* cmp = (unsigned int*)base;
+    fill_kernel<<<(unsigned)((w.bytes + 255) / 256), 256>>>(w.raw, w.bytes, 17u + type, type == IZB_Q4_K ? 0 : 1);
+    if (type == IZB_Q4_K) fix_q4k_headers<<<(unsigned)((w.bytes / 144 + 255) / 256), 256>>>(w.raw, w.bytes / 144, 5u);
+    else fix_q8_headers<<<(unsigned)((w.bytes / 272 * 8 + 255) / 256), 256>>>(w.raw, w.bytes / 272, 5u);
+    fill_kernel<<<(unsigned)(((size_t)Mp * K + 255) / 256), 256>>>((uint8_t*)aq, (size_t)Mp * K, 99u, 1);
+    fill_scales<<<(unsigned)(((size_t)nb * Mp + 255) / 256), 256>>>(asc, (size_t)nb * Mp, 7u);
+    IZB_CUDA(cudaGetLastError());
+    if (izb_make_raw_tensor_map(&w) != IZB_OK) { izb_set_tc_ok(device, 0); IZB_FAIL(IZB_ERR_SELFCHECK, "selfcheck: cannot encode a tensor map"); }
+    w.has_tmap = true;
+    unsigned int h[3];
+    // dots
+    int rc = izb_gemm_tc_launch(&w, 0, aq, nullptr, M, M, nullptr, 0, 0, 0, d_tc, 0);
+    if (rc == 0) rc = izb_gemm_core_launch(&w, w.raw, aq, nullptr, M, M, nullptr, 0, 0, 0, d_core, 0);
+    if (rc != 0) { izb_set_tc_ok(device, 0); return rc < 0 ? rc : IZB_ERR_SELFCHECK; }
+    IZB_CUDA(cudaMemset(cmp, 0, 12));
+    compare_kernel<<<(unsigned)((n_dots + 255) / 256), 256>>>((const float*)d_tc, (const float*)d_core, n_dots, 1, cmp);
+    IZB_CUDA(cudaMemcpy(h, cmp, 12, cudaMemcpyDeviceToHost));
+    if (h[0]) { verdict = IZB_ERR_SELFCHECK; izb_set_error("selfcheck: type %d: %u block dots differ between the tensor-core and CUDA-core kernels", type, h[0]); break; }
+    for (int acc = 0; acc < 3 && verdict == IZB_OK; ++acc) {
+      fill_scales<<<(unsigned)((n_out + 255) / 256), 256>>>(c_tc, n_out, 3u);
+      fill_scales<<<(unsigned)((n_out + 255) / 256), 256>>>(c_core, n_out, 3u);
+      rc = izb_gemm_tc_launch(&w, 0, aq, asc, M, Mp, c_tc, N, 0, acc, nullptr, 0);
+      if (rc == 0) rc = izb_gemm_core_launch(&w, w.raw, aq, asc, M, Mp, c_core, N, 0, acc, nullptr, 0);
+      if (rc != 0) { izb_set_tc_ok(device, 0); return rc < 0 ? rc : IZB_ERR_SELFCHECK; }
+      IZB_CUDA(cudaMemset(cmp, 0, 12));
+      compare_kernel<<<(unsigned)((n_out + 255) / 256), 256>>>(c_tc, c_core, n_out, 0, cmp);
+      IZB_CUDA(cudaMemcpy(h, cmp, 12, cudaMemcpyDeviceToHost));
+      float err, ref;
+      memcpy(&err, &h[1], 4);
+      memcpy(&ref, &h[2], 4);
+      if (h[0] || !(err <= 1e-5f * ref)) {
+        verdict = IZB_ERR_SELFCHECK;
+        izb_set_error("selfcheck: type %d store mode %d: max|err| %g vs max|ref| %g (%u NaN)", type, acc, err, ref, h[0]);
+      }
+    }
+    if (verdict != IZB_OK) break;
+  }
+  uint32_t word = 0;
+  const int st = izb_device_status(device, &word);
+  if (st != IZB_OK && verdict == IZB_OK) { verdict = st; }
+  izb_set_tc_ok(device, verdict == IZB_OK ? 1 : 0);
+  return verdict;
+}

@@ -55,8 +55,7 @@ int launch_qt(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const f
     IZB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
     attr_set = true;
   }
-  gemv_kernel<QT, T><<<grid, kWarps * 32, smem, st>>>(raw, w->N, w->K, aq, asc, Mp, C, ldc, c_off, acc, spc);
-  IZB_LAUNCHED();
+  IZB_LAUNCH("gemv", st, gemv_kernel<QT, T><<<grid, kWarps * 32, smem, st>>>(raw, w->N, w->K, aq, asc, Mp, C, ldc, c_off, acc, spc));
   return IZB_OK;
 }
 

@@ -103,8 +103,7 @@ extern "C" int izb_quantize_act(const float* d_x, int ldx, int M_valid, int Mp, 
                                 int16_t* d_absum, void* stream) {
   if (int rc = check_quant_args(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, K)) return rc;
   dim3 grid(K / 256, (Mp + 31) / 32);
-  quantize_act_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0);
-  IZB_LAUNCHED();
+  IZB_LAUNCH("quantize_act", (cudaStream_t)stream, quantize_act_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0));
   return IZB_OK;
 }
 

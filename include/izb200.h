@@ -59,6 +59,11 @@ const char* izb_status_string(int status);
 const char* izb_last_error(void);
 /* number of kernels this library has launched in the calling process (benchmark bookkeeping) */
 uint64_t izb_launch_count(void);
+/* Per-kernel timing, as Engine::profile / collect_profile (zero/engine.h:936-950): between start and stop every kernel
+ * launch of the library is bracketed by two CUDA event records on its stream.  stop synchronises the device and writes
+ * {"kernel": {"launches": n, "ms": total}, ...} as JSON text into `json`. */
+int izb_profile_start(void);
+int izb_profile_stop(char* json, size_t cap);
 /* Reads and clears the device-side error word of `device`: non-zero when a kernel gave up on a bounded wait
  * (value = where).  Synchronises the device. */
 int izb_device_status(int device, uint32_t* word);

@@ -13,7 +13,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libizb200.so")
+LIB_PATH = os.environ.get("IZB200_LIB") or os.path.join(HERE, "libizb200.so")  # IZB200_LIB: another build of the library
 
 Q8_0, Q4_K = 8, 12
 GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2

@@ -56,24 +56,28 @@ constexpr int OFF_VS = OFF_RAW_Q4 + 2 * RAW_Q4;       // 200704
 constexpr int OFF_DM = OFF_VS + 2 * 4096;             // 208896: 4 x [2][128] f32
 constexpr int OFF_RAW_Q8 = OFF_X;                     // 131072
 constexpr int OFF_D8 = OFF_RAW_Q8 + 2 * RAW_Q8;       // 200704: 4 x [8][128] f32
-constexpr int OFF_BAR = 217088;                       // after the larger of the two maps
-constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;      // barriers + alignment slack
+constexpr int NASC = 3;
+constexpr int OFF_ASC = 217088;                       // after the larger of the two maps: NASC x [8 blocks][128 rows] f32
+constexpr int OFF_BAR = OFF_ASC + NASC * 4096;        // 229376
+constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;     // barriers (+ debug counters) + alignment slack = 231424 <= 227 KB
 
 enum Bar {  // 8-byte mbarriers
   A_FULL = 0, A_EMPTY = A_FULL + NA, B_FULL = A_EMPTY + NA, B_EMPTY = B_FULL + NB, RAW_FULL = B_EMPTY + NB,
   RAW_EMPTY = RAW_FULL + 2, D1_FULL = RAW_EMPTY + 2, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1, D2_EMPTY,
-  AB2_FULL, MINS_DONE = AB2_FULL + 2, NUM_BARS = MINS_DONE + 2
+  AB2_FULL, MINS_DONE = AB2_FULL + 2, ASC_FULL = MINS_DONE + 2, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
 };
 static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
 
 // error-word codes (which wait gave up)
 enum : uint32_t { E_APROD = 1, E_WPROD = 2, E_DEQ = 4, E_PREP = 8, E_MMA = 16, E_EPI = 32 };
+#ifdef IZB_TC_STATS
+__device__ unsigned long long g_tc_wait[80];  // [72] = CTA cycles, [73] = CTAs
+#endif
 
 struct TcParams {
   const uint16_t* aimg;   // [tiles][K/64][128][64] fp16, rows 128-byte swizzled
   const float* vsum;      // [tiles][K/32][128] f32 = asc * asum (Q4_K)
-  const float* asc;       // [K/32][lda]
-  int lda;                // Mp (or Sp)
+  const float* ascimg;    // [tiles][K/32][128] f32: the tile rows' activation scales, gathered
   const int32_t* tiles;   // grouped: [1 + 3*max_tiles]; dense: null
   const int32_t* rowmap;  // grouped gather of activation rows (slot -> token) or null
   const float* rowscale;  // per output row factor or null
@@ -109,10 +113,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  false = gave up (or another thread did): the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
                                           uint32_t code) {
+#ifdef IZB_TC_STATS
+  // debug build: cycles every wait site spends blocked, summed per barrier (index = barrier number, +32 for the warp
+  // that builds the min-term operand) by lane 0 of each warp
+  const long long t0 = clock64();  // (try_wait itself may block for a while: time the first attempt too)
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) {
+      if ((threadIdx.x & 31) == 0) {  // shared-memory counters (flushed once per CTA): slot = barrier index, prep warp + 36
+        const uint32_t sa = (bar & ~511u) + 384u + 8u * (((bar & 511u) >> 3) + (code == E_PREP ? 36u : 0u));
+        const unsigned long long dt = (unsigned long long)(clock64() - t0);
+        asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(sa), "l"(dt) : "memory");
+      }
+      return true;
+    }
+    if ((it & 255u) == 255u && *abort_flag) return false;
+  }
+#else
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
+#endif
   *abort_flag = 1;
   atomicOr(err, code);
   return false;
@@ -174,7 +195,7 @@ template <int QT>
 __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asc, int lda,
                                                           int K, int rows_total, const int32_t* __restrict__ tiles,
                                                           const int32_t* __restrict__ rowmap, uint16_t* __restrict__ aimg,
-                                                          float* __restrict__ vsum, int want_vsum) {
+                                                          float* __restrict__ vsum, float* __restrict__ ascimg, int want_vsum) {
   const int tile = blockIdx.y;
   int r0, nr;
   if (tiles) {
@@ -210,14 +231,15 @@ __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restri
   const size_t nstages = K / KS;
   uint8_t* dst = reinterpret_cast<uint8_t*>(aimg) + ((size_t)tile * nstages + stage) * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
   *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-  if (QT == IZB_Q4_K && want_vsum) {
+  if (asc) {  // (null in the block-dot verification mode: no scales are used)
     int s = a[0] + a[1] + a[2] + a[3] + a[4] + a[5] + a[6] + a[7];
     s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
     s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);  // the four chunks of a 32-block are four consecutive threads of one row
     if ((ch & 3) == 0) {
       const int b = ch >> 2;
       const float sc = src >= 0 ? asc[(size_t)b * lda + src] : 0.0f;
-      vsum[((size_t)tile * (K / 32) + b) * BM + r] = __fmul_rn(sc, (float)s);
+      ascimg[((size_t)tile * (K / 32) + b) * BM + r] = sc;
+      if (QT == IZB_Q4_K && want_vsum) vsum[((size_t)tile * (K / 32) + b) * BM + r] = __fmul_rn(sc, (float)s);
     }
   }
 }
@@ -247,6 +269,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     r0 = tile * BM;
     nr = min(BM, p.M - r0);
   }
+#ifdef IZB_TC_STATS
+  const long long t_cta = clock64();
+#endif
   const int n0 = blockIdx.x * BN;
   const int nsb = p.K >> 8, nb = p.K >> 5, nstages = p.K / KS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -255,6 +280,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   constexpr int OFF_RAW = QT == IZB_Q4_K ? OFF_RAW_Q4 : OFF_RAW_Q8;
   constexpr bool kMins = QT == IZB_Q4_K && !kDots;
 
+#ifdef IZB_TC_STATS
+  if (threadIdx.x < 80) reinterpret_cast<unsigned long long*>(smem + OFF_BAR + 384)[threadIdx.x] = 0ull;
+#endif
   if (threadIdx.x == 0) {
     for (int i = 0; i < NA; ++i) { mbar_init(bar(A_FULL + i), 1); mbar_init(bar(A_EMPTY + i), 1); }
     for (int i = 0; i < NB; ++i) { mbar_init(bar(B_FULL + i), 4); mbar_init(bar(B_EMPTY + i), 1); }
@@ -267,6 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 8); }
     mbar_init(bar(D2_FULL), 1);
     mbar_init(bar(D2_EMPTY), 8);
+    for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -304,6 +333,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
         if (kMins)
           bulk_g2s(smem_u32(smem + OFF_VS + rb * 4096), p.vsum + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(RAW_FULL + rb));
+        if (!kDots) {  // the superblock's activation scales for the combine warps
+          const int sq = s % NASC;
+          if (!mbar_wait(bar(ASC_EMPTY + sq), ((s / NASC) & 1) ^ 1, abort_flag, p.err, E_WPROD)) break;
+          mbar_expect_tx(bar(ASC_FULL + sq), 4096);
+          bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
+        }
       }
     } else if (warp == 2 && kMins) {
       // ================= min-term activation operand: vsum (f32) -> three bf16 terms, swizzled K-major half tile
@@ -485,25 +520,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     const int r = 32 * q + lane;
     const bool row_ok = r < nr;
     const int out_row = r0 + r;
-    int arow = -1;
-    if (row_ok) arow = p.rowmap ? p.rowmap[out_row] : out_row;
     const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(half * 64);
     float res[64], tq[64];
 #pragma unroll
     for (int c = 0; c < 64; ++c) res[c] = tq[c] = 0.0f;
-    float a_cur[8];  // this row's activation scales, fetched one superblock (8 blocks) ahead of their use
+    float a_cur[8];  // this row's activation scales of the current superblock (from the shared-memory ring)
 #pragma unroll
-    for (int b = 0; b < 8; ++b) a_cur[b] = (!kDots && arow >= 0) ? p.asc[(size_t)b * p.lda + arow] : 0.0f;
+    for (int b = 0; b < 8; ++b) a_cur[b] = 0.0f;
     bool ok = true;
     int j = 0;
     for (int s = 0; s < nsb && ok; ++s) {
+      if (!kDots) {
+        const int sq = s % NASC;
+        if (!mbar_wait(bar(ASC_FULL + sq), (s / NASC) & 1, abort_flag, p.err, E_EPI)) break;
+        const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) a_cur[b] = as[b * BM];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(ASC_EMPTY + sq));
+      }
 #pragma unroll
       for (int b = 0; b < 8; ++b, ++j) {
         const int d = j % ND1;
         if (!mbar_wait(bar(D1_FULL + d), (j / ND1) & 1, abort_flag, p.err, E_EPI)) { ok = false; break; }
         tc_fence_after();
         const float a = a_cur[b];
-        a_cur[b] = (!kDots && arow >= 0 && s + 1 < nsb) ? p.asc[(size_t)(8 * (s + 1) + b) * p.lda + arow] : 0.0f;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {  // the thread's 64 columns in two passes of 32 (registers)
           uint32_t v[32];
@@ -591,6 +632,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   // ---- teardown
   tc_fence_before();
   __syncthreads();
+#ifdef IZB_TC_STATS
+  if (threadIdx.x < 72) atomicAdd(&g_tc_wait[threadIdx.x], reinterpret_cast<unsigned long long*>(smem + OFF_BAR + 384)[threadIdx.x]);
+  if (threadIdx.x == 0) {
+    atomicAdd(&g_tc_wait[72], (unsigned long long)(clock64() - t_cta));
+    atomicAdd(&g_tc_wait[73], 1ull);
+  }
+#endif
   if (*abort_flag) {
     // a wait gave up: let copies and MMAs still in flight land before shared memory and TMEM are released
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
@@ -638,22 +686,22 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
   if (w->N % BN || w->K % 256) return 1;
   const int K = w->K, nb = K / 32, nstages = K / KS;
   const size_t img_bytes = (size_t)n_tiles_grid * nstages * STAGE_BYTES;
-  const size_t vs_bytes = w->type == IZB_Q4_K ? (size_t)n_tiles_grid * nb * BM * 4 : 0;
+  const size_t vs_bytes = (size_t)n_tiles_grid * nb * BM * 4;  // each of: the min-term factors (Q4_K) and the scales
   void* ws = nullptr;
-  if (int rc = izb_workspace(w->device, ws_slot, img_bytes + vs_bytes, &ws)) return rc;
+  if (int rc = izb_workspace(w->device, ws_slot, img_bytes + 2 * vs_bytes, &ws)) return rc;
   uint16_t* aimg = (uint16_t*)ws;
   float* vsum = (float*)((unsigned char*)ws + img_bytes);
+  float* ascimg = (float*)((unsigned char*)ws + img_bytes + vs_bytes);
   dim3 pg((BM * (K / 8) + 255) / 256, n_tiles_grid);
   const int want_vs = (w->type == IZB_Q4_K && !dots) ? 1 : 0;
   if (w->type == IZB_Q4_K)
-    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, want_vs));
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, ascimg, want_vs));
   else
-    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, 0));
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, ascimg, 0));
   TcParams p;
   p.aimg = aimg;
   p.vsum = vsum;
-  p.asc = asc;
-  p.lda = lda;
+  p.ascimg = ascimg;
   p.tiles = tiles;
   p.rowmap = rowmap;
   p.rowscale = rowscale;
@@ -674,6 +722,17 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
 }
 
 }  // namespace
+
+#ifdef IZB_TC_STATS
+// debug build only: reads and clears the wait-cycle counters of gemm_tc_kernel
+extern "C" int izb_tc_wait_stats(unsigned long long* out72) {  // 80 values
+  IZB_CUDA(cudaDeviceSynchronize());
+  IZB_CUDA(cudaMemcpyFromSymbol(out72, g_tc_wait, sizeof(unsigned long long) * 80));
+  unsigned long long zero[80] = {0};
+  IZB_CUDA(cudaMemcpyToSymbol(g_tc_wait, zero, sizeof zero));
+  return IZB_OK;
+}
+#endif
 
 int izb_make_raw_tensor_map(izb_weight* w) {
   EncodeTiledFn enc = get_encode();

@@ -40,7 +40,7 @@ int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* 
 namespace {
 
 constexpr int BM = 128, BN = 128, KS = 64;
-constexpr int NA = 5, NB = 3, ND1 = 3;
+constexpr int NS = 4, NA = NS, NB = NS, ND1 = 3;  // operand stages (activations and weights share a ring position)
 constexpr int STAGE_BYTES = BM * KS * 2;  // 16 KB: 128 rows x 128 B
 constexpr int kThreads = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -62,7 +62,7 @@ constexpr int OFF_BAR = OFF_ASC + NASC * 4096;        // 229376
 constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;     // barriers (+ debug counters) + alignment slack = 231424 <= 227 KB
 
 enum Bar {  // 8-byte mbarriers
-  A_FULL = 0, A_EMPTY = A_FULL + NA, B_FULL = A_EMPTY + NA, B_EMPTY = B_FULL + NB, RAW_FULL = B_EMPTY + NB,
+  S_FULL = 0, S_EMPTY = S_FULL + NS, RAW_FULL = S_EMPTY + NS,  // S_*: one barrier per stage for both operand tiles
   RAW_EMPTY = RAW_FULL + 2, D1_FULL = RAW_EMPTY + 2, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1, D2_EMPTY,
   AB2_FULL, MINS_DONE = AB2_FULL + 2, ASC_FULL = MINS_DONE + 2, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
 };
@@ -72,6 +72,17 @@ static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
 enum : uint32_t { E_APROD = 1, E_WPROD = 2, E_DEQ = 4, E_PREP = 8, E_MMA = 16, E_EPI = 32 };
 #ifdef IZB_TC_STATS
 __device__ unsigned long long g_tc_wait[80];  // [72] = CTA cycles, [73] = CTAs
+#define STAT_T0() const long long stat_t0 = clock64()
+#define STAT_ADD(slot)                                                                                        \
+  do {                                                                                                        \
+    if ((threadIdx.x & 31) == 0) {                                                                            \
+      const unsigned long long dt__ = (unsigned long long)(clock64() - stat_t0);                              \
+      asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(bar0 + 384u + 8u * (slot)), "l"(dt__) : "memory");   \
+    }                                                                                                         \
+  } while (0)
+#else
+#define STAT_T0()
+#define STAT_ADD(slot)
 #endif
 
 struct TcParams {
@@ -284,8 +295,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   if (threadIdx.x < 80) reinterpret_cast<unsigned long long*>(smem + OFF_BAR + 384)[threadIdx.x] = 0ull;
 #endif
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NA; ++i) { mbar_init(bar(A_FULL + i), 1); mbar_init(bar(A_EMPTY + i), 1); }
-    for (int i = 0; i < NB; ++i) { mbar_init(bar(B_FULL + i), 4); mbar_init(bar(B_EMPTY + i), 1); }
+    // S_FULL: the activation producer's expect_tx arrival + the four dequantiser warps; S_EMPTY: one tcgen05.commit
+    for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), 5); mbar_init(bar(S_EMPTY + i), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(RAW_FULL + i), 1);
       mbar_init(bar(RAW_EMPTY + i), kMins ? 5 : 4);
@@ -314,109 +325,125 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == 0 && lane == 0) {
+    // Every role loop below is executed by its whole warp (uniform waits, lane 0 issues), so no lane of a role warp
+    // sits at the final CTA barrier while another lane of the same warp is still working.
+    if (warp == 0) {
       // ================= activation producer
       const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
       for (int g = 0; g < nstages; ++g) {
-        const int sa = g % NA;
-        if (!mbar_wait(bar(A_EMPTY + sa), ((g / NA) & 1) ^ 1, abort_flag, p.err, E_APROD)) break;
-        mbar_expect_tx(bar(A_FULL + sa), STAGE_BYTES);
-        bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(A_FULL + sa));
-      }
-    } else if (warp == 3 && lane == 0) {
-      // ================= weight producer
-      const int wrow = expert * p.N + n0;
-      for (int s = 0; s < nsb; ++s) {
-        const int rb = s & 1;
-        if (!mbar_wait(bar(RAW_EMPTY + rb), ((s >> 1) & 1) ^ 1, abort_flag, p.err, E_WPROD)) break;
-        mbar_expect_tx(bar(RAW_FULL + rb), RAW + (kMins ? 4096 : 0));
-        tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
-        if (kMins)
-          bulk_g2s(smem_u32(smem + OFF_VS + rb * 4096), p.vsum + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(RAW_FULL + rb));
-        if (!kDots) {  // the superblock's activation scales for the combine warps
-          const int sq = s % NASC;
-          if (!mbar_wait(bar(ASC_EMPTY + sq), ((s / NASC) & 1) ^ 1, abort_flag, p.err, E_WPROD)) break;
-          mbar_expect_tx(bar(ASC_FULL + sq), 4096);
-          bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
-        }
-      }
-    } else if (warp == 2 && kMins) {
-      // ================= min-term activation operand: vsum (f32) -> three bf16 terms, swizzled K-major half tile
-      for (int s = 0; s < nsb; ++s) {
-        const int rb = s & 1, h = s & 1, u = s >> 1;
-        if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_PREP)) break;
-        if (!mbar_wait(bar(MINS_DONE + h), (u & 1) ^ 1, abort_flag, p.err, E_PREP)) break;
-        const float* vs = reinterpret_cast<const float*>(smem + OFF_VS + rb * 4096);
-#pragma unroll 1
-        for (int i = 0; i < 4; ++i) {
-          const int r = lane + 32 * i;
-          uint32_t hi[4], mid[4], lo[4];
-#pragma unroll
-          for (int b2 = 0; b2 < 4; ++b2) {
-            uint32_t w3[3] = {0, 0, 0};
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-              const float v = vs[(2 * b2 + k) * BM + r];
-              const __nv_bfloat16 h1 = __float2bfloat16_rn(v);
-              const float r1 = __fsub_rn(v, __bfloat162float(h1));
-              const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
-              const float r2 = __fsub_rn(r1, __bfloat162float(h2));
-              const __nv_bfloat16 h3 = __float2bfloat16_rn(r2);
-              w3[0] |= (uint32_t)__bfloat16_as_ushort(h1) << (16 * k);
-              w3[1] |= (uint32_t)__bfloat16_as_ushort(h2) << (16 * k);
-              w3[2] |= (uint32_t)__bfloat16_as_ushort(h3) << (16 * k);
-            }
-            hi[b2] = w3[0]; mid[b2] = w3[1]; lo[b2] = w3[2];
-          }
-          unsigned char* row = smem + OFF_A2 + r * 128;
-          *reinterpret_cast<uint4*>(row + (((4 * h + 0) ^ (r & 7)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<uint4*>(row + (((4 * h + 1) ^ (r & 7)) << 4)) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
-          *reinterpret_cast<uint4*>(row + (((4 * h + 2) ^ (r & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-        fence_proxy_async();
-        __syncwarp();
+        const int sa = g & (NS - 1);
+        if (!mbar_wait(bar(S_EMPTY + sa), ((g / NS) & 1) ^ 1, abort_flag, p.err, E_APROD)) break;
         if (lane == 0) {
-          mbar_arrive(bar(AB2_FULL + h));
-          mbar_arrive(bar(RAW_EMPTY + rb));
+          mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
+          bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
+        }
+        __syncwarp();
+      }
+    } else if (warp == 3) {
+      // ================= weight producer (TMA of the raw superblocks, scales) and, one superblock behind, the min-term
+      // activation operand: vsum (f32) -> three bf16 terms, swizzled K-major half tile
+      const int wrow = expert * p.N + n0;
+      int sq = 0, pq = 1;
+      for (int s = 0; s <= nsb; ++s) {
+        if (s < nsb) {
+          const int rb = s & 1;
+          if (!mbar_wait(bar(RAW_EMPTY + rb), ((s >> 1) & 1) ^ 1, abort_flag, p.err, E_WPROD)) break;
+          if (lane == 0) {
+            mbar_expect_tx(bar(RAW_FULL + rb), RAW + (kMins ? 4096 : 0));
+            tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
+            if (kMins)
+              bulk_g2s(smem_u32(smem + OFF_VS + rb * 4096), p.vsum + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(RAW_FULL + rb));
+          }
+          if (!kDots) {  // the superblock's activation scales for the combine warps
+            if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, E_WPROD)) break;
+            if (lane == 0) {
+              mbar_expect_tx(bar(ASC_FULL + sq), 4096);
+              bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
+            }
+            if (++sq == NASC) { sq = 0; pq ^= 1; }
+          }
+          __syncwarp();
+        }
+        if (kMins && s > 0) {
+          const int sp = s - 1, rb = sp & 1, h = sp & 1, u = sp >> 1;
+          if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_PREP)) break;
+          if (!mbar_wait(bar(MINS_DONE + h), (u & 1) ^ 1, abort_flag, p.err, E_PREP)) break;
+          const float* vs = reinterpret_cast<const float*>(smem + OFF_VS + rb * 4096);
+#pragma unroll 1
+          for (int i = 0; i < 4; ++i) {
+            const int r = lane + 32 * i;
+            unsigned char* row = smem + OFF_A2 + r * 128;
+#pragma unroll 1
+            for (int half8 = 0; half8 < 2; ++half8) {  // blocks 4*half8 .. 4*half8+3 -> two of the four words of each chunk
+              uint32_t w3[2][3] = {{0, 0, 0}, {0, 0, 0}};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float v = vs[(4 * half8 + k) * BM + r];
+                const __nv_bfloat16 h1 = __float2bfloat16_rn(v);
+                const float r1 = __fsub_rn(v, __bfloat162float(h1));
+                const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+                const float r2 = __fsub_rn(r1, __bfloat162float(h2));
+                const __nv_bfloat16 h3 = __float2bfloat16_rn(r2);
+                w3[k >> 1][0] |= (uint32_t)__bfloat16_as_ushort(h1) << (16 * (k & 1));
+                w3[k >> 1][1] |= (uint32_t)__bfloat16_as_ushort(h2) << (16 * (k & 1));
+                w3[k >> 1][2] |= (uint32_t)__bfloat16_as_ushort(h3) << (16 * (k & 1));
+              }
+#pragma unroll
+              for (int part = 0; part < 3; ++part)
+                *reinterpret_cast<uint2*>(row + (((4 * h + part) ^ (r & 7)) << 4) + 8 * half8) = make_uint2(w3[0][part], w3[1][part]);
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(bar(AB2_FULL + h));
+            mbar_arrive(bar(RAW_EMPTY + rb));
+          }
         }
       }
-    } else if (warp == 1 && lane == 0) {
-      // ================= MMA issuer
+    } else {
+      // ================= MMA issuers: warp 1 takes the even stages, warp 2 the odd ones (and the min-term MMA of every
+      // superblock).  A stage is two 32-blocks, each into its own accumulator buffer: two MMAs (K = 16) + one commit.
+      // Two issuers because what a thread pays per block -- barrier polls and commits between MMAs -- is longer than
+      // the 128 cycles the two MMAs run.
       bool ok = true;
-      int j = 0;  // block counter -> accumulator ring
-      for (int g = 0; g < nstages && ok; ++g) {
-        const int sa = g % NA, sbq = g % NB;
-        ok = mbar_wait(bar(A_FULL + sa), (g / NA) & 1, abort_flag, p.err, E_MMA) &&
-             mbar_wait(bar(B_FULL + sbq), (g / NB) & 1, abort_flag, p.err, E_MMA);
-        if (!ok) break;
+      for (int g = warp - 1; g < nstages && ok; g += 2) {
+        const int sa = g & (NS - 1);
+        if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, E_MMA)) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sbq * STAGE_BYTES);
+        const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sa * STAGE_BYTES);
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk, ++j) {
-          const int d = j % ND1;
+        for (int blk = 0; blk < 2; ++blk) {
+          const int j = 2 * g + blk, d = j % ND1;
           if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t dt = tmem_base + (uint32_t)(d * BN);
+          if (lane == 0) {
+            const uint32_t dt = tmem_base + (uint32_t)(d * BN);
 #pragma unroll
-          for (int k16 = 0; k16 < 2; ++k16)
-            tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
-          tc_commit(bar(D1_FULL + d));
+            for (int k16 = 0; k16 < 2; ++k16)
+              tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
+            tc_commit(bar(D1_FULL + d));
+          }
+          __syncwarp();
         }
         if (!ok) break;
-        tc_commit(bar(A_EMPTY + sa));
-        tc_commit(bar(B_EMPTY + sbq));
+        if (lane == 0) tc_commit(bar(S_EMPTY + sa));
+        __syncwarp();
         if (kMins && (g & 3) == 3) {
           const int s = g >> 2, h = s & 1, u = s >> 1;
           ok = mbar_wait(bar(AB2_FULL + h), u & 1, abort_flag, p.err, E_MMA) &&
                mbar_wait(bar(D2_EMPTY), (s & 1) ^ 1, abort_flag, p.err, E_MMA);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a2 = smem_u32(smem + OFF_A2) + 64 * h, b2 = smem_u32(smem + OFF_B2) + 64 * h;
+          if (lane == 0) {
+            const uint32_t a2 = smem_u32(smem + OFF_A2) + 64 * h, b2 = smem_u32(smem + OFF_B2) + 64 * h;
 #pragma unroll
-          for (int k16 = 0; k16 < 2; ++k16)
-            tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a2 + k16 * 32), umma_desc(b2 + k16 * 32), kIdescBF16, k16);
-          tc_commit(bar(D2_FULL));
-          tc_commit(bar(MINS_DONE + h));
+            for (int k16 = 0; k16 < 2; ++k16)
+              tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a2 + k16 * 32), umma_desc(b2 + k16 * 32), kIdescBF16, k16);
+            tc_commit(bar(D2_FULL));
+            tc_commit(bar(MINS_DONE + h));
+          }
+          __syncwarp();
         }
       }
     }
@@ -425,6 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     const int t = threadIdx.x - 128;
     bool ok = true;
+    int sbq = 0, pbq = 1;  // operand ring position and wait parity
     for (int s = 0; s < nsb && ok; ++s) {
       const int rb = s & 1, u = s >> 1;
       if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_DEQ)) break;
@@ -462,10 +490,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        const int g = 4 * s + c, sbq = g % NB;
-        if (!mbar_wait(bar(B_EMPTY + sbq), ((g / NB) & 1) ^ 1, abort_flag, p.err, E_DEQ)) { ok = false; break; }
+        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) { ok = false; break; }
+        STAT_T0();
         unsigned char* orow = smem + OFF_B + sbq * STAGE_BYTES + t * 128;
+#ifdef IZB_EXP_NO_DEQ
+        if (false) {
+#else
         if (QT == IZB_Q4_K) {
+#endif
           const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c), q1 = *reinterpret_cast<const uint4*>(rrow + 32 + 32 * c);
           const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
           int sc_lo = 1, sc_hi = 1, mn_unused;
@@ -488,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             *reinterpret_cast<uint4*>(orow + (((4 + jj) ^ (t & 7)) << 4)) =
                 make_uint4(cvt(w0, 4, shi, nhi), cvt(w0, 12, shi, nhi), cvt(w1, 4, shi, nhi), cvt(w1, 12, shi, nhi));
           }
-        } else {
+        } else if (QT == IZB_Q8_0) {
           const __half2 bias = __half2half2(__int2half_rn(1152));
           auto cvt = [&](uint32_t x, uint32_t sel) -> uint32_t {
             const uint32_t bitsv = __byte_perm(x, 0x64646464u, sel);  // (1024 + (q + 128)) in both halves
@@ -505,9 +537,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 make_uint4(cvt(x2, 0x4140), cvt(x2, 0x4342), cvt(x3, 0x4140), cvt(x3, 0x4342));
           }
         }
+        if (warp == 4) STAT_ADD(62);
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_FULL + sbq));
+        if (lane == 0) mbar_arrive(bar(S_FULL + sbq));
+        if (warp == 4) STAT_ADD(63);
+        if (++sbq == NB) { sbq = 0; pbq ^= 1; }
       }
       if (!ok) break;
       __syncwarp();
@@ -524,32 +559,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     float res[64], tq[64];
 #pragma unroll
     for (int c = 0; c < 64; ++c) res[c] = tq[c] = 0.0f;
-    float a_cur[8];  // this row's activation scales of the current superblock (from the shared-memory ring)
-#pragma unroll
-    for (int b = 0; b < 8; ++b) a_cur[b] = 0.0f;
     bool ok = true;
-    int j = 0;
+    int d = 0, pd = 0, sq = 0, pq = 0;  // accumulator ring / scale ring positions and wait parities
     for (int s = 0; s < nsb && ok; ++s) {
-      if (!kDots) {
-        const int sq = s % NASC;
-        if (!mbar_wait(bar(ASC_FULL + sq), (s / NASC) & 1, abort_flag, p.err, E_EPI)) break;
-        const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;
+      const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;  // this row's 8 block scales
+      if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, E_EPI)) break;
 #pragma unroll
-        for (int b = 0; b < 8; ++b) a_cur[b] = as[b * BM];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(ASC_EMPTY + sq));
-      }
-#pragma unroll
-      for (int b = 0; b < 8; ++b, ++j) {
-        const int d = j % ND1;
-        if (!mbar_wait(bar(D1_FULL + d), (j / ND1) & 1, abort_flag, p.err, E_EPI)) { ok = false; break; }
+      for (int b = 0; b < 8; ++b) {
+        const float a = kDots ? 0.0f : as[b * BM];
+        if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, E_EPI)) { ok = false; break; }
         tc_fence_after();
-        const float a = a_cur[b];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {  // the thread's 64 columns in two passes of 32 (registers)
           uint32_t v[32];
-          tc_ld32(t_lane + (uint32_t)(d * BN + 32 * hh), v);
-          tc_wait_ld();
+          {
+            STAT_T0();
+#ifdef IZB_EXP_NO_LD
+            for (int c = 0; c < 32; ++c) v[c] = c + d;
+#else
+            tc_ld32(t_lane + (uint32_t)(d * BN + 32 * hh), v);
+            tc_wait_ld();
+#endif
+            if (warp == 8) STAT_ADD(61);
+          }
           if (hh == 1) {  // both halves read: the accumulator buffer may be overwritten
             tc_fence_before();
             __syncwarp();
@@ -563,7 +595,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             }
           } else if (QT == IZB_Q4_K) {
 #pragma unroll
+#ifdef IZB_EXP_NO_FMA
+            for (int c = 0; c < 32; c += 16) tq[32 * hh + c] = fmaf(a, __uint_as_float(v[c]), tq[32 * hh + c]);
+#else
             for (int c = 0; c < 32; ++c) tq[32 * hh + c] = fmaf(a, __uint_as_float(v[c]), tq[32 * hh + c]);
+#endif
           } else {
             const float4* d8 = reinterpret_cast<const float4*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256 + hh * 128);
 #pragma unroll
@@ -576,8 +612,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             }
           }
         }
+        if (++d == ND1) { d = 0; pd ^= 1; }
       }
       if (!ok) break;
+      if (!kDots) {  // the superblock's scales are read: its ring slot may be refilled
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(ASC_EMPTY + sq));
+        if (++sq == NASC) { sq = 0; pq ^= 1; }
+      }
       if (kMins) {
         if (!mbar_wait(bar(D2_FULL), s & 1, abort_flag, p.err, E_EPI)) break;
         tc_fence_after();

@@ -80,9 +80,21 @@ __device__ unsigned long long g_tc_wait[80];  // [72] = CTA cycles, [73] = CTAs
       asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(bar0 + 384u + 8u * (slot)), "l"(dt__) : "memory");   \
     }                                                                                                         \
   } while (0)
+#define STAT_LAP_INIT() long long stat_lap = clock64()
+#define STAT_LAP(slot)                                                                                        \
+  do {                                                                                                        \
+    const long long now__ = clock64();                                                                        \
+    if (threadIdx.x == 256) {                                                                                 \
+      const unsigned long long dt__ = (unsigned long long)(now__ - stat_lap);                                 \
+      asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(bar0 + 384u + 8u * (slot)), "l"(dt__) : "memory");   \
+    }                                                                                                         \
+    stat_lap = clock64();                                                                                     \
+  } while (0)
 #else
 #define STAT_T0()
 #define STAT_ADD(slot)
+#define STAT_LAP_INIT()
+#define STAT_LAP(slot)
 #endif
 
 struct TcParams {
@@ -114,11 +126,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#ifdef IZB_EXP_HINT
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"((uint32_t)IZB_EXP_HINT)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait.  false = gave up (or another thread did): the caller leaves its loop.
@@ -142,6 +162,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 #else
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef IZB_EXP_SLEEP
+    __nanosleep(IZB_EXP_SLEEP);
+#endif
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
 #endif
@@ -183,6 +206,46 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// tcgen05.ld of 32 columns + wait, delivered as 16 register pairs (columns 2i, 2i+1) for the f32x2 arithmetic
+__device__ __forceinline__ void tc_ld32_pairs(uint32_t taddr, unsigned long long (&r)[16]) {
+  asm volatile(
+      "{\n\t.reg .b32 t<32>;\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {t0,t1,t2,t3,t4,t5,t6,t7,t8,t9,t10,t11,t12,t13,t14,t15,t16,t17,t18,t19,t20,t21,t22,t23,"
+      "t24,t25,t26,t27,t28,t29,t30,t31}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;\n\t"
+      "mov.b64 %0, {t0,t1};\n\tmov.b64 %1, {t2,t3};\n\tmov.b64 %2, {t4,t5};\n\tmov.b64 %3, {t6,t7};\n\t"
+      "mov.b64 %4, {t8,t9};\n\tmov.b64 %5, {t10,t11};\n\tmov.b64 %6, {t12,t13};\n\tmov.b64 %7, {t14,t15};\n\t"
+      "mov.b64 %8, {t16,t17};\n\tmov.b64 %9, {t18,t19};\n\tmov.b64 %10, {t20,t21};\n\tmov.b64 %11, {t22,t23};\n\t"
+      "mov.b64 %12, {t24,t25};\n\tmov.b64 %13, {t26,t27};\n\tmov.b64 %14, {t28,t29};\n\tmov.b64 %15, {t30,t31};\n\t}"
+      : "=l"(r[0]), "=l"(r[1]), "=l"(r[2]), "=l"(r[3]), "=l"(r[4]), "=l"(r[5]), "=l"(r[6]), "=l"(r[7]), "=l"(r[8]), "=l"(r[9]),
+        "=l"(r[10]), "=l"(r[11]), "=l"(r[12]), "=l"(r[13]), "=l"(r[14]), "=l"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// packed f32x2 arithmetic (two IEEE round-to-nearest operations per instruction)
+__device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+#ifdef IZB_EXP_SCALAR_FMA
+  const float lo = fmaf(__uint_as_float((uint32_t)a), __uint_as_float((uint32_t)b), __uint_as_float((uint32_t)acc));
+  const float hi = fmaf(__uint_as_float((uint32_t)(a >> 32)), __uint_as_float((uint32_t)(b >> 32)), __uint_as_float((uint32_t)(acc >> 32)));
+  acc = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(hi) << 32);
+#else
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+#endif
+}
+__device__ __forceinline__ unsigned long long fmul2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long pack2(float x) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ unsigned long long neg2(unsigned long long a) { return a ^ 0x8000000080000000ull; }
+__device__ __forceinline__ float lo_f(unsigned long long a) { return __uint_as_float((uint32_t)a); }
+__device__ __forceinline__ float hi_f(unsigned long long a) { return __uint_as_float((uint32_t)(a >> 32)); }
 
 // K-major operand tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart (tcgen05 shared-memory
 // descriptor: start address >> 4, stride byte offset >> 4 at bit 32, descriptor version 1 at bit 46, swizzle mode 2
@@ -333,10 +396,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       for (int g = 0; g < nstages; ++g) {
         const int sa = g & (NS - 1);
         if (!mbar_wait(bar(S_EMPTY + sa), ((g / NS) & 1) ^ 1, abort_flag, p.err, E_APROD)) break;
+#ifdef IZB_EXP_NO_ATMA
+        if (lane == 0) mbar_arrive(bar(S_FULL + sa));
+#else
         if (lane == 0) {
           mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
           bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
         }
+#endif
         __syncwarp();
       }
     } else if (warp == 3) {
@@ -420,8 +487,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           if (lane == 0) {
             const uint32_t dt = tmem_base + (uint32_t)(d * BN);
 #pragma unroll
+#ifndef IZB_EXP_NO_MMA
             for (int k16 = 0; k16 < 2; ++k16)
               tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
+#endif
             tc_commit(bar(D1_FULL + d));
           }
           __syncwarp();
@@ -488,7 +557,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
         for (int b = 0; b < 8; ++b) d8[b * 128 + t] = half_bits_to_float((b & 1) ? hw[b >> 1] >> 16 : hw[b >> 1] & 0xFFFFu);
       }
-#pragma unroll 1
+#pragma unroll 1  // (rolled on purpose: with the four role loops resident at once, code size costs more than the loop)
       for (int c = 0; c < 4; ++c) {
         if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) { ok = false; break; }
         STAT_T0();
@@ -500,13 +569,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #endif
           const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c), q1 = *reinterpret_cast<const uint4*>(rrow + 32 + 32 * c);
           const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          // the chunk's two 6-bit sub-block scales (static indices: the chunk loop is unrolled), as half2 pairs
+          // (sc, sc) and (-1024 sc, -1024 sc): 0x6400 | sc is the fp16 number 1024 + sc
           int sc_lo = 1, sc_hi = 1, mn_unused;
           if (!kDots) {
             q4k_scale_min(s3, 2 * c, sc_lo, mn_unused);
             q4k_scale_min(s3, 2 * c + 1, sc_hi, mn_unused);
           }
-          const __half2 slo = __half2half2(__int2half_rn(sc_lo)), shi = __half2half2(__int2half_rn(sc_hi));
-          const __half2 nlo = __half2half2(__int2half_rn(-1024 * sc_lo)), nhi = __half2half2(__int2half_rn(-1024 * sc_hi));
+          const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400)), kneg = __half2half2(__ushort_as_half((unsigned short)0xE400));
+          const uint32_t blo = 0x64006400u | (uint32_t)sc_lo | ((uint32_t)sc_lo << 16), bhi = 0x64006400u | (uint32_t)sc_hi | ((uint32_t)sc_hi << 16);
+          const __half2 slo = __hsub2(*reinterpret_cast<const __half2*>(&blo), k1024), shi = __hsub2(*reinterpret_cast<const __half2*>(&bhi), k1024);
+          const __half2 nlo = __hmul2(slo, kneg), nhi = __hmul2(shi, kneg);
           auto cvt = [](uint32_t word, int sh, __half2 scale, __half2 neg) -> uint32_t {
             const uint32_t bitsv = ((word >> sh) & 0x000F000Fu) | 0x64006400u;  // (1024 + q) in both halves
             const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&bitsv), scale, neg);  // = sc * q exactly
@@ -549,39 +622,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       if (lane == 0) mbar_arrive(bar(RAW_EMPTY + rb));
     }
   } else {
-    // ================= combine: thread <-> TMEM lane (token row) 32*(warp%4) + lane, 64 of the 128 columns
+    // ================= combine: thread <-> TMEM lane (token row) 32*(warp%4) + lane, 64 of the 128 columns.
+    // All f32 arithmetic is done on register pairs (fma.rn.f32x2): half the instructions for the same IEEE results.
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const int q = warp & 3, half = (warp - 8) >> 2;
     const int r = 32 * q + lane;
     const bool row_ok = r < nr;
     const int out_row = r0 + r;
     const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(half * 64);
-    float res[64], tq[64];
+    unsigned long long res2[32], tq2[32];  // pairs of columns (2i, 2i+1)
 #pragma unroll
-    for (int c = 0; c < 64; ++c) res[c] = tq[c] = 0.0f;
+    for (int c = 0; c < 32; ++c) res2[c] = tq2[c] = 0ull;
     bool ok = true;
+    STAT_LAP_INIT();
     int d = 0, pd = 0, sq = 0, pq = 0;  // accumulator ring / scale ring positions and wait parities
     for (int s = 0; s < nsb && ok; ++s) {
       const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;  // this row's 8 block scales
       if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, E_EPI)) break;
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
-        const float a = kDots ? 0.0f : as[b * BM];
+        const unsigned long long a2 = pack2(kDots ? 0.0f : as[b * BM]);
         if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, E_EPI)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {  // the thread's 64 columns in two passes of 32 (registers)
-          uint32_t v[32];
-          {
-            STAT_T0();
+          unsigned long long v[16];
 #ifdef IZB_EXP_NO_LD
-            for (int c = 0; c < 32; ++c) v[c] = c + d;
+          for (int c = 0; c < 16; ++c) v[c] = c + d;
 #else
-            tc_ld32(t_lane + (uint32_t)(d * BN + 32 * hh), v);
-            tc_wait_ld();
+          tc_ld32_pairs(t_lane + (uint32_t)(d * BN + 32 * hh), v);
 #endif
-            if (warp == 8) STAT_ADD(61);
-          }
           if (hh == 1) {  // both halves read: the accumulator buffer may be overwritten
             tc_fence_before();
             __syncwarp();
@@ -591,24 +661,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if (row_ok) {
               int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64 + 32 * hh) * nb + 8 * s + b;
 #pragma unroll
-              for (int c = 0; c < 32; ++c) o[(size_t)c * nb] = __float2int_rn(__uint_as_float(v[c]));
+              for (int c = 0; c < 16; ++c) {
+                o[(size_t)(2 * c) * nb] = __float2int_rn(lo_f(v[c]));
+                o[(size_t)(2 * c + 1) * nb] = __float2int_rn(hi_f(v[c]));
+              }
             }
           } else if (QT == IZB_Q4_K) {
-#pragma unroll
 #ifdef IZB_EXP_NO_FMA
-            for (int c = 0; c < 32; c += 16) tq[32 * hh + c] = fmaf(a, __uint_as_float(v[c]), tq[32 * hh + c]);
+            for (int c = 0; c < 16; c += 8) ffma2(tq2[16 * hh + c], a2, v[c]);
 #else
-            for (int c = 0; c < 32; ++c) tq[32 * hh + c] = fmaf(a, __uint_as_float(v[c]), tq[32 * hh + c]);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) ffma2(tq2[16 * hh + c], a2, v[c]);
 #endif
           } else {
-            const float4* d8 = reinterpret_cast<const float4*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256 + hh * 128);
+            const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256 + hh * 128);
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
-              const float4 dd = d8[c4];
-              res[32 * hh + 4 * c4 + 0] = fmaf(__fmul_rn(a, dd.x), __uint_as_float(v[4 * c4 + 0]), res[32 * hh + 4 * c4 + 0]);
-              res[32 * hh + 4 * c4 + 1] = fmaf(__fmul_rn(a, dd.y), __uint_as_float(v[4 * c4 + 1]), res[32 * hh + 4 * c4 + 1]);
-              res[32 * hh + 4 * c4 + 2] = fmaf(__fmul_rn(a, dd.z), __uint_as_float(v[4 * c4 + 2]), res[32 * hh + 4 * c4 + 2]);
-              res[32 * hh + 4 * c4 + 3] = fmaf(__fmul_rn(a, dd.w), __uint_as_float(v[4 * c4 + 3]), res[32 * hh + 4 * c4 + 3]);
+              const ulonglong2 dd = d8[c4];  // four column scales
+              ffma2(res2[16 * hh + 2 * c4], fmul2(a2, dd.x), v[2 * c4]);
+              ffma2(res2[16 * hh + 2 * c4 + 1], fmul2(a2, dd.y), v[2 * c4 + 1]);
             }
           }
         }
@@ -625,28 +696,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         tc_fence_after();
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          uint32_t v[32];
-          tc_ld32(t_lane + (uint32_t)(ND1 * BN + 32 * hh), v);
-          tc_wait_ld();
+          unsigned long long v[16];
+          tc_ld32_pairs(t_lane + (uint32_t)(ND1 * BN + 32 * hh), v);
           if (hh == 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(D2_EMPTY));
           }
-          const float4* dv = reinterpret_cast<const float4*>(smem + OFF_DM + (s & 3) * 1024 + half * 256 + hh * 128);
-          const float4* mv = reinterpret_cast<const float4*>(smem + OFF_DM + (s & 3) * 1024 + 512 + half * 256 + hh * 128);
+          const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (s & 3) * 1024 + half * 256 + hh * 128);
+          const ulonglong2* mv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (s & 3) * 1024 + 512 + half * 256 + hh * 128);
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 dd = dv[c4], mm = mv[c4];
-            const int c = 32 * hh + 4 * c4;
-            res[c + 0] = fmaf(dd.x, tq[c + 0], fmaf(-mm.x, __uint_as_float(v[4 * c4 + 0]), res[c + 0]));
-            res[c + 1] = fmaf(dd.y, tq[c + 1], fmaf(-mm.y, __uint_as_float(v[4 * c4 + 1]), res[c + 1]));
-            res[c + 2] = fmaf(dd.z, tq[c + 2], fmaf(-mm.z, __uint_as_float(v[4 * c4 + 2]), res[c + 2]));
-            res[c + 3] = fmaf(dd.w, tq[c + 3], fmaf(-mm.w, __uint_as_float(v[4 * c4 + 3]), res[c + 3]));
+          for (int c4 = 0; c4 < 8; ++c4) {  // res = fma(d, tq, fma(-dmin, tmn, res))
+            const ulonglong2 dd = dv[c4], mm = mv[c4];
+            ffma2(res2[16 * hh + 2 * c4], neg2(mm.x), v[2 * c4]);
+            ffma2(res2[16 * hh + 2 * c4 + 1], neg2(mm.y), v[2 * c4 + 1]);
+            ffma2(res2[16 * hh + 2 * c4], dd.x, tq2[16 * hh + 2 * c4]);
+            ffma2(res2[16 * hh + 2 * c4 + 1], dd.y, tq2[16 * hh + 2 * c4 + 1]);
+            tq2[16 * hh + 2 * c4] = 0ull;
+            tq2[16 * hh + 2 * c4 + 1] = 0ull;
           }
         }
-#pragma unroll
-        for (int c = 0; c < 64; ++c) tq[c] = 0.0f;
       }
     }
     if (ok && !kDots && row_ok && !*abort_flag) {
@@ -654,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
 #pragma unroll
       for (int c4 = 0; c4 < 16; ++c4) {
-        float4 v = make_float4(res[4 * c4], res[4 * c4 + 1], res[4 * c4 + 2], res[4 * c4 + 3]);
+        float4 v = make_float4(lo_f(res2[2 * c4]), hi_f(res2[2 * c4]), lo_f(res2[2 * c4 + 1]), hi_f(res2[2 * c4 + 1]));
         if (p.rowscale) { v.x = __fmul_rn(rs, v.x); v.y = __fmul_rn(rs, v.y); v.z = __fmul_rn(rs, v.z); v.w = __fmul_rn(rs, v.w); }
         float4* dst = reinterpret_cast<float4*>(cp) + c4;
         if (p.acc == 1) {

@@ -92,13 +92,15 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t h16) { return __hal
 // Q4_K: 6-bit scale and min of sub-block j (0..7) from the 12 packed bytes held as three little-endian words
 // (get_scale_min_k4, src/quants.h:61-69)
 __device__ __forceinline__ void q4k_scale_min(const uint32_t s[3], int j, int& sc, int& mn) {
-  auto byte = [&](int i) -> uint32_t { return (s[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+  // shifts only, no indexing of s by a run-time value (that would put the three words in local memory)
+  const int sh = 8 * (j & 3);
+  const uint32_t a = s[0] >> sh, b = s[1] >> sh, c = s[2] >> sh;
   if (j < 4) {
-    sc = byte(j) & 63;
-    mn = byte(j + 4) & 63;
+    sc = a & 63;
+    mn = b & 63;
   } else {
-    sc = (byte(j + 4) & 0xF) | ((byte(j - 4) >> 6) << 4);
-    mn = (byte(j + 4) >> 4) | ((byte(j) >> 6) << 4);
+    sc = (c & 0xF) | (((a >> 6) & 3) << 4);
+    mn = ((c >> 4) & 0xF) | (((b >> 6) & 3) << 4);
   }
 }
 __device__ __forceinline__ float warp_sum(float v) {

@@ -13,6 +13,9 @@
 // 16 int8 values each lane pairs with a min.
 #include "izb_gemv_body.cuh"
 
+int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int T, int Mp, float* C,
+                           int ldc, int c_off, int acc, cudaStream_t st);
+
 namespace {
 using namespace izb_gemvk;
 
@@ -78,6 +81,10 @@ extern "C" int izb_gemv(const izb_weight* w, int mat, const int8_t* d_aq, const 
   if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "gemv: aq not 16-byte aligned");
   const uint8_t* raw = w->raw + (size_t)mat * w->N * w->row_bytes;
   cudaStream_t st = (cudaStream_t)stream;
+  {  // the streaming kernel takes every call whose staged activations fit in shared memory
+    const int rc = izb_gemv_stream_launch(w, raw, d_aq, d_asc, T, Mp, d_C, ldc, c_off, acc, st);
+    if (rc <= 0) return rc;
+  }
   switch (T) {
     case 1: return launch<1>(w, raw, d_aq, d_asc, Mp, d_C, ldc, c_off, acc, st);
     case 2: return launch<2>(w, raw, d_aq, d_asc, Mp, d_C, ldc, c_off, acc, st);

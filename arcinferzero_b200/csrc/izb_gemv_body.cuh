@@ -34,6 +34,23 @@ __device__ __forceinline__ void gemv_q4k_body(unsigned char* smem, const uint8_t
 
   for (int s0 = 0; s0 < nsteps; s0 += steps_per_chunk) {
     const int s1 = min(nsteps, s0 + steps_per_chunk);
+    // the first step's weights are requested before the activations are staged, so both latencies overlap
+    uint4 hdr[kRows], qv[kRows];
+    auto load = [&](int step, uint4* h, uint4* q) {
+      const int sb = step * 4 + (lane >> 3);
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        if (sb < nsb) {
+          const uint8_t* p = rp[r] + (size_t)sb * 144;
+          h[r] = ldg_stream_v4(p);
+          q[r] = ldg_stream_v4(p + 16 + 16 * piece);
+        } else {
+          h[r] = make_uint4(0, 0, 0, 0);
+          q[r] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    };
+    load(s0, hdr, qv);
     __syncthreads();
     // ---- stage activations of steps [s0, s1): entry (step, t, lane)
     for (int i = threadIdx.x; i < (s1 - s0) * T * 32; i += blockDim.x) {
@@ -60,22 +77,6 @@ __device__ __forceinline__ void gemv_q4k_body(unsigned char* smem, const uint8_t
     }
     __syncthreads();
 
-    uint4 hdr[kRows], qv[kRows];
-    auto load = [&](int step, uint4* h, uint4* q) {
-      const int sb = step * 4 + (lane >> 3);
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        if (sb < nsb) {
-          const uint8_t* p = rp[r] + (size_t)sb * 144;
-          h[r] = ldg_stream_v4(p);
-          q[r] = ldg_stream_v4(p + 16 + 16 * piece);
-        } else {
-          h[r] = make_uint4(0, 0, 0, 0);
-          q[r] = make_uint4(0, 0, 0, 0);
-        }
-      }
-    };
-    load(s0, hdr, qv);
     for (int step = s0; step < s1; ++step) {
       uint4 hn[kRows], qn[kRows];
       if (step + 1 < s1) load(step + 1, hn, qn);
@@ -132,22 +133,7 @@ __device__ __forceinline__ void gemv_q8_0_body(unsigned char* smem, const uint8_
 
   for (int s0 = 0; s0 < nsteps; s0 += steps_per_chunk) {
     const int s1 = min(nsteps, s0 + steps_per_chunk);
-    __syncthreads();
-    for (int i = threadIdx.x; i < (s1 - s0) * T * 32; i += blockDim.x) {
-      const int l = i & 31, t = (i >> 5) % T, st = (i >> 5) / T;
-      const int sb = (s0 + st) * 2 + (l >> 4), pc = l & 15;
-      uint4 a = make_uint4(0, 0, 0, 0);
-      float sc = 0.0f;
-      if (sb < nsb) {
-        a = *reinterpret_cast<const uint4*>(aq + (size_t)tok[t] * K + sb * 256 + pc * 16);
-        sc = asc[(size_t)(sb * 8 + (pc >> 1)) * Mp + tok[t]];
-      }
-      unsigned char* base = smem + (size_t)(st * T + t) * kQ8StepBytes;
-      reinterpret_cast<uint4*>(base)[l] = a;
-      reinterpret_cast<float*>(base + 512)[l] = sc;
-    }
-    __syncthreads();
-
+    // the first step's weights are requested before the activations are staged, so both latencies overlap
     uint4 hdr[kRows], qv[kRows];
     auto load = [&](int step, uint4* h, uint4* q) {
       const int sb = step * 2 + (lane >> 4);
@@ -164,6 +150,22 @@ __device__ __forceinline__ void gemv_q8_0_body(unsigned char* smem, const uint8_
       }
     };
     load(s0, hdr, qv);
+    __syncthreads();
+    for (int i = threadIdx.x; i < (s1 - s0) * T * 32; i += blockDim.x) {
+      const int l = i & 31, t = (i >> 5) % T, st = (i >> 5) / T;
+      const int sb = (s0 + st) * 2 + (l >> 4), pc = l & 15;
+      uint4 a = make_uint4(0, 0, 0, 0);
+      float sc = 0.0f;
+      if (sb < nsb) {
+        a = *reinterpret_cast<const uint4*>(aq + (size_t)tok[t] * K + sb * 256 + pc * 16);
+        sc = asc[(size_t)(sb * 8 + (pc >> 1)) * Mp + tok[t]];
+      }
+      unsigned char* base = smem + (size_t)(st * T + t) * kQ8StepBytes;
+      reinterpret_cast<uint4*>(base)[l] = a;
+      reinterpret_cast<float*>(base + 512)[l] = sc;
+    }
+    __syncthreads();
+
     for (int step = s0; step < s1; ++step) {
       uint4 hn[kRows], qn[kRows];
       if (step + 1 < s1) load(step + 1, hn, qn);

@@ -1,0 +1,235 @@
+// Streaming decode GEMV (1..8 activation rows): the kernel izb_gemv uses whenever its shared-memory plan fits.
+// Same arithmetic as izb_gemv_body.cuh (zero/kernels/decode.cl:913-1034, :1581-1694); different data movement.
+//
+// A decode matrix streams in a few microseconds at HBM speed, so what decides the achieved bandwidth is how many weight
+// bytes are in flight from the first cycle to the last, not the arithmetic.  Registers cannot hold enough, shared
+// memory can:
+//   * one persistent CTA of 16 warps per SM; warp w of the grid owns weight rows w, w + W, w + 2W, ... (W = warps in the
+//     grid), so every SM holds the same share of every part of the matrix;
+//   * every warp has its own ring of kSlots row buffers in shared memory, filled by the TMA engine (cp.async.bulk, one
+//     copy per weight row: a row of K/256 superblocks is contiguous and a multiple of 16 bytes) and tracked by one
+//     mbarrier per slot: all its rows (~190 KB) are in flight per SM at any time, across row boundaries;
+//   * the first ring fill is issued before the CTA stages the activation rows, so the two latencies overlap.
+// Per lane and step: Q4_K lane = (superblock lane/8 of the step's four, 16-byte nibble piece lane%8);
+//                    Q8_0 lane = (superblock lane/16 of the step's two, 16-byte piece lane%16).
+// Waits are bounded; a wait that gives up sets the device error word and the warp stops (izb_device_status).
+#include "izb_gemv_body.cuh"
+
+namespace {
+using namespace izb_gemvk;
+
+constexpr uint32_t kSpin = 1u << 24;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void row_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar) : "memory");
+}
+
+// warps per CTA (32 with half the ring slots measured slower for every shape but one)
+template <int T> __host__ __device__ constexpr int stream_warps() { return 16; }
+
+template <int QT, int T>
+__global__ void __launch_bounds__(stream_warps<T>() * 32, 1) gemv_stream_kernel(const uint8_t* __restrict__ raw, int N, int K,
+                                                                      const int8_t* __restrict__ aq, const float* __restrict__ asc,
+                                                                      int Mp, float* __restrict__ C, int ldc, int c_off, int acc,
+                                                                      int slots, int slot_bytes, uint32_t* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int SBS = QT == IZB_Q4_K ? 4 : 2;  // superblocks per step
+  constexpr int SBB = QT == IZB_Q4_K ? 144 : 272;
+  constexpr int STEP = QT == IZB_Q4_K ? kQ4StepBytes : kQ8StepBytes;
+  constexpr int kSWarps = stream_warps<T>();
+  const int nsb = K >> 8, nsteps = (nsb + SBS - 1) / SBS;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int W = gridDim.x * kSWarps, w0 = blockIdx.x * kSWarps + warp;
+  const uint32_t row_bytes = (uint32_t)nsb * SBB;
+  const int my_rows = w0 < N ? (N - w0 + W - 1) / W : 0;
+  const int sub = QT == IZB_Q4_K ? lane >> 3 : lane >> 4;   // superblock of the step
+  const int piece = QT == IZB_Q4_K ? lane & 7 : lane & 15;  // 16-byte piece of its quants
+  // shared memory: [activation staging: nsteps * T * STEP][16 warps x slots x slot_bytes][16 x slots mbarriers]
+  unsigned char* act = smem;
+  unsigned char* ring = smem + (((size_t)nsteps * T * STEP + 127) & ~(size_t)127) + (size_t)warp * slots * slot_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (((size_t)nsteps * T * STEP + 127) & ~(size_t)127) +
+                                               (size_t)kSWarps * slots * slot_bytes) + warp * slots;
+  if (lane == 0) {
+    for (int s = 0; s < slots; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(&bars[s])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int s = 0; s < slots && s < my_rows; ++s)
+      row_copy(s_u32(ring + (size_t)s * slot_bytes), raw + (size_t)(w0 + s * W) * row_bytes, row_bytes, s_u32(&bars[s]));
+  }
+  // ---- stage the T activation rows for all steps: entry (step, t, lane), laid out as in izb_gemv_body.cuh
+  for (int i = threadIdx.x; i < nsteps * T * 32; i += blockDim.x) {
+    const int l = i & 31, t = (i >> 5) % T, st = (i >> 5) / T;
+    unsigned char* base = act + (size_t)(st * T + t) * STEP;
+    if (QT == IZB_Q4_K) {
+      const int sb = st * 4 + (l >> 3), pc = l & 7;
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      float2 sc = make_float2(0.0f, 0.0f);
+      int2 sm = make_int2(0, 0);
+      if (sb < nsb) {
+        const int e = sb * 256 + (pc >> 1) * 64 + (pc & 1) * 16;
+        lo = *reinterpret_cast<const uint4*>(aq + (size_t)t * K + e);
+        hi = *reinterpret_cast<const uint4*>(aq + (size_t)t * K + e + 32);
+        const int b = sb * 8 + (pc >> 1) * 2;
+        sc.x = asc[(size_t)b * Mp + t];
+        sc.y = asc[(size_t)(b + 1) * Mp + t];
+        sm.x = __dp4a((int)lo.x, 0x01010101, __dp4a((int)lo.y, 0x01010101, __dp4a((int)lo.z, 0x01010101, __dp4a((int)lo.w, 0x01010101, 0))));
+        sm.y = __dp4a((int)hi.x, 0x01010101, __dp4a((int)hi.y, 0x01010101, __dp4a((int)hi.z, 0x01010101, __dp4a((int)hi.w, 0x01010101, 0))));
+      }
+      reinterpret_cast<uint4*>(base)[l] = lo;
+      reinterpret_cast<uint4*>(base + 512)[l] = hi;
+      reinterpret_cast<float2*>(base + 1024)[l] = sc;
+      reinterpret_cast<int2*>(base + 1280)[l] = sm;
+    } else {
+      const int sb = st * 2 + (l >> 4), pc = l & 15;
+      uint4 a = make_uint4(0, 0, 0, 0);
+      float sc = 0.0f;
+      if (sb < nsb) {
+        a = *reinterpret_cast<const uint4*>(aq + (size_t)t * K + sb * 256 + pc * 16);
+        sc = asc[(size_t)(sb * 8 + (pc >> 1)) * Mp + t];
+      }
+      reinterpret_cast<uint4*>(base)[l] = a;
+      reinterpret_cast<float*>(base + 512)[l] = sc;
+    }
+  }
+  __syncthreads();
+
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < my_rows; ++i) {
+    const int row = w0 + i * W;
+    bool ready = false;
+    for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[slot]), parity);
+    if (!ready) {  // (bounded wait gave up)
+      if (lane == 0) atomicOr(err, 64u);
+      break;
+    }
+    const unsigned char* wrow = ring + (size_t)slot * slot_bytes;
+    float accv[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) accv[t] = 0.0f;
+    for (int step = 0; step < nsteps; ++step) {
+      const int sb = step * SBS + sub;
+      if (sb < nsb) {
+        const uint4 h = *reinterpret_cast<const uint4*>(wrow + sb * SBB);
+        const uint4 qw = *reinterpret_cast<const uint4*>(wrow + sb * SBB + 16 + 16 * piece);
+        const unsigned char* sbase = act + (size_t)step * T * STEP;
+        const uint32_t w[4] = {qw.x, qw.y, qw.z, qw.w};
+        if (QT == IZB_Q4_K) {
+          const float d = half_bits_to_float(h.x & 0xFFFFu), dmin = half_bits_to_float(h.x >> 16);
+          const uint32_t s3[3] = {h.y, h.z, h.w};
+          int sc_lo, mn_lo, sc_hi, mn_hi;
+          q4k_scale_min(s3, 2 * (piece >> 1), sc_lo, mn_lo);
+          q4k_scale_min(s3, 2 * (piece >> 1) + 1, sc_hi, mn_hi);
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const unsigned char* b = sbase + (size_t)t * STEP;
+            const uint4 alo = reinterpret_cast<const uint4*>(b)[lane];
+            const uint4 ahi = reinterpret_cast<const uint4*>(b + 512)[lane];
+            const float2 sa = reinterpret_cast<const float2*>(b + 1024)[lane];
+            const int2 as = reinterpret_cast<const int2*>(b + 1280)[lane];
+            const uint32_t al[4] = {alo.x, alo.y, alo.z, alo.w}, ah[4] = {ahi.x, ahi.y, ahi.z, ahi.w};
+            int lo = 0, hi = 0;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              lo = __dp4a((int)al[kk], (int)(w[kk] & 0x0F0F0F0Fu), lo);
+              hi = __dp4a((int)ah[kk], (int)((w[kk] >> 4) & 0x0F0F0F0Fu), hi);
+            }
+            accv[t] += sa.x * (d * (float)(sc_lo * lo) - dmin * (float)(mn_lo * as.x)) +
+                       sa.y * (d * (float)(sc_hi * hi) - dmin * (float)(mn_hi * as.y));
+          }
+        } else {
+          const int blk = piece >> 1;
+          const uint32_t pair = blk < 2 ? h.x : blk < 4 ? h.y : blk < 6 ? h.z : h.w;
+          const float d = half_bits_to_float((blk & 1) ? (pair >> 16) : (pair & 0xFFFFu));
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            const unsigned char* b = sbase + (size_t)t * STEP;
+            const uint4 a4 = reinterpret_cast<const uint4*>(b)[lane];
+            const float sa = reinterpret_cast<const float*>(b + 512)[lane];
+            const uint32_t a[4] = {a4.x, a4.y, a4.z, a4.w};
+            int dot = 0;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) dot = __dp4a((int)a[kk], (int)w[kk], dot);
+            accv[t] += sa * d * (float)dot;
+          }
+        }
+      }
+    }
+    // the slot is read: request the row `slots` ahead into it, then reduce and store this one
+    __syncwarp();
+    if (lane == 0 && i + slots < my_rows)
+      row_copy(s_u32(ring + (size_t)slot * slot_bytes), raw + (size_t)(row + slots * W) * row_bytes, row_bytes, s_u32(&bars[slot]));
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      const float v = warp_sum(accv[t]);
+      if (lane == 0) {
+        float* c = C + (size_t)t * ldc + c_off + row;
+        *c = acc ? *c + v : v;
+      }
+    }
+    if (++slot == slots) { slot = 0; parity ^= 1; }
+  }
+}
+
+template <int QT, int T>
+int launch_stream(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc,
+                  int c_off, int acc, cudaStream_t st) {
+  constexpr int STEP = QT == IZB_Q4_K ? kQ4StepBytes : kQ8StepBytes;
+  constexpr size_t kBudget = 200 * 1024;
+  constexpr int kSWarps = stream_warps<T>();
+  const int nsb = w->K / 256, nsteps = QT == IZB_Q4_K ? (nsb + 3) / 4 : (nsb + 1) / 2;
+  const size_t act = ((size_t)nsteps * T * STEP + 127) & ~(size_t)127;
+  const int slot_bytes = (int)((w->row_bytes + 127) & ~(size_t)127);
+  if (act + 4096 >= kBudget) return 1;
+  int slots = (int)((kBudget - act - 4096) / ((size_t)kSWarps * slot_bytes));
+  if (slots < 2) return 1;  // (rows too long for a ring: the chunked kernel takes the call)
+  if (slots > 8) slots = 8;
+  const size_t smem = act + (size_t)kSWarps * slots * slot_bytes + (size_t)kSWarps * slots * 8;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    IZB_CUDA(cudaGetDevice(&dev));
+    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    IZB_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<QT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
+  }
+  int grid = sms;
+  const int need = (w->N + kSWarps - 1) / kSWarps;
+  if (grid > need) grid = need;
+  uint32_t* err = izb_device_error_word(w->device);
+  if (!err) IZB_FAIL(IZB_ERR_NOMEM, "gemv: no device error word");
+  IZB_LAUNCH("gemv", st, gemv_stream_kernel<QT, T><<<grid, kSWarps * 32, smem, st>>>(raw, w->N, w->K, aq, asc, Mp, C, ldc, c_off, acc,
+                                                                                    slots, slot_bytes, err));
+  return IZB_OK;
+}
+
+}  // namespace
+
+// +1: the shared-memory plan does not fit (the chunked kernel of izb_gemv.cu takes the call)
+template <int T>
+static int stream_t(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc,
+                    int c_off, int acc, cudaStream_t st) {
+  return w->type == IZB_Q4_K ? launch_stream<IZB_Q4_K, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st)
+                             : launch_stream<IZB_Q8_0, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+}
+
+int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int T, int Mp, float* C,
+                           int ldc, int c_off, int acc, cudaStream_t st) {
+  switch (T) {
+    case 1: return stream_t<1>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 2: return stream_t<2>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 3: return stream_t<3>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 4: return stream_t<4>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 5: return stream_t<5>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 6: return stream_t<6>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 7: return stream_t<7>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    default: return stream_t<8>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+  }
+}

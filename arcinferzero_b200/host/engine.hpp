@@ -1,0 +1,131 @@
+// Host-side mirror of the reference engine's matmul interface over the izb200 C ABI.
+//
+// The reference's layer code (zero/engine_qwen.h, zero/engine_moe.h) talks to its GEMM back end through a handful of
+// Engine members: quant_rows / rmsnorm_quant fill the engine-wide activation buffers aq_ / asc_ / absum_
+// (zero/engine_alloc.h:10,39,41), matmul(name, w, Mp, C, ldc, c_off, acc, act32) multiplies them with a GpuWeight
+// (zero/engine.h:1080), tp_out(name, w, Mp, act32) does the same for a row-parallel projection and sums the partial
+// outputs over the GPUs (zero/mgpu/engine_tp_shard.h:318).  This header keeps those names, argument meanings and error
+// behaviour (std::runtime_error before any launch on a bad shape, zero/engine.h:1233-1235), so the call sites of the
+// reference read the same; underneath, every call is one C-ABI call of include/izb200.h.  There is no CPU fallback.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/izb200.h"
+
+namespace izb {
+
+inline void check(int rc, const char* what) {
+  if (rc != IZB_OK) throw std::runtime_error(std::string(what) + ": " + izb_status_string(rc) + ": " + izb_last_error());
+}
+
+// GpuWeight of the reference (zero/engine.h:27-34): type, N, K and the device copy, owned here.
+struct GpuWeight {
+  int type = 0, N = 0, K = 0, n_mats = 1;
+  izb_weight* h = nullptr;
+  GpuWeight() = default;
+  GpuWeight(const GpuWeight&) = delete;
+  GpuWeight& operator=(const GpuWeight&) = delete;
+  GpuWeight(GpuWeight&& o) noexcept { *this = std::move(o); }
+  GpuWeight& operator=(GpuWeight&& o) noexcept {
+    std::swap(type, o.type); std::swap(N, o.N); std::swap(K, o.K); std::swap(n_mats, o.n_mats); std::swap(h, o.h);
+    return *this;
+  }
+  ~GpuWeight() { izb_weight_destroy(h); }
+};
+
+class Engine {
+ public:
+  explicit Engine(int device = 0, cudaStream_t stream = nullptr) : device_(device), stream_(stream) {}
+  ~Engine() { release(); }
+  Engine(const Engine&) = delete;
+  Engine& operator=(const Engine&) = delete;
+
+  // make_weight (zero/engine_load.h:157): GGUF rows of one tensor -> device weight
+  GpuWeight make_weight(int ggml_type, const void* gguf_rows, int N, int K, int n_mats = 1) const {
+    GpuWeight w;
+    check(izb_weight_create(ggml_type, gguf_rows, n_mats, N, K, device_, &w.h), "make_weight");
+    w.type = ggml_type; w.N = N; w.K = K; w.n_mats = n_mats;
+    return w;
+  }
+  // T(): this rank's slice of a tensor (zero/mgpu/engine_tp_shard.h:243-279): rows [n0, n1), input columns [k0, k1)
+  GpuWeight make_weight_slice(int ggml_type, const void* gguf_rows, int N, int K, int n0, int n1, int k0, int k1) const {
+    GpuWeight w;
+    check(izb_weight_create_slice(ggml_type, gguf_rows, 1, N, K, n0, n1, k0, k1, device_, &w.h), "make_weight_slice");
+    w.type = ggml_type; w.N = n1 - n0; w.K = k1 - k0;
+    return w;
+  }
+
+  // alloc_buffers (zero/engine_alloc.h:4): activation buffers for up to max_rows rows of up to max_k values
+  void alloc_buffers(int max_rows, int max_k) {
+    release_buffers();
+    max_rows_ = pad_rows(max_rows);
+    max_k_ = max_k;
+    if (cudaSetDevice(device_) != cudaSuccess || cudaMalloc(&aq_, (size_t)max_rows_ * max_k) != cudaSuccess ||
+        cudaMalloc(&asc_, (size_t)max_rows_ * (max_k / 32) * sizeof(float)) != cudaSuccess)
+      throw std::runtime_error("alloc_buffers: out of device memory");
+  }
+  // row padding of a chunk (zero/engine.h:521-522)
+  static int pad_rows(int T) { return T >= 128 ? (T + 127) / 128 * 128 : (T + 15) / 16 * 16; }
+  void set_rows(int T) { cur_T_ = T; }
+  int cur_T() const { return cur_T_; }
+
+  // quant_rows (zero/engine.h:1445): f32 rows -> aq_ / asc_ (rows cur_T_..Mp-1 become zeros with scale 0)
+  void quant_rows(const float* x, int ldx, int K, int Mp) {
+    if (Mp > max_rows_ || K > max_k_) throw std::runtime_error("quant_rows: activation buffers too small");
+    check(izb_quantize_act(x, ldx, cur_T_, Mp, K, aq_, asc_, nullptr, stream_), "quant_rows");
+    cur_K_ = K; cur_Mp_ = Mp;
+  }
+  // swiglu_quant (zero/kernels/ops.cl:272): gu = [gate | up] rows of 2F -> quantised silu(gate) * up
+  void swiglu_quant(const float* gu, int ldgu, int F, int Mp) {
+    if (Mp > max_rows_ || F > max_k_) throw std::runtime_error("swiglu_quant: activation buffers too small");
+    check(izb_swiglu_quant(gu, ldgu, 1, cur_T_, Mp, F, nullptr, aq_, asc_, nullptr, stream_), "swiglu_quant");
+    cur_K_ = F; cur_Mp_ = Mp;
+  }
+  // matmul (zero/engine.h:1080): C[.][c_off + n] (op)= quantised rows x w; acc 0 store, 1 add, 2 fused SwiGLU.
+  // `name` is the reference's profiling label; act32 is always on (per-32 scales, the reference's default).
+  void matmul(const char* name, const GpuWeight& w, int Mp, float* C, int ldc, int c_off, int acc, bool act32 = true) {
+    (void)name;
+    if (!act32) throw std::runtime_error("matmul: only per-32 activation scales (act32) are implemented");
+    if (w.K != cur_K_ || Mp != cur_Mp_) throw std::runtime_error("matmul: the quantised activations do not match this weight");
+    check(izb_matmul(w.h, 0, aq_, asc_, nullptr, cur_T_, Mp, C, ldc, c_off, acc, stream_), "matmul");
+  }
+
+  // tp_setup (zero/mgpu/engine_tp_shard.h:88): join the communicator; id128 from izb_tp_unique_id on rank 0
+  void tp_setup(int nranks, int rank, const void* id128) {
+    nranks_ = nranks; rank_ = rank;
+    check(izb_tp_create(nranks, rank, id128, device_, &tp_), "tp_setup");
+  }
+  // tp_range (zero/mgpu/engine_tp_shard.h:68-72)
+  void tp_range(int64_t total, int64_t unit, int64_t* b, int64_t* e) const { check(izb_tp_range(total, unit, nranks_, rank_, b, e), "tp_range"); }
+  // tp_out (zero/mgpu/engine_tp_shard.h:318-325): row-parallel projection into `part`, summed over the ranks into x
+  void tp_out(const char* name, const GpuWeight& w, int Mp, float* x, float* part, int E) {
+    matmul(name, w, Mp, part, E, 0, 0);
+    check(izb_tp_allreduce_rows(tp_, x, part, Mp, E, stream_), "tp_out");
+  }
+
+ private:
+  void release_buffers() {
+    if (aq_) cudaFree(aq_);
+    if (asc_) cudaFree(asc_);
+    aq_ = nullptr; asc_ = nullptr;
+  }
+  void release() {
+    release_buffers();
+    if (tp_) izb_tp_destroy(tp_);
+    tp_ = nullptr;
+  }
+  int device_ = 0;
+  cudaStream_t stream_ = nullptr;
+  int8_t* aq_ = nullptr;
+  float* asc_ = nullptr;
+  int max_rows_ = 0, max_k_ = 0, cur_T_ = 0, cur_K_ = 0, cur_Mp_ = 0;
+  int nranks_ = 1, rank_ = 0;
+  izb_tp* tp_ = nullptr;
+};
+
+}  // namespace izb

@@ -124,6 +124,52 @@ def cpu_baseline(seconds_target: float = 15.0) -> dict:
             "sample": f"{ms} tokens x {Ns} of {N} weight rows x K={K} in {t:.2f} s, scaled by N/{Ns}"}
 
 
+def gemv_section(izb, torch, hbm_peak: float, peak_src: str) -> list:
+    """Decode GEMV (BASELINE.json config 3): batch 1 and 2, K = 5120; Q4_K N = 5120 and 17408, Q8_0 N = 151936.
+    Each launch reads a different copy of the weights (enough copies to exceed the 126 MB L2), so the bytes come from
+    HBM; GB/s = (weight bytes + activation bytes + output bytes) / mean launch time over the timed launches."""
+    from arcinferzero_b200 import synth as S
+    out = []
+    for qt, Nn in ((12, 5120), (12, 17408), (8, 151936)):
+        w = S.make_weight(qt, Nn, K, SEED + Nn)
+        wbytes = w.size
+        copies = max(1, -(-300_000_000 // wbytes)) if wbytes < 400_000_000 else 2
+        Ws = [izb.Weight(qt, w, Nn, K) for _ in range(copies)]
+        del w
+        for T in (1, 2):
+            x = torch.from_numpy(S.make_act(T, K, SEED + T)).cuda()
+            aq, asc, _ = izb.quantize_act(x, Mp=16)
+            y = torch.empty((T, Nn), dtype=torch.float32, device="cuda")
+            for i in range(max(3, copies)):
+                izb.gemv(Ws[i % copies], aq, asc, T, out=y)
+            torch.cuda.synchronize()
+            # the launches of one sweep over the copies are captured in a CUDA graph, so that the host's per-call cost
+            # (Python + ctypes) is not what is measured
+            launches = max(20, 4 * copies)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(launches):
+                    izb.gemv(Ws[i % copies], aq, asc, T, out=y)
+            graph.replay()
+            torch.cuda.synchronize()
+            reps = 5
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
+            nbytes = wbytes + T * (K + K // 32 * 4) + T * Nn * 4
+            gbs = nbytes / (us * 1e-6) / 1e9
+            out.append({"type": "Q4_K" if qt == 12 else "Q8_0", "N": Nn, "K": K, "batch": T, "us_per_launch": us,
+                        "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
+                        "peak": f"{hbm_peak} GB/s {peak_src} copy", "weight_copies_in_rotation": copies})
+        for W_ in Ws:
+            W_.close()
+    return out
+
+
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
@@ -150,6 +196,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gemv", action="store_true", help="skip the decode GEMV section (BASELINE.json config 3)")
     ap.add_argument("--tokens", type=int, default=M, help="profiling only: fewer token rows than the configured 8192")
     args = ap.parse_args()
     if args.tokens != M:
@@ -265,6 +312,8 @@ def main() -> None:
             "e2e": {"value": M / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * Nr * 4},
             "gpu_launches": launches, "clocks": clocks, "device_wait_errors": status,
         }
+        if not args.no_gemv and world == 1:
+            line["decode_gemv"] = gemv_section(izb, torch, hbm, src)
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)

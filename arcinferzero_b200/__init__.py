@@ -23,7 +23,7 @@ SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
     "izb_quantize_act", "izb_swiglu_quant",
-    "izb_matmul", "izb_gemv", "izb_gemm", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
+    "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
     "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_destroy", "izb_tp_allreduce_rows",
     "izb_tp_reduce_quant_gather",
@@ -178,6 +178,21 @@ def gemm(w: Weight, aq, asc, M: int | None = None, out=None, c_off: int = 0, acc
     if out is None:
         out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
     _check(lib().izb_gemm(w.handle, mat, _p(aq), _p(asc), M, Mp, _p(out), out.stride(0), c_off, acc, impl, _stream()))
+    return out
+
+
+NOALLOC_SCRATCH_BYTES = 24 << 20
+
+
+def gemm_noalloc(w: Weight, aq, asc, M: int | None = None, out=None, c_off: int = 0, acc: int = 0, mat: int = 0, status=None):
+    """izb_gemm_noalloc: the tensor-core GEMM with its scratch in the library's fixed device array (no allocation inside
+    the call).  `out` must be given by callers that really cannot allocate; it is created here only for convenience."""
+    import torch
+    Mp = asc.shape[1]
+    M = M or Mp
+    if out is None:
+        out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
+    _check(lib().izb_gemm_noalloc(w.handle, mat, _p(aq), _p(asc), M, Mp, _p(out), out.stride(0), c_off, acc, _p(status), _stream()))
     return out
 
 

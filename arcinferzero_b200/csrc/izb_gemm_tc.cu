@@ -30,6 +30,8 @@
 #include <cuda_bf16.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "izb_common.cuh"
 
 void izb_set_tc_ok(int device, int ok);
@@ -999,4 +1001,101 @@ extern "C" int izb_selfcheck(int device) {
   if (st != IZB_OK && verdict == IZB_OK) { verdict = st; }
   izb_set_tc_ok(device, verdict == IZB_OK ? 1 : 0);
   return verdict;
+}
+
+// ---------------------------------------------------------------------------------------------- GEMM without allocation
+// izb_gemm_noalloc: the tensor-core GEMM for callers that must not allocate device memory while they run -- a serving
+// loop that has handed the whole GPU to its own arena, a process whose CUDA calls are being captured into a graph, or
+// code that runs under an allocator it cannot re-enter.  izb_gemm keeps its activation images (the fp16 operand tiles,
+// the min-term factors and the gathered scales that act_prepare_kernel writes) in an arena that grows with cudaMalloc;
+// this entry point keeps them in a fixed array that is part of the library's device image instead.
+//
+// The array is a device symbol: in host code its name stands for the symbol, not for an address a kernel could use, so
+// the address is looked up with cudaGetSymbolAddress -- once per device, with that device current -- and only that
+// pointer is ever handed to a kernel.
+namespace {
+constexpr size_t kNoAllocBytes = IZB_NOALLOC_SCRATCH_BYTES;  // 24 MiB per GPU that loads the library, held until the process exits
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+static __device__ __align__(256) uint32_t g_noalloc_status[64];
+
+struct NoAllocDev {
+  unsigned char* scratch = nullptr;
+  uint32_t* status = nullptr;
+};
+NoAllocDev g_noalloc_dev[16];
+std::mutex g_noalloc_mu;
+
+// Looks the two symbols up for `device` (which must be the current device) the first time it is called for it.
+int noalloc_setup(int device, NoAllocDev** out) {
+  if (device < 0 || device >= 16) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: device %d out of range", device);
+  int cur = -1;
+  IZB_CUDA(cudaGetDevice(&cur));
+  if (cur != device) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: device %d must be current (current is %d)", device, cur);
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoAllocDev& d = g_noalloc_dev[device];
+  if (!d.scratch) {
+    void* p = nullptr;
+    void* s = nullptr;
+    IZB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    IZB_CUDA(cudaGetSymbolAddress(&s, g_noalloc_status));
+    d.status = (uint32_t*)s;
+    d.scratch = (unsigned char*)p;
+  }
+  *out = &d;
+  return IZB_OK;
+}
+}  // namespace
+
+extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int M, int Mp, float* d_C,
+                                int ldc, int c_off, int acc, uint32_t* d_status, void* stream) {
+  if (!w || !d_aq || !d_asc || !d_C) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: null pointer");
+  if (mat < 0 || mat >= w->n_mats) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: matrix %d of %d", mat, w->n_mats);
+  if (acc < 0 || acc > 2) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: store mode %d", acc);
+  if (Mp % 16 || w->N % BN || w->K % 256 || M < 1 || M > Mp)
+    IZB_FAIL(IZB_ERR_SHAPE, "gemm_noalloc: M=%d Mp=%d N=%d K=%d (need Mp %% 16, N %% 128, K %% 256, 1 <= M <= Mp)", M, Mp, w->N, w->K);
+  if (c_off < 0 || ldc < c_off + w->N) IZB_FAIL(IZB_ERR_SHAPE, "gemm_noalloc: ldc = %d < c_off + N = %d", ldc, c_off + w->N);
+  if (!izb_aligned(d_aq, 16) || !izb_aligned(d_asc, 16) || !izb_aligned(d_C, 16) || ldc % 4 || c_off % 4 || (d_status && !izb_aligned(d_status, 4)))
+    IZB_FAIL(IZB_ERR_ALIGN, "gemm_noalloc: aq, asc, C must be 16-byte aligned, ldc and c_off multiples of 4");
+  if (!w->has_tmap) IZB_FAIL(IZB_ERR_CUDA, "gemm_noalloc: the weight has no tensor map (driver entry point missing at creation)");
+  const int K = w->K, nb = K / 32, nstages = K / KS;
+  const int n_tiles = (M + BM - 1) / BM;
+  const size_t img_bytes = (size_t)n_tiles * nstages * STAGE_BYTES, vs_bytes = (size_t)n_tiles * nb * BM * 4;
+  if (img_bytes + 2 * vs_bytes > kNoAllocBytes || n_tiles > 65535)
+    IZB_FAIL(IZB_ERR_LIMIT, "gemm_noalloc: M=%d K=%d needs %zu scratch bytes, the fixed array holds %zu (use izb_gemm, or fewer rows per call)",
+             M, K, img_bytes + 2 * vs_bytes, kNoAllocBytes);
+  NoAllocDev* dev = nullptr;
+  if (int rc = noalloc_setup(w->device, &dev)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint16_t* aimg = (uint16_t*)dev->scratch;
+  float* vsum = (float*)(dev->scratch + img_bytes);
+  float* ascimg = (float*)(dev->scratch + img_bytes + vs_bytes);
+  // Everything the GEMM reads from the array is rewritten by the pre-pass of the same call (all rows of all its tiles,
+  // padding rows as zeros), so nothing stale from an earlier call is ever read; the status word is the one thing that
+  // must start at zero.
+  uint32_t* status = d_status ? d_status : dev->status;
+  IZB_CUDA(cudaMemsetAsync(status, 0, 4, st));
+  dim3 pg((BM * (K / 8) + 255) / 256, n_tiles);
+  if (w->type == IZB_Q4_K)
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(d_aq, d_asc, Mp, K, Mp, nullptr, nullptr, aimg, vsum, ascimg, 1));
+  else
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(d_aq, d_asc, Mp, K, Mp, nullptr, nullptr, aimg, vsum, ascimg, 0));
+  TcParams p;
+  p.aimg = aimg;
+  p.vsum = vsum;
+  p.ascimg = ascimg;
+  p.tiles = nullptr;
+  p.rowmap = nullptr;
+  p.rowscale = nullptr;
+  p.M = M;
+  p.N = w->N;
+  p.K = K;
+  p.mat = mat;
+  p.C = d_C;
+  p.ldc = ldc;
+  p.c_off = c_off;
+  p.acc = acc;
+  p.dots = nullptr;
+  p.err = status;
+  dim3 grid(w->N / BN, n_tiles);
+  return w->type == IZB_Q4_K ? launch_tc<IZB_Q4_K, false>(w, p, grid, st) : launch_tc<IZB_Q8_0, false>(w, p, grid, st);
 }

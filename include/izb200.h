@@ -117,6 +117,27 @@ int izb_block_dots(const izb_weight* w, int mat, const int8_t* d_aq, int M, int3
  * Synchronous.  IZB_ERR_SELFCHECK on disagreement; izb_matmul then keeps to the CUDA-core kernel on that device. */
 int izb_selfcheck(int device);
 
+/* izb_gemm for callers that cannot allocate device memory while they run.  It has no counterpart in the reference.
+ * Who needs it: an inference server that gave the whole GPU to its own memory pool at start-up (a cudaMalloc inside a
+ * request would fail or fragment it), code running inside a stream capture, where cudaMalloc is not allowed, and hosts
+ * that forbid allocator calls on their hot path.  izb_gemm keeps the tensor-core kernel's activation images in an arena
+ * that it grows with cudaMalloc when a call is larger than any before; this call keeps them in a fixed array of
+ * IZB_NOALLOC_SCRATCH_BYTES that lives in the library's device image: every GPU that loads the library holds those
+ * bytes until the process exits, and the call itself calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - Same arguments and results as izb_gemm with impl = IZB_GEMM_TC (N % 128 == 0 is required here: there is no second
+ *     kernel to fall back to), plus d_status.
+ *   - Limit: ceil(M/128) * (K/64 * 16384 + K/32 * 1024) bytes must fit in the array (e.g. M = 1024 at K = 5120, or
+ *     M = 512 at K = 10240); a larger call returns IZB_ERR_LIMIT and launches nothing.
+ *   - d_status: a device uint32 of the caller's (or NULL to use one inside the library).  It is cleared at the start of
+ *     the call and is non-zero afterwards if a bounded device-side wait gave up (the output is then incomplete).
+ *   - The first call on a device looks up the array's device address (the device must be current, as for every call):
+ *     make that first call before any stream capture begins.
+ *   - All calls share the one array and it keeps the last call's contents; each call rewrites everything it reads.  Two
+ *     calls whose kernels can overlap on the GPU (different streams, no ordering between them) race on it: order them. */
+#define IZB_NOALLOC_SCRATCH_BYTES (24u << 20)
+int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int M_rows, int Mp, float* d_C,
+                     int ldc, int c_off, int acc, uint32_t* d_status, void* stream);
+
 /* Host-buffer convenience call = what a caller without device code does per projection: copies h_x [M][K] to the
  * device, quantises, multiplies, copies C [M][N] back, synchronises.  Uses library-owned staging buffers per device. */
 int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, int M, float* h_C, void* stream);

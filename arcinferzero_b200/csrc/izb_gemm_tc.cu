@@ -1005,8 +1005,7 @@ extern "C" int izb_selfcheck(int device) {
 
 // ---------------------------------------------------------------------------------------------- GEMM without allocation
 // izb_gemm_noalloc: the tensor-core GEMM for callers that must not allocate device memory while they run -- a serving
-// loop that has handed the whole GPU to its own arena, a process whose CUDA calls are being captured into a graph, or
-// code that runs under an allocator it cannot re-enter.  izb_gemm keeps its activation images (the fp16 operand tiles,
+// loop that has handed the whole GPU to its own arena, or code that runs under an allocator it cannot re-enter.  izb_gemm keeps its activation images (the fp16 operand tiles,
 // the min-term factors and the gathered scales that act_prepare_kernel writes) in an arena that grows with cudaMalloc;
 // this entry point keeps them in a fixed array that is part of the library's device image instead.
 //

@@ -119,8 +119,8 @@ int izb_selfcheck(int device);
 
 /* izb_gemm for callers that cannot allocate device memory while they run.  It has no counterpart in the reference.
  * Who needs it: an inference server that gave the whole GPU to its own memory pool at start-up (a cudaMalloc inside a
- * request would fail or fragment it), code running inside a stream capture, where cudaMalloc is not allowed, and hosts
- * that forbid allocator calls on their hot path.  izb_gemm keeps the tensor-core kernel's activation images in an arena
+ * request would fail or fragment it), and hosts that forbid allocator calls on their hot path (real-time loops,
+ * processes whose device heap is locked down after initialisation).  izb_gemm keeps the tensor-core kernel's activation images in an arena
  * that it grows with cudaMalloc when a call is larger than any before; this call keeps them in a fixed array of
  * IZB_NOALLOC_SCRATCH_BYTES that lives in the library's device image: every GPU that loads the library holds those
  * bytes until the process exits, and the call itself calls no cudaMalloc, cudaFree or other allocating routine.

@@ -1,0 +1,236 @@
+"""Tensor-parallel projection stack: the split the reference's multi-GPU mode performs (zero/mgpu/engine_tp_shard.h)
+applied to a stack of dense layers, one process per GPU.
+
+Per layer (BASELINE.json config 5; no attention, no norms: only the quantised projections and what lies between them):
+
+    x [T, E] f32 --quantise--> QKV (column parallel: this rank's rows of the Q, K and V blocks)
+      q = the rank's Q columns --quantise--> O (row parallel: the matching K range) --sum over ranks--> x += .
+    x --quantise--> gate, up (column parallel; up stored with the fused SwiGLU mode: h = up * silu(gate))
+      h --quantise--> down (row parallel) --sum over ranks--> x += .
+
+Ranges follow tp_range (zero/mgpu/engine_tp_shard.h:68-72): whole units, the first `units % N` ranks one unit more.
+FFN rows split in units of 256 (:128-144).  The Q rows also split in units of 256 here (= two 128-wide heads) rather than
+by kv-head group: with 8 ranks a head-group split leaves the O projection 640 input columns per rank, which is not a
+whole number of 256-element superblocks (the reference refuses such a split, :128, :216); K and V rows split evenly.
+
+Two ways to sum the row-parallel partial outputs:
+  "allreduce"  f32 all-reduce of the partials, added to the residual stream (tp_out / tp_reduce_at, tp_add);
+  "rs_quant_ag"  reduce-scatter by token rows, add the residual rows, quantise them, all-gather int8 + scales:
+               every element is summed on one rank only (all ranks end up with identical int8 rows) and fewer bytes
+               cross NVLink; the next projection consumes the gathered int8 rows directly.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import synth as S
+
+
+@dataclass
+class StackConfig:
+    layers: int = 8
+    tokens: int = 32768
+    hidden: int = 5120
+    q_rows: int = 5120      # 40 heads x 128
+    kv_rows: int = 1024     # 8 kv heads x 128 (each of K and V)
+    ffn: int = 17408
+    qtype: int = S.GGML_Q4_K
+    seed: int = 20261125
+
+    @property
+    def ops_per_pass(self) -> float:
+        """2*M*N*K integer operations of one pass over all layers (all ranks together)."""
+        per_tok = self.hidden * (self.q_rows + 2 * self.kv_rows) + self.q_rows * self.hidden + 2 * self.hidden * self.ffn + self.ffn * self.hidden
+        return 2.0 * self.tokens * self.layers * per_tok
+
+
+def tp_range(total: int, unit: int, n: int, r: int) -> tuple[int, int]:
+    """zero/mgpu/engine_tp_shard.h:68-72 (host copy of izb_tp_range, usable without the CUDA library)."""
+    units = total // unit
+    base, extra = divmod(units, n)
+    b = r * base + min(r, extra)
+    e = b + base + (1 if r < extra else 0)
+    return b * unit, e * unit
+
+
+@dataclass
+class ShardPlan:
+    q: tuple[int, int]      # this rank's Q rows of the QKV matrix = its K range of O
+    kv: tuple[int, int]     # its rows inside the K block (and inside the V block)
+    ffn: tuple[int, int]    # its gate / up rows = its K range of down
+
+    @property
+    def qkv_rows(self) -> int:
+        return (self.q[1] - self.q[0]) + 2 * (self.kv[1] - self.kv[0])
+
+
+def shard_plan(cfg: StackConfig, world: int, rank: int) -> ShardPlan:
+    return ShardPlan(q=tp_range(cfg.q_rows, 256, world, rank), kv=tp_range(cfg.kv_rows, 128, world, rank),
+                     ffn=tp_range(cfg.ffn, 256, world, rank))
+
+
+def layer_weights(cfg: StackConfig, layer: int) -> dict[str, np.ndarray]:
+    """Full (unsplit) GGUF rows of one layer, seeded per tensor."""
+    s = cfg.seed + 100 * layer
+    E = cfg.hidden
+    return {
+        "qkv": S.make_weight(cfg.qtype, cfg.q_rows + 2 * cfg.kv_rows, E, s + 1),
+        "o": S.make_weight(cfg.qtype, E, cfg.q_rows, s + 2),
+        "gate": S.make_weight(cfg.qtype, cfg.ffn, E, s + 3),
+        "up": S.make_weight(cfg.qtype, cfg.ffn, E, s + 4),
+        "down": S.make_weight(cfg.qtype, E, cfg.ffn, s + 5),
+    }
+
+
+def shard_rows(cfg: StackConfig, w: dict[str, np.ndarray], plan: ShardPlan) -> dict[str, tuple[np.ndarray, int, int, tuple | None]]:
+    """This rank's part of every tensor as (rows_bytes, N, K, col_range): QKV rows are gathered from the three blocks on
+    the host (Engine::T(), zero/mgpu/engine_tp_shard.h:243-279); the K ranges of O / down are cut by the library."""
+    E = cfg.hidden
+    q0, q1 = plan.q
+    k0, k1 = plan.kv
+    qkv = np.concatenate([w["qkv"][q0:q1], w["qkv"][cfg.q_rows + k0:cfg.q_rows + k1],
+                          w["qkv"][cfg.q_rows + cfg.kv_rows + k0:cfg.q_rows + cfg.kv_rows + k1]])
+    f0, f1 = plan.ffn
+    return {
+        "qkv": (qkv, qkv.shape[0], E, None),
+        "o": (w["o"], E, cfg.q_rows, (q0, q1)),
+        "gate": (np.ascontiguousarray(w["gate"][f0:f1]), f1 - f0, E, None),
+        "up": (np.ascontiguousarray(w["up"][f0:f1]), f1 - f0, E, None),
+        "down": (w["down"], E, cfg.ffn, (f0, f1)),
+    }
+
+
+def slice_cols(qtype: int, rows: np.ndarray, K: int, k0: int, k1: int) -> np.ndarray:
+    """Columns [k0, k1) of GGUF rows, cut at 256-element superblocks (tp_slice, zero/mgpu/engine_tp_shard.h:202-234)."""
+    if k0 % 256 or k1 % 256 or not 0 <= k0 < k1 <= K:
+        raise ValueError(f"column range [{k0}, {k1}) of {K} must be whole 256-element superblocks")
+    sb = S.sb_bytes(qtype)
+    n = rows.shape[0]
+    return np.ascontiguousarray(rows.reshape(n, K // 256, sb)[:, k0 // 256:k1 // 256]).reshape(n, -1)
+
+
+class PeerGone(RuntimeError):
+    """Another rank announced that it left (or never confirmed a step) before this rank's next launch."""
+
+
+class StepGuard:
+    """Host-side liveness check between steps (the reference's barrier timeout, zero/mgpu/engine_tp.h:57-60,960-977, moved
+    in front of the launch: no kernel or collective is started once a peer is known to be gone).
+
+    Each rank adds 1 to the counter `step/<k>` of a torch.distributed store when it is about to start step k and sets the
+    key `gone` when it leaves between steps.  `enter(k)` returns when all ranks have arrived, raises PeerGone when `gone`
+    is set or when the others do not arrive within `timeout_s`."""
+
+    def __init__(self, store, world: int, rank: int, timeout_s: float = 5.0):
+        self.store, self.world, self.rank, self.timeout_s = store, world, rank, timeout_s
+
+    def leave(self, why: str = "left") -> None:
+        self.store.set("gone", f"rank {self.rank}: {why}")
+
+    def enter(self, k: int) -> None:
+        import time
+        self.store.add(f"step/{k}", 1)
+        t_end = time.monotonic() + self.timeout_s
+        while True:
+            if self.store.check(["gone"]):
+                raise PeerGone(self.store.get("gone").decode())
+            if self.store.add(f"step/{k}", 0) >= self.world:
+                return
+            if time.monotonic() > t_end:
+                raise PeerGone(f"rank {self.rank}: peers did not reach step {k} within {self.timeout_s} s")
+            time.sleep(0.01)
+
+
+class Stack:
+    """The rank-local stack on one GPU (needs the CUDA library and torch.distributed when world > 1).
+
+    distinct_layers=False uploads one generated layer `cfg.layers` times (separate device copies, same bytes): the
+    benchmark's way to keep host-side generation short; timing and traffic are those of distinct layers."""
+
+    def __init__(self, cfg: StackConfig, world: int, rank: int, device: int, mode: str = "allreduce", distinct_layers: bool = True):
+        import torch
+
+        import arcinferzero_b200 as izb
+        self.izb, self.torch = izb, torch
+        self.cfg, self.world, self.rank, self.device, self.mode = cfg, world, rank, device, mode
+        assert mode in ("allreduce", "rs_quant_ag")
+        self.plan = shard_plan(cfg, world, rank)
+        self.layers = []
+        sh = None
+        for li in range(cfg.layers):
+            if sh is None or distinct_layers:
+                sh = shard_rows(cfg, layer_weights(cfg, li), self.plan)
+            self.layers.append({k: izb.Weight(cfg.qtype, rows, N, K, device=device, col_range=cr) for k, (rows, N, K, cr) in sh.items()})
+        self.comm = izb.TpComm(world, rank, device)
+        T, E = cfg.tokens, cfg.hidden
+        dev = torch.device("cuda", device)
+        f32, i8 = torch.float32, torch.int8
+        self.x = torch.empty((T, E), dtype=f32, device=dev)
+        self.part = torch.empty((T, E), dtype=f32, device=dev)
+        self.qkv = torch.empty((T, self.plan.qkv_rows), dtype=f32, device=dev)
+        nf = self.plan.ffn[1] - self.plan.ffn[0]
+        self.h = torch.empty((T, nf), dtype=f32, device=dev)
+        kmax = max(E, nf)
+        self.aq = torch.empty((T * kmax,), dtype=i8, device=dev)
+        self.asc = torch.empty((T * (kmax // 32),), dtype=f32, device=dev)
+        self.xq = torch.empty((T, E), dtype=i8, device=dev)       # quantised residual stream (input of QKV / gate / up)
+        self.xsc = torch.empty((E // 32, T), dtype=f32, device=dev)
+
+    def _quant(self, src, K):
+        T = self.cfg.tokens
+        aq = self.aq[:T * K].view(T, K)
+        asc = self.asc[:T * (K // 32)].view(K // 32, T)
+        self.izb.quantize_act(src, Mp=T, out=(aq, asc, None))
+        return aq, asc
+
+    def _sum(self, layer_out_of: str):
+        """Row-parallel partials in self.part -> residual stream; leaves the quantised stream in xq / xsc."""
+        izb, T = self.izb, self.cfg.tokens
+        if self.mode == "allreduce":
+            self.comm.allreduce_rows(self.x, self.part)
+            izb.quantize_act(self.x, Mp=T, out=(self.xq, self.xsc, None))
+        else:
+            own = T // self.world
+            xs = self.x[self.rank * own:(self.rank + 1) * own]
+            self.comm.reduce_quant_gather(self.x, self.part, self.xq, self.xsc, xsum=xs)
+
+    def set_input(self, x):
+        self.x.copy_(x)
+        self.izb.quantize_act(self.x, Mp=self.cfg.tokens, out=(self.xq, self.xsc, None))
+
+    def forward(self, trace: list | None = None):
+        """One pass over all layers.  `trace` (tests only) receives per layer a dict of copies of every stage's output, so
+        that each stage can be checked against the oracle from the stage before it."""
+        izb, T = self.izb, self.cfg.tokens
+        nq = self.plan.q[1] - self.plan.q[0]
+        for L in self.layers:
+            t = {} if trace is not None else None
+            if t is not None:
+                t["xq0"], t["xsc0"] = self.xq.clone(), self.xsc.clone()
+            izb.matmul(L["qkv"], self.xq, self.xsc, T, out=self.qkv)
+            aq, asc = self._quant(self.qkv[:, :nq], nq)
+            izb.matmul(L["o"], aq, asc, T, out=self.part)
+            if t is not None:
+                t["qkv"], t["o_part"], t["x0"] = self.qkv.clone(), self.part.clone(), self.x.clone()
+            self._sum("o")
+            if t is not None:
+                t["x1"], t["xq1"], t["xsc1"] = self.x.clone(), self.xq.clone(), self.xsc.clone()
+            izb.matmul(L["gate"], self.xq, self.xsc, T, out=self.h)
+            izb.matmul(L["up"], self.xq, self.xsc, T, out=self.h, acc=2)
+            aq, asc = self._quant(self.h, self.h.shape[1])
+            izb.matmul(L["down"], aq, asc, T, out=self.part)
+            if t is not None:
+                t["h"], t["down_part"] = self.h.clone(), self.part.clone()
+            self._sum("down")
+            if t is not None:
+                t["x2"], t["xq2"], t["xsc2"] = self.x.clone(), self.xq.clone(), self.xsc.clone()
+                trace.append(t)
+        return self.x
+
+    def close(self):
+        for L in self.layers:
+            for w in L.values():
+                w.close()
+        self.comm.close()

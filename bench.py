@@ -57,7 +57,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -170,6 +170,50 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str) -> list:
     return out
 
 
+def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens: int, passes: int = 2) -> list:
+    """BASELINE.json config 5: the projections of 8 dense layers (Q4_K, hidden 5120, FFN 17408, 7168 QKV rows) over 32768
+    token rows, split over the ranks as the reference's tensor-parallel mode splits them, in both summation modes of
+    arcinferzero_b200/tp.py.  Device-timed per pass, max over ranks."""
+    from arcinferzero_b200 import synth as S
+    from arcinferzero_b200 import tp
+    cfg = tp.StackConfig(tokens=tokens)
+    x_in = torch.from_numpy(S.make_act(cfg.tokens, cfg.hidden, SEED + 5)).cuda() * 0.05
+    out = []
+    for mode in ("allreduce", "rs_quant_ag"):
+        st = tp.Stack(cfg, world, rank, local, mode=mode, distinct_layers=False)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ms = 0.0
+        l0 = 0
+        for p in range(1 + passes):
+            st.set_input(x_in)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            if p == 1:
+                l0 = izb.launch_count()
+            e0.record()
+            st.forward()
+            e1.record()
+            torch.cuda.synchronize()
+            if p >= 1:
+                ms += e0.elapsed_time(e1)
+        launches = izb.launch_count() - l0
+        t = torch.tensor([ms / passes], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_pass = float(t.item())
+        finite = bool(torch.isfinite(st.x[rank * (cfg.tokens // world):(rank + 1) * (cfg.tokens // world)]).all().item())
+        nbytes = cfg.tokens * cfg.hidden * 4
+        out.append({"mode": mode, "ms_per_pass": ms_pass, "tokens_per_s": cfg.tokens / (ms_pass * 1e-3),
+                    "tops_all_ranks": cfg.ops_per_pass / (ms_pass * 1e-3) / 1e12, "sums_per_pass": 2 * cfg.layers,
+                    "bytes_per_sum_f32": nbytes, "gpu_launches_per_pass": launches // passes, "finite": finite,
+                    "workload": f"config 5: {cfg.layers} layers x (QKV 7168, O, gate, up, down) Q4_K, T={cfg.tokens}, hidden 5120, FFN 17408"})
+        st.close()
+        del st
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
@@ -197,6 +241,10 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemv", action="store_true", help="skip the decode GEMV section (BASELINE.json config 3)")
+    ap.add_argument("--gemv-only", action="store_true", help="profiling only: run just the decode GEMV section")
+    ap.add_argument("--tp-stack", action="store_true", help="also run the tensor-parallel projection stack (config 5); default when --gpus > 1")
+    ap.add_argument("--no-tp-stack", action="store_true")
+    ap.add_argument("--tp-tokens", type=int, default=32768, help="profiling only: token rows of the stack section")
     ap.add_argument("--tokens", type=int, default=M, help="profiling only: fewer token rows than the configured 8192")
     args = ap.parse_args()
     if args.tokens != M:
@@ -217,6 +265,10 @@ def main() -> None:
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (the library has no CPU path)"
     torch.cuda.set_device(local)
+    if args.gemv_only:
+        hbm, _, _, src = peaks()
+        print(json.dumps({"decode_gemv": gemv_section(izb, torch, hbm, src)}), flush=True)
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
@@ -285,6 +337,12 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_e2e = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
+    tp_stack = None
+    if (args.tp_stack or world > 1) and not args.no_tp_stack:
+        W.close()
+        del x, aq, asc, out
+        torch.cuda.empty_cache()
+        tp_stack = tp_stack_section(izb, torch, dist, world, rank, local, args.tp_tokens)
     status = izb.device_status(local)
 
     if rank == 0:
@@ -312,6 +370,8 @@ def main() -> None:
             "e2e": {"value": M / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * Nr * 4},
             "gpu_launches": launches, "clocks": clocks, "device_wait_errors": status,
         }
+        if tp_stack is not None:
+            line["tp_stack"] = tp_stack
         if not args.no_gemv and world == 1:
             line["decode_gemv"] = gemv_section(izb, torch, hbm, src)
         if not args.no_cpu_baseline and world == 1:

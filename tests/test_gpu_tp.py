@@ -1,0 +1,36 @@
+"""Tensor-parallel stack on GPUs: one rank in-process, and all visible GPUs (2..8) as torch.distributed.run children with
+NCCL.  Every stage is checked against the oracle inside tests/tp_gpu_worker.py."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+pytestmark = pytest.mark.gpu
+
+
+def test_stack_one_rank(izb):
+    sys.path.insert(0, HERE)
+    import tp_gpu_worker as W
+    for mode in ("allreduce", "rs_quant_ag"):
+        W.check_mode(mode, 1, 0, 0)
+
+
+def test_stack_all_visible_gpus(izb):
+    import torch
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("one GPU visible: the multi-rank run needs at least two")
+    n = 1 << (n.bit_length() - 1)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "tp_gpu_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_WORKER_OK") == 2 * n, r.stdout[-3000:]

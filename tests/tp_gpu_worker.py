@@ -1,0 +1,111 @@
+"""One rank of the tensor-parallel GPU check (run in-process for one GPU, under torch.distributed.run for several).
+
+Runs arcinferzero_b200.tp.Stack on a small configuration in both summation modes and checks every stage against the
+oracle from the stage before it: column-parallel outputs, row-parallel partial outputs, the summed residual stream
+(x += sum of partials in rank order, zero/kernels/tp.cl:5-11) and the quantised stream every rank must hold identically."""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+from arcinferzero_b200 import synth as S  # noqa: E402
+from arcinferzero_b200 import tp  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+TOL = 1e-5
+
+
+def relerr(a, b) -> float:
+    return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))) / max(1e-30, np.max(np.abs(b))))
+
+
+def silu_mul(g, u):
+    g = g.astype(np.float32)
+    return (u.astype(np.float32) * (g / (np.float32(1) + np.exp(-g, dtype=np.float32)))).astype(np.float32)
+
+
+def gather(t, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return [t.cpu().numpy()]
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t.contiguous())
+    return [o.cpu().numpy() for o in out]
+
+
+def check_mode(mode: str, world: int, rank: int, device: int) -> None:
+    import torch
+    cfg = tp.StackConfig(layers=2, tokens=256, hidden=512, q_rows=512, kv_rows=256, ffn=1024, seed=4242)
+    QT, E, T = cfg.qtype, cfg.hidden, cfg.tokens
+    st = tp.Stack(cfg, world, rank, device, mode=mode)
+    x_in = (S.make_act(T, E, cfg.seed) * np.float32(0.1)).astype(np.float32)
+    st.set_input(torch.from_numpy(x_in).cuda(device))
+    trace = []
+    st.forward(trace)
+    torch.cuda.synchronize()
+    plan = st.plan
+    own = T // world
+    mine = slice(rank * own, (rank + 1) * own) if mode == "rs_quant_ag" else slice(0, T)
+    nq = plan.q[1] - plan.q[0]
+    for li, t in enumerate(trace):
+        sh = tp.shard_rows(cfg, tp.layer_weights(cfg, li), plan)
+        n = {k: v.cpu().numpy() for k, v in t.items()}
+        # column-parallel QKV from the quantised stream all ranks share
+        ref = O.matmul(QT, sh["qkv"][0], E, n["xq0"], n["xsc0"], T)
+        assert relerr(n["qkv"], ref) <= TOL, (mode, li, "qkv", relerr(n["qkv"], ref))
+        # row-parallel O from this rank's Q columns
+        hq, hsc, _ = O.quantize_act(np.ascontiguousarray(n["qkv"][:, :nq]))
+        rows, _, K, cr = sh["o"]
+        ref = O.matmul(QT, tp.slice_cols(QT, rows, K, *cr), nq, hq, hsc, T)
+        assert relerr(n["o_part"], ref) <= TOL, (mode, li, "o_part")
+        # the sum over ranks, added to the residual stream
+        parts = np.stack(gather(t["o_part"], world))
+        x1_ref = O.tp_add(n["x0"], parts)
+        assert relerr(n["x1"][mine], x1_ref[mine]) <= TOL, (mode, li, "x1", relerr(n["x1"][mine], x1_ref[mine]))
+        # every rank holds the same quantised stream, and it is the quantiser applied to the summed rows
+        for key in ("xq1", "xsc1"):
+            g = gather(t[key], world)
+            assert all(np.array_equal(g[0], gi) for gi in g[1:]), (mode, li, key, "differs between ranks")
+        aq, asc, _ = O.quantize_act(np.ascontiguousarray(n["x1"][mine]))
+        assert np.array_equal(n["xq1"][mine], aq), (mode, li, "xq1")
+        assert np.array_equal(n["xsc1"][:, mine], asc), (mode, li, "xsc1")
+        # FFN: gate / up (SwiGLU store mode) and down
+        rows_g, _, K, _ = sh["gate"]
+        h_ref = silu_mul(O.matmul(QT, rows_g, K, n["xq1"], n["xsc1"], T), O.matmul(QT, sh["up"][0], K, n["xq1"], n["xsc1"], T))
+        assert relerr(n["h"], h_ref) <= TOL, (mode, li, "h", relerr(n["h"], h_ref))
+        hq, hsc, _ = O.quantize_act(n["h"])
+        rows, _, K, cr = sh["down"]
+        ref = O.matmul(QT, tp.slice_cols(QT, rows, K, *cr), cr[1] - cr[0], hq, hsc, T)
+        assert relerr(n["down_part"], ref) <= TOL, (mode, li, "down_part")
+        parts = np.stack(gather(t["down_part"], world))
+        x2_ref = O.tp_add(n["x1"], parts)
+        assert relerr(n["x2"][mine], x2_ref[mine]) <= TOL, (mode, li, "x2")
+        for key in ("xq2", "xsc2"):
+            g = gather(t[key], world)
+            assert all(np.array_equal(g[0], gi) for gi in g[1:]), (mode, li, key, "differs between ranks")
+    st.close()
+
+
+def main() -> int:
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    try:
+        for mode in ("allreduce", "rs_quant_ag"):
+            check_mode(mode, world, rank, local)
+            print(f"TP_WORKER_OK mode={mode} rank={rank}/{world}", flush=True)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

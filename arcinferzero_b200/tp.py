@@ -71,16 +71,36 @@ def shard_plan(cfg: StackConfig, world: int, rank: int) -> ShardPlan:
                      ffn=tp_range(cfg.ffn, 256, world, rank))
 
 
+def condition_weight(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:
+    """Rescale the fp16 super-scales of generated rows in place so that a stack without normalisation layers stays finite:
+    zero-mean weights with a root-mean-square of 1/sqrt(K) (each projection then keeps the magnitude of its input).
+    The generator's Q4_K weights d*sc*q - dmin*mn have mean ~1 and rms ~1.8; dmin is raised by 7.5 (= mean q) to centre
+    them, then both scales shrink by 1/(1.77*sqrt(K)).  Bit layout and integer fields are untouched."""
+    n = rows.shape[0]
+    f = np.float32(1.0 / (1.77 * np.sqrt(K)))
+    if qtype == S.GGML_Q4_K:
+        v = rows.reshape(n, K // 256, 144)
+        dd = np.ascontiguousarray(v[:, :, :4]).view(np.float16).astype(np.float32)
+        dd[:, :, 0] *= f
+        dd[:, :, 1] *= np.float32(7.5) * f
+        v[:, :, :4] = dd.astype(np.float16).view(np.uint8).reshape(n, K // 256, 4)
+    else:
+        v = rows.reshape(n, K // 32, 34)
+        d = np.ascontiguousarray(v[:, :, :2]).view(np.float16).astype(np.float32) * (f * np.float32(1.77 / 0.85))
+        v[:, :, :2] = d.astype(np.float16).view(np.uint8).reshape(n, K // 32, 2)
+    return rows
+
+
 def layer_weights(cfg: StackConfig, layer: int) -> dict[str, np.ndarray]:
     """Full (unsplit) GGUF rows of one layer, seeded per tensor."""
     s = cfg.seed + 100 * layer
-    E = cfg.hidden
+    E, qt = cfg.hidden, cfg.qtype
     return {
-        "qkv": S.make_weight(cfg.qtype, cfg.q_rows + 2 * cfg.kv_rows, E, s + 1),
-        "o": S.make_weight(cfg.qtype, E, cfg.q_rows, s + 2),
-        "gate": S.make_weight(cfg.qtype, cfg.ffn, E, s + 3),
-        "up": S.make_weight(cfg.qtype, cfg.ffn, E, s + 4),
-        "down": S.make_weight(cfg.qtype, E, cfg.ffn, s + 5),
+        "qkv": condition_weight(qt, S.make_weight(qt, cfg.q_rows + 2 * cfg.kv_rows, E, s + 1), E),
+        "o": condition_weight(qt, S.make_weight(qt, E, cfg.q_rows, s + 2), cfg.q_rows),
+        "gate": condition_weight(qt, S.make_weight(qt, cfg.ffn, E, s + 3), E),
+        "up": condition_weight(qt, S.make_weight(qt, cfg.ffn, E, s + 4), E),
+        "down": condition_weight(qt, S.make_weight(qt, E, cfg.ffn, s + 5), cfg.ffn),
     }
 
 

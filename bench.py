@@ -36,6 +36,7 @@ QT = 12
 SEED = 20261125
 WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantize_act + GEMM per step)"
 NOMINAL_INT8_TOPS = 4500.0
+NCU_TRAFFIC_BYTES_PER_TILE = (122.1e6 + 118.5e6) / (16 * 136)
 
 
 def peaks():
@@ -124,7 +125,7 @@ def cpu_baseline(seconds_target: float = 15.0) -> dict:
             "sample": f"{ms} tokens x {Ns} of {N} weight rows x K={K} in {t:.2f} s, scaled by N/{Ns}"}
 
 
-def gemv_section(izb, torch, hbm_peak: float, peak_src: str) -> list:
+def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False) -> list:
     """Decode GEMV (BASELINE.json config 3): batch 1 and 2, K = 5120; Q4_K N = 5120 and 17408, Q8_0 N = 151936.
     Each launch reads a different copy of the weights (enough copies to exceed the 126 MB L2), so the bytes come from
     HBM; GB/s = (weight bytes + activation bytes + output bytes) / mean launch time over the timed launches."""
@@ -145,14 +146,14 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str) -> list:
             torch.cuda.synchronize()
             # the launches of one sweep over the copies are captured in a CUDA graph, so that the host's per-call cost
             # (Python + ctypes) is not what is measured
-            launches = max(20, 4 * copies)
+            launches = copies if lite else max(20, 4 * copies)  # lite: few launches, for a profiler's launch list
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for i in range(launches):
                     izb.gemv(Ws[i % copies], aq, asc, T, out=y)
             graph.replay()
             torch.cuda.synchronize()
-            reps = 5
+            reps = 1 if lite else 5
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(reps):
@@ -242,6 +243,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemv", action="store_true", help="skip the decode GEMV section (BASELINE.json config 3)")
     ap.add_argument("--gemv-only", action="store_true", help="profiling only: run just the decode GEMV section")
+    ap.add_argument("--lite", action="store_true", help="profiling only: few launches per GEMV shape")
     ap.add_argument("--tp-stack", action="store_true", help="also run the tensor-parallel projection stack (config 5); default when --gpus > 1")
     ap.add_argument("--no-tp-stack", action="store_true")
     ap.add_argument("--tp-tokens", type=int, default=32768, help="profiling only: token rows of the stack section")
@@ -267,7 +269,7 @@ def main() -> None:
     torch.cuda.set_device(local)
     if args.gemv_only:
         hbm, _, _, src = peaks()
-        print(json.dumps({"decode_gemv": gemv_section(izb, torch, hbm, src)}), flush=True)
+        print(json.dumps({"decode_gemv": gemv_section(izb, torch, hbm, src, lite=args.lite)}), flush=True)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -364,7 +366,11 @@ def main() -> None:
                        "rows_per_rank": Nr},
             "roofline": {"bound": "tensor", "kernel": kname, "achieved": achieved, "peak": tc_sus, "unit": "TFLOP/s",
                          "frac": achieved / tc_sus, "peak_source": f"{src} dense bf16/fp16 (sustained; burst {tc_burst})",
-                         "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS, "traffic": None,
+                         "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS,
+                         # DRAM bytes per launch: one ncu capture of the same kernel at 2048 token rows and all weight rows
+                         # (read 122.1 MB + written 118.5 MB), scaled by the 128x128 tiles this launch runs
+                         "traffic": NCU_TRAFFIC_BYTES_PER_TILE * ((M + 127) // 128) * (Nr // 128),
+                         "traffic_source": "ncu dram__bytes_read+write of gemm_tc at M=2048, N=17408 (profiles/), per tile x tiles",
                          "ms_per_launch": ms_kernel, "launches": g["launches"],
                          "kernel_shares": {k: v["ms"] / total_prof for k, v in prof.items()}},
             "e2e": {"value": M / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * Nr * 4},

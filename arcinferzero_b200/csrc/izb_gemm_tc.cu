@@ -10,20 +10,25 @@
 //     so the f32 accumulator holds it exactly (the verification mode reads these accumulators back and the tests
 //     compare them bit for bit with the CPU's int32 dots).  A kind::i8 accumulator would need an int->float
 //     conversion and a second multiply per element, which costs more than the slower fp16 MMA rate saves.
-//   * Q4_K:  tq += asc[m][b] * D_b   per block;   res = fma(d[n], tq, fma(-dmin[n], tmn, res))   per superblock
-//     with tmn = sum_b (asc*asum)[m][b] * mn[n][b] computed on the tensor cores too (kind::f16, bf16 operands: the f32
-//     activation factor split into three bf16 terms, mn exact in bf16), one K=32 MMA pair per superblock.
+//   * Q4_K:  tq += asc[m][b] * D_b   per block;   res = fma(d[n], tq, res)   per superblock.
+//     The min term  - sum_b (asc*asum)[m][b] * (dmin*mn)[n][b]  never touches the CUDA cores: it is one more GEMM on the
+//     tensor cores, accumulated over the whole of K in a fourth TMEM accumulator and read once per tile.  Both factors
+//     are f32 numbers, fed as bf16 triples (v = v1+v2+v3, u = u1+u2+u3, the six products that matter: v1u1, v1u2, v2u1,
+//     v1u3, v2u2, v3u1; u = -dmin*mn has 17 significant bits, so its split is exact, v is exact to 2^-24).  Those 48
+//     K-entries per superblock travel as a fifth "stage" through the same operand ring as the four fp16 stages.
 //   * Q8_0:  res += (asc[m][b] * d[n][b]) * D_b.
 //
 // CTA = one 128 (tokens, TMEM lanes) x 128 (weight rows, TMEM columns) output tile, 16 warps:
-//   warp 0      activation producer: cp.async.bulk of pre-swizzled fp16 tiles (made by act_prepare_kernel) into a
-//               5-deep ring;
-//   warp 3      weight producer: TMA (cp.async.bulk.tensor.2d) of the raw GGUF superblocks of 128 rows, double-buffered;
+//   warp 0      activation producer: cp.async.bulk of pre-swizzled operand tiles (made by act_prepare_kernel) into the
+//               operand ring;
+//   warp 3      weight producer: TMA (cp.async.bulk.tensor.2d) of the raw GGUF superblocks of 128 rows into a ring, and
+//               the tile's activation scales;
 //   warps 4-7   dequantisers: one thread per weight row, nibbles -> fp16 sc*q written in the 128-byte-swizzled K-major
-//               operand layout (3-deep ring), block scales / mins to shared memory;
-//   warp 2      builds the bf16 operand of the min-term MMA;
-//   warp 1      issues tcgen05.mma (one thread) into a ring of three 128-column accumulators + one for the min term;
-//   warps 8-15  combine: tcgen05.ld, one fma per element, final store with the reference's store modes.
+//               operand layout, the min-term operand, block scales to shared memory;
+//   warps 1-2   issue tcgen05.mma (one thread each, alternating stages) into a ring of three 128-column accumulators +
+//               the min-term accumulator (always warp 2, so that one thread orders all updates of it);
+//   warps 8-15  combine: tcgen05.ld of 64 columns at a time, one fma per element, final store with the reference's
+//               store modes.
 // All waits are bounded: a wait that gives up sets a CTA-wide abort flag and a device error word, the CTA drains and
 // returns without storing (izb_device_status reports it).
 #include <cuda.h>
@@ -42,66 +47,38 @@ int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* 
 namespace {
 
 constexpr int BM = 128, BN = 128, KS = 64;
-constexpr int NS = 4, NA = NS, NB = NS, ND1 = 3;  // operand stages (activations and weights share a ring position)
+constexpr int NS = 4, ND1 = 3;            // operand stages (activation and weight tile share a ring position), accumulators
 constexpr int STAGE_BYTES = BM * KS * 2;  // 16 KB: 128 rows x 128 B
 constexpr int kThreads = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr int OFF_A = 0;
-constexpr int OFF_B = OFF_A + NA * STAGE_BYTES;       // 81920
-constexpr int OFF_X = OFF_B + NB * STAGE_BYTES;       // 131072: Q4_K: A2 pair tile, B2 pair tile, raw[2], vsum[2], d/dmin ring
+constexpr int OFF_B = OFF_A + NS * STAGE_BYTES;      // 65536
+constexpr int OFF_RAW = OFF_B + NS * STAGE_BYTES;    // 131072: ring of raw superblock tiles
 constexpr int RAW_Q4 = 128 * 144, RAW_Q8 = 128 * 272;  // 18432, 34816
-constexpr int OFF_A2 = OFF_X, OFF_B2 = OFF_X + STAGE_BYTES;
-constexpr int OFF_RAW_Q4 = OFF_X + 2 * STAGE_BYTES;   // 163840
-constexpr int OFF_VS = OFF_RAW_Q4 + 2 * RAW_Q4;       // 200704
-constexpr int OFF_DM = OFF_VS + 2 * 4096;             // 208896: 4 x [2][128] f32
-constexpr int OFF_RAW_Q8 = OFF_X;                     // 131072
-constexpr int OFF_D8 = OFF_RAW_Q8 + 2 * RAW_Q8;       // 200704: 4 x [8][128] f32
+constexpr int NR_Q4 = 4, NR_Q8 = 2;                  // raw ring depth
+constexpr int OFF_DM = OFF_RAW + NR_Q4 * RAW_Q4;     // 204800: Q4_K: 4 x [128] f32 superblock scales d
+constexpr int OFF_D8 = OFF_RAW + NR_Q8 * RAW_Q8;     // 200704: Q8_0: 4 x [8][128] f32 block scales
 constexpr int NASC = 3;
-constexpr int OFF_ASC = 217088;                       // after the larger of the two maps: NASC x [8 blocks][128 rows] f32
-constexpr int OFF_BAR = OFF_ASC + NASC * 4096;        // 229376
-constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;     // barriers (+ debug counters) + alignment slack = 231424 <= 227 KB
+constexpr int OFF_ASC = 217088;                      // after the larger of the two maps: NASC x [8 blocks][128 rows] f32
+constexpr int OFF_BAR = OFF_ASC + NASC * 4096;       // 229376
+constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;    // barriers + alignment slack = 231424 <= 227 KB
+static_assert(OFF_DM + 4 * 512 <= OFF_ASC && OFF_D8 + 4 * 4096 <= OFF_ASC, "shared memory map");
 
 enum Bar {  // 8-byte mbarriers
   S_FULL = 0, S_EMPTY = S_FULL + NS, RAW_FULL = S_EMPTY + NS,  // S_*: one barrier per stage for both operand tiles
-  RAW_EMPTY = RAW_FULL + 2, D1_FULL = RAW_EMPTY + 2, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1, D2_EMPTY,
-  AB2_FULL, MINS_DONE = AB2_FULL + 2, ASC_FULL = MINS_DONE + 2, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
+  RAW_EMPTY = RAW_FULL + 4, D1_FULL = RAW_EMPTY + 4, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1,
+  ASC_FULL, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
 };
 static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
 
 // error-word codes (which wait gave up)
-enum : uint32_t { E_APROD = 1, E_WPROD = 2, E_DEQ = 4, E_PREP = 8, E_MMA = 16, E_EPI = 32 };
-#ifdef IZB_TC_STATS
-__device__ unsigned long long g_tc_wait[80];  // [72] = CTA cycles, [73] = CTAs
-#define STAT_T0() const long long stat_t0 = clock64()
-#define STAT_ADD(slot)                                                                                        \
-  do {                                                                                                        \
-    if ((threadIdx.x & 31) == 0) {                                                                            \
-      const unsigned long long dt__ = (unsigned long long)(clock64() - stat_t0);                              \
-      asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(bar0 + 384u + 8u * (slot)), "l"(dt__) : "memory");   \
-    }                                                                                                         \
-  } while (0)
-#define STAT_LAP_INIT() long long stat_lap = clock64()
-#define STAT_LAP(slot)                                                                                        \
-  do {                                                                                                        \
-    const long long now__ = clock64();                                                                        \
-    if (threadIdx.x == 256) {                                                                                 \
-      const unsigned long long dt__ = (unsigned long long)(now__ - stat_lap);                                 \
-      asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(bar0 + 384u + 8u * (slot)), "l"(dt__) : "memory");   \
-    }                                                                                                         \
-    stat_lap = clock64();                                                                                     \
-  } while (0)
-#else
-#define STAT_T0()
-#define STAT_ADD(slot)
-#define STAT_LAP_INIT()
-#define STAT_LAP(slot)
-#endif
+enum : uint32_t { E_APROD = 1, E_WPROD = 2, E_DEQ = 4, E_MMA = 16, E_EPI = 32 };
 
 struct TcParams {
-  const uint16_t* aimg;   // [tiles][K/64][128][64] fp16, rows 128-byte swizzled
-  const float* vsum;      // [tiles][K/32][128] f32 = asc * asum (Q4_K)
+  const uint16_t* aimg;   // [tiles][stages][128][64] 16-bit operand tiles, rows 128-byte swizzled; stages = K/64, and
+                          // for the Q4_K GEMM one bf16 min-term tile after every four (5 per superblock)
   const float* ascimg;    // [tiles][K/32][128] f32: the tile rows' activation scales, gathered
   const int32_t* tiles;   // grouped: [1 + 3*max_tiles]; dense: null
   const int32_t* rowmap;  // grouped gather of activation rows (slot -> token) or null
@@ -128,48 +105,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#ifdef IZB_EXP_HINT
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"((uint32_t)IZB_EXP_HINT)
-      : "memory");
-#else
   asm volatile(
       "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
 // Bounded wait.  false = gave up (or another thread did): the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
                                           uint32_t code) {
-#ifdef IZB_TC_STATS
-  // debug build: cycles every wait site spends blocked, summed per barrier (index = barrier number, +32 for the warp
-  // that builds the min-term operand) by lane 0 of each warp
-  const long long t0 = clock64();  // (try_wait itself may block for a while: time the first attempt too)
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) {
-      if ((threadIdx.x & 31) == 0) {  // shared-memory counters (flushed once per CTA): slot = barrier index, prep warp + 36
-        const uint32_t sa = (bar & ~511u) + 384u + 8u * (((bar & 511u) >> 3) + (code == E_PREP ? 36u : 0u));
-        const unsigned long long dt = (unsigned long long)(clock64() - t0);
-        asm volatile("red.shared.add.u64 [%0], %1;" ::"r"(sa), "l"(dt) : "memory");
-      }
-      return true;
-    }
-    if ((it & 255u) == 255u && *abort_flag) return false;
-  }
-#else
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef IZB_EXP_SLEEP
-    __nanosleep(IZB_EXP_SLEEP);
-#endif
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
-#endif
   *abort_flag = 1;
   atomicOr(err, code);
   return false;
@@ -209,31 +158,53 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// tcgen05.ld of 32 columns + wait, delivered as 16 register pairs (columns 2i, 2i+1) for the f32x2 arithmetic
-__device__ __forceinline__ void tc_ld32_pairs(uint32_t taddr, unsigned long long (&r)[16]) {
+// tcgen05.ld of 64 columns + wait, delivered as 32 register pairs (columns 2i, 2i+1) for the f32x2 arithmetic.  The
+// load, the wait and the moves are one asm block: nothing that uses the values can be scheduled before the wait.
+__device__ __forceinline__ void tc_ld64_pairs(uint32_t taddr, unsigned long long (&r)[32]) {
   asm volatile(
-      "{\n\t.reg .b32 t<32>;\n\t"
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {t0,t1,t2,t3,t4,t5,t6,t7,t8,t9,t10,t11,t12,t13,t14,t15,t16,t17,t18,t19,t20,t21,t22,t23,"
-      "t24,t25,t26,t27,t28,t29,t30,t31}, [%16];\n\t"
+      "{\n\t.reg .b32 t<64>;\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {t0,t1,t2,t3,t4,t5,t6,t7,t8,t9,t10,t11,t12,t13,t14,t15,t16,t17,t18,t19,t20,t21,t22,t23,t24,t25,t26,t27,t28,t29,t30,t31,t32,t33,t34,t35,t36,t37,t38,t39,t40,t41,t42,t43,t44,t45,t46,t47,t48,t49,t50,t51,t52,t53,t54,t55,t56,t57,t58,t59,t60,t61,t62,t63}, [%32];\n\t"
       "tcgen05.wait::ld.sync.aligned;\n\t"
-      "mov.b64 %0, {t0,t1};\n\tmov.b64 %1, {t2,t3};\n\tmov.b64 %2, {t4,t5};\n\tmov.b64 %3, {t6,t7};\n\t"
-      "mov.b64 %4, {t8,t9};\n\tmov.b64 %5, {t10,t11};\n\tmov.b64 %6, {t12,t13};\n\tmov.b64 %7, {t14,t15};\n\t"
-      "mov.b64 %8, {t16,t17};\n\tmov.b64 %9, {t18,t19};\n\tmov.b64 %10, {t20,t21};\n\tmov.b64 %11, {t22,t23};\n\t"
-      "mov.b64 %12, {t24,t25};\n\tmov.b64 %13, {t26,t27};\n\tmov.b64 %14, {t28,t29};\n\tmov.b64 %15, {t30,t31};\n\t}"
-      : "=l"(r[0]), "=l"(r[1]), "=l"(r[2]), "=l"(r[3]), "=l"(r[4]), "=l"(r[5]), "=l"(r[6]), "=l"(r[7]), "=l"(r[8]), "=l"(r[9]),
-        "=l"(r[10]), "=l"(r[11]), "=l"(r[12]), "=l"(r[13]), "=l"(r[14]), "=l"(r[15])
+      "mov.b64 %0, {t0,t1};\n\t"
+      "mov.b64 %1, {t2,t3};\n\t"
+      "mov.b64 %2, {t4,t5};\n\t"
+      "mov.b64 %3, {t6,t7};\n\t"
+      "mov.b64 %4, {t8,t9};\n\t"
+      "mov.b64 %5, {t10,t11};\n\t"
+      "mov.b64 %6, {t12,t13};\n\t"
+      "mov.b64 %7, {t14,t15};\n\t"
+      "mov.b64 %8, {t16,t17};\n\t"
+      "mov.b64 %9, {t18,t19};\n\t"
+      "mov.b64 %10, {t20,t21};\n\t"
+      "mov.b64 %11, {t22,t23};\n\t"
+      "mov.b64 %12, {t24,t25};\n\t"
+      "mov.b64 %13, {t26,t27};\n\t"
+      "mov.b64 %14, {t28,t29};\n\t"
+      "mov.b64 %15, {t30,t31};\n\t"
+      "mov.b64 %16, {t32,t33};\n\t"
+      "mov.b64 %17, {t34,t35};\n\t"
+      "mov.b64 %18, {t36,t37};\n\t"
+      "mov.b64 %19, {t38,t39};\n\t"
+      "mov.b64 %20, {t40,t41};\n\t"
+      "mov.b64 %21, {t42,t43};\n\t"
+      "mov.b64 %22, {t44,t45};\n\t"
+      "mov.b64 %23, {t46,t47};\n\t"
+      "mov.b64 %24, {t48,t49};\n\t"
+      "mov.b64 %25, {t50,t51};\n\t"
+      "mov.b64 %26, {t52,t53};\n\t"
+      "mov.b64 %27, {t54,t55};\n\t"
+      "mov.b64 %28, {t56,t57};\n\t"
+      "mov.b64 %29, {t58,t59};\n\t"
+      "mov.b64 %30, {t60,t61};\n\t"
+      "mov.b64 %31, {t62,t63};\n\t"
+      "}"
+      : "=l"(r[0]), "=l"(r[1]), "=l"(r[2]), "=l"(r[3]), "=l"(r[4]), "=l"(r[5]), "=l"(r[6]), "=l"(r[7]), "=l"(r[8]), "=l"(r[9]), "=l"(r[10]), "=l"(r[11]), "=l"(r[12]), "=l"(r[13]), "=l"(r[14]), "=l"(r[15]), "=l"(r[16]), "=l"(r[17]), "=l"(r[18]), "=l"(r[19]), "=l"(r[20]), "=l"(r[21]), "=l"(r[22]), "=l"(r[23]), "=l"(r[24]), "=l"(r[25]), "=l"(r[26]), "=l"(r[27]), "=l"(r[28]), "=l"(r[29]), "=l"(r[30]), "=l"(r[31])
       : "r"(taddr)
       : "memory");
 }
 // packed f32x2 arithmetic (two IEEE round-to-nearest operations per instruction)
 __device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
-#ifdef IZB_EXP_SCALAR_FMA
-  const float lo = fmaf(__uint_as_float((uint32_t)a), __uint_as_float((uint32_t)b), __uint_as_float((uint32_t)acc));
-  const float hi = fmaf(__uint_as_float((uint32_t)(a >> 32)), __uint_as_float((uint32_t)(b >> 32)), __uint_as_float((uint32_t)(acc >> 32)));
-  acc = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(hi) << 32);
-#else
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
-#endif
 }
 __device__ __forceinline__ unsigned long long fmul2(unsigned long long a, unsigned long long b) {
   unsigned long long r;
@@ -265,13 +236,16 @@ constexpr uint32_t kIdescBF16 = kIdescF16 | (1u << 7) | (1u << 10);
 __device__ __forceinline__ int q4k_perm8(int p) { return (p & 4) | ((p & 1) << 1) | ((p >> 1) & 1); }
 
 // ---------------------------------------------------------------------------------------------- activation pre-pass
-// Per 128-row tile: fp16 operand images (one 16 KB swizzled stage per 64 elements of K) and, for Q4_K, the min-term
-// factor vsum[b][r] = asc * (float)asum.  One thread per (row, 16-byte output chunk).
+// Per 128-row tile: fp16 operand images (one 16 KB swizzled stage per 64 elements of K), the tile's activation scales
+// and, with sps == 5 (the Q4_K GEMM), after every four stages one more 16 KB image: the min-term factor
+// v = asc * (float)asum of the superblock's eight blocks as three bf16 terms, laid out as the six 16-byte K-chunks
+// (v1, v1, v2, v1, v2, v3) x eight blocks that meet the weight side's (u1, u2, u1, u3, u2, u1).
+// One thread per (row, 16-byte output chunk).
 template <int QT>
 __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asc, int lda,
                                                           int K, int rows_total, const int32_t* __restrict__ tiles,
                                                           const int32_t* __restrict__ rowmap, uint16_t* __restrict__ aimg,
-                                                          float* __restrict__ vsum, float* __restrict__ ascimg, int want_vsum) {
+                                                          float* __restrict__ ascimg, int sps) {
   const int tile = blockIdx.y;
   int r0, nr;
   if (tiles) {
@@ -304,8 +278,9 @@ __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restri
     const __half2 h = __floats2half2_rn((float)a[e0], (float)a[e1]);
     o[i] = *reinterpret_cast<const uint32_t*>(&h);
   }
-  const size_t nstages = K / KS;
-  uint8_t* dst = reinterpret_cast<uint8_t*>(aimg) + ((size_t)tile * nstages + stage) * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+  const size_t nstages = (size_t)(K / 256) * sps;
+  uint8_t* tile_img = reinterpret_cast<uint8_t*>(aimg) + (size_t)tile * nstages * STAGE_BYTES;
+  uint8_t* dst = tile_img + ((size_t)(stage >> 2) * sps + (stage & 3)) * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
   *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
   if (asc) {  // (null in the block-dot verification mode: no scales are used)
     int s = a[0] + a[1] + a[2] + a[3] + a[4] + a[5] + a[6] + a[7];
@@ -315,7 +290,18 @@ __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restri
       const int b = ch >> 2;
       const float sc = src >= 0 ? asc[(size_t)b * lda + src] : 0.0f;
       ascimg[((size_t)tile * (K / 32) + b) * BM + r] = sc;
-      if (QT == IZB_Q4_K && want_vsum) vsum[((size_t)tile * (K / 32) + b) * BM + r] = __fmul_rn(sc, (float)s);
+      if (QT == IZB_Q4_K && sps == 5) {
+        const float v = __fmul_rn(sc, (float)s);
+        const __nv_bfloat16 h1 = __float2bfloat16_rn(v);
+        const float r1 = __fsub_rn(v, __bfloat162float(h1));
+        const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+        const __nv_bfloat16 h3 = __float2bfloat16_rn(__fsub_rn(r1, __bfloat162float(h2)));
+        uint8_t* row = tile_img + ((size_t)(b >> 3) * 5 + 4) * STAGE_BYTES + r * 128 + 2 * (b & 7);
+        const unsigned short t3[3] = {__bfloat16_as_ushort(h1), __bfloat16_as_ushort(h2), __bfloat16_as_ushort(h3)};
+        constexpr int term[6] = {0, 0, 1, 0, 1, 2};
+#pragma unroll
+        for (int k = 0; k < 6; ++k) *reinterpret_cast<unsigned short*>(row + ((k ^ (r & 7)) << 4)) = t3[term[k]];
+      }
     }
   }
 }
@@ -345,39 +331,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     r0 = tile * BM;
     nr = min(BM, p.M - r0);
   }
-#ifdef IZB_TC_STATS
-  const long long t_cta = clock64();
-#endif
   const int n0 = blockIdx.x * BN;
-  const int nsb = p.K >> 8, nb = p.K >> 5, nstages = p.K / KS;
+  const int nsb = p.K >> 8, nb = p.K >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int SBB = QT == IZB_Q4_K ? 144 : 272;
   constexpr int RAW = QT == IZB_Q4_K ? RAW_Q4 : RAW_Q8;
-  constexpr int OFF_RAW = QT == IZB_Q4_K ? OFF_RAW_Q4 : OFF_RAW_Q8;
+  constexpr int NR = QT == IZB_Q4_K ? NR_Q4 : NR_Q8;
   constexpr bool kMins = QT == IZB_Q4_K && !kDots;
+  constexpr int SPS = kMins ? 5 : 4;  // operand stages per superblock: four of 64 K-elements (+ the min-term stage)
+  const int nstages = SPS * nsb;
 
-#ifdef IZB_TC_STATS
-  if (threadIdx.x < 80) reinterpret_cast<unsigned long long*>(smem + OFF_BAR + 384)[threadIdx.x] = 0ull;
-#endif
   if (threadIdx.x == 0) {
     // S_FULL: the activation producer's expect_tx arrival + the four dequantiser warps; S_EMPTY: one tcgen05.commit
     for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), 5); mbar_init(bar(S_EMPTY + i), 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(RAW_FULL + i), 1);
-      mbar_init(bar(RAW_EMPTY + i), kMins ? 5 : 4);
-      mbar_init(bar(AB2_FULL + i), 5);
-      mbar_init(bar(MINS_DONE + i), 1);
-    }
+    for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), 4); }
     for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 8); }
     mbar_init(bar(D2_FULL), 1);
-    mbar_init(bar(D2_EMPTY), 8);
     for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (kMins) {  // the padding chunks of the min-term operands stay zero for the whole kernel
-    for (int i = threadIdx.x; i < 2 * STAGE_BYTES / 16; i += kThreads) reinterpret_cast<uint4*>(smem + OFF_A2)[i] = make_uint4(0, 0, 0, 0);
-    fence_proxy_async();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
@@ -393,126 +365,77 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     // Every role loop below is executed by its whole warp (uniform waits, lane 0 issues), so no lane of a role warp
     // sits at the final CTA barrier while another lane of the same warp is still working.
     if (warp == 0) {
-      // ================= activation producer
+      // ================= activation producer: the tile's stage images lie back to back in global memory
       const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
+      int sa = 0, pa = 1;
       for (int g = 0; g < nstages; ++g) {
-        const int sa = g & (NS - 1);
-        if (!mbar_wait(bar(S_EMPTY + sa), ((g / NS) & 1) ^ 1, abort_flag, p.err, E_APROD)) break;
-#ifdef IZB_EXP_NO_ATMA
-        if (lane == 0) mbar_arrive(bar(S_FULL + sa));
-#else
+        if (!mbar_wait(bar(S_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) break;
         if (lane == 0) {
           mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
           bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
         }
-#endif
         __syncwarp();
+        if (++sa == NS) { sa = 0; pa ^= 1; }
       }
     } else if (warp == 3) {
-      // ================= weight producer (TMA of the raw superblocks, scales) and, one superblock behind, the min-term
-      // activation operand: vsum (f32) -> three bf16 terms, swizzled K-major half tile
+      // ================= weight producer: TMA of the raw superblocks of the tile's 128 weight rows, and per superblock the
+      // 8 x 128 activation scales the combine warps need
       const int wrow = expert * p.N + n0;
-      int sq = 0, pq = 1;
-      for (int s = 0; s <= nsb; ++s) {
-        if (s < nsb) {
-          const int rb = s & 1;
-          if (!mbar_wait(bar(RAW_EMPTY + rb), ((s >> 1) & 1) ^ 1, abort_flag, p.err, E_WPROD)) break;
-          if (lane == 0) {
-            mbar_expect_tx(bar(RAW_FULL + rb), RAW + (kMins ? 4096 : 0));
-            tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
-            if (kMins)
-              bulk_g2s(smem_u32(smem + OFF_VS + rb * 4096), p.vsum + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(RAW_FULL + rb));
-          }
-          if (!kDots) {  // the superblock's activation scales for the combine warps
-            if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, E_WPROD)) break;
-            if (lane == 0) {
-              mbar_expect_tx(bar(ASC_FULL + sq), 4096);
-              bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
-            }
-            if (++sq == NASC) { sq = 0; pq ^= 1; }
-          }
-          __syncwarp();
+      int rb = 0, pr = 1, sq = 0, pq = 1;
+      for (int s = 0; s < nsb; ++s) {
+        if (!mbar_wait(bar(RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) break;
+        if (lane == 0) {
+          mbar_expect_tx(bar(RAW_FULL + rb), RAW);
+          tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
         }
-        if (kMins && s > 0) {
-          const int sp = s - 1, rb = sp & 1, h = sp & 1, u = sp >> 1;
-          if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_PREP)) break;
-          if (!mbar_wait(bar(MINS_DONE + h), (u & 1) ^ 1, abort_flag, p.err, E_PREP)) break;
-          const float* vs = reinterpret_cast<const float*>(smem + OFF_VS + rb * 4096);
-#pragma unroll 1
-          for (int i = 0; i < 4; ++i) {
-            const int r = lane + 32 * i;
-            unsigned char* row = smem + OFF_A2 + r * 128;
-#pragma unroll 1
-            for (int half8 = 0; half8 < 2; ++half8) {  // blocks 4*half8 .. 4*half8+3 -> two of the four words of each chunk
-              uint32_t w3[2][3] = {{0, 0, 0}, {0, 0, 0}};
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const float v = vs[(4 * half8 + k) * BM + r];
-                const __nv_bfloat16 h1 = __float2bfloat16_rn(v);
-                const float r1 = __fsub_rn(v, __bfloat162float(h1));
-                const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
-                const float r2 = __fsub_rn(r1, __bfloat162float(h2));
-                const __nv_bfloat16 h3 = __float2bfloat16_rn(r2);
-                w3[k >> 1][0] |= (uint32_t)__bfloat16_as_ushort(h1) << (16 * (k & 1));
-                w3[k >> 1][1] |= (uint32_t)__bfloat16_as_ushort(h2) << (16 * (k & 1));
-                w3[k >> 1][2] |= (uint32_t)__bfloat16_as_ushort(h3) << (16 * (k & 1));
-              }
-#pragma unroll
-              for (int part = 0; part < 3; ++part)
-                *reinterpret_cast<uint2*>(row + (((4 * h + part) ^ (r & 7)) << 4) + 8 * half8) = make_uint2(w3[0][part], w3[1][part]);
-            }
-          }
-          fence_proxy_async();
-          __syncwarp();
+        if (++rb == NR) { rb = 0; pr ^= 1; }
+        if (!kDots) {
+          if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, E_WPROD)) break;
           if (lane == 0) {
-            mbar_arrive(bar(AB2_FULL + h));
-            mbar_arrive(bar(RAW_EMPTY + rb));
+            mbar_expect_tx(bar(ASC_FULL + sq), 4096);
+            bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
           }
+          if (++sq == NASC) { sq = 0; pq ^= 1; }
         }
+        __syncwarp();
       }
     } else {
-      // ================= MMA issuers: warp 1 takes the even stages, warp 2 the odd ones (and the min-term MMA of every
-      // superblock).  A stage is two 32-blocks, each into its own accumulator buffer: two MMAs (K = 16) + one commit.
-      // Two issuers because what a thread pays per block -- barrier polls and commits between MMAs -- is longer than
-      // the 128 cycles the two MMAs run.
+      // ================= MMA issuers.  Of a superblock's stages 0..3 (two 32-blocks each, every block into its own
+      // accumulator buffer: two MMAs of K = 16 + one commit) warp 1 takes 0 and 2, warp 2 takes 1, 3 and the min-term stage 4
+      // (three bf16 MMAs of K = 16 accumulated into the fourth TMEM buffer over the whole of K).  Two issuers because
+      // what a thread pays per block -- barrier polls and commits between MMAs -- is longer than the 128 cycles the two
+      // MMAs run; one issuer for the min term so that its accumulator is updated in program order.
       bool ok = true;
-      for (int g = warp - 1; g < nstages && ok; g += 2) {
-        const int sa = g & (NS - 1);
-        if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, E_MMA)) break;
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sa * STAGE_BYTES);
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          const int j = 2 * g + blk, d = j % ND1;
-          if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+      for (int s = 0; s < nsb && ok; ++s) {
+        for (int t = warp - 1; t < (warp == 1 ? 4 : SPS) && ok; t += (t == 3 ? 1 : 2)) {
+          const int g = SPS * s + t, sa = g % NS;
+          if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t dt = tmem_base + (uint32_t)(d * BN);
+          const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sa * STAGE_BYTES);
+          if (t < 4) {
 #pragma unroll
-#ifndef IZB_EXP_NO_MMA
-            for (int k16 = 0; k16 < 2; ++k16)
-              tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
-#endif
-            tc_commit(bar(D1_FULL + d));
+            for (int blk = 0; blk < 2; ++blk) {
+              const int j = 8 * s + 2 * t + blk, d = j % ND1;
+              if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+              tc_fence_after();
+              if (lane == 0) {
+                const uint32_t dt = tmem_base + (uint32_t)(d * BN);
+#pragma unroll
+                for (int k16 = 0; k16 < 2; ++k16)
+                  tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
+                tc_commit(bar(D1_FULL + d));
+              }
+              __syncwarp();
+            }
+            if (!ok) break;
+          } else if (lane == 0) {
+#pragma unroll
+            for (int k16 = 0; k16 < 3; ++k16)
+              tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a_addr + k16 * 32), umma_desc(b_addr + k16 * 32), kIdescBF16, (s | k16) ? 1u : 0u);
           }
-          __syncwarp();
-        }
-        if (!ok) break;
-        if (lane == 0) tc_commit(bar(S_EMPTY + sa));
-        __syncwarp();
-        if (kMins && (g & 3) == 3) {
-          const int s = g >> 2, h = s & 1, u = s >> 1;
-          ok = mbar_wait(bar(AB2_FULL + h), u & 1, abort_flag, p.err, E_MMA) &&
-               mbar_wait(bar(D2_EMPTY), (s & 1) ^ 1, abort_flag, p.err, E_MMA);
-          if (!ok) break;
-          tc_fence_after();
           if (lane == 0) {
-            const uint32_t a2 = smem_u32(smem + OFF_A2) + 64 * h, b2 = smem_u32(smem + OFF_B2) + 64 * h;
-#pragma unroll
-            for (int k16 = 0; k16 < 2; ++k16)
-              tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a2 + k16 * 32), umma_desc(b2 + k16 * 32), kIdescBF16, k16);
-            tc_commit(bar(D2_FULL));
-            tc_commit(bar(MINS_DONE + h));
+            tc_commit(bar(S_EMPTY + sa));
+            if (kMins && t == 4 && s == nsb - 1) tc_commit(bar(D2_FULL));
           }
           __syncwarp();
         }
@@ -524,55 +447,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     const int t = threadIdx.x - 128;
     bool ok = true;
     int sbq = 0, pbq = 1;  // operand ring position and wait parity
+    int rb = 0, pr = 0;    // raw ring
     for (int s = 0; s < nsb && ok; ++s) {
-      const int rb = s & 1, u = s >> 1;
-      if (!mbar_wait(bar(RAW_FULL + rb), u & 1, abort_flag, p.err, E_DEQ)) break;
+      if (!mbar_wait(bar(RAW_FULL + rb), pr, abort_flag, p.err, E_DEQ)) break;
       const unsigned char* rrow = smem + OFF_RAW + rb * RAW + t * SBB;
       const uint4 hdr = *reinterpret_cast<const uint4*>(rrow);
       const uint32_t s3[3] = {hdr.y, hdr.z, hdr.w};
       if (QT == IZB_Q4_K) {
-        if (kMins) {
-          float* dm = reinterpret_cast<float*>(smem + OFF_DM + (s & 3) * 1024);
-          dm[t] = half_bits_to_float(hdr.x & 0xFFFFu);
-          dm[128 + t] = half_bits_to_float(hdr.x >> 16);
-          const int h = s & 1;
-          if (!mbar_wait(bar(MINS_DONE + h), (u & 1) ^ 1, abort_flag, p.err, E_DEQ)) break;
-          uint32_t m4[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            int sc0, mn0, sc1, mn1;
-            q4k_scale_min(s3, 2 * k, sc0, mn0);
-            q4k_scale_min(s3, 2 * k + 1, sc1, mn1);
-            m4[k] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)mn0)) |
-                    ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn((float)mn1)) << 16);
-          }
-          unsigned char* row = smem + OFF_B2 + t * 128;
-#pragma unroll
-          for (int k = 0; k < 3; ++k) *reinterpret_cast<uint4*>(row + (((4 * h + k) ^ (t & 7)) << 4)) = make_uint4(m4[0], m4[1], m4[2], m4[3]);
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(AB2_FULL + h));
-        }
+        if (kMins) reinterpret_cast<float*>(smem + OFF_DM + (s & 3) * 512)[t] = half_bits_to_float(hdr.x & 0xFFFFu);
       } else {
         float* d8 = reinterpret_cast<float*>(smem + OFF_D8 + (s & 3) * 4096);
         const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
 #pragma unroll
         for (int b = 0; b < 8; ++b) d8[b * 128 + t] = half_bits_to_float((b & 1) ? hw[b >> 1] >> 16 : hw[b >> 1] & 0xFFFFu);
       }
-#pragma unroll 1  // (rolled on purpose: with the four role loops resident at once, code size costs more than the loop)
+#pragma unroll 1  // (rolled on purpose: with the role loops resident at once, code size costs more than the loop)
       for (int c = 0; c < 4; ++c) {
         if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) { ok = false; break; }
-        STAT_T0();
         unsigned char* orow = smem + OFF_B + sbq * STAGE_BYTES + t * 128;
-#ifdef IZB_EXP_NO_DEQ
-        if (false) {
-#else
         if (QT == IZB_Q4_K) {
-#endif
           const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c), q1 = *reinterpret_cast<const uint4*>(rrow + 32 + 32 * c);
           const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-          // the chunk's two 6-bit sub-block scales (static indices: the chunk loop is unrolled), as half2 pairs
-          // (sc, sc) and (-1024 sc, -1024 sc): 0x6400 | sc is the fp16 number 1024 + sc
+          // the chunk's two 6-bit sub-block scales as half2 pairs (sc, sc) and (-1024 sc, -1024 sc): 0x6400 | sc is the
+          // fp16 number 1024 + sc
           int sc_lo = 1, sc_hi = 1, mn_unused;
           if (!kDots) {
             q4k_scale_min(s3, 2 * c, sc_lo, mn_unused);
@@ -595,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             *reinterpret_cast<uint4*>(orow + (((4 + jj) ^ (t & 7)) << 4)) =
                 make_uint4(cvt(w0, 4, shi, nhi), cvt(w0, 12, shi, nhi), cvt(w1, 4, shi, nhi), cvt(w1, 12, shi, nhi));
           }
-        } else if (QT == IZB_Q8_0) {
+        } else {
           const __half2 bias = __half2half2(__int2half_rn(1152));
           auto cvt = [&](uint32_t x, uint32_t sel) -> uint32_t {
             const uint32_t bitsv = __byte_perm(x, 0x64646464u, sel);  // (1024 + (q + 128)) in both halves
@@ -612,16 +509,55 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 make_uint4(cvt(x2, 0x4140), cvt(x2, 0x4342), cvt(x3, 0x4140), cvt(x3, 0x4342));
           }
         }
-        if (warp == 4) STAT_ADD(62);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(S_FULL + sbq));
-        if (warp == 4) STAT_ADD(63);
-        if (++sbq == NB) { sbq = 0; pbq ^= 1; }
+        if (++sbq == NS) { sbq = 0; pbq ^= 1; }
       }
       if (!ok) break;
+      if (kMins) {
+        // the min-term stage: u[b] = -dmin * mn[b] (exact in f32: 11 x 6 bits) as three bf16 terms u1 + u2 + u3; the
+        // stage's six 16-byte chunks hold (u1, u2, u1, u3, u2, u1) for the eight blocks, against the activation side's
+        // (v1, v1, v2, v1, v2, v3)
+        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) break;
+        const float ndmin = -half_bits_to_float(hdr.x >> 16);
+        uint32_t u1[4], u2[4], u3[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint32_t h[2][3];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            int sc_unused, mn;
+            q4k_scale_min(s3, 2 * k + e, sc_unused, mn);
+            const float u = __fmul_rn(ndmin, (float)mn);
+            const __nv_bfloat16 h1 = __float2bfloat16_rn(u);
+            const float r1 = __fsub_rn(u, __bfloat162float(h1));
+            const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 h3 = __float2bfloat16_rn(__fsub_rn(r1, __bfloat162float(h2)));
+            h[e][0] = __bfloat16_as_ushort(h1);
+            h[e][1] = __bfloat16_as_ushort(h2);
+            h[e][2] = __bfloat16_as_ushort(h3);
+          }
+          u1[k] = h[0][0] | (h[1][0] << 16);
+          u2[k] = h[0][1] | (h[1][1] << 16);
+          u3[k] = h[0][2] | (h[1][2] << 16);
+        }
+        unsigned char* orow = smem + OFF_B + sbq * STAGE_BYTES + t * 128;
+        const uint4 c1 = make_uint4(u1[0], u1[1], u1[2], u1[3]), c2 = make_uint4(u2[0], u2[1], u2[2], u2[3]), c3 = make_uint4(u3[0], u3[1], u3[2], u3[3]);
+        *reinterpret_cast<uint4*>(orow + ((0 ^ (t & 7)) << 4)) = c1;
+        *reinterpret_cast<uint4*>(orow + ((1 ^ (t & 7)) << 4)) = c2;
+        *reinterpret_cast<uint4*>(orow + ((2 ^ (t & 7)) << 4)) = c1;
+        *reinterpret_cast<uint4*>(orow + ((3 ^ (t & 7)) << 4)) = c3;
+        *reinterpret_cast<uint4*>(orow + ((4 ^ (t & 7)) << 4)) = c2;
+        *reinterpret_cast<uint4*>(orow + ((5 ^ (t & 7)) << 4)) = c1;
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(S_FULL + sbq));
+        if (++sbq == NS) { sbq = 0; pbq ^= 1; }
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(RAW_EMPTY + rb));
+      if (++rb == NR) { rb = 0; pr ^= 1; }
     }
   } else {
     // ================= combine: thread <-> TMEM lane (token row) 32*(warp%4) + lane, 64 of the 128 columns.
@@ -636,7 +572,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
     for (int c = 0; c < 32; ++c) res2[c] = tq2[c] = 0ull;
     bool ok = true;
-    STAT_LAP_INIT();
     int d = 0, pd = 0, sq = 0, pq = 0;  // accumulator ring / scale ring positions and wait parities
     for (int s = 0; s < nsb && ok; ++s) {
       const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;  // this row's 8 block scales
@@ -646,43 +581,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         const unsigned long long a2 = pack2(kDots ? 0.0f : as[b * BM]);
         if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, E_EPI)) { ok = false; break; }
         tc_fence_after();
+        unsigned long long v[32];
+        tc_ld64_pairs(t_lane + (uint32_t)(d * BN), v);  // the thread's 64 columns of this block; returns when they are in registers
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
+        if (kDots) {
+          if (row_ok) {
+            int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64) * nb + 8 * s + b;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {  // the thread's 64 columns in two passes of 32 (registers)
-          unsigned long long v[16];
-#ifdef IZB_EXP_NO_LD
-          for (int c = 0; c < 16; ++c) v[c] = c + d;
-#else
-          tc_ld32_pairs(t_lane + (uint32_t)(d * BN + 32 * hh), v);
-#endif
-          if (hh == 1) {  // both halves read: the accumulator buffer may be overwritten
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(D1_EMPTY + d));
+            for (int c = 0; c < 32; ++c) {
+              o[(size_t)(2 * c) * nb] = __float2int_rn(lo_f(v[c]));
+              o[(size_t)(2 * c + 1) * nb] = __float2int_rn(hi_f(v[c]));
+            }
           }
-          if (kDots) {
-            if (row_ok) {
-              int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64 + 32 * hh) * nb + 8 * s + b;
+        } else if (QT == IZB_Q4_K) {
+          if (b == 0) {
 #pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                o[(size_t)(2 * c) * nb] = __float2int_rn(lo_f(v[c]));
-                o[(size_t)(2 * c + 1) * nb] = __float2int_rn(hi_f(v[c]));
-              }
-            }
-          } else if (QT == IZB_Q4_K) {
-#ifdef IZB_EXP_NO_FMA
-            for (int c = 0; c < 16; c += 8) ffma2(tq2[16 * hh + c], a2, v[c]);
-#else
-#pragma unroll
-            for (int c = 0; c < 16; ++c) ffma2(tq2[16 * hh + c], a2, v[c]);
-#endif
+            for (int c = 0; c < 32; ++c) tq2[c] = fmul2(a2, v[c]);
           } else {
-            const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256 + hh * 128);
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
-              const ulonglong2 dd = d8[c4];  // four column scales
-              ffma2(res2[16 * hh + 2 * c4], fmul2(a2, dd.x), v[2 * c4]);
-              ffma2(res2[16 * hh + 2 * c4 + 1], fmul2(a2, dd.y), v[2 * c4 + 1]);
-            }
+            for (int c = 0; c < 32; ++c) ffma2(tq2[c], a2, v[c]);
+          }
+        } else {
+          const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256);
+#pragma unroll
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const ulonglong2 dd = d8[c4];  // four column scales
+            ffma2(res2[2 * c4], fmul2(a2, dd.x), v[2 * c4]);
+            ffma2(res2[2 * c4 + 1], fmul2(a2, dd.y), v[2 * c4 + 1]);
           }
         }
         if (++d == ND1) { d = 0; pd ^= 1; }
@@ -693,31 +620,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         if (lane == 0) mbar_arrive(bar(ASC_EMPTY + sq));
         if (++sq == NASC) { sq = 0; pq ^= 1; }
       }
-      if (kMins) {
-        if (!mbar_wait(bar(D2_FULL), s & 1, abort_flag, p.err, E_EPI)) break;
-        tc_fence_after();
+      if (kMins) {  // res += d * tq
+        const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (s & 3) * 512 + half * 256);
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          unsigned long long v[16];
-          tc_ld32_pairs(t_lane + (uint32_t)(ND1 * BN + 32 * hh), v);
-          if (hh == 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(D2_EMPTY));
-          }
-          const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (s & 3) * 1024 + half * 256 + hh * 128);
-          const ulonglong2* mv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (s & 3) * 1024 + 512 + half * 256 + hh * 128);
-#pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {  // res = fma(d, tq, fma(-dmin, tmn, res))
-            const ulonglong2 dd = dv[c4], mm = mv[c4];
-            ffma2(res2[16 * hh + 2 * c4], neg2(mm.x), v[2 * c4]);
-            ffma2(res2[16 * hh + 2 * c4 + 1], neg2(mm.y), v[2 * c4 + 1]);
-            ffma2(res2[16 * hh + 2 * c4], dd.x, tq2[16 * hh + 2 * c4]);
-            ffma2(res2[16 * hh + 2 * c4 + 1], dd.y, tq2[16 * hh + 2 * c4 + 1]);
-            tq2[16 * hh + 2 * c4] = 0ull;
-            tq2[16 * hh + 2 * c4 + 1] = 0ull;
-          }
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const ulonglong2 dd = dv[c4];
+          ffma2(res2[2 * c4], dd.x, tq2[2 * c4]);
+          ffma2(res2[2 * c4 + 1], dd.y, tq2[2 * c4 + 1]);
         }
+      }
+    }
+    if (kMins && ok) {  // the min term of the whole row of K (already negative)
+      ok = mbar_wait(bar(D2_FULL), 0, abort_flag, p.err, E_EPI);
+      if (ok) {
+        tc_fence_after();
+        unsigned long long v[32];
+        tc_ld64_pairs(t_lane + (uint32_t)(ND1 * BN), v);
+        const unsigned long long one2 = pack2(1.0f);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);
       }
     }
     if (ok && !kDots && row_ok && !*abort_flag) {
@@ -745,13 +666,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   // ---- teardown
   tc_fence_before();
   __syncthreads();
-#ifdef IZB_TC_STATS
-  if (threadIdx.x < 72) atomicAdd(&g_tc_wait[threadIdx.x], reinterpret_cast<unsigned long long*>(smem + OFF_BAR + 384)[threadIdx.x]);
-  if (threadIdx.x == 0) {
-    atomicAdd(&g_tc_wait[72], (unsigned long long)(clock64() - t_cta));
-    atomicAdd(&g_tc_wait[73], 1ull);
-  }
-#endif
   if (*abort_flag) {
     // a wait gave up: let copies and MMAs still in flight land before shared memory and TMEM are released
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
@@ -791,29 +705,33 @@ int launch_tc(const izb_weight* w, const TcParams& p, dim3 grid, cudaStream_t st
   return IZB_OK;
 }
 
+// scratch of one call: the operand images (sps stage images of 16 KB per superblock and tile) and the gathered scales
+void tc_scratch_bytes(int n_tiles, int K, int sps, size_t* img_bytes, size_t* asc_bytes) {
+  *img_bytes = (size_t)n_tiles * (K / 256) * sps * STAGE_BYTES;
+  *asc_bytes = (size_t)n_tiles * (K / 32) * BM * 4;
+}
+
 // the activation pre-pass + the GEMM for one tile set
 int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int lda, int rows_total, const int32_t* tiles,
            int n_tiles_grid, const int32_t* rowmap, const float* rowscale, int M_store, float* C, int ldc, int c_off, int acc,
            int32_t* dots, int ws_slot, cudaStream_t st) {
   if (!w->has_tmap) return 1;
   if (w->N % BN || w->K % 256) return 1;
-  const int K = w->K, nb = K / 32, nstages = K / KS;
-  const size_t img_bytes = (size_t)n_tiles_grid * nstages * STAGE_BYTES;
-  const size_t vs_bytes = (size_t)n_tiles_grid * nb * BM * 4;  // each of: the min-term factors (Q4_K) and the scales
+  const int K = w->K;
+  const int sps = (w->type == IZB_Q4_K && !dots) ? 5 : 4;
+  size_t img_bytes, asc_bytes;
+  tc_scratch_bytes(n_tiles_grid, K, sps, &img_bytes, &asc_bytes);
   void* ws = nullptr;
-  if (int rc = izb_workspace(w->device, ws_slot, img_bytes + 2 * vs_bytes, &ws)) return rc;
+  if (int rc = izb_workspace(w->device, ws_slot, img_bytes + asc_bytes, &ws)) return rc;
   uint16_t* aimg = (uint16_t*)ws;
-  float* vsum = (float*)((unsigned char*)ws + img_bytes);
-  float* ascimg = (float*)((unsigned char*)ws + img_bytes + vs_bytes);
+  float* ascimg = (float*)((unsigned char*)ws + img_bytes);
   dim3 pg((BM * (K / 8) + 255) / 256, n_tiles_grid);
-  const int want_vs = (w->type == IZB_Q4_K && !dots) ? 1 : 0;
   if (w->type == IZB_Q4_K)
-    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, ascimg, want_vs));
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, ascimg, sps));
   else
-    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, vsum, ascimg, 0));
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, ascimg, 4));
   TcParams p;
   p.aimg = aimg;
-  p.vsum = vsum;
   p.ascimg = ascimg;
   p.tiles = tiles;
   p.rowmap = rowmap;
@@ -835,17 +753,6 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
 }
 
 }  // namespace
-
-#ifdef IZB_TC_STATS
-// debug build only: reads and clears the wait-cycle counters of gemm_tc_kernel
-extern "C" int izb_tc_wait_stats(unsigned long long* out72) {  // 80 values
-  IZB_CUDA(cudaDeviceSynchronize());
-  IZB_CUDA(cudaMemcpyFromSymbol(out72, g_tc_wait, sizeof(unsigned long long) * 80));
-  unsigned long long zero[80] = {0};
-  IZB_CUDA(cudaMemcpyToSymbol(g_tc_wait, zero, sizeof zero));
-  return IZB_OK;
-}
-#endif
 
 int izb_make_raw_tensor_map(izb_weight* w) {
   EncodeTiledFn enc = get_encode();
@@ -1056,18 +963,19 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   if (!izb_aligned(d_aq, 16) || !izb_aligned(d_asc, 16) || !izb_aligned(d_C, 16) || ldc % 4 || c_off % 4 || (d_status && !izb_aligned(d_status, 4)))
     IZB_FAIL(IZB_ERR_ALIGN, "gemm_noalloc: aq, asc, C must be 16-byte aligned, ldc and c_off multiples of 4");
   if (!w->has_tmap) IZB_FAIL(IZB_ERR_CUDA, "gemm_noalloc: the weight has no tensor map (driver entry point missing at creation)");
-  const int K = w->K, nb = K / 32, nstages = K / KS;
+  const int K = w->K;
   const int n_tiles = (M + BM - 1) / BM;
-  const size_t img_bytes = (size_t)n_tiles * nstages * STAGE_BYTES, vs_bytes = (size_t)n_tiles * nb * BM * 4;
-  if (img_bytes + 2 * vs_bytes > kNoAllocBytes || n_tiles > 65535)
+  const int sps = w->type == IZB_Q4_K ? 5 : 4;
+  size_t img_bytes, asc_bytes;
+  tc_scratch_bytes(n_tiles, K, sps, &img_bytes, &asc_bytes);
+  if (img_bytes + asc_bytes > kNoAllocBytes || n_tiles > 65535)
     IZB_FAIL(IZB_ERR_LIMIT, "gemm_noalloc: M=%d K=%d needs %zu scratch bytes, the fixed array holds %zu (use izb_gemm, or fewer rows per call)",
-             M, K, img_bytes + 2 * vs_bytes, kNoAllocBytes);
+             M, K, img_bytes + asc_bytes, kNoAllocBytes);
   NoAllocDev* dev = nullptr;
   if (int rc = noalloc_setup(w->device, &dev)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   uint16_t* aimg = (uint16_t*)dev->scratch;
-  float* vsum = (float*)(dev->scratch + img_bytes);
-  float* ascimg = (float*)(dev->scratch + img_bytes + vs_bytes);
+  float* ascimg = (float*)(dev->scratch + img_bytes);
   // Everything the GEMM reads from the array is rewritten by the pre-pass of the same call (all rows of all its tiles,
   // padding rows as zeros), so nothing stale from an earlier call is ever read; the status word is the one thing that
   // must start at zero.
@@ -1075,12 +983,11 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   IZB_CUDA(cudaMemsetAsync(status, 0, 4, st));
   dim3 pg((BM * (K / 8) + 255) / 256, n_tiles);
   if (w->type == IZB_Q4_K)
-    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(d_aq, d_asc, Mp, K, Mp, nullptr, nullptr, aimg, vsum, ascimg, 1));
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(d_aq, d_asc, Mp, K, Mp, nullptr, nullptr, aimg, ascimg, 5));
   else
-    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(d_aq, d_asc, Mp, K, Mp, nullptr, nullptr, aimg, vsum, ascimg, 0));
+    IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(d_aq, d_asc, Mp, K, Mp, nullptr, nullptr, aimg, ascimg, 4));
   TcParams p;
   p.aimg = aimg;
-  p.vsum = vsum;
   p.ascimg = ascimg;
   p.tiles = nullptr;
   p.rowmap = nullptr;
@@ -1098,3 +1005,4 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   dim3 grid(w->N / BN, n_tiles);
   return w->type == IZB_Q4_K ? launch_tc<IZB_Q4_K, false>(w, p, grid, st) : launch_tc<IZB_Q8_0, false>(w, p, grid, st);
 }
+

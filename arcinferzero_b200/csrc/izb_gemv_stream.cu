@@ -179,6 +179,208 @@ __global__ void __launch_bounds__(stream_warps<T>() * 32, 1) gemv_stream_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------- Q4_K, one activation row
+// The decode case proper (batch 1, K a multiple of 1024 up to 5120).  Same ring of TMA-filled row buffers per warp, but
+//   * a lane owns one pair of 32-blocks (32 bytes of nibbles) of one of the eight superblocks of a step, so the superblock
+//     header is decoded by four lanes, not eight, and it meets the same activation bytes in every weight row: it keeps
+//     them -- 64 int8 values, two block scales and the two scaled block sums per step -- in registers for the whole
+//     kernel: nothing is staged in shared memory and the CTA never synchronises;
+//   * a warp works on two weight rows at a time, so that two independent dependency chains hide each other's latencies
+//     and the per-row bookkeeping (waits, re-arming the copies, the warp reduction) is paid once per pair;
+//   * the pair of 6-bit (scale, min) values a lane needs is unpacked without branches (q4k_pair).
+// Per 32-block: acc += d * (asc * (float)(sc * dot)) - dmin * ((asc * (float)asum) * (float)mn), the factors that depend
+// only on the activations precomputed.
+
+// Q4_K: the 6-bit (scale, min) values of sub-blocks 2*pp and 2*pp + 1 (pp = 0..3) as two bytes each.  Sub-blocks 0..3
+// keep their values in the low six bits of bytes 0..7; sub-blocks 4..7 have the low four bits in bytes 8..11 and the high
+// two in the top bits of bytes 0..7 (get_scale_min_k4, src/quants.h:61-69).
+__device__ __forceinline__ void q4k_pair(const uint4 h, int sh, bool upper, uint32_t& sc2, uint32_t& mn2) {
+  const uint32_t a = h.y >> sh, b = h.z >> sh, c = h.w >> sh;
+  sc2 = upper ? ((c & 0x0F0Fu) | ((a >> 2) & 0x3030u)) : (a & 0x3F3Fu);
+  mn2 = upper ? (((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u)) : (b & 0x3F3Fu);
+}
+
+// signed x unsigned byte dot product
+__device__ __forceinline__ int dp4a_su(int a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// Two CTAs of eight warps per SM rather than one of sixteen: with programmatic dependent launch the next kernel's CTAs
+// move in, and start their first ring fill, as soon as half an SM is free.
+constexpr int kRegWarps = 8;
+
+template <int NSB4>  // K / 1024
+__global__ void __launch_bounds__(kRegWarps * 32, 2) gemv_q4k_reg_kernel(const uint8_t* __restrict__ raw, int N,
+                                                                         const int8_t* __restrict__ aq, const float* __restrict__ asc,
+                                                                         int Mp, float* __restrict__ C, int c_off, int acc,
+                                                                         int slots, int slot_bytes, uint32_t* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int nsb = 4 * NSB4, WS = (nsb + 7) / 8;  // steps of eight superblocks (the last one may be half empty)
+  constexpr uint32_t row_bytes = nsb * 144;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int W = gridDim.x * kRegWarps, w0 = blockIdx.x * kRegWarps + warp;
+  const int my_rows = w0 < N ? (N - w0 + W - 1) / W : 0;
+  const int sub = lane >> 2, pp = lane & 3;  // superblock of the step, pair of 32-blocks (2 pp, 2 pp + 1) inside it
+  unsigned char* ring = smem + (size_t)warp * slots * slot_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kRegWarps * slots * slot_bytes) + warp * slots;
+  if (lane == 0) {
+    for (int s = 0; s < slots; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(&bars[s])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int s = 0; s < slots && s < my_rows; ++s)
+      row_copy(s_u32(ring + (size_t)s * slot_bytes), raw + (size_t)(w0 + s * W) * row_bytes, row_bytes, s_u32(&bars[s]));
+  }
+  __syncwarp();
+  // Programmatic dependent launch: the weights do not depend on the kernel before this one in the stream, so the ring
+  // fill above may run while that kernel drains; its results (the activations, and C when accumulating) are read only
+  // after griddepcontrol.wait.  launch_dependents lets the next kernel of the stream do the same with this one.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // ---- this lane's activations: per step the 2 x 32 int8 values of its block pair, the two block scales (the second one
+  // divided by 16, see below) and the two scaled block sums
+  uint4 alo[WS][2], ahi[WS][2];
+  float sx[WS], sy16[WS], px[WS], py[WS];
+#pragma unroll
+  for (int st = 0; st < WS; ++st) {
+    const int sb = st * 8 + sub;
+    alo[st][0] = alo[st][1] = ahi[st][0] = ahi[st][1] = make_uint4(0, 0, 0, 0);
+    sx[st] = sy16[st] = px[st] = py[st] = 0.0f;
+    if (sb < nsb) {
+      const int8_t* a = aq + sb * 256 + pp * 64;
+      alo[st][0] = *reinterpret_cast<const uint4*>(a);
+      alo[st][1] = *reinterpret_cast<const uint4*>(a + 16);
+      ahi[st][0] = *reinterpret_cast<const uint4*>(a + 32);
+      ahi[st][1] = *reinterpret_cast<const uint4*>(a + 48);
+      const int b = sb * 8 + pp * 2;
+      const float s0 = asc[(size_t)b * Mp], s1 = asc[(size_t)(b + 1) * Mp];
+      const uint32_t l[8] = {alo[st][0].x, alo[st][0].y, alo[st][0].z, alo[st][0].w, alo[st][1].x, alo[st][1].y, alo[st][1].z, alo[st][1].w};
+      const uint32_t g[8] = {ahi[st][0].x, ahi[st][0].y, ahi[st][0].z, ahi[st][0].w, ahi[st][1].x, ahi[st][1].y, ahi[st][1].z, ahi[st][1].w};
+      int sl = 0, sh = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        sl = __dp4a((int)l[k], 0x01010101, sl);
+        sh = __dp4a((int)g[k], 0x01010101, sh);
+      }
+      sx[st] = s0;
+      sy16[st] = s1 * 0.0625f;
+      px[st] = s0 * (float)sl;
+      py[st] = s1 * (float)sh;
+    }
+  }
+  const int pp_sh = 16 * (pp & 1);  // where this lane's pair of sub-block scales sits in the packed words
+  const bool pp_upper = pp >= 2;
+  const uint32_t h_off = sub * 144, q_off = sub * 144 + 16 + 32 * pp;
+
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < my_rows; i += 2) {
+    const bool two = i + 1 < my_rows;  // (uniform over the warp)
+    bool ready = false;
+    for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[slot]), parity);
+    if (ready && two) {
+      ready = false;
+      for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[slot + 1]), parity);
+    }
+    if (!ready) {  // (bounded wait gave up)
+      if (lane == 0) atomicOr(err, 64u);
+      break;
+    }
+    const unsigned char* w0p = ring + (size_t)slot * slot_bytes;
+    const unsigned char* w1p = two ? w0p + slot_bytes : w0p;  // (a lone last row is computed twice, stored once)
+    float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+    for (int st = 0; st < WS; ++st) {
+      if (st * 8 + 7 < nsb || sub < nsb - st * 8) {  // (only the last step of K = 1024 * odd can be half empty)
+        const uint32_t al[8] = {alo[st][0].x, alo[st][0].y, alo[st][0].z, alo[st][0].w, alo[st][1].x, alo[st][1].y, alo[st][1].z, alo[st][1].w};
+        const uint32_t ah[8] = {ahi[st][0].x, ahi[st][0].y, ahi[st][0].z, ahi[st][0].w, ahi[st][1].x, ahi[st][1].y, ahi[st][1].z, ahi[st][1].w};
+        auto one = [&](const unsigned char* wp, float accv) -> float {
+          const uint4 h = *reinterpret_cast<const uint4*>(wp + st * 1152 + h_off);
+          const uint4 qa = *reinterpret_cast<const uint4*>(wp + st * 1152 + q_off);
+          const uint4 qb = *reinterpret_cast<const uint4*>(wp + st * 1152 + q_off + 16);
+          const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&h.x));  // (d, dmin)
+          uint32_t sc2, mn2;
+          q4k_pair(h, pp_sh, pp_upper, sc2, mn2);
+          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+          // low nibbles against the first block; the high nibbles stay where they are, as unsigned bytes 16 * q, against
+          // the second block: hi = 16 * dot, and the factor 1/16 sits in the activation scale
+          int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            lo0 = __dp4a((int)al[kk], (int)(w[kk] & 0x0F0F0F0Fu), lo0);
+            lo1 = __dp4a((int)al[4 + kk], (int)(w[4 + kk] & 0x0F0F0F0Fu), lo1);
+            hi0 = dp4a_su((int)ah[kk], w[kk] & 0xF0F0F0F0u, hi0);
+            hi1 = dp4a_su((int)ah[4 + kk], w[4 + kk] & 0xF0F0F0F0u, hi1);
+          }
+          const float tq = fmaf(sx[st], (float)((int)(sc2 & 0xFFu) * (lo0 + lo1)), sy16[st] * (float)((int)(sc2 >> 8) * (hi0 + hi1)));
+          const float tm = fmaf(px[st], (float)(mn2 & 0xFFu), py[st] * (float)(mn2 >> 8));
+          return fmaf(df.x, tq, fmaf(-df.y, tm, accv));
+        };
+        acc0 = one(w0p, acc0);
+        acc1 = one(w1p, acc1);
+      }
+    }
+    // the slots are read: request the rows `slots` ahead into them, then reduce and store
+    __syncwarp();
+    const int row = w0 + i * W;
+    if (lane == 0) {
+      if (i + slots < my_rows)
+        row_copy(s_u32(ring + (size_t)slot * slot_bytes), raw + (size_t)(row + slots * W) * row_bytes, row_bytes, s_u32(&bars[slot]));
+      if (i + 1 + slots < my_rows)
+        row_copy(s_u32(ring + (size_t)(slot + 1) * slot_bytes), raw + (size_t)(row + (slots + 1) * W) * row_bytes, row_bytes, s_u32(&bars[slot + 1]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, o);
+      acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, o);
+    }
+    if (lane < 2 && (lane == 0 || two)) {
+      float* c = C + c_off + row + lane * W;
+      const float v = lane ? acc1 : acc0;
+      *c = acc ? *c + v : v;
+    }
+    slot += 2;
+    if (slot >= slots) { slot = 0; parity ^= 1; }
+  }
+}
+
+template <int NSTEPS>
+int launch_q4k_reg(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int c_off, int acc,
+                   cudaStream_t st) {
+  constexpr size_t kBudget = 100 * 1024;  // per CTA, two CTAs per SM
+  const int slot_bytes = (int)((w->row_bytes + 127) & ~(size_t)127);
+  int slots = (int)((kBudget - 4096) / ((size_t)kRegWarps * slot_bytes));
+  slots = slots > 8 ? 8 : (slots & ~1);  // rows are taken two at a time
+  if (slots < 2) return 1;
+  const size_t smem = (size_t)kRegWarps * slots * slot_bytes + (size_t)kRegWarps * slots * 8;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    IZB_CUDA(cudaGetDevice(&dev));
+    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    IZB_CUDA(cudaFuncSetAttribute(gemv_q4k_reg_kernel<NSTEPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
+  }
+  int grid = 2 * sms;
+  const int need = (w->N + kRegWarps - 1) / kRegWarps;
+  if (grid > need) grid = need;
+  uint32_t* err = izb_device_error_word(w->device);
+  if (!err) IZB_FAIL(IZB_ERR_NOMEM, "gemv: no device error word");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kRegWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int N = w->N;
+  IZB_LAUNCH("gemv", st, cudaLaunchKernelEx(&cfg, gemv_q4k_reg_kernel<NSTEPS>, raw, N, aq, asc, Mp, C, c_off, acc, slots, slot_bytes, err));
+  return IZB_OK;
+}
+
 template <int QT, int T>
 int launch_stream(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc,
                   int c_off, int acc, cudaStream_t st) {
@@ -222,6 +424,15 @@ static int stream_t(const izb_weight* w, const uint8_t* raw, const int8_t* aq, c
 
 int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int T, int Mp, float* C,
                            int ldc, int c_off, int acc, cudaStream_t st) {
+  if (T == 1 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= 8192) {  // (fewer rows: under four per warp)
+    switch (w->K / 1024) {
+      case 1: return launch_q4k_reg<1>(w, raw, aq, asc, Mp, C, c_off, acc, st);
+      case 2: return launch_q4k_reg<2>(w, raw, aq, asc, Mp, C, c_off, acc, st);
+      case 3: return launch_q4k_reg<3>(w, raw, aq, asc, Mp, C, c_off, acc, st);
+      case 4: return launch_q4k_reg<4>(w, raw, aq, asc, Mp, C, c_off, acc, st);
+      default: return launch_q4k_reg<5>(w, raw, aq, asc, Mp, C, c_off, acc, st);
+    }
+  }
   switch (T) {
     case 1: return stream_t<1>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
     case 2: return stream_t<2>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);

@@ -171,6 +171,63 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
     return out
 
 
+def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> dict:
+    """BASELINE.json config 4: 4096 tokens, hidden 2048, 128 experts (gate / up 768 x 2048, down 2048 x 768, Q4_K), top-8
+    routing from softmax of N(0,1) logits.  One pass = route, sort by expert, grouped gate/up GEMM with the SwiGLU store,
+    quantise, grouped down GEMM scaled by the router weights, weighted sum per token.  Device-timed."""
+    from arcinferzero_b200 import synth as S
+    T, E, F, NE, NU, TM = 4096, 2048, 768, 128, 8, 128
+    rng = np.random.default_rng(SEED + 9)
+    Wg = izb.Weight(QT, S.make_weight(QT, NE * F, E, SEED + 11), F, E, n_mats=NE)
+    Wu = izb.Weight(QT, S.make_weight(QT, NE * F, E, SEED + 12), F, E, n_mats=NE)
+    Wd = izb.Weight(QT, S.make_weight(QT, NE * E, F, SEED + 13), E, F, n_mats=NE)
+    x = torch.from_numpy(S.make_act(T, E, SEED + 14)).cuda()
+    logits = torch.from_numpy(rng.standard_normal((T, NE), dtype=np.float32)).cuda()
+    Sn = T * NU
+    Sp = izb.pad_rows(Sn)
+    out = torch.empty_like(x)
+
+    def one_pass():
+        out.copy_(x)
+        aq, asc, _ = izb.quantize_act(x, Mp=T)
+        ids, wts, counts = izb.moe_route(logits, NU)
+        offs, tiles, max_tiles, stok, swt, inv = izb.moe_sort(ids, wts, counts, TM)
+        h = izb.moe_gateup(Wg, Wu, aq, asc, tiles, max_tiles, TM, stok, Sn)
+        hq, hsc, _ = izb.quantize_act(h, Mp=Sp)
+        y = izb.moe_down(Wd, hq, hsc, tiles, max_tiles, TM, swt, Sn)
+        izb.moe_combine(out, y, inv, NU)
+        return counts
+
+    for _ in range(3):
+        counts = one_pass()
+    torch.cuda.synchronize()
+    l0 = izb.launch_count()
+    izb.profile_start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    prof = izb.profile_stop()
+    ms = e0.elapsed_time(e1) / iters
+    launches = (izb.launch_count() - l0) // iters
+    ops = 2.0 * Sn * 3 * F * E
+    c = counts.cpu().numpy()
+    tc_ms = sum(v["ms"] for k, v in prof.items() if k == "gemm_tc") / iters
+    res = {"workload": "config 4: 4096 tokens x top-8 of 128 experts, hidden 2048, expert FFN 768, Q4_K",
+           "ms_per_pass": ms, "tokens_per_s": T / (ms * 1e-3), "tops": ops / (ms * 1e-3) / 1e12,
+           "grouped_gemm_ms_per_pass": tc_ms, "grouped_gemm_tops": ops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else None,
+           "frac_of_tensor_peak_grouped_gemm": (ops / (tc_ms * 1e-3) / 1e12) / tc_peak if tc_ms > 0 else None,
+           "peak": f"{tc_peak} TFLOP/s {peak_src} dense 16-bit sustained", "gpu_launches_per_pass": launches,
+           "expert_load": {"max": int(c.max()), "min": int(c.min()), "mean": float(c.mean())},
+           "kernel_ms_per_pass": {k: v["ms"] / iters for k, v in prof.items()},
+           "finite": bool(torch.isfinite(out).all().item())}
+    for W in (Wg, Wu, Wd):
+        W.close()
+    return res
+
+
 def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens: int, passes: int = 2) -> list:
     """BASELINE.json config 5: the projections of 8 dense layers (Q4_K, hidden 5120, FFN 17408, 7168 QKV rows) over 32768
     token rows, split over the ranks as the reference's tensor-parallel mode splits them, in both summation modes of
@@ -242,6 +299,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gemv", action="store_true", help="skip the decode GEMV section (BASELINE.json config 3)")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE section (BASELINE.json config 4)")
+    ap.add_argument("--moe-only", action="store_true", help="profiling only: run just the MoE section")
     ap.add_argument("--gemv-only", action="store_true", help="profiling only: run just the decode GEMV section")
     ap.add_argument("--lite", action="store_true", help="profiling only: few launches per GEMV shape")
     ap.add_argument("--tp-stack", action="store_true", help="also run the tensor-parallel projection stack (config 5); default when --gpus > 1")
@@ -267,6 +326,10 @@ def main() -> None:
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (the library has no CPU path)"
     torch.cuda.set_device(local)
+    if args.moe_only:
+        _, _, tc_sus, src = peaks()
+        print(json.dumps({"moe": moe_section(izb, torch, tc_sus, src, iters=3)}), flush=True)
+        return
     if args.gemv_only:
         hbm, _, _, src = peaks()
         print(json.dumps({"decode_gemv": gemv_section(izb, torch, hbm, src, lite=args.lite)}), flush=True)
@@ -378,6 +441,8 @@ def main() -> None:
         }
         if tp_stack is not None:
             line["tp_stack"] = tp_stack
+        if not args.no_moe and world == 1:
+            line["moe"] = moe_section(izb, torch, tc_sus, src)
         if not args.no_gemv and world == 1:
             line["decode_gemv"] = gemv_section(izb, torch, hbm, src)
         if not args.no_cpu_baseline and world == 1:

@@ -52,7 +52,7 @@ def test_noalloc_gemm_rejects_what_does_not_fit(izb):
     import torch
     N, K = 128, 5120
     W = izb.Weight(12, S.make_weight(12, N, K, 3), N, K)
-    M = 4096  # 32 tiles x (80 x 16 KiB + 160 x 1 KiB) = 45 MiB > 24 MiB
+    M = 4096  # 32 tiles x (20 x 5 x 16 KiB + 160 x 0.5 KiB) = 52 MiB > 24 MiB
     aq = torch.zeros((M, K), dtype=torch.int8, device="cuda")
     asc = torch.zeros((K // 32, M), dtype=torch.float32, device="cuda")
     out = torch.zeros((M, N), dtype=torch.float32, device="cuda")

@@ -69,7 +69,7 @@ static_assert(OFF_DM + 4 * 512 <= OFF_ASC && OFF_D8 + 4 * 4096 <= OFF_ASC, "shar
 enum Bar {  // 8-byte mbarriers
   S_FULL = 0, S_EMPTY = S_FULL + NS, RAW_FULL = S_EMPTY + NS,  // S_*: one barrier per stage for both operand tiles
   RAW_EMPTY = RAW_FULL + 4, D1_FULL = RAW_EMPTY + 4, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1,
-  ASC_FULL, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
+  D2_EMPTY, ASC_FULL, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
 };
 static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
 
@@ -84,6 +84,7 @@ struct TcParams {
   const int32_t* rowmap;  // grouped gather of activation rows (slot -> token) or null
   const float* rowscale;  // per output row factor or null
   int M;                  // dense: rows to store
+  int n_mtiles;           // dense: row tiles (grouped: tiles[0], read on the device)
   int N, K;               // per matrix
   int mat;                // dense: matrix of the stack
   float* C;
@@ -317,21 +318,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) -> uint32_t { return bar0 + 8u * (uint32_t)i; };
 
-  // ---- which tile
-  int tile, expert, r0, nr;
-  if (p.tiles) {
-    tile = blockIdx.y;
-    if (tile >= p.tiles[0]) return;  // uniform over the CTA, before any barrier or TMEM use
-    expert = p.tiles[1 + 3 * tile];
-    r0 = p.tiles[2 + 3 * tile];
-    nr = p.tiles[3 + 3 * tile];
-  } else {
-    tile = blockIdx.y;
-    expert = p.mat;
-    r0 = tile * BM;
-    nr = min(BM, p.M - r0);
-  }
-  const int n0 = blockIdx.x * BN;
+  // ---- the CTA's work: output tiles blockIdx.x, blockIdx.x + gridDim.x, ... of (row tiles) x (N / 128 column tiles), column
+  // tile fastest.  Every role walks the same list; its ring positions and barrier parities run on from tile to tile, so
+  // the producers, the dequantisers and the MMA issuers are already inside the next tile while the combine warps
+  // store the current one.
+  const int n_ntiles = p.N / BN;
+  const int n_work = (p.tiles ? p.tiles[0] : p.n_mtiles) * n_ntiles;
+  if ((int)blockIdx.x >= n_work) return;  // uniform over the CTA, before any barrier or TMEM use
   const int nsb = p.K >> 8, nb = p.K >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int SBB = QT == IZB_Q4_K ? 144 : 272;
@@ -347,6 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), 4); }
     for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 8); }
     mbar_init(bar(D2_FULL), 1);
+    mbar_init(bar(D2_EMPTY), 8);
     for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -366,31 +360,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     // sits at the final CTA barrier while another lane of the same warp is still working.
     if (warp == 0) {
       // ================= activation producer: the tile's stage images lie back to back in global memory
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
       int sa = 0, pa = 1;
-      for (int g = 0; g < nstages; ++g) {
-        if (!mbar_wait(bar(S_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) break;
-        if (lane == 0) {
-          mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
-          bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int tile = w / n_ntiles;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
+        for (int g = 0; g < nstages; ++g) {
+          if (!mbar_wait(bar(S_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) { ok = false; break; }
+          if (lane == 0) {
+            mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
+            bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
+          }
+          __syncwarp();
+          if (++sa == NS) { sa = 0; pa ^= 1; }
         }
-        __syncwarp();
-        if (++sa == NS) { sa = 0; pa ^= 1; }
       }
     } else if (warp == 3) {
       // ================= weight producer: TMA of the raw superblocks of the tile's 128 weight rows, and per superblock the
       // 8 x 128 activation scales the combine warps need
-      const int wrow = expert * p.N + n0;
       int rb = 0, pr = 1, sq = 0, pq = 1;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const int tile = w / n_ntiles;
+      const int wrow = (p.tiles ? p.tiles[1 + 3 * tile] : p.mat) * p.N + (w % n_ntiles) * BN;
       for (int s = 0; s < nsb; ++s) {
-        if (!mbar_wait(bar(RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) break;
+        if (!mbar_wait(bar(RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) { ok = false; break; }
         if (lane == 0) {
           mbar_expect_tx(bar(RAW_FULL + rb), RAW);
           tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
         }
         if (++rb == NR) { rb = 0; pr ^= 1; }
         if (!kDots) {
-          if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, E_WPROD)) break;
+          if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, E_WPROD)) { ok = false; break; }
           if (lane == 0) {
             mbar_expect_tx(bar(ASC_FULL + sq), 4096);
             bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
@@ -399,6 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
         __syncwarp();
       }
+      }
     } else {
       // ================= MMA issuers.  Of a superblock's stages 0..3 (two 32-blocks each, every block into its own
       // accumulator buffer: two MMAs of K = 16 + one commit) warp 1 takes 0 and 2, warp 2 takes 1, 3 and the min-term stage 4
@@ -406,16 +408,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       // what a thread pays per block -- barrier polls and commits between MMAs -- is longer than the 128 cycles the two
       // MMAs run; one issuer for the min term so that its accumulator is updated in program order.
       bool ok = true;
+      int it = 0;  // tiles done: stage and block counts run on across tiles
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+      const int gs = it * nstages, jb = it * nb;
       for (int s = 0; s < nsb && ok; ++s) {
         for (int t = warp - 1; t < (warp == 1 ? 4 : SPS) && ok; t += (t == 3 ? 1 : 2)) {
-          const int g = SPS * s + t, sa = g % NS;
+          const int g = gs + SPS * s + t, sa = g % NS;
           if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sa * STAGE_BYTES);
           if (t < 4) {
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
-              const int j = 8 * s + 2 * t + blk, d = j % ND1;
+              const int j = jb + 8 * s + 2 * t + blk, d = j % ND1;
               if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
               tc_fence_after();
               if (lane == 0) {
@@ -428,10 +433,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
               __syncwarp();
             }
             if (!ok) break;
-          } else if (lane == 0) {
+          } else {
+            // the min-term accumulator of the tile before must have been read before this tile's first MMA clears it
+            if (s == 0 && it > 0 && !mbar_wait(bar(D2_EMPTY), (it - 1) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+            tc_fence_after();
+            if (lane == 0) {
 #pragma unroll
-            for (int k16 = 0; k16 < 3; ++k16)
-              tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a_addr + k16 * 32), umma_desc(b_addr + k16 * 32), kIdescBF16, (s | k16) ? 1u : 0u);
+              for (int k16 = 0; k16 < 3; ++k16)
+                tc_mma_f16(tmem_base + ND1 * BN, umma_desc(a_addr + k16 * 32), umma_desc(b_addr + k16 * 32), kIdescBF16, (s | k16) ? 1u : 0u);
+            }
           }
           if (lane == 0) {
             tc_commit(bar(S_EMPTY + sa));
@@ -439,6 +449,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           }
           __syncwarp();
         }
+      }
       }
     }
   } else if (warp < 8) {
@@ -448,15 +459,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     bool ok = true;
     int sbq = 0, pbq = 1;  // operand ring position and wait parity
     int rb = 0, pr = 0;    // raw ring
-    for (int s = 0; s < nsb && ok; ++s) {
-      if (!mbar_wait(bar(RAW_FULL + rb), pr, abort_flag, p.err, E_DEQ)) break;
+    int sbc = 0;           // superblocks done (all tiles): position in the 4-deep ring of superblock scales
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x)
+    for (int s = 0; s < nsb && ok; ++s, ++sbc) {
+      if (!mbar_wait(bar(RAW_FULL + rb), pr, abort_flag, p.err, E_DEQ)) { ok = false; break; }
       const unsigned char* rrow = smem + OFF_RAW + rb * RAW + t * SBB;
       const uint4 hdr = *reinterpret_cast<const uint4*>(rrow);
       const uint32_t s3[3] = {hdr.y, hdr.z, hdr.w};
       if (QT == IZB_Q4_K) {
-        if (kMins) reinterpret_cast<float*>(smem + OFF_DM + (s & 3) * 512)[t] = half_bits_to_float(hdr.x & 0xFFFFu);
+        if (kMins) reinterpret_cast<float*>(smem + OFF_DM + (sbc & 3) * 512)[t] = half_bits_to_float(hdr.x & 0xFFFFu);
       } else {
-        float* d8 = reinterpret_cast<float*>(smem + OFF_D8 + (s & 3) * 4096);
+        float* d8 = reinterpret_cast<float*>(smem + OFF_D8 + (sbc & 3) * 4096);
         const uint32_t hw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
 #pragma unroll
         for (int b = 0; b < 8; ++b) d8[b * 128 + t] = half_bits_to_float((b & 1) ? hw[b >> 1] >> 16 : hw[b >> 1] & 0xFFFFu);
@@ -519,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         // the min-term stage: u[b] = -dmin * mn[b] (exact in f32: 11 x 6 bits) as three bf16 terms u1 + u2 + u3; the
         // stage's six 16-byte chunks hold (u1, u2, u1, u3, u2, u1) for the eight blocks, against the activation side's
         // (v1, v1, v2, v1, v2, v3)
-        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) break;
+        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) { ok = false; break; }
         const float ndmin = -half_bits_to_float(hdr.x >> 16);
         uint32_t u1[4], u2[4], u3[4];
 #pragma unroll
@@ -565,17 +578,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const int q = warp & 3, half = (warp - 8) >> 2;
     const int r = 32 * q + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(half * 64);
+    bool ok = true;
+    int d = 0, pd = 0, sq = 0, pq = 0;  // accumulator ring / scale ring positions and wait parities
+    int sbc = 0, it = 0;                // superblocks and tiles done
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
+    const int tile = w / n_ntiles, n0 = (w % n_ntiles) * BN;
+    const int r0 = p.tiles ? p.tiles[2 + 3 * tile] : tile * BM;
+    const int nr = p.tiles ? p.tiles[3 + 3 * tile] : min(BM, p.M - r0);
     const bool row_ok = r < nr;
     const int out_row = r0 + r;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(half * 64);
     unsigned long long res2[32], tq2[32];  // pairs of columns (2i, 2i+1)
 #pragma unroll
     for (int c = 0; c < 32; ++c) res2[c] = tq2[c] = 0ull;
-    bool ok = true;
-    int d = 0, pd = 0, sq = 0, pq = 0;  // accumulator ring / scale ring positions and wait parities
-    for (int s = 0; s < nsb && ok; ++s) {
+    for (int s = 0; s < nsb && ok; ++s, ++sbc) {
       const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;  // this row's 8 block scales
-      if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, E_EPI)) break;
+      if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, E_EPI)) { ok = false; break; }
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
         const unsigned long long a2 = pack2(kDots ? 0.0f : as[b * BM]);
@@ -604,7 +622,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             for (int c = 0; c < 32; ++c) ffma2(tq2[c], a2, v[c]);
           }
         } else {
-          const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (s & 3) * 4096 + b * 512 + half * 256);
+          const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (sbc & 3) * 4096 + b * 512 + half * 256);
 #pragma unroll
           for (int c4 = 0; c4 < 16; ++c4) {
             const ulonglong2 dd = d8[c4];  // four column scales
@@ -621,7 +639,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         if (++sq == NASC) { sq = 0; pq ^= 1; }
       }
       if (kMins) {  // res += d * tq
-        const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (s & 3) * 512 + half * 256);
+        const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (sbc & 3) * 512 + half * 256);
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const ulonglong2 dd = dv[c4];
@@ -631,11 +649,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
     }
     if (kMins && ok) {  // the min term of the whole row of K (already negative)
-      ok = mbar_wait(bar(D2_FULL), 0, abort_flag, p.err, E_EPI);
+      ok = mbar_wait(bar(D2_FULL), it & 1, abort_flag, p.err, E_EPI);
       if (ok) {
         tc_fence_after();
         unsigned long long v[32];
         tc_ld64_pairs(t_lane + (uint32_t)(ND1 * BN), v);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(D2_EMPTY));  // the next tile's min term may start
         const unsigned long long one2 = pack2(1.0f);
 #pragma unroll
         for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);
@@ -661,6 +682,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
         *dst = v;
       }
+    }
     }
   }
   // ---- teardown
@@ -705,6 +727,16 @@ int launch_tc(const izb_weight* w, const TcParams& p, dim3 grid, cudaStream_t st
   return IZB_OK;
 }
 
+// persistent grid: one CTA per SM (shared memory allows no more), fewer when there are fewer tiles
+int tc_grid(int n_work) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  }
+  return n_work < sms ? (n_work > 0 ? n_work : 1) : sms;
+}
+
 // scratch of one call: the operand images (sps stage images of 16 KB per superblock and tile) and the gathered scales
 void tc_scratch_bytes(int n_tiles, int K, int sps, size_t* img_bytes, size_t* asc_bytes) {
   *img_bytes = (size_t)n_tiles * (K / 256) * sps * STAGE_BYTES;
@@ -747,7 +779,8 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
   p.dots = dots;
   p.err = izb_device_error_word(w->device);
   if (!p.err) IZB_FAIL(IZB_ERR_NOMEM, "gemm: no device error word");
-  dim3 grid(w->N / BN, n_tiles_grid);
+  p.n_mtiles = n_tiles_grid;
+  dim3 grid(tc_grid(w->N / BN * n_tiles_grid));
   if (w->type == IZB_Q4_K) return dots ? launch_tc<IZB_Q4_K, true>(w, p, grid, st) : launch_tc<IZB_Q4_K, false>(w, p, grid, st);
   return dots ? launch_tc<IZB_Q8_0, true>(w, p, grid, st) : launch_tc<IZB_Q8_0, false>(w, p, grid, st);
 }
@@ -1002,7 +1035,8 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   p.acc = acc;
   p.dots = nullptr;
   p.err = status;
-  dim3 grid(w->N / BN, n_tiles);
+  p.n_mtiles = n_tiles;
+  dim3 grid(tc_grid(w->N / BN * n_tiles));
   return w->type == IZB_Q4_K ? launch_tc<IZB_Q4_K, false>(w, p, grid, st) : launch_tc<IZB_Q8_0, false>(w, p, grid, st);
 }
 

@@ -37,7 +37,8 @@ def gather(t, world):
 
 def check_mode(mode: str, world: int, rank: int, device: int) -> None:
     import torch
-    cfg = tp.StackConfig(layers=2, tokens=256, hidden=512, q_rows=512, kv_rows=256, ffn=1024, seed=4242)
+    n = max(2, world)  # every rank gets at least one 256-wide unit of each split dimension
+    cfg = tp.StackConfig(layers=2, tokens=256, hidden=512, q_rows=256 * n, kv_rows=128 * n, ffn=256 * max(4, world), seed=4242)
     QT, E, T = cfg.qtype, cfg.hidden, cfg.tokens
     st = tp.Stack(cfg, world, rank, device, mode=mode)
     x_in = (S.make_act(T, E, cfg.seed) * np.float32(0.1)).astype(np.float32)

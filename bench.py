@@ -36,7 +36,7 @@ QT = 12
 SEED = 20261125
 WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantize_act + GEMM per step)"
 NOMINAL_INT8_TOPS = 4500.0
-NCU_TRAFFIC_BYTES_PER_TILE = (122.1e6 + 118.5e6) / (16 * 136)
+NCU_TRAFFIC_BYTES_PER_TILE = (128.8e6 + 114.2e6) / (16 * 136)
 
 
 def peaks():
@@ -431,7 +431,7 @@ def main() -> None:
                          "frac": achieved / tc_sus, "peak_source": f"{src} dense bf16/fp16 (sustained; burst {tc_burst})",
                          "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS,
                          # DRAM bytes per launch: one ncu capture of the same kernel at 2048 token rows and all weight rows
-                         # (read 122.1 MB + written 118.5 MB), scaled by the 128x128 tiles this launch runs
+                         # (read 128.8 MB + written 114.2 MB), scaled by the 128x128 tiles this launch runs
                          "traffic": NCU_TRAFFIC_BYTES_PER_TILE * ((M + 127) // 128) * (Nr // 128),
                          "traffic_source": "ncu dram__bytes_read+write of gemm_tc at M=2048, N=17408 (profiles/), per tile x tiles",
                          "ms_per_launch": ms_kernel, "launches": g["launches"],

@@ -123,6 +123,9 @@ struct DevState {
   size_t ws_bytes[4] = {0, 0, 0, 0};
   void* stage = nullptr;  // staging of the host-buffer call
   size_t stage_bytes = 0;
+  cudaStream_t hs[3] = {nullptr, nullptr, nullptr};  // host-buffer call: copy-in, compute, copy-out streams
+  cudaEvent_t he[2][3] = {{nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr}};  // per staging buffer: in, computed, out
+  cudaEvent_t hstart = nullptr;
   int tc_ok = -1;  // -1 unknown, 0 self-check failed, 1 passed
 };
 DevState g_dev[kMaxDev];
@@ -357,10 +360,17 @@ extern "C" int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, i
   IZB_CUDA(cudaSetDevice(w->device));
   cudaStream_t st = (cudaStream_t)stream;
   const int K = w->K, N = w->N;
-  const int Mp = M <= 8 ? 16 : (M >= 128 ? (M + 127) / 128 * 128 : (M + 15) / 16 * 16);  // zero/engine.h:521-522
-  const size_t bx = (size_t)M * K * 4, baq = (size_t)Mp * K, basc = (size_t)(K / 32) * Mp * 4, bc = (size_t)Mp * N * 4;
+  // Rows travel in chunks through two staging buffers and three streams (copy in, quantise + multiply, copy out), so
+  // that both directions of the host link and the GPU work at the same time; a call of up to kChunk rows is one chunk.
+  constexpr int kChunk = 1024;
+  const int rows_max = M < kChunk ? M : kChunk;
+  auto pad = [](int m) { return m <= 8 ? 16 : (m >= 128 ? (m + 127) / 128 * 128 : (m + 15) / 16 * 16); };  // zero/engine.h:521-522
+  const int Mp_max = pad(rows_max);
+  const size_t bx = (size_t)rows_max * K * 4, baq = (size_t)Mp_max * K, basc = (size_t)(K / 32) * Mp_max * 4, bc = (size_t)Mp_max * N * 4;
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
-  const size_t total = up(bx) + up(baq) + up(basc) + up(bc);
+  const size_t per_buf = up(bx) + up(baq) + up(basc) + up(bc);
+  const int nchunks = (M + kChunk - 1) / kChunk, nbuf = nchunks > 1 ? 2 : 1;
+  const size_t total = per_buf * nbuf;
   DevState& d = g_dev[w->device];
   {
     std::lock_guard<std::mutex> lk(d.mu);
@@ -377,16 +387,41 @@ extern "C" int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, i
       }
       d.stage_bytes = total;
     }
+    if (!d.hstart) {
+      for (int i = 0; i < 3; ++i) IZB_CUDA(cudaStreamCreateWithFlags(&d.hs[i], cudaStreamNonBlocking));
+      for (int b = 0; b < 2; ++b)
+        for (int i = 0; i < 3; ++i) IZB_CUDA(cudaEventCreateWithFlags(&d.he[b][i], cudaEventDisableTiming));
+      IZB_CUDA(cudaEventCreateWithFlags(&d.hstart, cudaEventDisableTiming));
+    }
   }
-  uint8_t* p = (uint8_t*)d.stage;
-  float* dx = (float*)p;
-  int8_t* daq = (int8_t*)(p + up(bx));
-  float* dasc = (float*)(p + up(bx) + up(baq));
-  float* dC = (float*)(p + up(bx) + up(baq) + up(basc));
-  IZB_CUDA(cudaMemcpyAsync(dx, h_x, bx, cudaMemcpyHostToDevice, st));
-  if (int rc = izb_quantize_act(dx, K, M, Mp, K, daq, dasc, nullptr, st)) return rc;
-  if (int rc = izb_matmul(w, mat, daq, dasc, nullptr, M, Mp, dC, N, 0, 0, st)) return rc;
-  IZB_CUDA(cudaMemcpyAsync(h_C, dC, (size_t)M * N * 4, cudaMemcpyDeviceToHost, st));
+  // everything below is ordered after what the caller's stream holds
+  IZB_CUDA(cudaEventRecord(d.hstart, st));
+  for (int i = 0; i < 3; ++i) IZB_CUDA(cudaStreamWaitEvent(d.hs[i], d.hstart, 0));
+  for (int c = 0; c < nchunks; ++c) {
+    const int b = c & 1, m0 = c * kChunk, m = (M - m0) < kChunk ? (M - m0) : kChunk, Mp = pad(m);
+    uint8_t* p = (uint8_t*)d.stage + (size_t)b * per_buf;
+    float* dx = (float*)p;
+    int8_t* daq = (int8_t*)(p + up(bx));
+    float* dasc = (float*)(p + up(bx) + up(baq));
+    float* dC = (float*)(p + up(bx) + up(baq) + up(basc));
+    // copy in: the buffer's previous chunk must have been quantised
+    if (c >= 2) IZB_CUDA(cudaStreamWaitEvent(d.hs[0], d.he[b][1], 0));
+    IZB_CUDA(cudaMemcpyAsync(dx, h_x + (size_t)m0 * K, (size_t)m * K * 4, cudaMemcpyHostToDevice, d.hs[0]));
+    IZB_CUDA(cudaEventRecord(d.he[b][0], d.hs[0]));
+    // compute: after the copy in, and after the buffer's previous result has left
+    IZB_CUDA(cudaStreamWaitEvent(d.hs[1], d.he[b][0], 0));
+    if (c >= 2) IZB_CUDA(cudaStreamWaitEvent(d.hs[1], d.he[b][2], 0));
+    if (int rc = izb_quantize_act(dx, K, m, Mp, K, daq, dasc, nullptr, d.hs[1])) return rc;
+    if (int rc = izb_matmul(w, mat, daq, dasc, nullptr, m, Mp, dC, N, 0, 0, d.hs[1])) return rc;
+    IZB_CUDA(cudaEventRecord(d.he[b][1], d.hs[1]));
+    // copy out
+    IZB_CUDA(cudaStreamWaitEvent(d.hs[2], d.he[b][1], 0));
+    IZB_CUDA(cudaMemcpyAsync(h_C + (size_t)m0 * N, dC, (size_t)m * N * 4, cudaMemcpyDeviceToHost, d.hs[2]));
+    IZB_CUDA(cudaEventRecord(d.he[b][2], d.hs[2]));
+  }
+  // the caller's stream continues after the last copy out; the call itself returns when the result is in h_C
+  IZB_CUDA(cudaStreamWaitEvent(st, d.he[(nchunks - 1) & 1][2], 0));
+  IZB_CUDA(cudaStreamSynchronize(d.hs[2]));
   IZB_CUDA(cudaStreamSynchronize(st));
   return IZB_OK;
 }

@@ -146,19 +146,6 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
 // tcgen05.ld of 64 columns + wait, delivered as 32 register pairs (columns 2i, 2i+1) for the f32x2 arithmetic.  The
 // load, the wait and the moves are one asm block: nothing that uses the values can be scheduled before the wait.
 __device__ __forceinline__ void tc_ld64_pairs(uint32_t taddr, unsigned long long (&r)[32]) {
@@ -217,7 +204,6 @@ __device__ __forceinline__ unsigned long long pack2(float x) {
   asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
   return r;
 }
-__device__ __forceinline__ unsigned long long neg2(unsigned long long a) { return a ^ 0x8000000080000000ull; }
 __device__ __forceinline__ float lo_f(unsigned long long a) { return __uint_as_float((uint32_t)a); }
 __device__ __forceinline__ float hi_f(unsigned long long a) { return __uint_as_float((uint32_t)(a >> 32)); }
 

@@ -139,7 +139,10 @@ int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq, const flo
                      int ldc, int c_off, int acc, uint32_t* d_status, void* stream);
 
 /* Host-buffer convenience call = what a caller without device code does per projection: copies h_x [M][K] to the
- * device, quantises, multiplies, copies C [M][N] back, synchronises.  Uses library-owned staging buffers per device. */
+ * device, quantises, multiplies, copies C [M][N] back, synchronises.  Uses library-owned staging buffers per device.
+ * Rows travel in chunks of 1024 through two staging buffers and three library-owned streams (copy in, compute, copy
+ * out), ordered after the work already in `stream`, so that both directions of the host link and the GPU are busy at
+ * once; pinned host buffers are needed for the copies to overlap.  Returns when h_C is complete. */
 int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, int M, float* h_C, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ mixture of experts

@@ -22,7 +22,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
-    "izb_quantize_act", "izb_swiglu_quant",
+    "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
     "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_destroy", "izb_tp_allreduce_rows",
@@ -148,6 +148,18 @@ def swiglu_quant(gu, F: int, Mp: int | None = None, want_h: bool = False):
     asc = torch.empty((F // 32, Mp), dtype=torch.float32, device=gu.device)
     h = torch.empty((M, F), dtype=torch.float32, device=gu.device) if want_h else None
     _check(lib().izb_swiglu_quant(_p(gu), gu.stride(0), 1, M, Mp, F, _p(h), _p(aq), _p(asc), None, _stream()))
+    return aq, asc, h
+
+
+def rmsnorm_quant(x, w, eps: float, Mp: int | None = None, want_h: bool = False):
+    """x: [M, K] f32, w: [K] f32 -> quantised y = (x * r) * w, r = 1/sqrt(mean(x^2) + eps) per row; optionally y itself."""
+    import torch
+    M, K = x.shape
+    Mp = Mp or pad_rows(M)
+    aq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
+    asc = torch.empty((K // 32, Mp), dtype=torch.float32, device=x.device)
+    h = torch.empty((M, K), dtype=torch.float32, device=x.device) if want_h else None
+    _check(lib().izb_rmsnorm_quant(_p(x), x.stride(0), _p(w), C.c_float(eps), M, Mp, K, _p(h), _p(aq), _p(asc), None, _stream()))
     return aq, asc, h
 
 

@@ -119,8 +119,8 @@ constexpr int kMaxDev = 16;
 struct DevState {
   std::mutex mu;
   uint32_t* err_word = nullptr;
-  void* ws[4] = {nullptr, nullptr, nullptr, nullptr};  // scratch arenas by user (izb_common.cuh: kWs*)
-  size_t ws_bytes[4] = {0, 0, 0, 0};
+  void* ws[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // scratch arenas by user (izb_common.cuh: kWs*)
+  size_t ws_bytes[5] = {0, 0, 0, 0, 0};
   void* stage = nullptr;  // staging of the host-buffer call
   size_t stage_bytes = 0;
   cudaStream_t hs[3] = {nullptr, nullptr, nullptr};  // host-buffer call: copy-in, compute, copy-out streams

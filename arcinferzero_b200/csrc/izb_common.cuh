@@ -77,7 +77,7 @@ uint32_t* izb_device_error_word(int device);
 // Per-device scratch arenas, one per user so that independent users never share bytes; each is grown on demand
 // (cudaMalloc only when a call needs more than any call before it).  Calls that use the same arena must be ordered on
 // one stream.
-enum { kWsGemm = 0, kWsTp = 1, kWsMoe = 2, kWsCheck = 3 };
+enum { kWsGemm = 0, kWsTp = 1, kWsMoe = 2, kWsCheck = 3, kWsNorm = 4 };
 int izb_workspace(int device, int slot, size_t bytes, void** out);
 
 // ---------------------------------------------------------------------------------------------- device helpers

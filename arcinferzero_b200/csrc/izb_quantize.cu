@@ -11,11 +11,42 @@
 
 namespace {
 
-template <bool kSwiglu>
+// 1 / sqrt(mean(x^2) + eps) of every row, in a summation order that is part of the definition (the CPU oracle repeats
+// it, so the quantised rows that follow are reproducible bit for bit): thread t of 256 accumulates x[t], x[t + 256], ...
+// with fused multiply-adds; every warp folds its 32 partial sums with the xor butterfly 16, 8, 4, 2, 1; the eight warp
+// sums are added in warp order.  (rmsnorm_quant, zero/kernels/ops.cl:108-120, leaves the order to the OpenCL work-group
+// reduction.)
+__global__ void __launch_bounds__(256) rms_rows_kernel(const float* __restrict__ x, int ldx, int M, int K, float eps,
+                                                       float* __restrict__ rrow) {
+  __shared__ float s_w[8];
+  const int m = blockIdx.x;
+  const float* xr = x + (size_t)m * ldx;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < K; i += 256) {
+    const float v = xr[i];
+    ss = __fmaf_rn(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xFFFFFFFFu, ss, o));
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = s_w[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t = __fadd_rn(t, s_w[w]);
+    rrow[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)K), eps)));
+  }
+}
+
+// kMode 0: quantise x.  1 (SwiGLU): x holds gate | up at column offset F, quantise h = silu(gate) * up.
+// 2 (RMSNorm): quantise (x * rrow[m]) * wnorm[column].  hout (modes 1, 2): optional f32 copy of what is quantised.
+template <int kMode>
 __global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restrict__ x, int ldx, int M, int Mp, int K,
                                                            int8_t* __restrict__ aq, float* __restrict__ asc,
                                                            int16_t* __restrict__ absum, float* __restrict__ hout,
-                                                           int F /* kSwiglu: up projection at column offset F */) {
+                                                           int F /* mode 1: up projection at column offset F */,
+                                                           const float* __restrict__ rrow, const float* __restrict__ wnorm) {
+  constexpr bool kSwiglu = kMode == 1;
   __shared__ float s_sc[8][33];
   __shared__ int16_t s_sum[16][34];
   const int sb = blockIdx.x, m0 = blockIdx.y * 32, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -37,6 +68,18 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restri
         for (int k = 0; k < 8; ++k) v[i][k] = __fmul_rn(__fdiv_rn(v[i][k], __fadd_rn(1.0f, expf(-v[i][k]))), u[k]);
         if (hout) {
           float4* ph = reinterpret_cast<float4*>(hout + (size_t)m * F + col);
+          ph[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          ph[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
+      }
+      if (kMode == 2) {  // y = x * r * w  (zero/kernels/ops.cl:131: the two products in this order)
+        const float r = rrow[m];
+        const float4 wa = *reinterpret_cast<const float4*>(wnorm + col), wb = *reinterpret_cast<const float4*>(wnorm + col + 4);
+        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[i][k] = __fmul_rn(__fmul_rn(v[i][k], r), wv[k]);
+        if (hout) {
+          float4* ph = reinterpret_cast<float4*>(hout + (size_t)m * K + col);
           ph[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
           ph[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
         }
@@ -103,7 +146,7 @@ extern "C" int izb_quantize_act(const float* d_x, int ldx, int M_valid, int Mp, 
                                 int16_t* d_absum, void* stream) {
   if (int rc = check_quant_args(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, K)) return rc;
   dim3 grid(K / 256, (Mp + 31) / 32);
-  IZB_LAUNCH("quantize_act", (cudaStream_t)stream, quantize_act_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0));
+  IZB_LAUNCH("quantize_act", (cudaStream_t)stream, quantize_act_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0, nullptr, nullptr));
   return IZB_OK;
 }
 
@@ -113,9 +156,27 @@ extern "C" int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_va
   if (d_h && !izb_aligned(d_h, 16)) IZB_FAIL(IZB_ERR_ALIGN, "swiglu_quant: h not 16-byte aligned");
   dim3 grid(F / 256, (Mp + 31) / 32);
   if (split)
-    quantize_act_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F);
+    quantize_act_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F, nullptr, nullptr);
   else
-    quantize_act_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0);
+    quantize_act_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0, nullptr, nullptr);
   IZB_LAUNCHED();
+  return IZB_OK;
+}
+
+extern "C" int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, float eps, int M_valid, int Mp, int K, float* d_h,
+                                 int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream) {
+  if (int rc = check_quant_args(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, K)) return rc;
+  if (!d_w) IZB_FAIL(IZB_ERR_ARG, "rmsnorm_quant: null weight");
+  if (!izb_aligned(d_w, 16) || (d_h && !izb_aligned(d_h, 16))) IZB_FAIL(IZB_ERR_ALIGN, "rmsnorm_quant: w and h must be 16-byte aligned");
+  if (!(eps >= 0.0f)) IZB_FAIL(IZB_ERR_ARG, "rmsnorm_quant: eps = %g", (double)eps);
+  cudaStream_t st = (cudaStream_t)stream;
+  int dev = 0;
+  IZB_CUDA(cudaGetDevice(&dev));
+  void* ws = nullptr;
+  if (int rc = izb_workspace(dev, kWsNorm, (size_t)Mp * 4, &ws)) return rc;
+  float* rrow = (float*)ws;
+  if (M_valid > 0) IZB_LAUNCH("rms_rows", st, rms_rows_kernel<<<M_valid, 256, 0, st>>>(d_x, ldx, M_valid, K, eps, rrow));
+  dim3 grid(K / 256, (Mp + 31) / 32);
+  IZB_LAUNCH("rmsnorm_quant", st, quantize_act_kernel<2><<<grid, 256, 0, st>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, d_h, 0, rrow, d_w));
   return IZB_OK;
 }

@@ -86,6 +86,13 @@ class Engine {
     check(izb_swiglu_quant(gu, ldgu, 1, cur_T_, Mp, F, nullptr, aq_, asc_, nullptr, stream_), "swiglu_quant");
     cur_K_ = F; cur_Mp_ = Mp;
   }
+  // rmsnorm_quant (zero/kernels/ops.cl:104): rows x -> quantised (x * r) * w, r = 1/sqrt(mean(x^2) + eps); hout (may be
+  // null) receives the normalised rows as f32
+  void rmsnorm_quant(const float* x, int ldx, const float* w, float eps, int K, int Mp, float* hout = nullptr) {
+    if (Mp > max_rows_ || K > max_k_) throw std::runtime_error("rmsnorm_quant: activation buffers too small");
+    check(izb_rmsnorm_quant(x, ldx, w, eps, cur_T_, Mp, K, hout, aq_, asc_, nullptr, stream_), "rmsnorm_quant");
+    cur_K_ = K; cur_Mp_ = Mp;
+  }
   // matmul (zero/engine.h:1080): C[.][c_off + n] (op)= quantised rows x w; acc 0 store, 1 add, 2 fused SwiGLU.
   // `name` is the reference's profiling label; act32 is always on (per-32 scales, the reference's default).
   void matmul(const char* name, const GpuWeight& w, int Mp, float* C, int ldc, int c_off, int acc, bool act32 = true) {

@@ -93,6 +93,13 @@ int izb_quantize_act(const float* d_x, int ldx, int M_valid, int Mp, int K, int8
  * split == 0: plain quantise).  d_h (may be NULL) receives h as f32 [M_valid][F]. */
 int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_valid, int Mp, int F, float* d_h, int8_t* d_aq,
                      float* d_asc, int16_t* d_absum, void* stream);
+/* RMSNorm then quantise (ops.cl rmsnorm_quant, zero/kernels/ops.cl:104-141): y = (x * r) * w with
+ * r = 1 / sqrt(sum(x^2) / K + eps) per row, quantised like izb_quantize_act; d_h (may be NULL) receives y as f32
+ * [M_valid][K].  d_w: [K] f32.  The reference leaves the order of the sum of squares to the OpenCL work-group reduction;
+ * here it is defined (256 strided fused-multiply-add chains, xor butterfly per 32, eight partial sums in order), so that
+ * the int8 rows are reproducible bit for bit; the oracle repeats that order. */
+int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, float eps, int M_valid, int Mp, int K, float* d_h,
+                      int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ matmul
  * Replaces Engine::matmul / matmul1 (zero/engine.h:1080,1147-1251): C[t][c_off + n] (op)= sum_k A[t][k] W[n][k] for

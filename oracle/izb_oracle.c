@@ -162,6 +162,43 @@ void orc_quantize_act(const float* x, int M, int K, int ldx, int Mp, int8_t* aq,
   }
 }
 
+/* ---------------------------------------------------------------- RMSNorm + quantise
+ * rmsnorm_quant, zero/kernels/ops.cl:104-141: r = rsqrt(sum(x^2) / K + eps); y = x * r * w; then quant_store16.  The
+ * kernel leaves the order of the sum to the OpenCL work-group reduction; the order written here is the CUDA kernel's
+ * (256 strided chains of fused multiply-adds, xor butterfly over each group of 32, the eight group sums in order), so
+ * that both produce the same bits.  hout (may be NULL): y as f32 [M][K]. */
+void orc_rmsnorm_quant(const float* x, int M, int K, int ldx, const float* w, float eps, int Mp, float* hout, int8_t* aq,
+                       float* asc, int16_t* absum) {
+  float* y = (float*)malloc((size_t)(M > 0 ? M : 1) * K * sizeof(float));
+  for (int m = 0; m < M; ++m) {
+    const float* xr = x + (size_t)m * ldx;
+    float part[256];
+    for (int t = 0; t < 256; ++t) {
+      float ss = 0.0f;
+      for (int i = t; i < K; i += 256) ss = fmaf(xr[i], xr[i], ss);
+      part[t] = ss;
+    }
+    float total = 0.0f;
+    for (int g = 0; g < 8; ++g) {
+      float v[32], n[32];
+      memcpy(v, part + 32 * g, sizeof v);
+      for (int o = 16; o > 0; o >>= 1) {
+        for (int l = 0; l < 32; ++l) n[l] = v[l] + v[l ^ o];
+        memcpy(v, n, sizeof v);
+      }
+      total = g == 0 ? v[0] : total + v[0];
+    }
+    const float r = 1.0f / sqrtf(total / (float)K + eps);
+    for (int i = 0; i < K; ++i) {
+      const float xr_r = xr[i] * r;
+      y[(size_t)m * K + i] = xr_r * w[i];
+    }
+  }
+  if (hout) memcpy(hout, y, (size_t)M * K * sizeof(float));
+  orc_quantize_act(y, M, K, K, Mp, aq, asc, absum);
+  free(y);
+}
+
 /* ---------------------------------------------------------------- per-block integer dots
  * zero/kernels/decode.cl:992-999, zero/kernels/gemm.cl:413-423: dot[m][n][b] = sum_i aq[m][32b+i] * qw[n][32b+i] (int32),
  * asum[m][b] = sum_i aq[m][32b+i].  These are the values every GPU kernel must reproduce bit for bit. */

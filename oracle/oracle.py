@@ -77,6 +77,20 @@ def quantize_act(x: np.ndarray, Mp: int | None = None, want_absum: bool = True):
     return aq, asc, absum
 
 
+def rmsnorm_quant(x: np.ndarray, w: np.ndarray, eps: float, Mp: int | None = None):
+    """y = (x * r) * w, r = 1/sqrt(sum(x^2)/K + eps) per row in the CUDA kernel's summation order -> y, aq, asc, absum."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    M, K = x.shape
+    Mp = Mp or M
+    y = np.empty((M, K), np.float32)
+    aq = np.empty((Mp, K), np.int8)
+    asc = np.empty((K // 32, Mp), np.float32)
+    absum = np.empty((K // 16, Mp), np.int16)
+    lib().orc_rmsnorm_quant(_vp(x), M, K, K, _vp(w), C.c_float(eps), Mp, _vp(y), _vp(aq), _vp(asc), _vp(absum))
+    return y, aq, asc, absum
+
+
 def decode_q4k_sb(p: np.ndarray):
     d, dmin = C.c_float(), C.c_float()
     sc, mn, q = np.empty(8, np.uint8), np.empty(8, np.uint8), np.empty(256, np.uint8)
@@ -202,6 +216,15 @@ def ref_quantize_act(x: np.ndarray):
     aq, asc, absum = np.empty((M, K), np.int8), np.empty((K // 32, M), np.float32), np.empty((K // 16, M), np.uint16)
     ref().ref_quantize_act(_vp(x), M, K, _vp(aq), _vp(asc), _vp(absum))
     return aq, asc, absum.view(np.int16)
+
+
+def ref_rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """tools/ref_forward.cpp rmsnorm() row by row."""
+    y = np.array(x, np.float32, copy=True, order="C")
+    w = np.ascontiguousarray(w, np.float32)
+    for m in range(y.shape[0]):
+        ref().ref_rmsnorm(_vp(y[m]), y.shape[1], _vp(w), C.c_float(eps))
+    return y
 
 
 def ref_decode_sb(qtype: int, p: np.ndarray):

@@ -21,6 +21,9 @@ void ref_quantize_act(const float* x, int M, int K, int8_t* aq, float* asc, uint
   quantize_act_cpu(x, M, K, aq, asc, absum, true);
 }
 
+// tools/ref_forward.cpp:314: in-place y = x * r * w, r from a double-precision sum of squares
+void ref_rmsnorm(float* x, int n, const float* w, float eps) { rmsnorm(x, n, w, eps); }
+
 // src/quants.h:89: one 256-element superblock (type 12: 144 B; type 8: eight 34-byte blocks)
 void ref_decode_sb(uint32_t type, const uint8_t* p, float* d, float* dmin, uint8_t* sc, uint8_t* mn, int16_t* q, float* d8) {
   DecodedSB o;

@@ -7,6 +7,7 @@ What is stored (all inputs seeded; every array small):
   fp16.npz       fp16_to_f32 over every 16-bit pattern, f32_to_fp16 over a seeded sample (src/quants.h:17-52)
   forward.npz    tools/ref_forward.cpp:251 matmul() outputs (REF_Q=all REF_QB=32) on small Q4_K / Q8_0 tensors
   rawsb.npz      gpu_raw_sb (src/quants.h:728) of Q8_0 superblocks: the regrouped form the weight loader must make
+  rmsnorm.npz    tools/ref_forward.cpp:314 rmsnorm() rows (double-precision sum of squares)
 """
 import os
 import sys
@@ -77,6 +78,15 @@ def main():
     # ---- reference GPU raw form of Q8_0
     raw = np.stack([O.ref_gpu_raw_sb(8, w8[n, 272 * s:272 * (s + 1)]) for n in range(6) for s in range(2)])
     np.savez_compressed(os.path.join(OUT, "rawsb.npz"), raw8=raw)
+    # ---- rmsnorm (tools/ref_forward.cpp:314) on rows of several magnitudes, one all-zero row
+    r2 = np.random.default_rng(7)
+    xn = r2.standard_normal((6, 1024), dtype=np.float32)
+    xn[1] *= 1e-3
+    xn[2] *= 300.0
+    xn[3] = 0.0
+    wn = (1.0 + 0.1 * r2.standard_normal(1024)).astype(np.float32)
+    yn = O.ref_rmsnorm(xn, wn, 1e-6)
+    np.savez_compressed(os.path.join(OUT, "rmsnorm.npz"), x=xn, w=wn, eps=np.float32(1e-6), y=yn)
     print("golden vectors written to", OUT)
 
 

@@ -77,6 +77,24 @@ def test_swiglu_quant_stagewise(izb, torch):
     assert (aq.cpu().numpy() == raq).all() and (bits(asc.cpu().numpy()) == bits(rasc)).all()
 
 
+@pytest.mark.parametrize("M,K", [(37, 5120), (300, 1024), (1, 256)])
+def test_rmsnorm_quant_bit_exact(izb, torch, M, K):
+    """izb_rmsnorm_quant against the oracle: the sum of squares is taken in the same defined order, so the normalised
+    rows, the int8 values and the scales are identical bit for bit; padding rows are zero."""
+    rng = np.random.default_rng(M * 7 + K)
+    x = rng.standard_normal((M, K), dtype=np.float32) * rng.uniform(0.01, 30.0, (M, 1)).astype(np.float32)
+    if M > 2:
+        x[2] = 0.0
+    w = (1.0 + 0.2 * rng.standard_normal(K)).astype(np.float32)
+    aq, asc, h = izb.rmsnorm_quant(dev(torch, x), dev(torch, w), 1e-6, want_h=True)
+    Mp = asc.shape[1]
+    ry, raq, rasc, _ = O.rmsnorm_quant(x, w, 1e-6, Mp=Mp)
+    assert (bits(h.cpu().numpy()) == bits(ry)).all()
+    assert (aq.cpu().numpy() == raq).all()
+    assert (bits(asc.cpu().numpy()) == bits(rasc)).all()
+    assert (aq.cpu().numpy()[M:] == 0).all()
+
+
 # ------------------------------------------------------------------------------------------------ GEMV
 @pytest.mark.parametrize("qt", [12, 8])
 @pytest.mark.parametrize("T", [1, 2, 3, 8])

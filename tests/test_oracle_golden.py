@@ -148,3 +148,19 @@ def test_tp_range_properties():
             sizes = [e - b for b, e in rs]
             assert all(s % unit == 0 for s in sizes) and sizes == sorted(sizes, reverse=True)
             assert max(sizes) - min(sizes) <= unit
+
+
+def test_rmsnorm_quant_matches_reference_rows(golden_dir):
+    """The restated rmsnorm_quant (zero/kernels/ops.cl:104-141, f32 sum in a defined order) against
+    tools/ref_forward.cpp's rmsnorm (double sum): the normalised rows agree to float rounding, the quantised rows are the
+    quantiser applied to them."""
+    g = np.load(os.path.join(golden_dir, "rmsnorm.npz"))
+    y, aq, asc, absum = O.rmsnorm_quant(g["x"], g["w"], float(g["eps"]), Mp=16)
+    err = np.max(np.abs(y.astype(np.float64) - g["y"].astype(np.float64))) / np.max(np.abs(g["y"]))
+    assert err <= 2e-6, err
+    assert (y[3] == 0).all()  # the all-zero row stays zero (r = 1/sqrt(eps) is finite)
+    raq, rasc, rabsum = O.quantize_act(y, Mp=16)
+    assert (aq == raq).all() and (bits(asc) == bits(rasc)).all() and (absum == rabsum).all()
+    if O.ref() is not None:
+        live = O.ref_rmsnorm(g["x"], g["w"], float(g["eps"]))
+        assert (bits(live) == bits(g["y"])).all()

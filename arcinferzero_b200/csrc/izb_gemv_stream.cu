@@ -381,6 +381,209 @@ int launch_q4k_reg(const izb_weight* w, const uint8_t* raw, const int8_t* aq, co
   return IZB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------- Q4_K, 2..4 activation rows
+// The same lane mapping, row pairs and ring as gemv_q4k_reg_kernel, for a few activation rows: their bytes do not fit
+// the registers, so each CTA stages them once in shared memory in the per-lane form the loop reads (per step and
+// token: four 16-byte pieces, the two block scales -- the second one / 16 -- and the two scaled block sums per lane).
+// A weight row's nibbles are masked once and multiplied into every token's accumulators.
+constexpr int kPairWarps = 16;
+constexpr int kPairActBytes = 4 * 512 + 4 * 128;  // per (step, token)
+
+template <int NSB4, int T>
+__global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_pair_kernel(const uint8_t* __restrict__ raw, int N,
+                                                                          const int8_t* __restrict__ aq, const float* __restrict__ asc,
+                                                                          int Mp, float* __restrict__ C, int ldc, int c_off, int acc,
+                                                                          int slots, int slot_bytes, uint32_t* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int nsb = 4 * NSB4, WS = (nsb + 7) / 8, K = nsb * 256;
+  constexpr uint32_t row_bytes = nsb * 144;
+  constexpr int kActBytes = WS * T * kPairActBytes;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int W = gridDim.x * kPairWarps, w0 = blockIdx.x * kPairWarps + warp;
+  const int my_rows = w0 < N ? (N - w0 + W - 1) / W : 0;
+  const int sub = lane >> 2, pp = lane & 3;
+  unsigned char* act = smem;
+  unsigned char* ring = smem + kActBytes + (size_t)warp * slots * slot_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kActBytes + (size_t)kPairWarps * slots * slot_bytes) + warp * slots;
+  if (lane == 0) {
+    for (int s = 0; s < slots; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(&bars[s])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int s = 0; s < slots && s < my_rows; ++s)
+      row_copy(s_u32(ring + (size_t)s * slot_bytes), raw + (size_t)(w0 + s * W) * row_bytes, row_bytes, s_u32(&bars[s]));
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // (see gemv_q4k_reg_kernel: the ring fill above runs ahead of it)
+  // ---- stage the activations: entry (step, token, lane)
+  for (int i = threadIdx.x; i < WS * T * 32; i += blockDim.x) {
+    const int l = i & 31, t = (i >> 5) % T, st = (i >> 5) / T;
+    const int sb = st * 8 + (l >> 2), p2 = l & 3;
+    uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, a2 = a0, a3 = a0;
+    float4 sc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (sb < nsb) {
+      const int8_t* a = aq + (size_t)t * K + sb * 256 + p2 * 64;
+      a0 = *reinterpret_cast<const uint4*>(a);
+      a1 = *reinterpret_cast<const uint4*>(a + 16);
+      a2 = *reinterpret_cast<const uint4*>(a + 32);
+      a3 = *reinterpret_cast<const uint4*>(a + 48);
+      const int b = sb * 8 + p2 * 2;
+      const float s0 = asc[(size_t)b * Mp + t], s1 = asc[(size_t)(b + 1) * Mp + t];
+      const uint32_t lw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, hw[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+      int sl = 0, sh = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        sl = __dp4a((int)lw[k], 0x01010101, sl);
+        sh = __dp4a((int)hw[k], 0x01010101, sh);
+      }
+      sc = make_float4(s0, s1 * 0.0625f, s0 * (float)sl, s1 * (float)sh);
+    }
+    unsigned char* base = act + (size_t)(st * T + t) * kPairActBytes;
+    reinterpret_cast<uint4*>(base)[l] = a0;
+    reinterpret_cast<uint4*>(base + 512)[l] = a1;
+    reinterpret_cast<uint4*>(base + 1024)[l] = a2;
+    reinterpret_cast<uint4*>(base + 1536)[l] = a3;
+    reinterpret_cast<float4*>(base + 2048)[l] = sc;
+  }
+  __syncthreads();
+  const int pp_sh = 16 * (pp & 1);
+  const bool pp_upper = pp >= 2;
+  const uint32_t h_off = sub * 144, q_off = sub * 144 + 16 + 32 * pp;
+
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < my_rows; i += 2) {
+    const bool two = i + 1 < my_rows;  // (uniform over the warp)
+    bool ready = false;
+    for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[slot]), parity);
+    if (ready && two) {
+      ready = false;
+      for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[slot + 1]), parity);
+    }
+    if (!ready) {  // (bounded wait gave up)
+      if (lane == 0) atomicOr(err, 64u);
+      break;
+    }
+    const unsigned char* wp[2] = {ring + (size_t)slot * slot_bytes, ring + (size_t)(two ? slot + 1 : slot) * slot_bytes};
+    float accv[2][T];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int t = 0; t < T; ++t) accv[r][t] = 0.0f;
+#pragma unroll
+    for (int st = 0; st < WS; ++st) {
+      if (st * 8 + 7 < nsb || sub < nsb - st * 8) {
+        uint32_t wl[2][8], wh[2][8], sc2[2], mn2[2];
+        float2 df[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint4 h = *reinterpret_cast<const uint4*>(wp[r] + st * 1152 + h_off);
+          const uint4 qa = *reinterpret_cast<const uint4*>(wp[r] + st * 1152 + q_off);
+          const uint4 qb = *reinterpret_cast<const uint4*>(wp[r] + st * 1152 + q_off + 16);
+          df[r] = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+          q4k_pair(h, pp_sh, pp_upper, sc2[r], mn2[r]);
+          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            wl[r][kk] = w[kk] & 0x0F0F0F0Fu;
+            wh[r][kk] = w[kk] & 0xF0F0F0F0u;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          const unsigned char* base = act + (size_t)(st * T + t) * kPairActBytes;
+          const uint4 a0 = reinterpret_cast<const uint4*>(base)[lane], a1 = reinterpret_cast<const uint4*>(base + 512)[lane];
+          const uint4 a2 = reinterpret_cast<const uint4*>(base + 1024)[lane], a3 = reinterpret_cast<const uint4*>(base + 1536)[lane];
+          const float4 sc = reinterpret_cast<const float4*>(base + 2048)[lane];  // (s0, s1/16, s0*sum0, s1*sum1)
+          const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              lo0 = __dp4a((int)al[kk], (int)wl[r][kk], lo0);
+              lo1 = __dp4a((int)al[4 + kk], (int)wl[r][4 + kk], lo1);
+              hi0 = dp4a_su((int)ah[kk], wh[r][kk], hi0);
+              hi1 = dp4a_su((int)ah[4 + kk], wh[r][4 + kk], hi1);
+            }
+            const float tq = fmaf(sc.x, (float)((int)(sc2[r] & 0xFFu) * (lo0 + lo1)), sc.y * (float)((int)(sc2[r] >> 8) * (hi0 + hi1)));
+            const float tm = fmaf(sc.z, (float)(mn2[r] & 0xFFu), sc.w * (float)(mn2[r] >> 8));
+            accv[r][t] = fmaf(df[r].x, tq, fmaf(-df[r].y, tm, accv[r][t]));
+          }
+        }
+      }
+    }
+    __syncwarp();
+    const int row = w0 + i * W;
+    if (lane == 0) {
+      if (i + slots < my_rows)
+        row_copy(s_u32(ring + (size_t)slot * slot_bytes), raw + (size_t)(row + slots * W) * row_bytes, row_bytes, s_u32(&bars[slot]));
+      if (i + 1 + slots < my_rows)
+        row_copy(s_u32(ring + (size_t)(slot + 1) * slot_bytes), raw + (size_t)(row + (slots + 1) * W) * row_bytes, row_bytes, s_u32(&bars[slot + 1]));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        const float v = warp_sum(accv[r][t]);
+        if (lane == 0 && (r == 0 || two)) {
+          float* c = C + (size_t)t * ldc + c_off + row + r * W;
+          *c = acc ? *c + v : v;
+        }
+      }
+    slot += 2;
+    if (slot >= slots) { slot = 0; parity ^= 1; }
+  }
+}
+
+template <int NSB4, int T>
+int launch_q4k_pair(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc, int c_off,
+                    int acc, cudaStream_t st) {
+  constexpr size_t kBudget = 216 * 1024;
+  constexpr int WS = (4 * NSB4 + 7) / 8;
+  const size_t act = (size_t)WS * T * kPairActBytes;
+  const int slot_bytes = (int)((w->row_bytes + 127) & ~(size_t)127);
+  int slots = (int)((kBudget - act - 4096) / ((size_t)kPairWarps * slot_bytes));
+  slots = slots > 8 ? 8 : (slots & ~1);
+  if (slots < 2) return 1;
+  const size_t smem = act + (size_t)kPairWarps * slots * slot_bytes + (size_t)kPairWarps * slots * 8;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    IZB_CUDA(cudaGetDevice(&dev));
+    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    IZB_CUDA(cudaFuncSetAttribute(gemv_q4k_pair_kernel<NSB4, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
+  }
+  int grid = sms;
+  const int need = (w->N + kPairWarps - 1) / kPairWarps;
+  if (grid > need) grid = need;
+  uint32_t* err = izb_device_error_word(w->device);
+  if (!err) IZB_FAIL(IZB_ERR_NOMEM, "gemv: no device error word");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kPairWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int N = w->N;
+  IZB_LAUNCH("gemv", st, cudaLaunchKernelEx(&cfg, gemv_q4k_pair_kernel<NSB4, T>, raw, N, aq, asc, Mp, C, ldc, c_off, acc, slots, slot_bytes, err));
+  return IZB_OK;
+}
+
+template <int T>
+int launch_q4k_pair_k(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc, int c_off,
+                      int acc, cudaStream_t st) {
+  switch (w->K / 1024) {
+    case 1: return launch_q4k_pair<1, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 2: return launch_q4k_pair<2, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 3: return launch_q4k_pair<3, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    case 4: return launch_q4k_pair<4, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+    default: return launch_q4k_pair<5, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+  }
+}
+
 template <int QT, int T>
 int launch_stream(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc,
                   int c_off, int acc, cudaStream_t st) {
@@ -431,6 +634,13 @@ int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t
       case 3: return launch_q4k_reg<3>(w, raw, aq, asc, Mp, C, c_off, acc, st);
       case 4: return launch_q4k_reg<4>(w, raw, aq, asc, Mp, C, c_off, acc, st);
       default: return launch_q4k_reg<5>(w, raw, aq, asc, Mp, C, c_off, acc, st);
+    }
+  }
+  if (T >= 2 && T <= 4 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= 8192) {
+    switch (T) {
+      case 2: return launch_q4k_pair_k<2>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+      case 3: return launch_q4k_pair_k<3>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
+      default: return launch_q4k_pair_k<4>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
     }
   }
   switch (T) {

@@ -1,5 +1,5 @@
 // Builds the reference's own CPU code for the path into oracle/_ref/libizb_ref.so, from the sources where they lie
-// (REF_ROOT, default /root/reference): nothing of the reference is copied.  TEST INFRASTRUCTURE ONLY: used to pin the
+// (the REF_ROOT of oracle/Makefile): nothing of the reference is copied.  TEST INFRASTRUCTURE ONLY: used to pin the
 // C restatement in izb_oracle.c, to generate tests/golden/, and as the "reference" CPU baseline of the benchmark.
 //
 // The translation unit includes tools/ref_forward.cpp whole (its main renamed), so its static matmul() -- dequant_row

@@ -118,6 +118,31 @@ def test_gemv_matches_oracle(izb, torch, qt, T, N, K):
     W.close()
 
 
+@pytest.mark.parametrize("T", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(8195, 1024), (9001, 3072), (8200, 5120), (17408, 5120)])
+def test_gemv_q4k_many_rows(izb, torch, T, N, K):
+    """The Q4_K decode kernels taken from 8192 weight rows on (activations in registers for one row, staged per lane for
+    2..4; two weight rows per warp pass): odd row counts, K with a half-empty last step, store offset and accumulate."""
+    qt = 12
+    w = S.make_weight(qt, N, K, 77 + N + K)
+    x = S.make_act(T, K, 88 + T + K)
+    aq, asc, _ = O.quantize_act(x, Mp=16)
+    W = izb.Weight(qt, w, N, K)
+    out = torch.full((T, N + 8), float("nan"), dtype=torch.float32, device="cuda")
+    izb.gemv(W, dev(torch, aq), dev(torch, asc), T, out=out, c_off=4)
+    got = out.cpu().numpy()
+    assert np.isnan(got[:, :4]).all() and np.isnan(got[:, N + 4:]).all()
+    ref = O.matmul(qt, w, K, aq, asc, T, "gemv")
+    assert rel(got[:, 4:N + 4], ref) < TOL
+    assert rel(got[:, 4:N + 4], O.matmul(qt, w, K, aq, asc, T, "f64")) < TOL
+    base = np.random.default_rng(6).standard_normal((T, N)).astype(np.float32) * 50
+    o2 = dev(torch, base)
+    izb.gemv(W, dev(torch, aq), dev(torch, asc), T, out=o2, acc=1)
+    assert rel(o2.cpu().numpy() - base, ref) < 1e-4
+    assert izb.device_status(0) == 0
+    W.close()
+
+
 def test_matmul_dispatch_by_rows(izb, torch):
     K, N = 1024, 64
     for qt in (12, 8):

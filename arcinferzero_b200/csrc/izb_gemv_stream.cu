@@ -625,9 +625,14 @@ static int stream_t(const izb_weight* w, const uint8_t* raw, const int8_t* aq, c
                              : launch_stream<IZB_Q8_0, T>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
 }
 
+#ifndef IZB_MANY_ROWS
+#define IZB_MANY_ROWS 1024
+#endif
+constexpr int kManyRows = IZB_MANY_ROWS;  // below it the matrix is a few hundred KB and the generic kernel does as well
+
 int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int T, int Mp, float* C,
                            int ldc, int c_off, int acc, cudaStream_t st) {
-  if (T == 1 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= 8192) {  // (fewer rows: under four per warp)
+  if (T == 1 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= kManyRows) {
     switch (w->K / 1024) {
       case 1: return launch_q4k_reg<1>(w, raw, aq, asc, Mp, C, c_off, acc, st);
       case 2: return launch_q4k_reg<2>(w, raw, aq, asc, Mp, C, c_off, acc, st);
@@ -636,7 +641,7 @@ int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t
       default: return launch_q4k_reg<5>(w, raw, aq, asc, Mp, C, c_off, acc, st);
     }
   }
-  if (T >= 2 && T <= 4 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= 8192) {
+  if (T >= 2 && T <= 4 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= kManyRows) {
     switch (T) {
       case 2: return launch_q4k_pair_k<2>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);
       case 3: return launch_q4k_pair_k<3>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st);

@@ -228,6 +228,34 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
     return res
 
 
+def q8_config1_section(izb, torch, tc_peak: float, iters: int = 20) -> dict:
+    """BASELINE.json config 1 (the reference's CPU-runnable case): one Q8_0 GEMM, M = 512, N = K = 4096, through the same
+    tensor-core kernel; device-timed, quantiser included."""
+    from arcinferzero_b200 import synth as S
+    Mq, Nq, Kq = 512, 4096, 4096
+    W = izb.Weight(8, S.make_weight(8, Nq, Kq, SEED + 21), Nq, Kq)
+    x = torch.from_numpy(S.make_act(Mq, Kq, SEED + 22)).cuda()
+    out = torch.empty((Mq, Nq), dtype=torch.float32, device="cuda")
+    aq = torch.empty((Mq, Kq), dtype=torch.int8, device="cuda")
+    asc = torch.empty((Kq // 32, Mq), dtype=torch.float32, device="cuda")
+    for _ in range(3):
+        izb.quantize_act(x, Mp=Mq, out=(aq, asc, None))
+        izb.matmul(W, aq, asc, Mq, out=out)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        izb.quantize_act(x, Mp=Mq, out=(aq, asc, None))
+        izb.matmul(W, aq, asc, Mq, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    tops = 2.0 * Mq * Nq * Kq / (ms * 1e-3) / 1e12
+    W.close()
+    return {"workload": "config 1: Q8_0 GEMM M=512 N=4096 K=4096 (quantize_act + GEMM)", "ms_per_step": ms,
+            "tokens_per_s": Mq / (ms * 1e-3), "tops": tops, "frac_of_tensor_peak": tops / tc_peak,
+            "note": "128 tiles on 148 SMs: a single partial wave, host launch cost included"}
+
+
 def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens: int, passes: int = 2) -> list:
     """BASELINE.json config 5: the projections of 8 dense layers (Q4_K, hidden 5120, FFN 17408, 7168 QKV rows) over 32768
     token rows, split over the ranks as the reference's tensor-parallel mode splits them, in both summation modes of
@@ -443,6 +471,7 @@ def main() -> None:
             line["tp_stack"] = tp_stack
         if not args.no_moe and world == 1:
             line["moe"] = moe_section(izb, torch, tc_sus, src)
+            line["q8_0_gemm_config1"] = q8_config1_section(izb, torch, tc_sus)
         if not args.no_gemv and world == 1:
             line["decode_gemv"] = gemv_section(izb, torch, hbm, src)
         if not args.no_cpu_baseline and world == 1:

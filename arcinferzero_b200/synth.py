@@ -87,20 +87,49 @@ def make_act(M: int, K: int, seed: int) -> np.ndarray:
     return np.random.default_rng(seed).standard_normal((M, K), dtype=np.float32)
 
 
-def write_gguf(path: str, tensors: dict[str, tuple[int, np.ndarray, int, int]]) -> None:
-    """Minimal GGUF v3 file (layout of src/gguf.h:306-359): tensors maps name -> (ggml_type, rows_bytes, N, K);
-    dims are stored as [K, N]; data is 32-byte aligned; no metadata keys."""
+def _gguf_value(v) -> bytes:
+    """u32 type + value of one metadata entry (int -> u32, float -> f32, str, bool, list of ints / strings)."""
+    def s8(x: str) -> bytes:
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+    if isinstance(v, bool):
+        return struct.pack("<I?", 7, v)
+    if isinstance(v, int):
+        return struct.pack("<II", 4, v)
+    if isinstance(v, float):
+        return struct.pack("<If", 6, v)
+    if isinstance(v, str):
+        return struct.pack("<I", 8) + s8(v)
+    if isinstance(v, (list, tuple)):
+        if v and isinstance(v[0], str):
+            return struct.pack("<IIQ", 9, 8, len(v)) + b"".join(s8(x) for x in v)
+        return struct.pack("<IIQ", 9, 5, len(v)) + b"".join(struct.pack("<i", x) for x in v)
+    raise TypeError(type(v))
+
+
+def write_gguf(path: str, tensors: dict[str, tuple], meta: dict | None = None) -> None:
+    """Minimal GGUF v3 file (layout of src/gguf.h:306-359): tensors maps name -> (ggml_type, rows_bytes, N, K) or
+    (ggml_type, rows_bytes, N, K, n_mats) for a stack of matrices; dims are stored as [K, N] / [K, N, n_mats]; data is
+    aligned to general.alignment (default 32); meta: optional key -> int / float / str / bool / list entries."""
+    meta = meta or {}
+    align = int(meta.get("general.alignment", 32))
     infos, blobs, off = [], [], 0
-    for name, (qtype, data, N, K) in tensors.items():
+    for name, spec in tensors.items():
+        qtype, data, N, K = spec[:4]
+        dims = (K, N) if len(spec) == 4 else (K, N, spec[4])
         b = np.ascontiguousarray(data).view(np.uint8).reshape(-1).tobytes()
         nb = name.encode()
-        infos.append(struct.pack("<Q", len(nb)) + nb + struct.pack("<I", 2) + struct.pack("<QQ", K, N)
+        infos.append(struct.pack("<Q", len(nb)) + nb + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
                      + struct.pack("<I", qtype) + struct.pack("<Q", off))
-        pad = (-len(b)) % 32
+        pad = (-len(b)) % align
         blobs.append(b + b"\0" * pad)
         off += len(b) + pad
-    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), 0) + b"".join(infos)
-    head += b"\0" * ((-len(head)) % 32)
+    kvs = b""
+    for k, v in meta.items():
+        kb = k.encode()
+        kvs += struct.pack("<Q", len(kb)) + kb + _gguf_value(v)
+    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), len(meta)) + kvs + b"".join(infos)
+    head += b"\0" * ((-len(head)) % align)
     with open(path, "wb") as f:
         f.write(head)
         for b in blobs:

@@ -48,15 +48,42 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons sampled while the timed region runs: NVML read-only queries from a thread every
+    few milliseconds (nvidia-smi every 100 ms when the NVML binding is missing)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.idx, self.rows, self.proc = gpu_index, [], None
+    def __init__(self, gpu_index: int, pci_bus_id: str | None = None):
+        self.idx, self.pci, self.rows, self.proc = gpu_index, pci_bus_id, [], None
+        self.sm, self.mx, self.reasons, self.stop_flag, self.thread, self.source = [], [], set(), False, None, None
+
+    def _nvml_loop(self, nv, h):
+        names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                 ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap))
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                for n, bit in names:
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                break
+            time.sleep(0.004)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByPciBusId(self.pci.encode()) if self.pci else nv.nvmlDeviceGetHandleByIndex(self.idx)
+            self.mx = [float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))]
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.source = "nvidia-smi"
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -69,6 +96,11 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self) -> dict:
+        if self.thread:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": max(self.mx) if self.mx else None,
+                    "reasons": sorted(self.reasons), "samples": len(self.sm), "source": self.source}
         if self.proc:
             self.proc.terminate()
             try:
@@ -84,7 +116,7 @@ class ClockSampler:
                     if v.lower().startswith("active"):
                         reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": self.source}
 
 
 def cpu_baseline(seconds_target: float = 15.0) -> dict:
@@ -392,7 +424,12 @@ def main() -> None:
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
-    sampler = ClockSampler(local)
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        pci = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+    except Exception:
+        pci = None
+    sampler = ClockSampler(local, pci)
     if rank == 0:
         sampler.start()
     launches0 = izb.launch_count()
@@ -457,7 +494,7 @@ def main() -> None:
                        "rows_per_rank": Nr},
             "roofline": {"bound": "tensor", "kernel": kname, "achieved": achieved, "peak": tc_sus, "unit": "TFLOP/s",
                          "frac": achieved / tc_sus, "peak_source": f"{src} dense bf16/fp16 (sustained; burst {tc_burst})",
-                         "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS,
+                         "frac_of_burst_peak": achieved / tc_burst, "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS,
                          # DRAM bytes per launch: one ncu capture of the same kernel at 2048 token rows and all weight rows
                          # (read 128.8 MB + written 114.2 MB), scaled by the 128x128 tiles this launch runs
                          "traffic": NCU_TRAFFIC_BYTES_PER_TILE * ((M + 127) // 128) * (Nr // 128),

@@ -68,7 +68,8 @@ def test_rejects_malformed_files(model, tmp_path):
 
 
 @pytest.mark.gpu
-def test_load_weight_from_file_matches_direct_upload(izb, torch, model):
+def test_load_weight_from_file_matches_direct_upload(izb, model):
+    import torch
     from oracle import oracle as O
     p, w4, _, _ = model
     x = S.make_act(3, 512, 5)

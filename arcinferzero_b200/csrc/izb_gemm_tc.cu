@@ -732,7 +732,9 @@ void tc_scratch_bytes(int n_tiles, int K, int sps, size_t* img_bytes, size_t* as
 // the activation pre-pass + the GEMM for one tile set
 int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int lda, int rows_total, const int32_t* tiles,
            int n_tiles_grid, const int32_t* rowmap, const float* rowscale, int M_store, float* C, int ldc, int c_off, int acc,
-           int32_t* dots, int ws_slot, cudaStream_t st) {
+           int32_t* dots, int ws_slot, cudaStream_t st, bool reuse_images = false) {
+  // reuse_images: the call before this one, on the same stream and arena, prepared the same activation rows for a weight
+  // of the same type and K (the up projection after the gate projection): its operand images are still there
   if (!w->has_tmap) return 1;
   if (w->N % BN || w->K % 256) return 1;
   const int K = w->K;
@@ -744,7 +746,8 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
   uint16_t* aimg = (uint16_t*)ws;
   float* ascimg = (float*)((unsigned char*)ws + img_bytes);
   dim3 pg((BM * (K / 8) + 255) / 256, n_tiles_grid);
-  if (w->type == IZB_Q4_K)
+  if (reuse_images) {
+  } else if (w->type == IZB_Q4_K)
     IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, ascimg, sps));
   else
     IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q8_0><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, ascimg, 4));
@@ -804,7 +807,8 @@ int izb_moe_gateup_tc(const izb_weight* wg, const izb_weight* wu, const int8_t* 
   const int F = wg->N;
   int rc = run_tc(wg, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, F, 0, 0, nullptr, kWsMoe, st);
   if (rc != 0) return rc;
-  return run_tc(wu, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, F, 0, 2, nullptr, kWsMoe, st);
+  const bool same = wu->type == wg->type && wu->K == wg->K;
+  return run_tc(wu, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, F, 0, 2, nullptr, kWsMoe, st, same);
 }
 
 int izb_moe_down_tc(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles, int max_tiles,

@@ -87,35 +87,49 @@ __global__ void moe_scan_kernel(const int32_t* __restrict__ counts, int NE, int 
 }
 
 // One CTA per expert: its pairs in increasing pair index take consecutive slots (a deterministic atomic_inc order).
+// A thread looks at four consecutive pairs per pass (one 128-bit load), so a pass covers 1024 pairs: an exclusive scan of
+// the per-thread counts over the warp (shuffles) and over the eight warps (shared memory, double-buffered so that one
+// barrier per pass is enough) gives every pair of the expert its slot.
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, int n,
                                                           int NU, const int32_t* __restrict__ offs, int32_t* __restrict__ stok,
                                                           float* __restrict__ swt, int32_t* __restrict__ inv) {
-  __shared__ int s_warp[8];
-  __shared__ int s_base;
+  __shared__ int s_warp[2][8];
   const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) s_base = offs[e];
-  __syncthreads();
-  for (int i0 = 0; i0 < n; i0 += 256) {
-    const int i = i0 + threadIdx.x;
-    const bool mine = i < n && ids[i] == e;
-    const unsigned bal = __ballot_sync(0xFFFFFFFFu, mine);
-    if (lane == 0) s_warp[warp] = __popc(bal);
+  int base = offs[e];  // (every thread keeps the running base: no broadcast needed)
+  int buf = 0;
+  for (int i0 = 0; i0 < n; i0 += 1024, buf ^= 1) {
+    const int i = i0 + 4 * threadIdx.x;
+    int4 v = make_int4(-1, -1, -1, -1);
+    if (i + 3 < n) {
+      v = *reinterpret_cast<const int4*>(ids + i);
+    } else {
+      if (i < n) v.x = ids[i];
+      if (i + 1 < n) v.y = ids[i + 1];
+      if (i + 2 < n) v.z = ids[i + 2];
+    }
+    const int m0 = v.x == e, m1 = v.y == e, m2 = v.z == e, m3 = v.w == e;
+    const int cnt = m0 + m1 + m2 + m3;
+    int incl = cnt;  // inclusive scan over the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) s_warp[buf][warp] = incl;
     __syncthreads();
     int before = 0, total = 0;
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
-      if (w < warp) before += s_warp[w];
-      total += s_warp[w];
+      const int c = s_warp[buf][w];
+      if (w < warp) before += c;
+      total += c;
     }
-    if (mine) {
-      const int s = s_base + before + __popc(bal & ((1u << lane) - 1));
-      stok[s] = i / NU;
-      swt[s] = wts[i];
-      inv[i] = s;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) s_base += total;
-    __syncthreads();
+    int s = base + before + incl - cnt;
+    if (m0) { stok[s] = i / NU; swt[s] = wts[i]; inv[i] = s; ++s; }
+    if (m1) { stok[s] = (i + 1) / NU; swt[s] = wts[i + 1]; inv[i + 1] = s; ++s; }
+    if (m2) { stok[s] = (i + 2) / NU; swt[s] = wts[i + 2]; inv[i + 2] = s; ++s; }
+    if (m3) { stok[s] = (i + 3) / NU; swt[s] = wts[i + 3]; inv[i + 3] = s; }
+    base += total;
   }
 }
 

@@ -130,6 +130,90 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restri
   }
 }
 
+// Sum over the CTA's 256 threads in the defined order: xor butterfly 16, 8, 4, 2, 1 inside every warp, then the eight
+// warp sums added in warp order; every thread returns the same value.  s_w: 8 floats of shared memory.
+__device__ __forceinline__ float cta_sum_ordered(float v, float* s_w) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  __syncthreads();  // (s_w may still be read from a call before)
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = s_w[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) t = __fadd_rn(t, s_w[w]);
+  return t;
+}
+
+// add_norm_quant (zero/kernels/ops_attn_g.cl:617-680), one CTA of 256 threads per row, K <= 256 * kAnqMax:
+//   x = (x + (t * r) * w) * s with r = 1/sqrt(sum(t^2)/K + eps);  y = w2 ? (x * r2) * w2 : x with r2 from the new x;
+//   y quantised per 32-block.  Thread j owns elements j, j + 256, ...: a warp owns one 32-block per step, so the
+// block maximum is a warp reduction; the new x stays in registers between the two steps.  Both sums of squares are
+// taken in the defined order of cta_sum_ordered over per-thread fused-multiply-add chains.
+constexpr int kAnqMax = 64;
+__global__ void __launch_bounds__(256) add_norm_quant_kernel(float* __restrict__ x, const float* __restrict__ t,
+                                                             const float* __restrict__ w, int K, float eps, float s,
+                                                             const float* __restrict__ w2, int Mp, int8_t* __restrict__ aq,
+                                                             float* __restrict__ asc, int16_t* __restrict__ absum) {
+  __shared__ float s_w[8];
+  const int m = blockIdx.x, lane = threadIdx.x & 31;
+  float* xr = x + (size_t)m * K;
+  const float* tr = t + (size_t)m * K;
+  const int nk = K / 256;
+  float ss = 0.0f;
+  for (int k = 0; k < nk; ++k) {
+    const float v = tr[threadIdx.x + 256 * k];
+    ss = __fmaf_rn(v, v, ss);
+  }
+  ss = cta_sum_ordered(ss, s_w);
+  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
+  float xv[kAnqMax];
+  float s2 = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kAnqMax; ++k) {
+    if (k < nk) {
+      const int i = threadIdx.x + 256 * k;
+      const float v = __fmul_rn(__fadd_rn(xr[i], __fmul_rn(__fmul_rn(tr[i], r), w[i])), s);
+      xv[k] = v;
+      xr[i] = v;
+      s2 = __fmaf_rn(v, v, s2);
+    }
+  }
+  float r2 = 1.0f;
+  if (w2) {
+    s2 = cta_sum_ordered(s2, s_w);
+    r2 = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s2, (float)K), eps)));
+  }
+#pragma unroll
+  for (int k = 0; k < kAnqMax; ++k) {
+    if (k < nk) {
+      const int i = threadIdx.x + 256 * k;
+      const float y = w2 ? __fmul_rn(__fmul_rn(xv[k], r2), w2[i]) : xv[k];
+      float amax = fabsf(y);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+      const float p = __fmul_rn(y, inv);
+      const int q = fabsf(p) <= 2147483520.0f ? __float2int_rn(p) : 0;  // (see quantize_act_kernel)
+      aq[(size_t)m * K + i] = (int8_t)q;
+      int s16 = q;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) s16 += __shfl_xor_sync(0xFFFFFFFFu, s16, o);
+      const int b = i >> 5;
+      if (lane == 0) asc[(size_t)b * Mp + m] = __fdiv_rn(amax, 127.0f);
+      if (absum && (lane & 15) == 0) absum[(size_t)(2 * b + (lane >> 4)) * Mp + m] = (int16_t)s16;
+    }
+  }
+}
+
+// rows M..Mp-1 of a quantised activation buffer: zeros with scale 0
+__global__ void zero_pad_rows_kernel(int M, int Mp, int K, int8_t* __restrict__ aq, float* __restrict__ asc, int16_t* __restrict__ absum) {
+  const int m = M + blockIdx.x;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) aq[(size_t)m * K + i] = 0;
+  for (int b = threadIdx.x; b < K / 32; b += blockDim.x) asc[(size_t)b * Mp + m] = 0.0f;
+  if (absum)
+    for (int b = threadIdx.x; b < K / 16; b += blockDim.x) absum[(size_t)b * Mp + m] = 0;
+}
+
 int check_quant_args(const float* x, int ldx, int M, int Mp, int K, const int8_t* aq, const float* asc, int width_needed) {
   if (!x || !aq || !asc) IZB_FAIL(IZB_ERR_ARG, "quantize: null pointer");
   if (K <= 0 || K % 256) IZB_FAIL(IZB_ERR_SHAPE, "quantize: K = %d is not a positive multiple of 256", K);
@@ -178,5 +262,18 @@ extern "C" int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, fl
   if (M_valid > 0) IZB_LAUNCH("rms_rows", st, rms_rows_kernel<<<M_valid, 256, 0, st>>>(d_x, ldx, M_valid, K, eps, rrow));
   dim3 grid(K / 256, (Mp + 31) / 32);
   IZB_LAUNCH("rmsnorm_quant", st, quantize_act_kernel<2><<<grid, 256, 0, st>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, d_h, 0, rrow, d_w));
+  return IZB_OK;
+}
+
+extern "C" int izb_add_norm_quant(float* d_x, const float* d_t, const float* d_w, float eps, float s, const float* d_w2, int M_valid,
+                                  int Mp, int K, int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream) {
+  if (!d_x || !d_t || !d_w || !d_aq || !d_asc) IZB_FAIL(IZB_ERR_ARG, "add_norm_quant: null pointer");
+  if (K <= 0 || K % 256 || K > 256 * kAnqMax) IZB_FAIL(IZB_ERR_SHAPE, "add_norm_quant: K = %d (a multiple of 256 up to %d)", K, 256 * kAnqMax);
+  if (Mp <= 0 || Mp % 16 || M_valid < 0 || M_valid > Mp) IZB_FAIL(IZB_ERR_SHAPE, "add_norm_quant: rows %d of Mp = %d (Mp must be a multiple of 16)", M_valid, Mp);
+  if (!(eps >= 0.0f)) IZB_FAIL(IZB_ERR_ARG, "add_norm_quant: eps = %g", (double)eps);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (M_valid > 0)
+    IZB_LAUNCH("add_norm_quant", st, add_norm_quant_kernel<<<M_valid, 256, 0, st>>>(d_x, d_t, d_w, K, eps, s, d_w2, Mp, d_aq, d_asc, d_absum));
+  if (Mp > M_valid) IZB_LAUNCH("zero_pad_rows", st, zero_pad_rows_kernel<<<Mp - M_valid, 256, 0, st>>>(M_valid, Mp, K, d_aq, d_asc, d_absum));
   return IZB_OK;
 }

@@ -93,6 +93,13 @@ class Engine {
     check(izb_rmsnorm_quant(x, ldx, w, eps, cur_T_, Mp, K, hout, aq_, asc_, nullptr, stream_), "rmsnorm_quant");
     cur_K_ = K; cur_Mp_ = Mp;
   }
+  // add_norm_quant (zero/kernels/ops_attn_g.cl:617): x = (x + rmsnorm(t) * w) * s in place, then the quantised
+  // rmsnorm(x) * w2 (w2 null: x itself) for the next GEMV
+  void add_norm_quant(float* x, const float* t, const float* w, float eps, float s, const float* w2, int K, int Mp) {
+    if (Mp > max_rows_ || K > max_k_) throw std::runtime_error("add_norm_quant: activation buffers too small");
+    check(izb_add_norm_quant(x, t, w, eps, s, w2, cur_T_, Mp, K, aq_, asc_, nullptr, stream_), "add_norm_quant");
+    cur_K_ = K; cur_Mp_ = Mp;
+  }
   // matmul (zero/engine.h:1080): C[.][c_off + n] (op)= quantised rows x w; acc 0 store, 1 add, 2 fused SwiGLU.
   // `name` is the reference's profiling label; act32 is always on (per-32 scales, the reference's default).
   void matmul(const char* name, const GpuWeight& w, int Mp, float* C, int ldc, int c_off, int acc, bool act32 = true) {

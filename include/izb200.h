@@ -100,6 +100,15 @@ int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_valid, int Mp
  * the int8 rows are reproducible bit for bit; the oracle repeats that order. */
 int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, float eps, int M_valid, int Mp, int K, float* d_h,
                       int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream);
+/* Residual add with a norm, then the next projection's quantised input (add_norm_quant, zero/kernels/ops_attn_g.cl:617-680;
+ * the decode path's producer between two GEMVs): per row, in place,
+ *   x = (x + (t * r) * w) * s,   r = 1 / sqrt(sum(t^2) / K + eps),
+ * then y = (x * r2) * w2 with r2 from the new x (d_w2 != NULL), or y = x (d_w2 == NULL), quantised like
+ * izb_quantize_act.  d_x, d_t: [M_valid][K] f32 (contiguous rows); d_w, d_w2: [K].  K % 256 == 0, K <= 16384 (the new row
+ * stays in registers between the two steps, as in the reference).  The sums of squares use the defined order of
+ * izb_rmsnorm_quant.  Rows M_valid..Mp-1 of the quantised outputs are zeros with scale 0. */
+int izb_add_norm_quant(float* d_x, const float* d_t, const float* d_w, float eps, float s, const float* d_w2, int M_valid, int Mp,
+                       int K, int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ matmul
  * Replaces Engine::matmul / matmul1 (zero/engine.h:1080,1147-1251): C[t][c_off + n] (op)= sum_k A[t][k] W[n][k] for

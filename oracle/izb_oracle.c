@@ -162,6 +162,55 @@ void orc_quantize_act(const float* x, int M, int K, int ldx, int Mp, int8_t* aq,
   }
 }
 
+/* ---------------------------------------------------------------- fused producers
+ * sum of v[i]^2 in the CUDA kernels' order: 256 strided chains of fused multiply-adds, xor butterfly over each group of 32,
+ * the eight group sums added in order */
+static float ordered_sumsq(const float* v, int K) {
+  float part[256];
+  for (int t = 0; t < 256; ++t) {
+    float ss = 0.0f;
+    for (int i = t; i < K; i += 256) ss = fmaf(v[i], v[i], ss);
+    part[t] = ss;
+  }
+  float total = 0.0f;
+  for (int g = 0; g < 8; ++g) {
+    float a[32], n[32];
+    memcpy(a, part + 32 * g, sizeof a);
+    for (int o = 16; o > 0; o >>= 1) {
+      for (int l = 0; l < 32; ++l) n[l] = a[l] + a[l ^ o];
+      memcpy(a, n, sizeof a);
+    }
+    total = g == 0 ? a[0] : total + a[0];
+  }
+  return total;
+}
+
+/* add_norm_quant, zero/kernels/ops_attn_g.cl:617-680: x = (x + (t * r) * w) * s, r = rsqrt(sum(t^2)/K + eps); then the next
+ * GEMV input y = w2 ? (x * r2) * w2 : x with r2 from the new x, quantised per 32.  x is updated in place. */
+void orc_add_norm_quant(float* x, const float* t, const float* w, float eps, float s, const float* w2, int M, int K, int Mp,
+                        int8_t* aq, float* asc, int16_t* absum) {
+  float* y = (float*)malloc((size_t)(M > 0 ? M : 1) * K * sizeof(float));
+  for (int m = 0; m < M; ++m) {
+    float* xr = x + (size_t)m * K;
+    const float* tr = t + (size_t)m * K;
+    const float r = 1.0f / sqrtf(ordered_sumsq(tr, K) / (float)K + eps);
+    for (int i = 0; i < K; ++i) {
+      const float a = tr[i] * r;
+      const float b = a * w[i];
+      const float c = xr[i] + b;
+      xr[i] = c * s;
+    }
+    float r2 = 1.0f;
+    if (w2) r2 = 1.0f / sqrtf(ordered_sumsq(xr, K) / (float)K + eps);
+    for (int i = 0; i < K; ++i) {
+      const float a = xr[i] * r2;
+      y[(size_t)m * K + i] = w2 ? a * w2[i] : xr[i];
+    }
+  }
+  orc_quantize_act(y, M, K, K, Mp, aq, asc, absum);
+  free(y);
+}
+
 /* ---------------------------------------------------------------- RMSNorm + quantise
  * rmsnorm_quant, zero/kernels/ops.cl:104-141: r = rsqrt(sum(x^2) / K + eps); y = x * r * w; then quant_store16.  The
  * kernel leaves the order of the sum to the OpenCL work-group reduction; the order written here is the CUDA kernel's
@@ -172,22 +221,7 @@ void orc_rmsnorm_quant(const float* x, int M, int K, int ldx, const float* w, fl
   float* y = (float*)malloc((size_t)(M > 0 ? M : 1) * K * sizeof(float));
   for (int m = 0; m < M; ++m) {
     const float* xr = x + (size_t)m * ldx;
-    float part[256];
-    for (int t = 0; t < 256; ++t) {
-      float ss = 0.0f;
-      for (int i = t; i < K; i += 256) ss = fmaf(xr[i], xr[i], ss);
-      part[t] = ss;
-    }
-    float total = 0.0f;
-    for (int g = 0; g < 8; ++g) {
-      float v[32], n[32];
-      memcpy(v, part + 32 * g, sizeof v);
-      for (int o = 16; o > 0; o >>= 1) {
-        for (int l = 0; l < 32; ++l) n[l] = v[l] + v[l ^ o];
-        memcpy(v, n, sizeof v);
-      }
-      total = g == 0 ? v[0] : total + v[0];
-    }
+    const float total = ordered_sumsq(xr, K);
     const float r = 1.0f / sqrtf(total / (float)K + eps);
     for (int i = 0; i < K; ++i) {
       const float xr_r = xr[i] * r;

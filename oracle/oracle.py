@@ -91,6 +91,22 @@ def rmsnorm_quant(x: np.ndarray, w: np.ndarray, eps: float, Mp: int | None = Non
     return y, aq, asc, absum
 
 
+def add_norm_quant(x: np.ndarray, t: np.ndarray, w: np.ndarray, eps: float, s: float, w2: np.ndarray | None, Mp: int | None = None):
+    """x_new = (x + (t * r) * w) * s; y = (x_new * r2) * w2 (or x_new when w2 is None) quantised -> x_new, aq, asc, absum."""
+    x = np.array(x, np.float32, copy=True, order="C")
+    t = np.ascontiguousarray(t, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    w2c = None if w2 is None else np.ascontiguousarray(w2, np.float32)
+    M, K = x.shape
+    Mp = Mp or M
+    aq = np.empty((Mp, K), np.int8)
+    asc = np.empty((K // 32, Mp), np.float32)
+    absum = np.empty((K // 16, Mp), np.int16)
+    lib().orc_add_norm_quant(_vp(x), _vp(t), _vp(w), C.c_float(eps), C.c_float(s), None if w2c is None else _vp(w2c), M, K, Mp,
+                             _vp(aq), _vp(asc), _vp(absum))
+    return x, aq, asc, absum
+
+
 def decode_q4k_sb(p: np.ndarray):
     d, dmin = C.c_float(), C.c_float()
     sc, mn, q = np.empty(8, np.uint8), np.empty(8, np.uint8), np.empty(256, np.uint8)

@@ -95,6 +95,23 @@ def test_rmsnorm_quant_bit_exact(izb, torch, M, K):
     assert (aq.cpu().numpy()[M:] == 0).all()
 
 
+@pytest.mark.parametrize("M,K,second", [(1, 5120, True), (5, 1024, False), (8, 16384, True)])
+def test_add_norm_quant_bit_exact(izb, torch, M, K, second):
+    """izb_add_norm_quant against the oracle (same defined summation orders): the updated residual rows, the int8 values
+    and the scales are identical bit for bit."""
+    rng = np.random.default_rng(M + K)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    t = rng.standard_normal((M, K), dtype=np.float32) * 3
+    w = (1.0 + 0.2 * rng.standard_normal(K)).astype(np.float32)
+    w2 = (1.0 + 0.2 * rng.standard_normal(K)).astype(np.float32) if second else None
+    xd = dev(torch, x)
+    aq, asc = izb.add_norm_quant(xd, dev(torch, t), dev(torch, w), 1e-6, 0.75, None if w2 is None else dev(torch, w2))
+    rx, raq, rasc, _ = O.add_norm_quant(x, t, w, 1e-6, 0.75, w2, Mp=asc.shape[1])
+    assert (bits(xd.cpu().numpy()) == bits(rx)).all()
+    assert (aq.cpu().numpy() == raq).all()
+    assert (bits(asc.cpu().numpy()) == bits(rasc)).all()
+
+
 # ------------------------------------------------------------------------------------------------ GEMV
 @pytest.mark.parametrize("qt", [12, 8])
 @pytest.mark.parametrize("T", [1, 2, 3, 8])

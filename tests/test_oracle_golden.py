@@ -164,3 +164,20 @@ def test_rmsnorm_quant_matches_reference_rows(golden_dir):
     if O.ref() is not None:
         live = O.ref_rmsnorm(g["x"], g["w"], float(g["eps"]))
         assert (bits(live) == bits(g["y"])).all()
+
+
+def test_add_norm_quant_composes_the_pinned_pieces(golden_dir):
+    """add_norm_quant (zero/kernels/ops_attn_g.cl:617-680) restated: with x = 0 and s = 1 its first step is rmsnorm(t) * w,
+    which must agree with tools/ref_forward.cpp's rmsnorm rows; its quantised output is the quantiser applied to the
+    (optionally normalised) new row."""
+    g = np.load(os.path.join(golden_dir, "rmsnorm.npz"))
+    t, w, eps = g["x"], g["w"], float(g["eps"])
+    xn, aq, asc, absum = O.add_norm_quant(np.zeros_like(t), t, w, eps, 1.0, None)
+    err = np.max(np.abs(xn.astype(np.float64) - g["y"].astype(np.float64))) / np.max(np.abs(g["y"]))
+    assert err <= 2e-6, err
+    raq, rasc, rabsum = O.quantize_act(xn)
+    assert (aq == raq).all() and (bits(asc) == bits(rasc)).all() and (absum == rabsum).all()
+    # with the second norm the quantised row is rmsnorm_quant of the new x
+    xn2, aq2, asc2, _ = O.add_norm_quant(np.ones_like(t), t, w, eps, 0.5, w)
+    y2, raq2, rasc2, _ = O.rmsnorm_quant(xn2, w, eps)
+    assert (aq2 == raq2).all() and (bits(asc2) == bits(rasc2)).all()

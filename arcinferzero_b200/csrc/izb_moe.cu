@@ -217,8 +217,7 @@ extern "C" int izb_moe_route(const float* d_logits, int ldl, int T, int NE, int 
     IZB_FAIL(IZB_ERR_SHAPE, "moe_route: T=%d NE=%d NU=%d ldl=%d (NE <= 512, NU <= 32)", T, NE, NU, ldl);
   cudaStream_t st = (cudaStream_t)stream;
   IZB_CUDA(cudaMemsetAsync(d_counts, 0, (size_t)NE * 4, st));
-  moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(d_logits, ldl, T, NE, NU, d_ids, d_wts, d_counts);
-  IZB_LAUNCHED();
+  IZB_LAUNCH("moe_route", st, moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(d_logits, ldl, T, NE, NU, d_ids, d_wts, d_counts));
   return IZB_OK;
 }
 
@@ -229,10 +228,8 @@ extern "C" int izb_moe_sort(const int32_t* d_ids, const float* d_wts, const int3
   if (T < 1 || NE < 1 || NE > 1024 || NU < 1 || TM < 1) IZB_FAIL(IZB_ERR_SHAPE, "moe_sort: T=%d NE=%d NU=%d TM=%d", T, NE, NU, TM);
   if (max_tiles < (T * NU + TM - 1) / TM + NE) IZB_FAIL(IZB_ERR_LIMIT, "moe_sort: max_tiles = %d < %d (pairs/TM + NE)", max_tiles, (T * NU + TM - 1) / TM + NE);
   cudaStream_t st = (cudaStream_t)stream;
-  moe_scan_kernel<<<1, 1024, 0, st>>>(d_counts, NE, TM, d_offs, d_tiles, max_tiles);
-  IZB_LAUNCHED();
-  moe_scatter_kernel<<<NE, 256, 0, st>>>(d_ids, d_wts, T * NU, NU, d_offs, d_stok, d_swt, d_inv);
-  IZB_LAUNCHED();
+  IZB_LAUNCH("moe_scan", st, moe_scan_kernel<<<1, 1024, 0, st>>>(d_counts, NE, TM, d_offs, d_tiles, max_tiles));
+  IZB_LAUNCH("moe_scatter", st, moe_scatter_kernel<<<NE, 256, 0, st>>>(d_ids, d_wts, T * NU, NU, d_offs, d_stok, d_swt, d_inv));
   return IZB_OK;
 }
 
@@ -277,8 +274,7 @@ extern "C" int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_in
   if (T < 1 || NU < 1 || E < 4 || E % 4) IZB_FAIL(IZB_ERR_SHAPE, "moe_combine: T=%d NU=%d E=%d (E %% 4 == 0)", T, NU, E);
   if (!izb_aligned(d_x, 16) || !izb_aligned(d_y, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_combine: x, y must be 16-byte aligned");
   dim3 grid((E / 4 + 127) / 128, T);
-  moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(d_x, d_y, d_inv, T, NU, E);
-  IZB_LAUNCHED();
+  IZB_LAUNCH("moe_combine", (cudaStream_t)stream, moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(d_x, d_y, d_inv, T, NU, E));
   return IZB_OK;
 }
 

@@ -239,11 +239,11 @@ extern "C" int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_va
   if (int rc = check_quant_args(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, split ? 2 * F : F)) return rc;
   if (d_h && !izb_aligned(d_h, 16)) IZB_FAIL(IZB_ERR_ALIGN, "swiglu_quant: h not 16-byte aligned");
   dim3 grid(F / 256, (Mp + 31) / 32);
+  cudaStream_t st = (cudaStream_t)stream;
   if (split)
-    quantize_act_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F, nullptr, nullptr);
+    IZB_LAUNCH("swiglu_quant", st, quantize_act_kernel<1><<<grid, 256, 0, st>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F, nullptr, nullptr));
   else
-    quantize_act_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0, nullptr, nullptr);
-  IZB_LAUNCHED();
+    IZB_LAUNCH("quantize_act", st, quantize_act_kernel<0><<<grid, 256, 0, st>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0, nullptr, nullptr));
   return IZB_OK;
 }
 

@@ -205,7 +205,7 @@ class Stack:
         self.izb.quantize_act(src, Mp=T, out=(aq, asc, None))
         return aq, asc
 
-    def _sum(self, layer_out_of: str):
+    def _sum(self):
         """Row-parallel partials in self.part -> residual stream; leaves the quantised stream in xq / xsc."""
         izb, T = self.izb, self.cfg.tokens
         if self.mode == "allreduce":
@@ -234,7 +234,7 @@ class Stack:
             izb.matmul(L["o"], aq, asc, T, out=self.part)
             if t is not None:
                 t["qkv"], t["o_part"], t["x0"] = self.qkv.clone(), self.part.clone(), self.x.clone()
-            self._sum("o")
+            self._sum()
             if t is not None:
                 t["x1"], t["xq1"], t["xsc1"] = self.x.clone(), self.xq.clone(), self.xsc.clone()
             izb.matmul(L["gate"], self.xq, self.xsc, T, out=self.h)
@@ -243,7 +243,7 @@ class Stack:
             izb.matmul(L["down"], aq, asc, T, out=self.part)
             if t is not None:
                 t["h"], t["down_part"] = self.h.clone(), self.part.clone()
-            self._sum("down")
+            self._sum()
             if t is not None:
                 t["x2"], t["xq2"], t["xsc2"] = self.x.clone(), self.xq.clone(), self.xsc.clone()
                 trace.append(t)

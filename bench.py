@@ -344,7 +344,7 @@ def run_reference(args, rank: int) -> None:
     vals = base["value"]
     line = {"impl": "reference", "metric": "Q4_K prefill GEMM throughput", "value": vals, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * M / vals, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate over dequantised f32 (CPU reference)",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f64",
             "data": "synthetic", "config": {"workload": WORKLOAD}, "cpu_baseline": base,
             "e2e": {"value": vals, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -487,9 +487,12 @@ def main() -> None:
             "metric": "Q4_K prefill GEMM throughput", "value": M / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": "exact integer dot products (int8 x 4-bit, fp16-encoded operands, f32 TMEM accumulators), f32 combine",
+            "dtype": "int8",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"weight rows split over {world} rank(s), no exchange",
+            "config": {"workload": WORKLOAD,
+                       "arithmetic": "exact integer dot products per 32-block (int8 x 4-bit; operands fed to the tensor cores as fp16 "
+                                     "holding exact integers, f32 TMEM accumulators), f32 combine",
+                       "parallelism": f"weight rows split over {world} rank(s), no exchange",
                        "l2": "per step 168 MB of f32 activations in and 570 MB of outputs written: larger than the 126 MB L2",
                        "rows_per_rank": Nr},
             "roofline": {"bound": "tensor", "kernel": kname, "achieved": achieved, "peak": tc_sus, "unit": "TFLOP/s",

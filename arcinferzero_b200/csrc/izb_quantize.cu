@@ -11,41 +11,13 @@
 
 namespace {
 
-// 1 / sqrt(mean(x^2) + eps) of every row, in a summation order that is part of the definition (the CPU oracle repeats
-// it, so the quantised rows that follow are reproducible bit for bit): thread t of 256 accumulates x[t], x[t + 256], ...
-// with fused multiply-adds; every warp folds its 32 partial sums with the xor butterfly 16, 8, 4, 2, 1; the eight warp
-// sums are added in warp order.  (rmsnorm_quant, zero/kernels/ops.cl:108-120, leaves the order to the OpenCL work-group
-// reduction.)
-__global__ void __launch_bounds__(256) rms_rows_kernel(const float* __restrict__ x, int ldx, int M, int K, float eps,
-                                                       float* __restrict__ rrow) {
-  __shared__ float s_w[8];
-  const int m = blockIdx.x;
-  const float* xr = x + (size_t)m * ldx;
-  float ss = 0.0f;
-  for (int i = threadIdx.x; i < K; i += 256) {
-    const float v = xr[i];
-    ss = __fmaf_rn(v, v, ss);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xFFFFFFFFu, ss, o));
-  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = s_w[0];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) t = __fadd_rn(t, s_w[w]);
-    rrow[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)K), eps)));
-  }
-}
-
-// kMode 0: quantise x.  1 (SwiGLU): x holds gate | up at column offset F, quantise h = silu(gate) * up.
-// 2 (RMSNorm): quantise (x * rrow[m]) * wnorm[column].  hout (modes 1, 2): optional f32 copy of what is quantised.
+// kMode 0: quantise x.  1 (SwiGLU): x holds gate | up at column offset F, quantise h = silu(gate) * up; hout: optional
+// f32 copy of h.
 template <int kMode>
 __global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restrict__ x, int ldx, int M, int Mp, int K,
                                                            int8_t* __restrict__ aq, float* __restrict__ asc,
                                                            int16_t* __restrict__ absum, float* __restrict__ hout,
-                                                           int F /* mode 1: up projection at column offset F */,
-                                                           const float* __restrict__ rrow, const float* __restrict__ wnorm) {
+                                                           int F /* mode 1: up projection at column offset F */) {
   constexpr bool kSwiglu = kMode == 1;
   __shared__ float s_sc[8][33];
   __shared__ int16_t s_sum[16][34];
@@ -68,18 +40,6 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restri
         for (int k = 0; k < 8; ++k) v[i][k] = __fmul_rn(__fdiv_rn(v[i][k], __fadd_rn(1.0f, expf(-v[i][k]))), u[k]);
         if (hout) {
           float4* ph = reinterpret_cast<float4*>(hout + (size_t)m * F + col);
-          ph[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-          ph[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
-        }
-      }
-      if (kMode == 2) {  // y = x * r * w  (zero/kernels/ops.cl:131: the two products in this order)
-        const float r = rrow[m];
-        const float4 wa = *reinterpret_cast<const float4*>(wnorm + col), wb = *reinterpret_cast<const float4*>(wnorm + col + 4);
-        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) v[i][k] = __fmul_rn(__fmul_rn(v[i][k], r), wv[k]);
-        if (hout) {
-          float4* ph = reinterpret_cast<float4*>(hout + (size_t)m * K + col);
           ph[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
           ph[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
         }
@@ -205,6 +165,63 @@ __global__ void __launch_bounds__(256) add_norm_quant_kernel(float* __restrict__
   }
 }
 
+// rmsnorm_quant (zero/kernels/ops.cl:104-141), one CTA of 256 threads per row: the row is read from HBM once (the second
+// pass finds it in L1 / L2).  Both passes use the quantiser's lane layout: thread j owns the groups of 8 consecutive values
+// j, j + 256, ... .  Pass 1: the sum of squares, a chain of fused multiply-adds over the thread's values in index order,
+// then cta_sum_ordered (this order is part of the definition: the oracle repeats it).  Pass 2: y = (x * r) * w, optional
+// f32 copy, and per 32-block (four adjacent threads) int8 + scale + sums of 16.
+__global__ void __launch_bounds__(256) rmsnorm_quant_row_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
+                                                                int K, float eps, int Mp, float* __restrict__ hout,
+                                                                int8_t* __restrict__ aq, float* __restrict__ asc,
+                                                                int16_t* __restrict__ absum) {
+  __shared__ float s_w[8];
+  const int m = blockIdx.x;
+  const float* xr = x + (size_t)m * ldx;
+  float ss = 0.0f;
+  for (int g = threadIdx.x; g < K / 8; g += 256) {
+    const float4 a = *reinterpret_cast<const float4*>(xr + 8 * g), b = *reinterpret_cast<const float4*>(xr + 8 * g + 4);
+    ss = __fmaf_rn(a.x, a.x, ss); ss = __fmaf_rn(a.y, a.y, ss); ss = __fmaf_rn(a.z, a.z, ss); ss = __fmaf_rn(a.w, a.w, ss);
+    ss = __fmaf_rn(b.x, b.x, ss); ss = __fmaf_rn(b.y, b.y, ss); ss = __fmaf_rn(b.z, b.z, ss); ss = __fmaf_rn(b.w, b.w, ss);
+  }
+  ss = cta_sum_ordered(ss, s_w);
+  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
+  for (int g = threadIdx.x; g < K / 8; g += 256) {  // (K / 8 is a multiple of 32: whole warps take part in the shuffles)
+    const int col = 8 * g;
+    const float4 a = *reinterpret_cast<const float4*>(xr + col), b = *reinterpret_cast<const float4*>(xr + col + 4);
+    const float4 wa = *reinterpret_cast<const float4*>(w + col), wb = *reinterpret_cast<const float4*>(w + col + 4);
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      v[k] = __fmul_rn(__fmul_rn(v[k], r), wv[k]);
+      amax = fmaxf(amax, fabsf(v[k]));
+    }
+    if (hout) {
+      float4* ph = reinterpret_cast<float4*>(hout + (size_t)m * K + col);
+      ph[0] = make_float4(v[0], v[1], v[2], v[3]);
+      ph[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    int q[8], s8 = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float p = __fmul_rn(v[k], inv);
+      q[k] = fabsf(p) <= 2147483520.0f ? __float2int_rn(p) : 0;  // (see quantize_act_kernel)
+      s8 += q[k];
+    }
+    const int s16 = s8 + __shfl_xor_sync(0xFFFFFFFFu, s8, 1);
+    uint2 pk;
+    pk.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    pk.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    *reinterpret_cast<uint2*>(aq + (size_t)m * K + col) = pk;
+    if ((g & 3) == 0) asc[(size_t)(g >> 2) * Mp + m] = __fdiv_rn(amax, 127.0f);
+    if (absum && (g & 1) == 0) absum[(size_t)(g >> 1) * Mp + m] = (int16_t)s16;
+  }
+}
+
 // rows M..Mp-1 of a quantised activation buffer: zeros with scale 0
 __global__ void zero_pad_rows_kernel(int M, int Mp, int K, int8_t* __restrict__ aq, float* __restrict__ asc, int16_t* __restrict__ absum) {
   const int m = M + blockIdx.x;
@@ -230,7 +247,7 @@ extern "C" int izb_quantize_act(const float* d_x, int ldx, int M_valid, int Mp, 
                                 int16_t* d_absum, void* stream) {
   if (int rc = check_quant_args(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, K)) return rc;
   dim3 grid(K / 256, (Mp + 31) / 32);
-  IZB_LAUNCH("quantize_act", (cudaStream_t)stream, quantize_act_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0, nullptr, nullptr));
+  IZB_LAUNCH("quantize_act", (cudaStream_t)stream, quantize_act_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, nullptr, 0));
   return IZB_OK;
 }
 
@@ -241,9 +258,9 @@ extern "C" int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_va
   dim3 grid(F / 256, (Mp + 31) / 32);
   cudaStream_t st = (cudaStream_t)stream;
   if (split)
-    IZB_LAUNCH("swiglu_quant", st, quantize_act_kernel<1><<<grid, 256, 0, st>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F, nullptr, nullptr));
+    IZB_LAUNCH("swiglu_quant", st, quantize_act_kernel<1><<<grid, 256, 0, st>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, d_h, F));
   else
-    IZB_LAUNCH("quantize_act", st, quantize_act_kernel<0><<<grid, 256, 0, st>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0, nullptr, nullptr));
+    IZB_LAUNCH("quantize_act", st, quantize_act_kernel<0><<<grid, 256, 0, st>>>(d_gu, ldgu, M_valid, Mp, F, d_aq, d_asc, d_absum, nullptr, 0));
   return IZB_OK;
 }
 
@@ -254,14 +271,9 @@ extern "C" int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, fl
   if (!izb_aligned(d_w, 16) || (d_h && !izb_aligned(d_h, 16))) IZB_FAIL(IZB_ERR_ALIGN, "rmsnorm_quant: w and h must be 16-byte aligned");
   if (!(eps >= 0.0f)) IZB_FAIL(IZB_ERR_ARG, "rmsnorm_quant: eps = %g", (double)eps);
   cudaStream_t st = (cudaStream_t)stream;
-  int dev = 0;
-  IZB_CUDA(cudaGetDevice(&dev));
-  void* ws = nullptr;
-  if (int rc = izb_workspace(dev, kWsNorm, (size_t)Mp * 4, &ws)) return rc;
-  float* rrow = (float*)ws;
-  if (M_valid > 0) IZB_LAUNCH("rms_rows", st, rms_rows_kernel<<<M_valid, 256, 0, st>>>(d_x, ldx, M_valid, K, eps, rrow));
-  dim3 grid(K / 256, (Mp + 31) / 32);
-  IZB_LAUNCH("rmsnorm_quant", st, quantize_act_kernel<2><<<grid, 256, 0, st>>>(d_x, ldx, M_valid, Mp, K, d_aq, d_asc, d_absum, d_h, 0, rrow, d_w));
+  if (M_valid > 0)
+    IZB_LAUNCH("rmsnorm_quant", st, rmsnorm_quant_row_kernel<<<M_valid, 256, 0, st>>>(d_x, ldx, d_w, K, eps, Mp, d_h, d_aq, d_asc, d_absum));
+  if (Mp > M_valid) IZB_LAUNCH("zero_pad_rows", st, zero_pad_rows_kernel<<<Mp - M_valid, 256, 0, st>>>(M_valid, Mp, K, d_aq, d_asc, d_absum));
   return IZB_OK;
 }
 

@@ -96,7 +96,7 @@ int izb_swiglu_quant(const float* d_gu, int ldgu, int split, int M_valid, int Mp
 /* RMSNorm then quantise (ops.cl rmsnorm_quant, zero/kernels/ops.cl:104-141): y = (x * r) * w with
  * r = 1 / sqrt(sum(x^2) / K + eps) per row, quantised like izb_quantize_act; d_h (may be NULL) receives y as f32
  * [M_valid][K].  d_w: [K] f32.  The reference leaves the order of the sum of squares to the OpenCL work-group reduction;
- * here it is defined (256 strided fused-multiply-add chains, xor butterfly per 32, eight partial sums in order), so that
+ * here it is defined (256 fused-multiply-add chains over groups of 8 values, xor butterfly per 32, eight partial sums in order), so that
  * the int8 rows are reproducible bit for bit; the oracle repeats that order. */
 int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, float eps, int M_valid, int Mp, int K, float* d_h,
                       int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream);
@@ -105,8 +105,8 @@ int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, float eps, in
  *   x = (x + (t * r) * w) * s,   r = 1 / sqrt(sum(t^2) / K + eps),
  * then y = (x * r2) * w2 with r2 from the new x (d_w2 != NULL), or y = x (d_w2 == NULL), quantised like
  * izb_quantize_act.  d_x, d_t: [M_valid][K] f32 (contiguous rows); d_w, d_w2: [K].  K % 256 == 0, K <= 16384 (the new row
- * stays in registers between the two steps, as in the reference).  The sums of squares use the defined order of
- * izb_rmsnorm_quant.  Rows M_valid..Mp-1 of the quantised outputs are zeros with scale 0. */
+ * stays in registers between the two steps, as in the reference).  The sums of squares are taken in a defined order as in
+ * izb_rmsnorm_quant (here the 256 chains are strided by one element).  Rows M_valid..Mp-1 of the quantised outputs are zeros with scale 0. */
 int izb_add_norm_quant(float* d_x, const float* d_t, const float* d_w, float eps, float s, const float* d_w2, int M_valid, int Mp,
                        int K, int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream);
 

@@ -185,6 +185,28 @@ static float ordered_sumsq(const float* v, int K) {
   return total;
 }
 
+/* the same with the chains of the rmsnorm_quant kernel: chain t takes the groups of 8 consecutive values t, t + 256, ... */
+static float ordered_sumsq8(const float* v, int K) {
+  float part[256];
+  for (int t = 0; t < 256; ++t) {
+    float ss = 0.0f;
+    for (int g = t; g < K / 8; g += 256)
+      for (int e = 0; e < 8; ++e) ss = fmaf(v[8 * g + e], v[8 * g + e], ss);
+    part[t] = ss;
+  }
+  float total = 0.0f;
+  for (int g = 0; g < 8; ++g) {
+    float a[32], n[32];
+    memcpy(a, part + 32 * g, sizeof a);
+    for (int o = 16; o > 0; o >>= 1) {
+      for (int l = 0; l < 32; ++l) n[l] = a[l] + a[l ^ o];
+      memcpy(a, n, sizeof a);
+    }
+    total = g == 0 ? a[0] : total + a[0];
+  }
+  return total;
+}
+
 /* add_norm_quant, zero/kernels/ops_attn_g.cl:617-680: x = (x + (t * r) * w) * s, r = rsqrt(sum(t^2)/K + eps); then the next
  * GEMV input y = w2 ? (x * r2) * w2 : x with r2 from the new x, quantised per 32.  x is updated in place. */
 void orc_add_norm_quant(float* x, const float* t, const float* w, float eps, float s, const float* w2, int M, int K, int Mp,
@@ -214,14 +236,14 @@ void orc_add_norm_quant(float* x, const float* t, const float* w, float eps, flo
 /* ---------------------------------------------------------------- RMSNorm + quantise
  * rmsnorm_quant, zero/kernels/ops.cl:104-141: r = rsqrt(sum(x^2) / K + eps); y = x * r * w; then quant_store16.  The
  * kernel leaves the order of the sum to the OpenCL work-group reduction; the order written here is the CUDA kernel's
- * (256 strided chains of fused multiply-adds, xor butterfly over each group of 32, the eight group sums in order), so
- * that both produce the same bits.  hout (may be NULL): y as f32 [M][K]. */
+ * (256 chains of fused multiply-adds over groups of 8 values, xor butterfly over each group of 32 chains, the eight group
+ * sums in order), so that both produce the same bits.  hout (may be NULL): y as f32 [M][K]. */
 void orc_rmsnorm_quant(const float* x, int M, int K, int ldx, const float* w, float eps, int Mp, float* hout, int8_t* aq,
                        float* asc, int16_t* absum) {
   float* y = (float*)malloc((size_t)(M > 0 ? M : 1) * K * sizeof(float));
   for (int m = 0; m < M; ++m) {
     const float* xr = x + (size_t)m * ldx;
-    const float total = ordered_sumsq(xr, K);
+    const float total = ordered_sumsq8(xr, K);
     const float r = 1.0f / sqrtf(total / (float)K + eps);
     for (int i = 0; i < K; ++i) {
       const float xr_r = xr[i] * r;

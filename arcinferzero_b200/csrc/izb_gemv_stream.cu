@@ -218,7 +218,10 @@ __global__ void __launch_bounds__(kRegWarps * 32, 2) gemv_q4k_reg_kernel(const u
                                                                          int Mp, float* __restrict__ C, int c_off, int acc,
                                                                          int slots, int slot_bytes, uint32_t* err) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int nsb = 4 * NSB4, WS = (nsb + 7) / 8;  // steps of eight superblocks (the last one may be half empty)
+  constexpr int nsb = 4 * NSB4, WS = (nsb + 7) / 8, FS = nsb / 8;  // steps of eight superblocks: FS full ones, and for an odd
+  constexpr bool kHalf = (nsb % 8) != 0;                            // K / 1024 a last step of four
+  // The half step does not leave half the warp idle: when a warp works on two rows, lanes 0..15 take the last four
+  // superblocks of the first row and lanes 16..31 those of the second, so a pair of rows costs 2 FS + 1 steps.
   constexpr uint32_t row_bytes = nsb * 144;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int W = gridDim.x * kRegWarps, w0 = blockIdx.x * kRegWarps + warp;
@@ -244,10 +247,8 @@ __global__ void __launch_bounds__(kRegWarps * 32, 2) gemv_q4k_reg_kernel(const u
   float sx[WS], sy16[WS], px[WS], py[WS];
 #pragma unroll
   for (int st = 0; st < WS; ++st) {
-    const int sb = st * 8 + sub;
-    alo[st][0] = alo[st][1] = ahi[st][0] = ahi[st][1] = make_uint4(0, 0, 0, 0);
-    sx[st] = sy16[st] = px[st] = py[st] = 0.0f;
-    if (sb < nsb) {
+    const int sb = st < FS ? st * 8 + sub : st * 8 + (sub & 3);  // (the half step: both half warps hold the same four)
+    {
       const int8_t* a = aq + sb * 256 + pp * 64;
       alo[st][0] = *reinterpret_cast<const uint4*>(a);
       alo[st][1] = *reinterpret_cast<const uint4*>(a + 16);
@@ -272,6 +273,7 @@ __global__ void __launch_bounds__(kRegWarps * 32, 2) gemv_q4k_reg_kernel(const u
   const int pp_sh = 16 * (pp & 1);  // where this lane's pair of sub-block scales sits in the packed words
   const bool pp_upper = pp >= 2;
   const uint32_t h_off = sub * 144, q_off = sub * 144 + 16 + 32 * pp;
+  const uint32_t h_off_half = (sub & 3) * 144, q_off_half = (sub & 3) * 144 + 16 + 32 * pp;
 
   int slot = 0;
   uint32_t parity = 0;
@@ -290,36 +292,39 @@ __global__ void __launch_bounds__(kRegWarps * 32, 2) gemv_q4k_reg_kernel(const u
     const unsigned char* w0p = ring + (size_t)slot * slot_bytes;
     const unsigned char* w1p = two ? w0p + slot_bytes : w0p;  // (a lone last row is computed twice, stored once)
     float acc0 = 0.0f, acc1 = 0.0f;
+    auto one = [&](int st, const unsigned char* wp, uint32_t ho, uint32_t qo, float accv) -> float {
+      const uint32_t al[8] = {alo[st][0].x, alo[st][0].y, alo[st][0].z, alo[st][0].w, alo[st][1].x, alo[st][1].y, alo[st][1].z, alo[st][1].w};
+      const uint32_t ah[8] = {ahi[st][0].x, ahi[st][0].y, ahi[st][0].z, ahi[st][0].w, ahi[st][1].x, ahi[st][1].y, ahi[st][1].z, ahi[st][1].w};
+      const uint4 h = *reinterpret_cast<const uint4*>(wp + st * 1152 + ho);
+      const uint4 qa = *reinterpret_cast<const uint4*>(wp + st * 1152 + qo);
+      const uint4 qb = *reinterpret_cast<const uint4*>(wp + st * 1152 + qo + 16);
+      const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&h.x));  // (d, dmin)
+      uint32_t sc2, mn2;
+      q4k_pair(h, pp_sh, pp_upper, sc2, mn2);
+      const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+      // low nibbles against the first block; the high nibbles stay where they are, as unsigned bytes 16 * q, against
+      // the second block: hi = 16 * dot, and the factor 1/16 sits in the activation scale
+      int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
 #pragma unroll
-    for (int st = 0; st < WS; ++st) {
-      if (st * 8 + 7 < nsb || sub < nsb - st * 8) {  // (only the last step of K = 1024 * odd can be half empty)
-        const uint32_t al[8] = {alo[st][0].x, alo[st][0].y, alo[st][0].z, alo[st][0].w, alo[st][1].x, alo[st][1].y, alo[st][1].z, alo[st][1].w};
-        const uint32_t ah[8] = {ahi[st][0].x, ahi[st][0].y, ahi[st][0].z, ahi[st][0].w, ahi[st][1].x, ahi[st][1].y, ahi[st][1].z, ahi[st][1].w};
-        auto one = [&](const unsigned char* wp, float accv) -> float {
-          const uint4 h = *reinterpret_cast<const uint4*>(wp + st * 1152 + h_off);
-          const uint4 qa = *reinterpret_cast<const uint4*>(wp + st * 1152 + q_off);
-          const uint4 qb = *reinterpret_cast<const uint4*>(wp + st * 1152 + q_off + 16);
-          const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&h.x));  // (d, dmin)
-          uint32_t sc2, mn2;
-          q4k_pair(h, pp_sh, pp_upper, sc2, mn2);
-          const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-          // low nibbles against the first block; the high nibbles stay where they are, as unsigned bytes 16 * q, against
-          // the second block: hi = 16 * dot, and the factor 1/16 sits in the activation scale
-          int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            lo0 = __dp4a((int)al[kk], (int)(w[kk] & 0x0F0F0F0Fu), lo0);
-            lo1 = __dp4a((int)al[4 + kk], (int)(w[4 + kk] & 0x0F0F0F0Fu), lo1);
-            hi0 = dp4a_su((int)ah[kk], w[kk] & 0xF0F0F0F0u, hi0);
-            hi1 = dp4a_su((int)ah[4 + kk], w[4 + kk] & 0xF0F0F0F0u, hi1);
-          }
-          const float tq = fmaf(sx[st], (float)((int)(sc2 & 0xFFu) * (lo0 + lo1)), sy16[st] * (float)((int)(sc2 >> 8) * (hi0 + hi1)));
-          const float tm = fmaf(px[st], (float)(mn2 & 0xFFu), py[st] * (float)(mn2 >> 8));
-          return fmaf(df.x, tq, fmaf(-df.y, tm, accv));
-        };
-        acc0 = one(w0p, acc0);
-        acc1 = one(w1p, acc1);
+      for (int kk = 0; kk < 4; ++kk) {
+        lo0 = __dp4a((int)al[kk], (int)(w[kk] & 0x0F0F0F0Fu), lo0);
+        lo1 = __dp4a((int)al[4 + kk], (int)(w[4 + kk] & 0x0F0F0F0Fu), lo1);
+        hi0 = dp4a_su((int)ah[kk], w[kk] & 0xF0F0F0F0u, hi0);
+        hi1 = dp4a_su((int)ah[4 + kk], w[4 + kk] & 0xF0F0F0F0u, hi1);
       }
+      const float tq = fmaf(sx[st], (float)((int)(sc2 & 0xFFu) * (lo0 + lo1)), sy16[st] * (float)((int)(sc2 >> 8) * (hi0 + hi1)));
+      const float tm = fmaf(px[st], (float)(mn2 & 0xFFu), py[st] * (float)(mn2 >> 8));
+      return fmaf(df.x, tq, fmaf(-df.y, tm, accv));
+    };
+#pragma unroll
+    for (int st = 0; st < FS; ++st) {
+      acc0 = one(st, w0p, h_off, q_off, acc0);
+      acc1 = one(st, w1p, h_off, q_off, acc1);
+    }
+    if (kHalf) {  // (for a lone last row w1p == w0p: lanes 16..31 repeat the work and their sum is dropped)
+      const float r = one(FS, lane < 16 ? w0p : w1p, h_off_half, q_off_half, 0.0f);
+      acc0 += lane < 16 ? r : 0.0f;
+      acc1 += lane < 16 ? 0.0f : r;
     }
     // the slots are read: request the rows `slots` ahead into them, then reduce and store
     __syncwarp();

@@ -400,7 +400,8 @@ __global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_pair_kernel(const
                                                                           int Mp, float* __restrict__ C, int ldc, int c_off, int acc,
                                                                           int slots, int slot_bytes, uint32_t* err) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int nsb = 4 * NSB4, WS = (nsb + 7) / 8, K = nsb * 256;
+  constexpr int nsb = 4 * NSB4, WS = (nsb + 7) / 8, FS = nsb / 8, K = nsb * 256;
+  constexpr bool kHalf = (nsb % 8) != 0;  // a last step of four superblocks: shared by the two rows of a pair (half a warp each)
   constexpr uint32_t row_bytes = nsb * 144;
   constexpr int kActBytes = WS * T * kPairActBytes;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -421,7 +422,7 @@ __global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_pair_kernel(const
   // ---- stage the activations: entry (step, token, lane)
   for (int i = threadIdx.x; i < WS * T * 32; i += blockDim.x) {
     const int l = i & 31, t = (i >> 5) % T, st = (i >> 5) / T;
-    const int sb = st * 8 + (l >> 2), p2 = l & 3;
+    const int sb = st < FS ? st * 8 + (l >> 2) : st * 8 + ((l >> 2) & 3), p2 = l & 3;
     uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, a2 = a0, a3 = a0;
     float4 sc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (sb < nsb) {
@@ -452,6 +453,7 @@ __global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_pair_kernel(const
   const int pp_sh = 16 * (pp & 1);
   const bool pp_upper = pp >= 2;
   const uint32_t h_off = sub * 144, q_off = sub * 144 + 16 + 32 * pp;
+  const uint32_t h_off_half = (sub & 3) * 144, q_off_half = (sub & 3) * 144 + 16 + 32 * pp;
 
   int slot = 0;
   uint32_t parity = 0;
@@ -474,8 +476,8 @@ __global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_pair_kernel(const
 #pragma unroll
       for (int t = 0; t < T; ++t) accv[r][t] = 0.0f;
 #pragma unroll
-    for (int st = 0; st < WS; ++st) {
-      if (st * 8 + 7 < nsb || sub < nsb - st * 8) {
+    for (int st = 0; st < FS; ++st) {
+      {
         uint32_t wl[2][8], wh[2][8], sc2[2], mn2[2];
         float2 df[2];
 #pragma unroll
@@ -514,6 +516,43 @@ __global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_pair_kernel(const
             accv[r][t] = fmaf(df[r].x, tq, fmaf(-df[r].y, tm, accv[r][t]));
           }
         }
+      }
+    }
+    if (kHalf) {  // lanes 0..15: the first row's last four superblocks, lanes 16..31: the second row's
+      const unsigned char* wph = lane < 16 ? wp[0] : wp[1];
+      const uint4 h = *reinterpret_cast<const uint4*>(wph + FS * 1152 + h_off_half);
+      const uint4 qa = *reinterpret_cast<const uint4*>(wph + FS * 1152 + q_off_half);
+      const uint4 qb = *reinterpret_cast<const uint4*>(wph + FS * 1152 + q_off_half + 16);
+      const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+      uint32_t sc2, mn2;
+      q4k_pair(h, pp_sh, pp_upper, sc2, mn2);
+      const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+      uint32_t wl[8], wh[8];
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        wl[kk] = w[kk] & 0x0F0F0F0Fu;
+        wh[kk] = w[kk] & 0xF0F0F0F0u;
+      }
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        const unsigned char* base = act + (size_t)(FS * T + t) * kPairActBytes;
+        const uint4 a0 = reinterpret_cast<const uint4*>(base)[lane], a1 = reinterpret_cast<const uint4*>(base + 512)[lane];
+        const uint4 a2 = reinterpret_cast<const uint4*>(base + 1024)[lane], a3 = reinterpret_cast<const uint4*>(base + 1536)[lane];
+        const float4 sc = reinterpret_cast<const float4*>(base + 2048)[lane];
+        const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+        int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          lo0 = __dp4a((int)al[kk], (int)wl[kk], lo0);
+          lo1 = __dp4a((int)al[4 + kk], (int)wl[4 + kk], lo1);
+          hi0 = dp4a_su((int)ah[kk], wh[kk], hi0);
+          hi1 = dp4a_su((int)ah[4 + kk], wh[4 + kk], hi1);
+        }
+        const float tq = fmaf(sc.x, (float)((int)(sc2 & 0xFFu) * (lo0 + lo1)), sc.y * (float)((int)(sc2 >> 8) * (hi0 + hi1)));
+        const float tm = fmaf(sc.z, (float)(mn2 & 0xFFu), sc.w * (float)(mn2 >> 8));
+        const float r = fmaf(df.x, tq, -df.y * tm);
+        accv[0][t] += lane < 16 ? r : 0.0f;
+        accv[1][t] += lane < 16 ? 0.0f : r;
       }
     }
     __syncwarp();

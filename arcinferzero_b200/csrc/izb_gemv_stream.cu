@@ -628,6 +628,199 @@ int launch_q4k_pair_k(const izb_weight* w, const uint8_t* raw, const int8_t* aq,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- Q4_K, long rows (K > 5120)
+// A row of a down projection (K = 17408: 9.8 KB) is too long for a ring of whole rows per warp, and such matrices have few
+// rows per warp (5120 rows over 2368 warps), so rows are not paired either.  Here the ring holds chunks of eight
+// superblocks (1152 B, one step of the lane mapping of gemv_q4k_pair_kernel) and a warp takes two consecutive chunks of
+// ONE row per pass (two independent dependency chains), its rows one after the other; the copies of the chunks
+// `slots / 2` passes ahead are in flight, across row boundaries.  K = 1024 * odd ends in a chunk of four superblocks
+// (lanes 16..31 repeat lanes 0..15 there and are dropped).  Activations staged per lane in shared memory (1..4 rows).
+constexpr int kChunkBytes = 8 * 144;
+
+template <int T>
+__global__ void __launch_bounds__(kPairWarps * 32, 1) gemv_q4k_chunk_kernel(const uint8_t* __restrict__ raw, int N, int K,
+                                                                           const int8_t* __restrict__ aq, const float* __restrict__ asc,
+                                                                           int Mp, float* __restrict__ C, int ldc, int c_off, int acc,
+                                                                           int slots, uint32_t* err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int nsb = K >> 8, FS = nsb >> 3, WS = (nsb + 7) >> 3;  // chunks per row: FS whole ones (+ one of four superblocks)
+  const int PP = (WS + 1) >> 1;                                 // passes per row (two chunks each, the last maybe one)
+  const uint32_t row_bytes = (uint32_t)nsb * 144;
+  const int act_bytes = WS * T * kPairActBytes;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int W = gridDim.x * kPairWarps, w0 = blockIdx.x * kPairWarps + warp;
+  const int my_rows = w0 < N ? (N - w0 + W - 1) / W : 0;
+  const int total = my_rows * PP;  // passes of this warp, in order (row, pass)
+  const int sub = lane >> 2, pp = lane & 3, hs = slots >> 1;
+  unsigned char* act = smem;
+  unsigned char* ring = smem + act_bytes + (size_t)warp * slots * kChunkBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + act_bytes + (size_t)kPairWarps * slots * kChunkBytes) + warp * slots;
+  // pass n -> copies of chunks 2 * (n % PP), + 1 of row n / PP into slots 2 * (n % hs), + 1
+  auto issue = [&](int n) {
+    const int ri = n / PP, c0 = 2 * (n - ri * PP), q = n % hs;
+    const uint8_t* src = raw + (size_t)(w0 + ri * W) * row_bytes + (size_t)c0 * kChunkBytes;
+    row_copy(s_u32(ring + (size_t)(2 * q) * kChunkBytes), src, c0 < FS ? kChunkBytes : kChunkBytes / 2, s_u32(&bars[2 * q]));
+    if (c0 + 1 < WS)
+      row_copy(s_u32(ring + (size_t)(2 * q + 1) * kChunkBytes), src + kChunkBytes, c0 + 1 < FS ? kChunkBytes : kChunkBytes / 2, s_u32(&bars[2 * q + 1]));
+    else  // (no second chunk in this pass: the slot's barrier still completes its phase, so that its parity keeps step)
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(&bars[2 * q + 1])) : "memory");
+  };
+  if (lane == 0) {
+    for (int s = 0; s < slots; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(&bars[s])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int n = 0; n < hs && n < total; ++n) issue(n);
+  }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // (see gemv_q4k_reg_kernel: the ring fill above runs ahead of it)
+  for (int i = threadIdx.x; i < WS * T * 32; i += blockDim.x) {
+    const int l = i & 31, t = (i >> 5) % T, st = (i >> 5) / T;
+    const int sb = st < FS ? st * 8 + (l >> 2) : st * 8 + ((l >> 2) & 3), p2 = l & 3;
+    const int8_t* a = aq + (size_t)t * K + sb * 256 + p2 * 64;
+    const uint4 a0 = *reinterpret_cast<const uint4*>(a), a1 = *reinterpret_cast<const uint4*>(a + 16);
+    const uint4 a2 = *reinterpret_cast<const uint4*>(a + 32), a3 = *reinterpret_cast<const uint4*>(a + 48);
+    const int b = sb * 8 + p2 * 2;
+    const float s0 = asc[(size_t)b * Mp + t], s1 = asc[(size_t)(b + 1) * Mp + t];
+    const uint32_t lw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, hw[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+    int sl = 0, sh = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      sl = __dp4a((int)lw[k], 0x01010101, sl);
+      sh = __dp4a((int)hw[k], 0x01010101, sh);
+    }
+    unsigned char* base = act + (size_t)(st * T + t) * kPairActBytes;
+    reinterpret_cast<uint4*>(base)[l] = a0;
+    reinterpret_cast<uint4*>(base + 512)[l] = a1;
+    reinterpret_cast<uint4*>(base + 1024)[l] = a2;
+    reinterpret_cast<uint4*>(base + 1536)[l] = a3;
+    reinterpret_cast<float4*>(base + 2048)[l] = make_float4(s0, s1 * 0.0625f, s0 * (float)sl, s1 * (float)sh);
+  }
+  __syncthreads();
+  const int pp_sh = 16 * (pp & 1);
+  const bool pp_upper = pp >= 2;
+  const uint32_t h_off = sub * 144, q_off = sub * 144 + 16 + 32 * pp;
+  const uint32_t h_off_half = (sub & 3) * 144, q_off_half = (sub & 3) * 144 + 16 + 32 * pp;
+
+  float accv[T];
+#pragma unroll
+  for (int t = 0; t < T; ++t) accv[t] = 0.0f;
+  // one chunk against every token: the chunk's nibbles are masked once
+  auto chunk = [&](const unsigned char* wp, uint32_t ho, uint32_t qo, const unsigned char* abase, float (&out)[T]) {
+    const uint4 h = *reinterpret_cast<const uint4*>(wp + ho);
+    const uint4 qa = *reinterpret_cast<const uint4*>(wp + qo), qb = *reinterpret_cast<const uint4*>(wp + qo + 16);
+    const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+    uint32_t sc2, mn2;
+    q4k_pair(h, pp_sh, pp_upper, sc2, mn2);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    uint32_t wl[8], wh[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      wl[kk] = w[kk] & 0x0F0F0F0Fu;
+      wh[kk] = w[kk] & 0xF0F0F0F0u;
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      const unsigned char* base = abase + (size_t)t * kPairActBytes;
+      const uint4 a0 = reinterpret_cast<const uint4*>(base)[lane], a1 = reinterpret_cast<const uint4*>(base + 512)[lane];
+      const uint4 a2 = reinterpret_cast<const uint4*>(base + 1024)[lane], a3 = reinterpret_cast<const uint4*>(base + 1536)[lane];
+      const float4 sc = reinterpret_cast<const float4*>(base + 2048)[lane];
+      const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+      int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        lo0 = __dp4a((int)al[kk], (int)wl[kk], lo0);
+        lo1 = __dp4a((int)al[4 + kk], (int)wl[4 + kk], lo1);
+        hi0 = dp4a_su((int)ah[kk], wh[kk], hi0);
+        hi1 = dp4a_su((int)ah[4 + kk], wh[4 + kk], hi1);
+      }
+      const float tq = fmaf(sc.x, (float)((int)(sc2 & 0xFFu) * (lo0 + lo1)), sc.y * (float)((int)(sc2 >> 8) * (hi0 + hi1)));
+      const float tm = fmaf(sc.z, (float)(mn2 & 0xFFu), sc.w * (float)(mn2 >> 8));
+      out[t] = fmaf(df.x, tq, -df.y * tm);
+    }
+  };
+  for (int n = 0; n < total; ++n) {
+    const int ri = n / PP, c0 = 2 * (n - ri * PP), q = n % hs;
+    const uint32_t parity = (uint32_t)(n / hs) & 1u;
+    const bool two = c0 + 1 < WS;  // (uniform over the warp)
+    bool ready = false;
+    for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[2 * q]), parity);
+    if (ready && two) {
+      ready = false;
+      for (uint32_t it = 0; it < kSpin && !ready; ++it) ready = try_wait(s_u32(&bars[2 * q + 1]), parity);
+    }
+    if (!ready) {  // (bounded wait gave up)
+      if (lane == 0) atomicOr(err, 64u);
+      break;
+    }
+    const unsigned char* wa = ring + (size_t)(2 * q) * kChunkBytes;
+    const unsigned char* abase = act + (size_t)c0 * T * kPairActBytes;
+    float r0[T], r1[T];
+    // a chunk of four superblocks is read with the half-warp mapping by all lanes; lanes 16..31 are dropped
+    const bool h0 = c0 >= FS, h1 = c0 + 1 >= FS;
+    chunk(wa, h0 ? h_off_half : h_off, h0 ? q_off_half : q_off, abase, r0);
+    const float k0 = (h0 && lane >= 16) ? 0.0f : 1.0f;
+    if (two) {
+      chunk(wa + kChunkBytes, h1 ? h_off_half : h_off, h1 ? q_off_half : q_off, abase + (size_t)T * kPairActBytes, r1);
+      const float k1 = (h1 && lane >= 16) ? 0.0f : 1.0f;
+#pragma unroll
+      for (int t = 0; t < T; ++t) accv[t] += k0 * r0[t] + k1 * r1[t];
+    } else {
+#pragma unroll
+      for (int t = 0; t < T; ++t) accv[t] += k0 * r0[t];
+    }
+    __syncwarp();
+    if (lane == 0 && n + hs < total) issue(n + hs);  // the slots are read: the pass `hs` ahead goes into them
+    if (c0 + 2 >= WS) {  // the row is complete
+      const int row = w0 + ri * W;
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        const float v = warp_sum(accv[t]);
+        if (lane == 0) {
+          float* cp = C + (size_t)t * ldc + c_off + row;
+          *cp = acc ? *cp + v : v;
+        }
+        accv[t] = 0.0f;
+      }
+    }
+  }
+}
+
+template <int T>
+int launch_q4k_chunk(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc, int c_off,
+                     int acc, cudaStream_t st) {
+  constexpr size_t kBudget = 216 * 1024;
+  const int nsb = w->K / 256, WS = (nsb + 7) / 8;
+  const size_t act = (size_t)WS * T * kPairActBytes;
+  if (act + 4096 + (size_t)kPairWarps * 4 * kChunkBytes > kBudget) return 1;
+  int slots = (int)((kBudget - act - 4096) / ((size_t)kPairWarps * kChunkBytes));
+  slots = slots > 12 ? 12 : (slots & ~1);
+  const size_t smem = act + (size_t)kPairWarps * slots * kChunkBytes + (size_t)kPairWarps * slots * 8;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    IZB_CUDA(cudaGetDevice(&dev));
+    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    IZB_CUDA(cudaFuncSetAttribute(gemv_q4k_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
+  }
+  int grid = sms;
+  const int need = (w->N + kPairWarps - 1) / kPairWarps;
+  if (grid > need) grid = need;
+  uint32_t* err = izb_device_error_word(w->device);
+  if (!err) IZB_FAIL(IZB_ERR_NOMEM, "gemv: no device error word");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kPairWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int N = w->N, K = w->K;
+  IZB_LAUNCH("gemv", st, cudaLaunchKernelEx(&cfg, gemv_q4k_chunk_kernel<T>, raw, N, K, aq, asc, Mp, C, ldc, c_off, acc, slots, err));
+  return IZB_OK;
+}
+
 template <int QT, int T>
 int launch_stream(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc,
                   int c_off, int acc, cudaStream_t st) {
@@ -684,6 +877,16 @@ int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t
       case 4: return launch_q4k_reg<4>(w, raw, aq, asc, Mp, C, c_off, acc, st);
       default: return launch_q4k_reg<5>(w, raw, aq, asc, Mp, C, c_off, acc, st);
     }
+  }
+  if (T <= 4 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K > 5120 && w->N >= kManyRows) {  // long rows: ring of chunks
+    int rc = 1;
+    switch (T) {
+      case 1: rc = launch_q4k_chunk<1>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st); break;
+      case 2: rc = launch_q4k_chunk<2>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st); break;
+      case 3: rc = launch_q4k_chunk<3>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st); break;
+      default: rc = launch_q4k_chunk<4>(w, raw, aq, asc, Mp, C, ldc, c_off, acc, st); break;
+    }
+    if (rc != 1) return rc;  // (+1: the activations alone do not fit: the kernels below take the call)
   }
   if (T >= 2 && T <= 4 && w->type == IZB_Q4_K && w->K % 1024 == 0 && w->K <= 5120 && w->N >= kManyRows) {
     switch (T) {

@@ -136,7 +136,7 @@ def test_gemv_matches_oracle(izb, torch, qt, T, N, K):
 
 
 @pytest.mark.parametrize("T", [1, 2, 3, 4])
-@pytest.mark.parametrize("N,K", [(1030, 2048), (8195, 1024), (9001, 3072), (5120, 5120), (17408, 5120)])
+@pytest.mark.parametrize("N,K", [(1030, 2048), (8195, 1024), (9001, 3072), (5120, 5120), (17408, 5120), (5120, 17408), (1501, 8192), (1100, 7168)])
 def test_gemv_q4k_many_rows(izb, torch, T, N, K):
     """The Q4_K decode kernels taken from 1024 weight rows on (activations in registers for one row, staged per lane for
     2..4; two weight rows per warp pass): odd row counts, K with a half-empty last step, store offset and accumulate."""

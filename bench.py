@@ -163,14 +163,15 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
     HBM; GB/s = (weight bytes + activation bytes + output bytes) / mean launch time over the timed launches."""
     from arcinferzero_b200 import synth as S
     out = []
-    for qt, Nn in ((12, 5120), (12, 17408), (8, 151936)):
-        w = S.make_weight(qt, Nn, K, SEED + Nn)
+    # config 3's three matrices, then the down-projection shape of the same model (long rows: not in config 3)
+    for qt, Nn, Kk in ((12, 5120, K), (12, 17408, K), (8, 151936, K), (12, 5120, 17408)):
+        w = S.make_weight(qt, Nn, Kk, SEED + Nn + (0 if Kk == K else Kk))
         wbytes = w.size
         copies = max(1, -(-300_000_000 // wbytes)) if wbytes < 400_000_000 else 2
-        Ws = [izb.Weight(qt, w, Nn, K) for _ in range(copies)]
+        Ws = [izb.Weight(qt, w, Nn, Kk) for _ in range(copies)]
         del w
         for T in (1, 2):
-            x = torch.from_numpy(S.make_act(T, K, SEED + T)).cuda()
+            x = torch.from_numpy(S.make_act(T, Kk, SEED + T)).cuda()
             aq, asc, _ = izb.quantize_act(x, Mp=16)
             y = torch.empty((T, Nn), dtype=torch.float32, device="cuda")
             for i in range(max(3, copies)):
@@ -193,9 +194,9 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
             e1.record()
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
-            nbytes = wbytes + T * (K + K // 32 * 4) + T * Nn * 4
+            nbytes = wbytes + T * (Kk + Kk // 32 * 4) + T * Nn * 4
             gbs = nbytes / (us * 1e-6) / 1e9
-            out.append({"type": "Q4_K" if qt == 12 else "Q8_0", "N": Nn, "K": K, "batch": T, "us_per_launch": us,
+            out.append({"type": "Q4_K" if qt == 12 else "Q8_0", "N": Nn, "K": Kk, "batch": T, "in_config3": Kk == K, "us_per_launch": us,
                         "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
                         "peak": f"{hbm_peak} GB/s {peak_src} copy", "weight_copies_in_rotation": copies})
         for W_ in Ws:

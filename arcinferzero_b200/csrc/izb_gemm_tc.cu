@@ -321,13 +321,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   const int nstages = SPS * nsb;
 
   if (threadIdx.x == 0) {
-    // S_FULL: the activation producer's expect_tx arrival + the four dequantiser warps; S_EMPTY: one tcgen05.commit
-    for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), 5); mbar_init(bar(S_EMPTY + i), 1); }
-    for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), 4); }
-    for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 8); }
+    // Consumers release a buffer with one arrival per THREAD, not per warp: an elected lane costs a divergent branch and a
+    // warp barrier per hand-over, which measured 10 % of the kernel.  S_FULL: the activation producer's expect_tx arrival
+    // + the 128 dequantiser threads; S_EMPTY: one tcgen05.commit
+    for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), 129); mbar_init(bar(S_EMPTY + i), 1); }
+    for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), 128); }
+    for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 256); }
     mbar_init(bar(D2_FULL), 1);
-    mbar_init(bar(D2_EMPTY), 8);
-    for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), 8); }
+    mbar_init(bar(D2_EMPTY), 256);
+    for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), 256); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -509,8 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           }
         }
         fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(S_FULL + sbq));
+        mbar_arrive(bar(S_FULL + sbq));  // (every thread after its own stores and fence)
         if (++sbq == NS) { sbq = 0; pbq ^= 1; }
       }
       if (!ok) break;
@@ -550,12 +551,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         *reinterpret_cast<uint4*>(orow + ((4 ^ (t & 7)) << 4)) = c2;
         *reinterpret_cast<uint4*>(orow + ((5 ^ (t & 7)) << 4)) = c1;
         fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(S_FULL + sbq));
+        mbar_arrive(bar(S_FULL + sbq));  // (every thread after its own stores and fence)
         if (++sbq == NS) { sbq = 0; pbq ^= 1; }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(RAW_EMPTY + rb));
+      mbar_arrive(bar(RAW_EMPTY + rb));
       if (++rb == NR) { rb = 0; pr ^= 1; }
     }
   } else {
@@ -588,8 +587,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         unsigned long long v[32];
         tc_ld64_pairs(t_lane + (uint32_t)(d * BN), v);  // the thread's 64 columns of this block; returns when they are in registers
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
+        mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
         if (kDots) {
           if (row_ok) {
             int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64) * nb + 8 * s + b;
@@ -620,8 +618,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
       if (!ok) break;
       if (!kDots) {  // the superblock's scales are read: its ring slot may be refilled
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(ASC_EMPTY + sq));
+        mbar_arrive(bar(ASC_EMPTY + sq));
         if (++sq == NASC) { sq = 0; pq ^= 1; }
       }
       if (kMins) {  // res += d * tq
@@ -641,8 +638,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         unsigned long long v[32];
         tc_ld64_pairs(t_lane + (uint32_t)(ND1 * BN), v);
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(D2_EMPTY));  // the next tile's min term may start
+        mbar_arrive(bar(D2_EMPTY));  // the next tile's min term may start
         const unsigned long long one2 = pack2(1.0f);
 #pragma unroll
         for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);

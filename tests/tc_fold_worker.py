@@ -52,6 +52,27 @@ def main():
     assert rowerr.max() < 1e-5, rowerr.max()  # per row too: the row factor keeps small rows exact
     assert (out[3] == 0).all()
     W.close()
+    # superblock scales d that are zero (with dmin != 0), denormal, negative: the min term travels through the accumulator
+    # that is multiplied by d, so these are the cases that could go wrong
+    M, N, K = 64, 256, 1024
+    w = S.make_weight(qt, N, K, 21).reshape(N, K // 256, 144).copy()
+    w[0, :, 0:2] = 0                       # d = 0 in every superblock of row 0
+    w[1, 1, 0:2] = 0                       # ... and in one superblock of row 1
+    w[2, :, 0] = 1; w[2, :, 1] = 0         # d = 2^-24 (smallest denormal)
+    w[3, :, 1] |= 0x80                     # d negative
+    w[130, 2, 0:2] = 0                     # (second half of the tile)
+    w = w.reshape(N, -1)
+    W = izb.Weight(qt, w, N, K)
+    Mp = izb.pad_rows(M)
+    aq, asc, _ = izb.quantize_act(torch.from_numpy(S.make_act(M, K, 22)).cuda(), Mp=Mp)
+    out = izb.gemm(W, aq, asc, M=M, impl=izb.GEMM_TC).cpu().numpy()[:M]
+    ref = O.matmul(qt, w, K, aq.cpu().numpy(), asc.cpu().numpy(), M, "f64")
+    for col in (0, 1, 2, 3, 130):
+        e = float(np.abs(out[:, col] - ref[:, col]).max() / max(np.abs(ref[:, col]).max(), 1e-30))
+        assert e < 1e-5, (col, e)
+    err = float(np.abs(out - ref).max() / np.abs(ref).max())
+    assert err < 1e-5, err
+    W.close()
     # several tiles per CTA (persistent walk), K = 5120
     M, N, K = 2048, 10240, 5120
     w = S.make_weight(qt, N, K, 1)

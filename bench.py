@@ -36,7 +36,7 @@ QT = 12
 SEED = 20261125
 WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantize_act + GEMM per step)"
 NOMINAL_INT8_TOPS = 4500.0
-NCU_TRAFFIC_BYTES_PER_TILE = (128.8e6 + 114.2e6) / (16 * 136)
+NCU_TRAFFIC_BYTES_PER_TILE = (132.1e6 + 116.6e6) / (16 * 136)
 
 
 def peaks():

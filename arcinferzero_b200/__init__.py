@@ -22,7 +22,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
-    "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant",
+    "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
     "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_destroy", "izb_tp_allreduce_rows",
@@ -172,6 +172,12 @@ def add_norm_quant(x, t, w, eps: float, s: float = 1.0, w2=None, Mp: int | None 
     asc = torch.empty((K // 32, Mp), dtype=torch.float32, device=x.device)
     _check(lib().izb_add_norm_quant(_p(x), _p(t), _p(w), C.c_float(eps), C.c_float(s), _p(w2), M, Mp, K, _p(aq), _p(asc), None, _stream()))
     return aq, asc
+
+
+def softcap_rows(c, rows: int, N: int, cap: float, off: int = 0):
+    """In place c[r, off:off+N] = cap * tanh(c[r, off:off+N] / cap) for r < rows (the output head's logit soft-cap)."""
+    _check(lib().izb_softcap_rows(_p(c), rows, c.stride(0), off, N, C.c_float(cap), _stream()))
+    return c
 
 
 def matmul(w: Weight, aq, asc, T: int, out=None, c_off: int = 0, acc: int = 0, mat: int = 0):

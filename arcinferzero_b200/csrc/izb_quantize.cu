@@ -289,3 +289,41 @@ extern "C" int izb_add_norm_quant(float* d_x, const float* d_t, const float* d_w
   if (Mp > M_valid) IZB_LAUNCH("zero_pad_rows", st, zero_pad_rows_kernel<<<Mp - M_valid, 256, 0, st>>>(M_valid, Mp, K, d_aq, d_asc, d_absum));
   return IZB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------- logit soft-cap
+// softcap_rows (zero/kernels/ops_attn_g.cl:724) and the output head's HEAD_OUT (zero/kernels/decode.cl:882-887):
+// v = cap * tanh(v * (1 / cap)) on columns off .. off+N-1 of `rows` rows.  One float4 per thread where the row start is
+// 16-byte aligned, scalars otherwise.
+namespace {
+__global__ void __launch_bounds__(256) softcap_rows_kernel(float* __restrict__ C, int ld, int off, int N, float cap, float rcap, int vec) {
+  float* p = C + (size_t)blockIdx.y * ld + off;
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (vec) {
+    if (4 * i + 3 < N) {
+      float4 v = *reinterpret_cast<float4*>(p + 4 * i);
+      v.x = __fmul_rn(cap, tanhf(__fmul_rn(v.x, rcap)));
+      v.y = __fmul_rn(cap, tanhf(__fmul_rn(v.y, rcap)));
+      v.z = __fmul_rn(cap, tanhf(__fmul_rn(v.z, rcap)));
+      v.w = __fmul_rn(cap, tanhf(__fmul_rn(v.w, rcap)));
+      *reinterpret_cast<float4*>(p + 4 * i) = v;
+    } else {
+      for (int n = 4 * i; n < N; ++n) p[n] = __fmul_rn(cap, tanhf(__fmul_rn(p[n], rcap)));
+    }
+  } else if (i < N) {
+    p[i] = __fmul_rn(cap, tanhf(__fmul_rn(p[i], rcap)));
+  }
+}
+}  // namespace
+
+extern "C" int izb_softcap_rows(float* d_C, int rows, int ld, int off, int N, float cap, void* stream) {
+  if (!d_C) IZB_FAIL(IZB_ERR_ARG, "softcap_rows: null pointer");
+  if (rows < 0 || N < 0 || off < 0 || (rows > 1 && ld < off + N)) IZB_FAIL(IZB_ERR_SHAPE, "softcap_rows: rows=%d ld=%d off=%d N=%d", rows, ld, off, N);
+  if (!(cap > 0.0f)) IZB_FAIL(IZB_ERR_ARG, "softcap_rows: cap = %g (must be positive)", (double)cap);
+  if (rows == 0 || N == 0) return IZB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int vec = izb_aligned(d_C, 16) && ld % 4 == 0 && off % 4 == 0;
+  const int per_row = vec ? (N + 3) / 4 : N;
+  dim3 grid((per_row + 255) / 256, rows);
+  IZB_LAUNCH("softcap_rows", st, softcap_rows_kernel<<<grid, 256, 0, st>>>(d_C, ld, off, N, cap, 1.0f / cap, vec));
+  return IZB_OK;
+}

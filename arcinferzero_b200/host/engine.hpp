@@ -100,6 +100,11 @@ class Engine {
     check(izb_add_norm_quant(x, t, w, eps, s, w2, cur_T_, Mp, K, aq_, asc_, nullptr, stream_), "add_norm_quant");
     cur_K_ = K; cur_Mp_ = Mp;
   }
+  // softcap_rows (zero/engine.h:1102-1111, zero/kernels/ops_attn_g.cl:724): the output head's logit soft-cap on the
+  // current rows of C, columns c_off .. c_off + N - 1
+  void softcap_rows(float* C, int ldc, int c_off, int N, float cap) {
+    check(izb_softcap_rows(C, cur_T_, ldc, c_off, N, cap, stream_), "softcap_rows");
+  }
   // matmul (zero/engine.h:1080): C[.][c_off + n] (op)= quantised rows x w; acc 0 store, 1 add, 2 fused SwiGLU.
   // `name` is the reference's profiling label; act32 is always on (per-32 scales, the reference's default).
   void matmul(const char* name, const GpuWeight& w, int Mp, float* C, int ldc, int c_off, int acc, bool act32 = true) {

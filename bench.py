@@ -170,12 +170,18 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
         copies = max(1, -(-300_000_000 // wbytes)) if wbytes < 400_000_000 else 2
         Ws = [izb.Weight(qt, w, Nn, Kk) for _ in range(copies)]
         del w
-        for T in (1, 2):
+        # (the output head once more with its logit soft-cap, as the reference's Gemma head runs: GEMV, then cap * tanh(v / cap))
+        for T, cap in ((1, 0.0), (2, 0.0)) + (((1, 30.0),) if qt == 8 else ()):
             x = torch.from_numpy(S.make_act(T, Kk, SEED + T)).cuda()
             aq, asc, _ = izb.quantize_act(x, Mp=16)
             y = torch.empty((T, Nn), dtype=torch.float32, device="cuda")
-            for i in range(max(3, copies)):
+            def launch(i):
                 izb.gemv(Ws[i % copies], aq, asc, T, out=y)
+                if cap > 0:
+                    izb.softcap_rows(y, T, Nn, cap)
+
+            for i in range(max(3, copies)):
+                launch(i)
             torch.cuda.synchronize()
             # the launches of one sweep over the copies are captured in a CUDA graph, so that the host's per-call cost
             # (Python + ctypes) is not what is measured
@@ -183,7 +189,7 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for i in range(launches):
-                    izb.gemv(Ws[i % copies], aq, asc, T, out=y)
+                    launch(i)
             graph.replay()
             torch.cuda.synchronize()
             reps = 1 if lite else 5
@@ -194,9 +200,9 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
             e1.record()
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
-            nbytes = wbytes + T * (Kk + Kk // 32 * 4) + T * Nn * 4
+            nbytes = wbytes + T * (Kk + Kk // 32 * 4) + T * Nn * 4 * (3 if cap > 0 else 1)  # (the cap reads and writes the row again)
             gbs = nbytes / (us * 1e-6) / 1e9
-            out.append({"type": "Q4_K" if qt == 12 else "Q8_0", "N": Nn, "K": Kk, "batch": T, "in_config3": Kk == K, "us_per_launch": us,
+            out.append({"type": "Q4_K" if qt == 12 else "Q8_0", "N": Nn, "K": Kk, "batch": T, "softcap": cap, "in_config3": Kk == K and cap == 0, "us_per_launch": us,
                         "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
                         "peak": f"{hbm_peak} GB/s {peak_src} copy", "weight_copies_in_rotation": copies})
         for W_ in Ws:

@@ -110,6 +110,12 @@ int izb_rmsnorm_quant(const float* d_x, int ldx, const float* d_w, float eps, in
 int izb_add_norm_quant(float* d_x, const float* d_t, const float* d_w, float eps, float s, const float* d_w2, int M_valid, int Mp,
                        int K, int8_t* d_aq, float* d_asc, int16_t* d_absum, void* stream);
 
+/* Logit soft-cap of the output head (softcap_rows, zero/kernels/ops_attn_g.cl:724; the head GEMVs' HEAD_OUT epilogue,
+ * zero/kernels/decode.cl:882-887; call site zero/engine.h:1102-1111): C[r][off + n] = cap * tanh(C[r][off + n] * (1 / cap))
+ * for r < rows, n < N, in place; row stride ld in floats (the reference passes ld = 0 for one row: any ld is accepted when
+ * rows == 1).  cap > 0.  Call it after izb_matmul / izb_gemv on the head's output rows. */
+int izb_softcap_rows(float* d_C, int rows, int ld, int off, int N, float cap, void* stream);
+
 /* ------------------------------------------------------------------------------------------------ matmul
  * Replaces Engine::matmul / matmul1 (zero/engine.h:1080,1147-1251): C[t][c_off + n] (op)= sum_k A[t][k] W[n][k] for
  * the T valid rows, dispatching on T as the reference does: T == 1 -> GEMV (decode.cl gemv, :913), 2..8 -> few-row

@@ -540,6 +540,17 @@ void orc_swiglu(const float* g, const float* u, size_t n, float* h) {
   for (size_t i = 0; i < n; ++i) h[i] = g[i] / (1.0f + expf(-g[i])) * u[i];
 }
 
+/* ---------------------------------------------------------------- logit soft-cap (zero/kernels/ops_attn_g.cl:724-729;
+ * zero/kernels/decode.cl:882-887 HEAD_OUT): v = cap * tanh(v * (1 / cap)) on columns off .. off+N-1 of `rows` rows */
+void orc_softcap_rows(float* c, int rows, int ld, int off, int N, float cap) {
+  const float rcap = 1.0f / cap;
+  for (int r = 0; r < rows; ++r)
+    for (int n = 0; n < N; ++n) {
+      float* p = c + (size_t)r * ld + off + n;
+      *p = cap * tanhf(*p * rcap);
+    }
+}
+
 /* ---------------------------------------------------------------- tensor parallel
  * rank r's part of `total` in whole units (zero/mgpu/engine_tp_shard.h:68-72) */
 void orc_tp_range(int64_t total, int64_t unit, int N, int r, int64_t* begin, int64_t* end) {

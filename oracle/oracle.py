@@ -217,6 +217,13 @@ def tp_range(total: int, unit: int, N: int, r: int):
     return b.value, e.value
 
 
+def softcap_rows(c: np.ndarray, rows: int, N: int, cap: float, off: int = 0) -> np.ndarray:
+    """Copy of c [R, ld] f32 with c[r, off:off+N] = cap * tanh(c / cap) for r < rows."""
+    out = np.ascontiguousarray(c, dtype=np.float32).copy()
+    lib().orc_softcap_rows(_vp(out), rows, out.shape[1], off, N, C.c_float(cap))
+    return out
+
+
 def tp_add(x: np.ndarray, parts: np.ndarray) -> np.ndarray:
     out = np.array(x, np.float32, copy=True, order="C")
     parts = np.ascontiguousarray(parts, np.float32)

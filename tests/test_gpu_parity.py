@@ -340,3 +340,36 @@ def test_matmul_host_round_trip(izb, torch):
     aq, asc, _ = O.quantize_act(x, Mp=izb.pad_rows(M))
     assert rel(oh.numpy(), O.matmul(qt, w, K, aq, asc, M, "f64")) < TOL
     W.close()
+
+
+@pytest.mark.parametrize("rows,ld,N,off,cap", [(1, 151936, 151936, 0, 30.0), (8, 1032, 1000, 4, 50.0), (3, 517, 501, 7, 30.0), (2, 64, 1, 3, 0.5)])
+def test_softcap_rows_against_the_oracle(izb, torch, rows, ld, N, off, cap):
+    """izb_softcap_rows (softcap_rows, zero/kernels/ops_attn_g.cl:724) against the oracle: within 1e-6 of the cap
+    (tanhf of two math libraries), vectorised and scalar row starts, everything outside the capped region untouched."""
+    rng = np.random.default_rng(N + off)
+    c = (rng.standard_normal((rows + 1, ld)) * 2 * cap).astype(np.float32)
+    c[0, off:off + min(N, 4)] = [0.0, 1e4, -1e4, 1e-20][:min(N, 4)]
+    d = torch.from_numpy(c).cuda()
+    izb.softcap_rows(d, rows, N, cap, off)
+    out = d.cpu().numpy()
+    ref = O.softcap_rows(c, rows, N, cap, off)
+    assert np.abs(out - ref).max() <= 1e-6 * cap
+    keep = np.ones_like(c, dtype=bool)
+    keep[:rows, off:off + N] = False
+    assert (out[keep] == c[keep]).all()
+    assert np.abs(out[:rows, off:off + N]).max() <= cap
+
+
+def test_softcap_after_the_head_gemv(izb, torch):
+    """The output head as the reference runs it (zero/engine.h:1080-1111): Q8_0 GEMV of one row, then the soft-cap."""
+    N, K, cap = 4096, 1024, 30.0
+    w = S.make_weight(8, N, K, 31)
+    W = izb.Weight(8, w, N, K)
+    x = S.make_act(1, K, 32) * 40
+    aq, asc, _ = izb.quantize_act(torch.from_numpy(x).cuda(), Mp=16)
+    out = izb.matmul(W, aq, asc, 1)
+    izb.softcap_rows(out, 1, N, cap)
+    ref = O.matmul(8, w, K, aq.cpu().numpy(), asc.cpu().numpy(), 1, "f64")[:1].astype(np.float64)
+    ref = cap * np.tanh(ref / cap)
+    assert np.abs(out.cpu().numpy()[:1] - ref).max() / np.abs(ref).max() < 1e-5
+    W.close()

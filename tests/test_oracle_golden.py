@@ -183,3 +183,19 @@ def test_add_norm_quant_composes_the_pinned_pieces(golden_dir):
     y2, raq2, rasc2, _ = O.rmsnorm_quant(xn2, w, eps)
     assert np.max(np.abs(aq2.astype(np.int32) - raq2.astype(np.int32))) <= 1
     assert np.allclose(asc2, rasc2, rtol=1e-6, atol=0)
+
+
+def test_softcap_rows_oracle_against_the_formula_in_double():
+    """cap * tanh(v / cap) (tools/ref_forward.cpp:1479-1483 is the reference's CPU form, zero/kernels/ops_attn_g.cl:724 the
+    device form): the oracle's f32 result against the same expression in f64; untouched outside the rows and columns."""
+    rng = np.random.default_rng(3)
+    c = (rng.standard_normal((5, 300)) * 40).astype(np.float32)
+    c[0, :6] = [0.0, -0.0, 1e-30, -1e4, 1e4, 29.999]
+    for cap, rows, N, off in ((30.0, 3, 256, 8), (50.0, 5, 300, 0), (0.5, 1, 7, 3)):
+        out = O.softcap_rows(c, rows, N, cap, off)
+        ref = c.astype(np.float64)
+        ref[:rows, off:off + N] = cap * np.tanh(ref[:rows, off:off + N] / cap)
+        assert np.abs(out - ref).max() <= 4e-7 * cap
+        keep = np.ones_like(c, dtype=bool)
+        keep[:rows, off:off + N] = False
+        assert (out[keep] == c[keep]).all()

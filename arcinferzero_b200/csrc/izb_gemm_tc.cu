@@ -125,6 +125,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   atomicOr(err, code);
   return false;
 }
+// The same for waiters that are not on the critical path: they sleep between polls, which leaves the issue slots of their
+// scheduler to the warps that are.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
+                                                  uint32_t code) {
+  for (uint32_t it = 0; it < (kSpinLimit >> 2); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(100);
+    if ((it & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicOr(err, code);
+  return false;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                "r"(bytes), "r"(bar)
@@ -898,7 +911,7 @@ __global__ void __launch_bounds__(F_THREADS, 1) gemm_tc_fold_kernel(const __grid
         for (int g = 0; g < 5 * nsb; ++g) {
           const int s = g / 5, t = g - 5 * s;
           const uint32_t bytes = t < 4 ? F_ASTAGE : STAGE_BYTES;
-          if (!mbar_wait(bar(F_A_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) { ok = false; break; }
+          if (!mbar_wait_relaxed(bar(F_A_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) { ok = false; break; }
           if (lane == 0) {
             mbar_expect_tx(bar(F_A_FULL + sa), bytes);
             bulk_g2s(smem_u32(smem + F_OFF_A + sa * F_ASTAGE), src + (size_t)s * F_SB_IMG + t * F_ASTAGE, bytes, bar(F_A_FULL + sa));
@@ -915,7 +928,7 @@ __global__ void __launch_bounds__(F_THREADS, 1) gemm_tc_fold_kernel(const __grid
         const int tile = w / n_ntiles;
         const int wrow = (p.tiles ? p.tiles[1 + 3 * tile] : p.mat) * p.N + (w % n_ntiles) * F_BN;
         for (int s2 = 0; s2 < 2 * nsb; ++s2) {  // (superblock, half)
-          if (!mbar_wait(bar(F_RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) { ok = false; break; }
+          if (!mbar_wait_relaxed(bar(F_RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) { ok = false; break; }
           if (lane == 0) {
             mbar_expect_tx(bar(F_RAW_FULL + rb), RAW_Q4);
             tma_2d(smem_u32(smem + F_OFF_RAW + rb * RAW_Q4), &tmW, (s2 >> 1) * (144 / 4), wrow + (s2 & 1) * BN, bar(F_RAW_FULL + rb));
@@ -1086,7 +1099,7 @@ __global__ void __launch_bounds__(F_THREADS, 1) gemm_tc_fold_kernel(const __grid
       for (int s = 0; s < nsb && ok; ++s, ++sbc) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          if (!mbar_wait(bar(F_D_FULL + h), sbc & 1, abort_flag, p.err, E_EPI)) { ok = false; break; }
+          if (!mbar_wait_relaxed(bar(F_D_FULL + h), sbc & 1, abort_flag, p.err, E_EPI)) { ok = false; break; }
           tc_fence_after();
           const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + F_OFF_DM + ((2 * sbc + h) & (F_NDM - 1)) * 512 + colq * 256);
 #pragma unroll

@@ -1219,16 +1219,25 @@ int launch_tc_fold(const izb_weight* w, const TcParams& p, dim3 grid, cudaStream
   return IZB_OK;
 }
 
-// Which kernel a Q4_K GEMM runs: the block-exact one, unless IZB_GEMM_FOLD=1 is set in the environment and N is a multiple
-// of 256.  The folded kernel is opt-in because it measured no faster (0.90 ms against 0.89 ms for 2048 x 17408 x 5120 on a
-// B200) while its pre-pass writes 1.8 times the operand bytes; the verification mode and Q8_0 always use the block-exact one.
-bool tc_use_fold(const izb_weight* w, const int32_t* dots) {
-  static int fold = -1;
-  if (fold < 0) {
+int tc_grid(int n_work);
+
+// Which kernel a Q4_K GEMM runs: the block-exact one, unless the environment asks for the folded kernel (N % 256 == 0
+// needed): IZB_GEMM_FOLD=1 wherever it can run, IZB_GEMM_FOLD=2 for dense GEMMs of at least eight 128 x 256 tiles per SM,
+// which is where it pays.  Measured on a B200, K = 5120, N = 17408: 2048 rows 0.88 ms against 0.89 ms for the block-exact
+// kernel; 8192 rows 3.25 ms against 3.48 ms in a short loop, but 3.45-3.51 ms against 3.58 ms per step in a sustained
+// run, where its doubled tensor-core work reaches the board's power cap; its pre-pass writes 1.8 times the operand
+// bytes.  A gain of 2-4 % does not outweigh a kernel with far more hours behind it, so it stays opt-in.  The
+// verification mode, Q8_0 and the grouped (MoE) GEMM (tile count only known on the device; mode 1 takes it there too)
+// otherwise always use the block-exact kernel.
+bool tc_use_fold(const izb_weight* w, const int32_t* dots, int n_mtiles, bool grouped) {
+  static int mode = -1;  // 0 never, 1 wherever possible, 2 large dense GEMMs
+  if (mode < 0) {
     const char* e = getenv("IZB_GEMM_FOLD");
-    fold = (e && e[0] == '1') ? 1 : 0;
+    mode = !e ? 0 : (e[0] == '1' ? 1 : (e[0] == '2' ? 2 : 0));
   }
-  return fold && w->type == IZB_Q4_K && !dots && w->N % F_BN == 0;
+  if (mode == 0 || w->type != IZB_Q4_K || dots || w->N % F_BN) return false;
+  if (mode == 1) return true;
+  return !grouped && (long long)n_mtiles * (w->N / F_BN) >= 8LL * tc_grid(1 << 30);
 }
 
 // persistent grid: one CTA per SM (shared memory allows no more), fewer when there are fewer tiles
@@ -1254,7 +1263,7 @@ int run_tc_on(const izb_weight* w, int mat, const int8_t* aq, const float* asc, 
               int n_tiles_grid, const int32_t* rowmap, const float* rowscale, int M_store, float* C, int ldc, int c_off, int acc,
               int32_t* dots, void* ws, uint32_t* err, cudaStream_t st, bool reuse_images) {
   const int K = w->K;
-  const bool fold = tc_use_fold(w, dots);
+  const bool fold = tc_use_fold(w, dots, n_tiles_grid, tiles != nullptr);
   const int sps = fold ? 9 : (w->type == IZB_Q4_K && !dots) ? 5 : 4;
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes(n_tiles_grid, K, sps, &img_bytes, &asc_bytes);
@@ -1300,7 +1309,7 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
   // of the same type and K (the up projection after the gate projection): its operand images are still there
   if (!w->has_tmap) return 1;
   if (w->N % BN || w->K % 256) return 1;
-  const int sps = tc_use_fold(w, dots) ? 9 : (w->type == IZB_Q4_K && !dots) ? 5 : 4;
+  const int sps = tc_use_fold(w, dots, n_tiles_grid, tiles != nullptr) ? 9 : (w->type == IZB_Q4_K && !dots) ? 5 : 4;
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes(n_tiles_grid, w->K, sps, &img_bytes, &asc_bytes);
   void* ws = nullptr;
@@ -1525,7 +1534,7 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   if (!w->has_tmap) IZB_FAIL(IZB_ERR_CUDA, "gemm_noalloc: the weight has no tensor map (driver entry point missing at creation)");
   const int K = w->K;
   const int n_tiles = (M + BM - 1) / BM;
-  const int sps = tc_use_fold(w, nullptr) ? 9 : w->type == IZB_Q4_K ? 5 : 4;
+  const int sps = tc_use_fold(w, nullptr, n_tiles, false) ? 9 : w->type == IZB_Q4_K ? 5 : 4;
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes(n_tiles, K, sps, &img_bytes, &asc_bytes);
   if (img_bytes + asc_bytes > kNoAllocBytes || n_tiles > 65535)

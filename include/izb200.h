@@ -150,7 +150,7 @@ int izb_selfcheck(int device);
  *     kernel to fall back to), plus d_status.
  *   - Limit: ceil(M/128) * (K/256 * S * 16384 + K/32 * 512) bytes, S = 5 for Q4_K and 4 for Q8_0, must fit in the array (e.g. M = 1024 at K = 5120, or
  *     M = 512 at K = 10240); a larger call returns IZB_ERR_LIMIT and launches nothing.  (With the opt-in folded-scale
- *     Q4_K kernel, IZB_GEMM_FOLD=1 in the environment and N % 256 == 0: ceil(M/128) * (K/256 * 9 * 16384 + 512) bytes.)
+ *     Q4_K kernel, IZB_GEMM_FOLD=1 or 2 in the environment, where it is selected: ceil(M/128) * (K/256 * 9 * 16384 + 512) bytes.)
  *   - d_status: a device uint32 of the caller's (or NULL to use one inside the library).  It is cleared at the start of
  *     the call and is non-zero afterwards if a bounded device-side wait gave up (the output is then incomplete).
  *   - The first call on a device looks up the array's device address (the device must be current, as for every call):

@@ -1227,17 +1227,17 @@ int tc_grid(int n_work);
 // kernel; 8192 rows 3.25 ms against 3.48 ms in a short loop, but 3.45-3.51 ms against 3.58 ms per step in a sustained
 // run, where its doubled tensor-core work reaches the board's power cap; its pre-pass writes 1.8 times the operand
 // bytes.  A gain of 2-4 % does not outweigh a kernel with far more hours behind it, so it stays opt-in.  The
-// verification mode, Q8_0 and the grouped (MoE) GEMM (tile count only known on the device; mode 1 takes it there too)
-// otherwise always use the block-exact kernel.
+// verification mode, Q8_0 and the grouped (MoE) GEMM (its tile count is only known on the device, and the folded kernel
+// has no parity test on grouped tiles) always use the block-exact kernel.
 bool tc_use_fold(const izb_weight* w, const int32_t* dots, int n_mtiles, bool grouped) {
   static int mode = -1;  // 0 never, 1 wherever possible, 2 large dense GEMMs
   if (mode < 0) {
     const char* e = getenv("IZB_GEMM_FOLD");
     mode = !e ? 0 : (e[0] == '1' ? 1 : (e[0] == '2' ? 2 : 0));
   }
-  if (mode == 0 || w->type != IZB_Q4_K || dots || w->N % F_BN) return false;
+  if (mode == 0 || grouped || w->type != IZB_Q4_K || dots || w->N % F_BN) return false;
   if (mode == 1) return true;
-  return !grouped && (long long)n_mtiles * (w->N / F_BN) >= 8LL * tc_grid(1 << 30);
+  return (long long)n_mtiles * (w->N / F_BN) >= 8LL * tc_grid(1 << 30);
 }
 
 // persistent grid: one CTA per SM (shared memory allows no more), fewer when there are fewer tiles

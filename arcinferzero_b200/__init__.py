@@ -21,6 +21,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 # every symbol include/izb200.h declares (tests check the library exports each of them)
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
+    "izb_reserve", "izb_debug_wait_test",
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
@@ -242,6 +243,16 @@ def device_status(device: int = 0) -> int:
     if rc not in (0, -7):
         _check(rc)
     return w.value
+
+
+def reserve(device: int, max_rows: int, max_K: int) -> None:
+    """Size the per-device scratch arenas once, so that later GEMM / MoE / TP calls neither allocate nor synchronise."""
+    _check(lib().izb_reserve(device, max_rows, max_K))
+
+
+def debug_wait_test(spin_limit: int, skip_stage: int) -> None:
+    """Diagnostics: the next tensor-core GEMM launch gives up its waits early and leaves one operand stage out."""
+    _check(lib().izb_debug_wait_test(C.c_uint32(spin_limit), skip_stage))
 
 
 def matmul_host(w: Weight, x_host, out_host, mat: int = 0) -> None:

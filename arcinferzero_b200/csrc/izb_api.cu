@@ -115,7 +115,6 @@ extern "C" int izb_profile_stop(char* json, size_t cap) {
 
 // ---------------------------------------------------------------------------------------------- per-device state
 namespace {
-constexpr int kMaxDev = 16;
 struct DevState {
   std::mutex mu;
   uint32_t* err_word = nullptr;
@@ -126,12 +125,14 @@ struct DevState {
   cudaStream_t hs[3] = {nullptr, nullptr, nullptr};  // host-buffer call: copy-in, compute, copy-out streams
   cudaEvent_t he[2][3] = {{nullptr, nullptr, nullptr}, {nullptr, nullptr, nullptr}};  // per staging buffer: in, computed, out
   cudaEvent_t hstart = nullptr;
-  int tc_ok = -1;  // -1 unknown, 0 self-check failed, 1 passed
+  std::atomic<int> tc_ok{-1};  // -1 unknown, 0 self-check failed, 1 passed
+  std::atomic<int> sms{0};
+  uint32_t* noalloc_status = nullptr;  // status word of izb_gemm_noalloc (a device symbol's address), once looked up
 };
-DevState g_dev[kMaxDev];
+DevState g_dev[kIzbMaxDev];
 
 int check_device(int device) {
-  if (device < 0 || device >= kMaxDev) IZB_FAIL(IZB_ERR_ARG, "device %d out of range", device);
+  if (device < 0 || device >= kIzbMaxDev) IZB_FAIL(IZB_ERR_ARG, "device %d out of range", device);
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || device >= n) IZB_FAIL(IZB_ERR_CUDA, "no CUDA device %d (this library has no CPU path)", device);
   cudaDeviceProp p;
@@ -139,8 +140,50 @@ int check_device(int device) {
   if (p.major != 10) IZB_FAIL(IZB_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, p.major, p.minor);
   return IZB_OK;
 }
+
+// Makes `device` current for the scope and puts the caller's device back: for the calls that name a device explicitly
+// (status, reserve) and may come from a thread that drives another GPU.
+struct DeviceScope {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t enter(int device) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev != device) {
+      e = cudaSetDevice(device);
+      switched = e == cudaSuccess;
+    }
+    return e;
+  }
+  ~DeviceScope() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
 }  // namespace
 
+int izb_require_device(int device, const char* what) {
+  if (device < 0 || device >= kIzbMaxDev) IZB_FAIL(IZB_ERR_ARG, "%s: device %d out of range", what, device);
+  int cur = -1;
+  IZB_CUDA(cudaGetDevice(&cur));
+  if (cur != device)
+    IZB_FAIL(IZB_ERR_ARG, "%s: the handle lives on device %d but device %d is current in this thread (cudaSetDevice(%d) first)", what,
+             device, cur, device);
+  return IZB_OK;
+}
+
+int izb_sm_count(int device) {
+  if (device < 0 || device >= kIzbMaxDev) return 148;
+  int n = g_dev[device].sms.load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return 148;
+  }
+  g_dev[device].sms.store(n, std::memory_order_relaxed);
+  return n;
+}
+
+// (called with `device` current: every caller has passed izb_require_device or holds a DeviceScope)
 uint32_t* izb_device_error_word(int device) {
   DevState& d = g_dev[device];
   std::lock_guard<std::mutex> lk(d.mu);
@@ -151,35 +194,80 @@ uint32_t* izb_device_error_word(int device) {
   return d.err_word;
 }
 
+void izb_note_noalloc_status(int device, uint32_t* status) {
+  std::lock_guard<std::mutex> lk(g_dev[device].mu);
+  g_dev[device].noalloc_status = status;
+}
+
+// An arena never shrinks and is only replaced when a call needs more than it holds.  Replacing waits for the device
+// (work in flight may still read the old block) -- izb_reserve moves that wait out of the hot path.
+static int grow_arena(DevState& d, int device, int slot, size_t bytes) {
+  if (bytes <= d.ws_bytes[slot]) return IZB_OK;
+  if (d.ws[slot]) {
+    IZB_CUDA(cudaDeviceSynchronize());
+    IZB_CUDA(cudaFree(d.ws[slot]));
+    d.ws[slot] = nullptr;
+    d.ws_bytes[slot] = 0;
+  }
+  const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+  if (cudaMalloc(&d.ws[slot], want) != cudaSuccess) {
+    cudaGetLastError();
+    IZB_FAIL(IZB_ERR_NOMEM, "workspace of %zu bytes on device %d", want, device);
+  }
+  d.ws_bytes[slot] = want;
+  return IZB_OK;
+}
+
 int izb_workspace(int device, int slot, size_t bytes, void** out) {
   DevState& d = g_dev[device];
   std::lock_guard<std::mutex> lk(d.mu);
-  if (bytes > d.ws_bytes[slot]) {
-    if (d.ws[slot]) {
-      IZB_CUDA(cudaDeviceSynchronize());
-      IZB_CUDA(cudaFree(d.ws[slot]));
-      d.ws[slot] = nullptr;
-      d.ws_bytes[slot] = 0;
-    }
-    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-    if (cudaMalloc(&d.ws[slot], want) != cudaSuccess) {
-      cudaGetLastError();
-      IZB_FAIL(IZB_ERR_NOMEM, "workspace of %zu bytes on device %d", want, device);
-    }
-    d.ws_bytes[slot] = want;
-  }
+  if (int rc = grow_arena(d, device, slot, bytes)) return rc;
   *out = d.ws[slot];
+  return IZB_OK;
+}
+
+size_t izb_gemm_tc_scratch_bytes(int type, int rows, int K);
+
+extern "C" int izb_reserve(int device, int max_rows, int max_K) {
+  if (max_rows < 1 || max_K < 256 || max_K % 256) IZB_FAIL(IZB_ERR_SHAPE, "reserve: rows = %d, K = %d (K in whole superblocks)", max_rows, max_K);
+  if (int rc = check_device(device)) return rc;
+  DeviceScope scope;
+  IZB_CUDA(scope.enter(device));
+  DevState& d = g_dev[device];
+  std::lock_guard<std::mutex> lk(d.mu);
+  const size_t gemm = izb_gemm_tc_scratch_bytes(IZB_Q4_K, max_rows, max_K);
+  if (int rc = grow_arena(d, device, kWsGemm, gemm)) return rc;
+  if (int rc = grow_arena(d, device, kWsMoe, gemm)) return rc;
+  if (int rc = grow_arena(d, device, kWsTp, (size_t)(max_K / 32) * max_rows * 4)) return rc;
+  if (!d.err_word) {
+    if (cudaMalloc(&d.err_word, 256) != cudaSuccess) { cudaGetLastError(); IZB_FAIL(IZB_ERR_NOMEM, "reserve: error word on device %d", device); }
+    IZB_CUDA(cudaMemset(d.err_word, 0, 256));
+  }
   return IZB_OK;
 }
 
 extern "C" int izb_device_status(int device, uint32_t* word) {
   if (!word) IZB_FAIL(IZB_ERR_ARG, "device_status: null pointer");
   if (int rc = check_device(device)) return rc;
+  DeviceScope scope;
+  IZB_CUDA(scope.enter(device));
   uint32_t* p = izb_device_error_word(device);
   if (!p) IZB_FAIL(IZB_ERR_NOMEM, "device_status: cannot allocate the error word");
   IZB_CUDA(cudaDeviceSynchronize());
   IZB_CUDA(cudaMemcpy(word, p, 4, cudaMemcpyDeviceToHost));
   IZB_CUDA(cudaMemset(p, 0, 4));
+  // the word izb_gemm_noalloc uses when its caller passes no status pointer (no allocation: a device symbol's address)
+  uint32_t* ns = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_dev[device].mu);
+    ns = g_dev[device].noalloc_status;
+  }
+  if (ns) {
+    uint32_t w2 = 0;
+    IZB_CUDA(cudaMemcpy(&w2, ns, 4, cudaMemcpyDeviceToHost));
+    IZB_CUDA(cudaMemset(ns, 0, 4));
+    *word |= w2;
+  }
   return *word ? IZB_ERR_TIMEOUT : IZB_OK;
 }
 
@@ -230,8 +318,9 @@ extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats,
   const size_t src_row = (size_t)(K / 256) * w->sb_bytes;  // the GGUF bytes of 256 values are 144 / 8*34 = 272 as well
   if (cudaMalloc(&w->raw, w->bytes + kRawSlack) != cudaSuccess) {
     cudaGetLastError();
+    const size_t want = w->bytes + kRawSlack;
     delete w;
-    IZB_FAIL(IZB_ERR_NOMEM, "weight_create: %zu bytes on device %d", w->bytes + kRawSlack, device);
+    IZB_FAIL(IZB_ERR_NOMEM, "weight_create: %zu bytes on device %d", want, device);
   }
   cudaError_t e = cudaMemset(w->raw + w->bytes, 0, kRawSlack);
   uint8_t* upload = w->raw;
@@ -307,9 +396,10 @@ static int check_gemm_args(const izb_weight* w, int mat, const int8_t* aq, const
 extern "C" int izb_gemm(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int M, int Mp, float* d_C, int ldc,
                         int c_off, int acc, int impl, void* stream) {
   if (int rc = check_gemm_args(w, mat, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc)) return rc;
+  if (int rc = izb_require_device(w->device, "gemm")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (impl == IZB_GEMM_AUTO || impl == IZB_GEMM_TC) {
-    const bool allowed = impl == IZB_GEMM_TC || g_dev[w->device].tc_ok != 0;
+    const bool allowed = impl == IZB_GEMM_TC || g_dev[w->device].tc_ok.load() != 0;
     if (allowed) {
       const int rc = izb_gemm_tc_launch(w, mat, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc, nullptr, st);
       if (rc <= 0) return rc;
@@ -326,6 +416,7 @@ extern "C" int izb_block_dots(const izb_weight* w, int mat, const int8_t* d_aq, 
   if (mat < 0 || mat >= w->n_mats) IZB_FAIL(IZB_ERR_ARG, "block_dots: matrix %d of %d", mat, w->n_mats);
   if (M < 1) IZB_FAIL(IZB_ERR_SHAPE, "block_dots: M = %d", M);
   if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "block_dots: aq not 16-byte aligned");
+  if (int rc = izb_require_device(w->device, "block_dots")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (impl == IZB_GEMM_TC) {
     const int rc = izb_gemm_tc_launch(w, mat, d_aq, nullptr, M, M, nullptr, 0, 0, 0, d_dots, st);
@@ -350,8 +441,8 @@ extern "C" int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, cons
 }
 
 // records the verdict of the start-up check (izb_selfcheck lives with the tensor-core kernel)
-void izb_set_tc_ok(int device, int ok) { g_dev[device].tc_ok = ok; }
-int izb_get_tc_ok(int device) { return g_dev[device].tc_ok; }
+void izb_set_tc_ok(int device, int ok) { g_dev[device].tc_ok.store(ok); }
+int izb_get_tc_ok(int device) { return g_dev[device].tc_ok.load(); }
 
 // ---------------------------------------------------------------------------------------------- host-buffer call
 extern "C" int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, int M, float* h_C, void* stream) {

@@ -70,6 +70,43 @@ void izb_prof_end(cudaStream_t st);
 
 static inline bool izb_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// ---------------------------------------------------------------------------------------------- per-device state
+// The reference drives N GPUs from N threads of ONE process (one Engine per GPU, zero/mgpu/engine_tp.h:825), so everything
+// that belongs to a device's context -- a kernel's opt-in to more than 48 KB of dynamic shared memory, the SM count, the
+// scratch arenas, the error word -- is kept per device here, never in a process-wide flag.
+constexpr int kIzbMaxDev = 16;
+
+// IZB_OK when `device` is the calling thread's current device.  Every entry point that takes a handle calls it: the
+// caller's stream, the handle's memory and the kernel attributes below must all belong to one device.
+int izb_require_device(int device, const char* what);
+// multiprocessor count of `device` (looked up once per device)
+int izb_sm_count(int device);
+
+// Work that must run once per device at one call site (idempotent work only: two threads that race on the first call of
+// a device may both run it).  One bit per device.
+struct izb_device_once {
+  std::atomic<uint32_t> done{0};
+  template <class F>
+  int run(int device, F&& f) {
+    if (device < 0 || device >= kIzbMaxDev) IZB_FAIL(IZB_ERR_ARG, "device %d out of range", device);
+    const uint32_t bit = 1u << device;
+    if (done.load(std::memory_order_acquire) & bit) return IZB_OK;
+    if (int rc = f()) return rc;
+    done.fetch_or(bit, std::memory_order_release);
+    return IZB_OK;
+  }
+};
+// the usual case: let `kernel` use up to `bytes` of dynamic shared memory on `device` (which must be current)
+#define IZB_SMEM_OPTIN(kernel, bytes, device)                                                                             \
+  do {                                                                                                                    \
+    static izb_device_once once__;                                                                                        \
+    if (int rc__ = once__.run((device), [&]() -> int {                                                                    \
+          IZB_CUDA(cudaFuncSetAttribute((kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)));            \
+          return IZB_OK;                                                                                                  \
+        }))                                                                                                               \
+      return rc__;                                                                                                        \
+  } while (0)
+
 // Device-side error word (one per device, in managed-free plain device memory): kernels that give up on a bounded
 // wait OR a code into it; izb_device_status reads and clears it.
 uint32_t* izb_device_error_word(int device);

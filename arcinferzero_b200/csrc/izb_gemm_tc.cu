@@ -41,6 +41,7 @@
 #include "izb_common.cuh"
 
 void izb_set_tc_ok(int device, int ok);
+void izb_note_noalloc_status(int device, uint32_t* status);
 int izb_get_tc_ok(int device);
 int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C,
                          int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st);
@@ -92,6 +93,8 @@ struct TcParams {
   int ldc, c_off, acc;
   int32_t* dots;          // verification mode output or null
   uint32_t* err;
+  uint32_t spin_limit;    // polls after which a wait gives up
+  int skip_stage;         // diagnostics: the operand stage the activation producer leaves out (-1: none)
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -116,23 +119,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  false = gave up (or another thread did): the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
-                                          uint32_t code) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+                                          uint32_t limit, uint32_t code) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicOr(err, code);
-  return false;
-}
-// The same for waiters that are not on the critical path: they sleep between polls, which leaves the issue slots of their
-// scheduler to the warps that are.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
-                                                  uint32_t code) {
-  for (uint32_t it = 0; it < (kSpinLimit >> 2); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(100);
-    if ((it & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicOr(err, code);
@@ -395,8 +385,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         const int tile = w / n_ntiles;
         const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
         for (int g = 0; g < nstages; ++g) {
-          if (!mbar_wait(bar(S_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) { ok = false; break; }
-          if (lane == 0) {
+          if (!mbar_wait(bar(S_EMPTY + sa), pa, abort_flag, p.err, p.spin_limit, E_APROD)) { ok = false; break; }
+          if (lane == 0 && g != p.skip_stage) {  // (skip_stage: diagnostics only, makes the waits of this stage run out)
             mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
             bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
           }
@@ -413,14 +403,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const int tile = w / n_ntiles;
       const int wrow = (p.tiles ? p.tiles[1 + 3 * tile] : p.mat) * p.N + (w % n_ntiles) * BN;
       for (int s = 0; s < nsb; ++s) {
-        if (!mbar_wait(bar(RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) { ok = false; break; }
+        if (!mbar_wait(bar(RAW_EMPTY + rb), pr, abort_flag, p.err, p.spin_limit, E_WPROD)) { ok = false; break; }
         if (lane == 0) {
           mbar_expect_tx(bar(RAW_FULL + rb), RAW);
           tma_2d(smem_u32(smem + OFF_RAW + rb * RAW), &tmW, s * (SBB / 4), wrow, bar(RAW_FULL + rb));
         }
         if (++rb == NR) { rb = 0; pr ^= 1; }
         if (!kDots) {
-          if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, E_WPROD)) { ok = false; break; }
+          if (!mbar_wait(bar(ASC_EMPTY + sq), pq, abort_flag, p.err, p.spin_limit, E_WPROD)) { ok = false; break; }
           if (lane == 0) {
             mbar_expect_tx(bar(ASC_FULL + sq), 4096);
             bulk_g2s(smem_u32(smem + OFF_ASC + sq * 4096), p.ascimg + ((size_t)tile * nb + 8 * s) * BM, 4096, bar(ASC_FULL + sq));
@@ -443,14 +433,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       for (int s = 0; s < nsb && ok; ++s) {
         for (int t = warp - 1; t < (warp == 1 ? 4 : SPS) && ok; t += (t == 3 ? 1 : 2)) {
           const int g = gs + SPS * s + t, sa = g % NS;
-          if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+          if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sa * STAGE_BYTES);
           if (t < 4) {
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
               const int j = jb + 8 * s + 2 * t + blk, d = j % ND1;
-              if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+              if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
               tc_fence_after();
               if (lane == 0) {
                 const uint32_t dt = tmem_base + (uint32_t)(d * BN);
@@ -464,7 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if (!ok) break;
           } else {
             // the min-term accumulator of the tile before must have been read before this tile's first MMA clears it
-            if (s == 0 && it > 0 && !mbar_wait(bar(D2_EMPTY), (it - 1) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
+            if (s == 0 && it > 0 && !mbar_wait(bar(D2_EMPTY), (it - 1) & 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
             tc_fence_after();
             if (lane == 0) {
 #pragma unroll
@@ -491,7 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     int sbc = 0;           // superblocks done (all tiles): position in the 4-deep ring of superblock scales
     for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x)
     for (int s = 0; s < nsb && ok; ++s, ++sbc) {
-      if (!mbar_wait(bar(RAW_FULL + rb), pr, abort_flag, p.err, E_DEQ)) { ok = false; break; }
+      if (!mbar_wait(bar(RAW_FULL + rb), pr, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
       const unsigned char* rrow = smem + OFF_RAW + rb * RAW + t * SBB;
       const uint4 hdr = *reinterpret_cast<const uint4*>(rrow);
       const uint32_t s3[3] = {hdr.y, hdr.z, hdr.w};
@@ -505,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
 #pragma unroll 1  // (rolled on purpose: with the role loops resident at once, code size costs more than the loop)
       for (int c = 0; c < 4; ++c) {
-        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) { ok = false; break; }
+        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
         unsigned char* orow = smem + OFF_B + sbq * STAGE_BYTES + t * 128;
         if (QT == IZB_Q4_K) {
           const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c), q1 = *reinterpret_cast<const uint4*>(rrow + 32 + 32 * c);
@@ -560,7 +550,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         // the min-term stage: u[b] = -dmin * mn[b] (exact in f32: 11 x 6 bits) as three bf16 terms u1 + u2 + u3; the
         // stage's six 16-byte chunks hold (u1, u2, u1, u3, u2, u1) for the eight blocks, against the activation side's
         // (v1, v1, v2, v1, v2, v3)
-        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, E_DEQ)) { ok = false; break; }
+        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
         const float ndmin = -half_bits_to_float(hdr.x >> 16);
         uint32_t u1[4], u2[4], u3[4];
 #pragma unroll
@@ -619,11 +609,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     for (int c = 0; c < 32; ++c) res2[c] = tq2[c] = 0ull;
     for (int s = 0; s < nsb && ok; ++s, ++sbc) {
       const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;  // this row's 8 block scales
-      if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, E_EPI)) { ok = false; break; }
+      if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, p.spin_limit, E_EPI)) { ok = false; break; }
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
         const unsigned long long a2 = pack2(kDots ? 0.0f : as[b * BM]);
-        if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, E_EPI)) { ok = false; break; }
+        if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, p.spin_limit, E_EPI)) { ok = false; break; }
         tc_fence_after();
         unsigned long long v[32];
         tc_ld64_pairs(t_lane + (uint32_t)(d * BN), v);  // the thread's 64 columns of this block; returns when they are in registers
@@ -673,7 +663,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
     }
     if (kMins && ok) {  // the min term of the whole row of K (already negative)
-      ok = mbar_wait(bar(D2_FULL), it & 1, abort_flag, p.err, E_EPI);
+      ok = mbar_wait(bar(D2_FULL), it & 1, abort_flag, p.err, p.spin_limit, E_EPI);
       if (ok) {
         tc_fence_after();
         unsigned long long v[32];
@@ -722,463 +712,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   }
 }
 
-// ---------------------------------------------------------------------------------------------- Q4_K with folded activation scales
-// The per-block hand-over above costs more than the MMAs it serves.  This form moves the activation scale INTO the
-// operand, so that a whole superblock (eight blocks) accumulates in TMEM and the CUDA cores see one accumulator per
-// superblock instead of eight:
-//   x[m][k] = asc[m][b(k)] * a[m][k] / f[m],  f[m] = the power of two at or below the row's largest block scale
-//   (|x| < 256), fed as TWO fp16 operands hi = fp16(x), lo = fp16(x - hi): hi + lo carries x to 2^-22 of the row's
-//   largest value, the products with the exact integers sc*q are exact, accumulation is f32.
-//   D_s = sum over the superblock of (hi + lo) * (sc*q)   (no read in between);
-//   res += d[n][s] * D_s per superblock;  C = f[m] * res + min term (as above, its own accumulator over all of K).
-// Twice the tensor-core work, an eighth of the TMEM reads, barriers and CUDA-core multiplies.  The (hi | lo) operand is
-// 4 bytes per activation, and a bulk copy from L2 takes ~2700 cycles from "slot free" to "slot full": a 128-wide tile
-// waits for its activation copies (measured: no faster than the block-exact kernel).  The tile is therefore
-// 128 tokens x 256 weight rows, two accumulators of 128 columns fed from the same activation stage (16 MMAs of K = 16
-// per 32 KB copied), one MMA issuer thread per half.  Measured on a B200 (2048 x 17408 x 5120): 0.90 ms, the block-exact
-// kernel 0.89 ms; a clock trace of the issuers shows per activation stage ~1000 cycles of MMA issue and commits and
-// ~900 of waits (activation slot 470: three 32 KB slots are held for copy latency + both halves' MMAs; weight sub-stage
-// 270; accumulator 175: TMEM has no room for a second pair), i.e. the tensor pipe is busy about half of the time.
-// Splitting hi and lo into separate 16 KB slots (more hand-overs) measured slower (1.03 ms).  Opt-in for that reason.
-constexpr int F_BN = 256;                                // weight rows per tile: two halves of 128
-constexpr int F_THREADS = 640;                           // 4 role warps, 8 dequantiser warps, 8 combine warps
-constexpr int F_NSA = 3, F_NSB = 3;                      // activation stages; weight sub-stages (one half each)
-constexpr int F_ASTAGE = 2 * STAGE_BYTES;                // activation tile of a stage: hi | lo
-constexpr int F_OFF_A = 0;
-constexpr int F_OFF_B = F_OFF_A + F_NSA * F_ASTAGE;      // 98304
-constexpr int F_OFF_RAW = F_OFF_B + F_NSB * STAGE_BYTES; // 147456
-constexpr int F_NR = 4;                                  // raw ring: half tiles (128 rows of one superblock)
-constexpr int F_OFF_DM = F_OFF_RAW + F_NR * RAW_Q4;      // 221184: ring of [128] f32 superblock scales d, one per half tile
-constexpr int F_NDM = 8;
-constexpr int F_OFF_BAR = F_OFF_DM + F_NDM * 512;        // 225280
-constexpr int F_SMEM_BYTES = F_OFF_BAR + 1024 + 1024;    // barriers + alignment slack
-constexpr int F_SB_IMG = 4 * F_ASTAGE + STAGE_BYTES;     // operand image bytes per superblock and tile: 4 x (hi | lo) + min term
-static_assert(F_SMEM_BYTES <= 232448, "shared memory of the folded kernel");
-enum FBar {
-  F_A_FULL = 0, F_A_EMPTY = F_A_FULL + F_NSA, F_B_FULL = F_A_EMPTY + F_NSA, F_B_EMPTY = F_B_FULL + F_NSB,
-  F_RAW_FULL = F_B_EMPTY + F_NSB, F_RAW_EMPTY = F_RAW_FULL + F_NR, F_D_FULL = F_RAW_EMPTY + F_NR, F_D_EMPTY = F_D_FULL + 2,
-  F_D2_FULL = F_D_EMPTY + 2, F_D2_EMPTY, F_NUM_BARS
-};
-static_assert(F_NUM_BARS * 8 + 16 <= 512, "barrier area");
-
-// f[m] per tile row (1 for padding rows): the row's largest block scale with its mantissa cleared, exponent field kept
-// inside [1, 253] so that 1/f is a normal number too.
-__global__ void __launch_bounds__(512) row_factor_kernel(const float* __restrict__ asc, int lda, int nb, int rows_total,
-                                                         const int32_t* __restrict__ tiles, const int32_t* __restrict__ rowmap,
-                                                         float* __restrict__ rowf) {
-  __shared__ float sm[4][BM];
-  const int tile = blockIdx.x;
-  int r0, nr;
-  if (tiles) {
-    if (tile >= tiles[0]) return;
-    r0 = tiles[2 + 3 * tile];
-    nr = tiles[3 + 3 * tile];
-  } else {
-    r0 = tile * BM;
-    nr = min(BM, rows_total - r0);
-  }
-  const int r = threadIdx.x & (BM - 1), part = threadIdx.x >> 7;
-  int src = -1;
-  if (r < nr) src = rowmap ? rowmap[r0 + r] : r0 + r;
-  float m = 0.0f;
-  if (src >= 0)
-    for (int b = part; b < nb; b += 4) m = fmaxf(m, fabsf(asc[(size_t)b * lda + src]));
-  sm[part][r] = m;
-  __syncthreads();
-  if (part == 0) {
-    m = fmaxf(fmaxf(sm[0][r], sm[1][r]), fmaxf(sm[2][r], sm[3][r]));
-    uint32_t e = (__float_as_uint(m) >> 23) & 0xFFu;
-    e = e < 1u ? 1u : (e > 253u ? 253u : e);
-    rowf[(size_t)tile * BM + r] = m > 0.0f ? __uint_as_float(e << 23) : 1.0f;
-  }
-}
-
-// Operand images of the folded kernel, one thread per (row, 8 elements of K): per superblock four stages of
-// [hi 16 KB | lo 16 KB] (64 elements of K each, rows 128-byte swizzled) and the 16 KB min-term tile.
-__global__ void __launch_bounds__(256) act_prepare_fold_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asc, int lda,
-                                                               int K, int rows_total, const int32_t* __restrict__ tiles,
-                                                               const int32_t* __restrict__ rowmap, uint16_t* __restrict__ aimg,
-                                                               const float* __restrict__ rowf) {
-  const int tile = blockIdx.y;
-  int r0, nr;
-  if (tiles) {
-    if (tile >= tiles[0]) return;
-    r0 = tiles[2 + 3 * tile];
-    nr = tiles[3 + 3 * tile];
-  } else {
-    r0 = tile * BM;
-    nr = min(BM, rows_total - r0);
-  }
-  const int nchunk = K / 8;
-  const int idx = blockIdx.x * 256 + threadIdx.x;
-  if (idx >= BM * nchunk) return;
-  const int r = idx / nchunk, ch = idx % nchunk;
-  const int stage = ch >> 3, c = ch & 7, b = ch >> 2;
-  int src = -1;
-  if (r < nr) src = rowmap ? rowmap[r0 + r] : r0 + r;
-  uint2 v = make_uint2(0, 0);
-  float sc = 0.0f;
-  if (src >= 0) {
-    v = *reinterpret_cast<const uint2*>(aq + (size_t)src * K + (size_t)ch * 8);
-    sc = asc[(size_t)b * lda + src];
-  }
-  const float inv = __uint_as_float((254u - (__float_as_uint(rowf[(size_t)tile * BM + r]) >> 23)) << 23);  // 1 / f, exact
-  const float scn = __fmul_rn(sc, inv);
-  int a[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    a[i] = (int)(int8_t)(v.x >> (8 * i));
-    a[4 + i] = (int)(int8_t)(v.y >> (8 * i));
-  }
-  uint32_t oh[4], ol[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float x0 = __fmul_rn(scn, (float)a[q4k_perm8(2 * i)]), x1 = __fmul_rn(scn, (float)a[q4k_perm8(2 * i + 1)]);
-    const __half2 h = __floats2half2_rn(x0, x1);
-    const float2 hf = __half22float2(h);
-    const __half2 l = __floats2half2_rn(__fsub_rn(x0, hf.x), __fsub_rn(x1, hf.y));
-    oh[i] = *reinterpret_cast<const uint32_t*>(&h);
-    ol[i] = *reinterpret_cast<const uint32_t*>(&l);
-  }
-  uint8_t* tile_img = reinterpret_cast<uint8_t*>(aimg) + (size_t)tile * (K / 256) * F_SB_IMG;
-  uint8_t* sb_img = tile_img + (size_t)(stage >> 2) * F_SB_IMG;
-  uint8_t* dst = sb_img + (stage & 3) * F_ASTAGE + r * 128 + ((c ^ (r & 7)) << 4);
-  *reinterpret_cast<uint4*>(dst) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
-  *reinterpret_cast<uint4*>(dst + STAGE_BYTES) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
-  int s = a[0] + a[1] + a[2] + a[3] + a[4] + a[5] + a[6] + a[7];
-  s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-  s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);  // the four chunks of a 32-block are four consecutive threads of one row
-  if ((ch & 3) == 0) {
-    const float mv = __fmul_rn(sc, (float)s);
-    const __nv_bfloat16 h1 = __float2bfloat16_rn(mv);
-    const float r1 = __fsub_rn(mv, __bfloat162float(h1));
-    const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
-    const __nv_bfloat16 h3 = __float2bfloat16_rn(__fsub_rn(r1, __bfloat162float(h2)));
-    uint8_t* row = sb_img + 4 * F_ASTAGE + r * 128 + 2 * (b & 7);
-    const unsigned short t3[3] = {__bfloat16_as_ushort(h1), __bfloat16_as_ushort(h2), __bfloat16_as_ushort(h3)};
-    constexpr int term[6] = {0, 0, 1, 0, 1, 2};
-#pragma unroll
-    for (int k = 0; k < 6; ++k) *reinterpret_cast<unsigned short*>(row + ((k ^ (r & 7)) << 4)) = t3[term[k]];
-  }
-}
-
-// Same warp roles as gemm_tc_kernel (persistent grid, 16 warps) on a 128 x 256 tile.  TMEM: columns 0..127 and 128..255 the two halves'
-// superblock accumulators, 256..383 and 384..511 their min-term accumulators.
-__global__ void __launch_bounds__(F_THREADS, 1) gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap tmW, const TcParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F_OFF_BAR);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + F_OFF_BAR + F_NUM_BARS * 8);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + F_OFF_BAR + F_NUM_BARS * 8 + 4);
-  const uint32_t bar0 = smem_u32(bars);
-  auto bar = [&](int i) -> uint32_t { return bar0 + 8u * (uint32_t)i; };
-
-  const int n_ntiles = p.N / F_BN;
-  const int n_work = (p.tiles ? p.tiles[0] : p.n_mtiles) * n_ntiles;
-  if ((int)blockIdx.x >= n_work) return;  // uniform over the CTA, before any barrier or TMEM use
-  const int nsb = p.K >> 8;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    // A_FULL: the producer's expect_tx arrival; B_FULL: the 256 dequantiser threads; B_EMPTY, D_FULL: one tcgen05.commit;
-    // A_EMPTY, D2_FULL: one commit from each of the two MMA issuers; consumers release with one arrival per thread
-    for (int i = 0; i < F_NSA; ++i) { mbar_init(bar(F_A_FULL + i), 1); mbar_init(bar(F_A_EMPTY + i), 2); }
-    for (int i = 0; i < F_NSB; ++i) { mbar_init(bar(F_B_FULL + i), 256); mbar_init(bar(F_B_EMPTY + i), 1); }
-    for (int i = 0; i < F_NR; ++i) { mbar_init(bar(F_RAW_FULL + i), 1); mbar_init(bar(F_RAW_EMPTY + i), 256); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar(F_D_FULL + i), 1); mbar_init(bar(F_D_EMPTY + i), 256); }
-    mbar_init(bar(F_D2_FULL), 2);
-    mbar_init(bar(F_D2_EMPTY), 256);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
-    if (warp == 0) {
-      // ================= activation producer: per superblock four (hi | lo) tiles of 32 KB and the 16 KB min-term tile
-      int sa = 0, pa = 1;
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)(w / n_ntiles) * nsb * F_SB_IMG;
-        for (int g = 0; g < 5 * nsb; ++g) {
-          const int s = g / 5, t = g - 5 * s;
-          const uint32_t bytes = t < 4 ? F_ASTAGE : STAGE_BYTES;
-          if (!mbar_wait_relaxed(bar(F_A_EMPTY + sa), pa, abort_flag, p.err, E_APROD)) { ok = false; break; }
-          if (lane == 0) {
-            mbar_expect_tx(bar(F_A_FULL + sa), bytes);
-            bulk_g2s(smem_u32(smem + F_OFF_A + sa * F_ASTAGE), src + (size_t)s * F_SB_IMG + t * F_ASTAGE, bytes, bar(F_A_FULL + sa));
-          }
-          __syncwarp();
-          if (++sa == F_NSA) { sa = 0; pa ^= 1; }
-        }
-      }
-    } else if (warp == 3) {
-      // ================= weight producer: TMA of the raw superblocks, one copy per half tile (128 weight rows)
-      int rb = 0, pr = 1;
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int tile = w / n_ntiles;
-        const int wrow = (p.tiles ? p.tiles[1 + 3 * tile] : p.mat) * p.N + (w % n_ntiles) * F_BN;
-        for (int s2 = 0; s2 < 2 * nsb; ++s2) {  // (superblock, half)
-          if (!mbar_wait_relaxed(bar(F_RAW_EMPTY + rb), pr, abort_flag, p.err, E_WPROD)) { ok = false; break; }
-          if (lane == 0) {
-            mbar_expect_tx(bar(F_RAW_FULL + rb), RAW_Q4);
-            tma_2d(smem_u32(smem + F_OFF_RAW + rb * RAW_Q4), &tmW, (s2 >> 1) * (144 / 4), wrow + (s2 & 1) * BN, bar(F_RAW_FULL + rb));
-          }
-          __syncwarp();
-          if (++rb == F_NR) { rb = 0; pr ^= 1; }
-        }
-      }
-    } else {
-      // ================= MMA issuers: warp 1 takes half 0 of the tile's weight rows, warp 2 half 1 (each half has its own
-      // accumulators, so each is updated by one thread in program order; two threads because what a thread pays per
-      // sub-stage -- polls and commits -- is longer than the MMAs run).  Per activation stage: 2 x 4 MMAs of K = 16 (hi and lo
-      // against the same weight sub-stage) into the half's accumulator; then the min-term stage (three bf16 MMAs).
-      const int h = warp - 1;
-      bool ok = true;
-      int ga = 0, sbc = 0, it = 0;  // activation stages, superblocks, tiles done
-      const uint32_t dt = tmem_base + (uint32_t)(h * BN), dmin_t = tmem_base + (uint32_t)((2 + h) * BN);
-      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
-        for (int s = 0; s < nsb && ok; ++s, ++sbc) {
-          for (int t = 0; t < 5; ++t, ++ga) {
-            const int sa = ga % F_NSA, gb = 2 * ga + h, sb = gb % F_NSB;
-            if (!mbar_wait(bar(F_A_FULL + sa), (ga / F_NSA) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
-            // (sub-stages are filled in order 0, 1, 2, ... by one group of threads, and this thread waited for sub-stage gb - 2
-            // before: the slot's barrier is at most one phase behind, which a parity wait can tell)
-            if (!mbar_wait(bar(F_B_FULL + sb), (gb / F_NSB) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
-            // the half's accumulator of the superblock before must have been read; the min-term accumulators of the tile before
-            if (t == 0 && !mbar_wait(bar(F_D_EMPTY + h), (sbc & 1) ^ 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
-            if (t == 4 && s == 0 && it > 0 && !mbar_wait(bar(F_D2_EMPTY), (it - 1) & 1, abort_flag, p.err, E_MMA)) { ok = false; break; }
-            tc_fence_after();
-            if (lane == 0) {
-              const uint32_t a_addr = smem_u32(smem + F_OFF_A + sa * F_ASTAGE), b_addr = smem_u32(smem + F_OFF_B + sb * STAGE_BYTES);
-              if (t < 4) {
-#pragma unroll
-                for (int part = 0; part < 2; ++part)
-#pragma unroll
-                  for (int k16 = 0; k16 < 4; ++k16)
-                    tc_mma_f16(dt, umma_desc(a_addr + part * STAGE_BYTES + k16 * 32), umma_desc(b_addr + k16 * 32), kIdescF16,
-                               (t | part | k16) ? 1u : 0u);
-              } else {
-#pragma unroll
-                for (int k16 = 0; k16 < 3; ++k16)
-                  tc_mma_f16(dmin_t, umma_desc(a_addr + k16 * 32), umma_desc(b_addr + k16 * 32), kIdescBF16, (s | k16) ? 1u : 0u);
-              }
-              tc_commit(bar(F_B_EMPTY + sb));
-              tc_commit(bar(F_A_EMPTY + sa));
-              if (t == 3) tc_commit(bar(F_D_FULL + h));
-              if (t == 4 && s == nsb - 1) tc_commit(bar(F_D2_FULL));
-            }
-            __syncwarp();
-          }
-        }
-      }
-    }
-  } else if (warp < 12) {
-    // ================= dequantisers: 256 threads, thread <-> (weight row of the current half, half of a 64-element chunk).
-    // ONE group fills the sub-stages in order (chunk, half): every parity wait on a slot is then at most one phase behind.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
-    const int t = (threadIdx.x - 128) & 127, part = (threadIdx.x - 128) >> 7;
-    bool ok = true;
-    int rb = 0, pr = 0;  // raw ring: a superblock takes two consecutive slots (half 0, half 1)
-    int sbc = 0;         // superblocks done (all tiles)
-    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x)
-    for (int s = 0; s < nsb && ok; ++s, ++sbc) {
-      if (!mbar_wait(bar(F_RAW_FULL + rb), pr, abort_flag, p.err, E_DEQ)) { ok = false; break; }
-      if (!mbar_wait(bar(F_RAW_FULL + rb + 1), pr, abort_flag, p.err, E_DEQ)) { ok = false; break; }
-      const unsigned char* rrow0 = smem + F_OFF_RAW + rb * RAW_Q4 + t * 144;
-      reinterpret_cast<float*>(smem + F_OFF_DM + ((2 * sbc + part) & (F_NDM - 1)) * 512)[t] =
-          half_bits_to_float(*reinterpret_cast<const uint32_t*>(rrow0 + part * RAW_Q4) & 0xFFFFu);
-#pragma unroll 1
-      for (int ch = 0; ch < 10; ++ch) {  // (chunk of 64 elements or the min-term stage, half)
-        const int c = ch >> 1, h = ch & 1;
-        const int gb = 10 * sbc + ch, sbq = gb % F_NSB;
-        if (!mbar_wait(bar(F_B_EMPTY + sbq), ((gb / F_NSB) & 1) ^ 1, abort_flag, p.err, E_DEQ)) { ok = false; break; }
-        const unsigned char* rrow = rrow0 + h * RAW_Q4;
-        const uint4 hdr = *reinterpret_cast<const uint4*>(rrow);
-        const uint32_t s3[3] = {hdr.y, hdr.z, hdr.w};
-        unsigned char* orow = smem + F_OFF_B + sbq * STAGE_BYTES + t * 128;
-        if (c < 4) {
-          const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c + 16 * part);  // words 4 * part .. 4 * part + 3 of the chunk
-          const uint32_t wv[4] = {q0.x, q0.y, q0.z, q0.w};
-          // the chunk's two 6-bit sub-block scales as half2 pairs (sc, sc) and (-1024 sc, -1024 sc): 0x6400 | sc is the
-          // fp16 number 1024 + sc
-          int sc_lo, sc_hi, mn_unused;
-          q4k_scale_min(s3, 2 * c, sc_lo, mn_unused);
-          q4k_scale_min(s3, 2 * c + 1, sc_hi, mn_unused);
-          const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400)), kneg = __half2half2(__ushort_as_half((unsigned short)0xE400));
-          const uint32_t blo = 0x64006400u | (uint32_t)sc_lo | ((uint32_t)sc_lo << 16), bhi = 0x64006400u | (uint32_t)sc_hi | ((uint32_t)sc_hi << 16);
-          const __half2 slo = __hsub2(*reinterpret_cast<const __half2*>(&blo), k1024), shi = __hsub2(*reinterpret_cast<const __half2*>(&bhi), k1024);
-          const __half2 nlo = __hmul2(slo, kneg), nhi = __hmul2(shi, kneg);
-          auto cvt = [](uint32_t word, int sh, __half2 scale, __half2 neg) -> uint32_t {
-            const uint32_t bitsv = ((word >> sh) & 0x000F000Fu) | 0x64006400u;  // (1024 + q) in both halves
-            const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&bitsv), scale, neg);  // = sc * q exactly
-            return *reinterpret_cast<const uint32_t*>(&r);
-          };
-#pragma unroll
-          for (int j2 = 0; j2 < 2; ++j2) {
-            const int jj = 2 * part + j2;
-            const uint32_t w0 = wv[2 * j2], w1 = wv[2 * j2 + 1];
-            *reinterpret_cast<uint4*>(orow + ((jj ^ (t & 7)) << 4)) =
-                make_uint4(cvt(w0, 0, slo, nlo), cvt(w0, 8, slo, nlo), cvt(w1, 0, slo, nlo), cvt(w1, 8, slo, nlo));
-            *reinterpret_cast<uint4*>(orow + (((4 + jj) ^ (t & 7)) << 4)) =
-                make_uint4(cvt(w0, 4, shi, nhi), cvt(w0, 12, shi, nhi), cvt(w1, 4, shi, nhi), cvt(w1, 12, shi, nhi));
-          }
-        } else {
-          // the min-term stage: u[b] = -dmin * mn[b] (exact in f32: 11 x 6 bits) as three bf16 terms u1 + u2 + u3; the
-          // stage's six 16-byte chunks hold (u1, u2, u1, u3, u2, u1) for the eight blocks, against the activation side's
-          // (v1, v1, v2, v1, v2, v3); each of the row's two threads stores three of them
-          const float ndmin = -half_bits_to_float(hdr.x >> 16);
-          uint32_t u1[4], u2[4], u3[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            uint32_t hh[2][3];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              int sc_unused, mn;
-              q4k_scale_min(s3, 2 * k + e, sc_unused, mn);
-              const float u = __fmul_rn(ndmin, (float)mn);
-              const __nv_bfloat16 h1 = __float2bfloat16_rn(u);
-              const float r1 = __fsub_rn(u, __bfloat162float(h1));
-              const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
-              const __nv_bfloat16 h3 = __float2bfloat16_rn(__fsub_rn(r1, __bfloat162float(h2)));
-              hh[e][0] = __bfloat16_as_ushort(h1);
-              hh[e][1] = __bfloat16_as_ushort(h2);
-              hh[e][2] = __bfloat16_as_ushort(h3);
-            }
-            u1[k] = hh[0][0] | (hh[1][0] << 16);
-            u2[k] = hh[0][1] | (hh[1][1] << 16);
-            u3[k] = hh[0][2] | (hh[1][2] << 16);
-          }
-          const uint4 c1 = make_uint4(u1[0], u1[1], u1[2], u1[3]), c2 = make_uint4(u2[0], u2[1], u2[2], u2[3]), c3 = make_uint4(u3[0], u3[1], u3[2], u3[3]);
-          if (part == 0) {
-            *reinterpret_cast<uint4*>(orow + ((0 ^ (t & 7)) << 4)) = c1;
-            *reinterpret_cast<uint4*>(orow + ((1 ^ (t & 7)) << 4)) = c2;
-            *reinterpret_cast<uint4*>(orow + ((2 ^ (t & 7)) << 4)) = c1;
-          } else {
-            *reinterpret_cast<uint4*>(orow + ((3 ^ (t & 7)) << 4)) = c3;
-            *reinterpret_cast<uint4*>(orow + ((4 ^ (t & 7)) << 4)) = c2;
-            *reinterpret_cast<uint4*>(orow + ((5 ^ (t & 7)) << 4)) = c1;
-          }
-        }
-        fence_proxy_async();
-        mbar_arrive(bar(F_B_FULL + sbq));  // (every thread after its own stores and fence)
-      }
-      if (!ok) break;
-      mbar_arrive(bar(F_RAW_EMPTY + rb));
-      mbar_arrive(bar(F_RAW_EMPTY + rb + 1));
-      rb += 2;
-      if (rb == F_NR) { rb = 0; pr ^= 1; }
-    }
-  } else {
-    // ================= combine: thread <-> TMEM lane (token row) 32*(warp%4) + lane, 64 of the 128 columns of each half
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
-    const int q = warp & 3, colq = (warp - 12) >> 2;
-    const int r = 32 * q + lane;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(colq * 64);
-    bool ok = true;
-    int sbc = 0, it = 0;  // superblocks and tiles done
-    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++it) {
-      const int tile = w / n_ntiles, n0 = (w % n_ntiles) * F_BN;
-      const int r0 = p.tiles ? p.tiles[2 + 3 * tile] : tile * BM;
-      const int nr = p.tiles ? p.tiles[3 + 3 * tile] : min(BM, p.M - r0);
-      const bool row_ok = r < nr;
-      const int out_row = r0 + r;
-      const float rf = p.ascimg[(size_t)tile * BM + r];  // f[m]
-      unsigned long long res2[2][32];                    // per half: pairs of columns (2i, 2i+1)
-#pragma unroll
-      for (int c = 0; c < 32; ++c) res2[0][c] = res2[1][c] = 0ull;
-      for (int s = 0; s < nsb && ok; ++s, ++sbc) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (!mbar_wait_relaxed(bar(F_D_FULL + h), sbc & 1, abort_flag, p.err, E_EPI)) { ok = false; break; }
-          tc_fence_after();
-          const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + F_OFF_DM + ((2 * sbc + h) & (F_NDM - 1)) * 512 + colq * 256);
-#pragma unroll
-          for (int piece = 0; piece < 2; ++piece) {  // (32 columns at a time: 128 accumulator registers are live here)
-            unsigned long long v[16];
-            tc_ld32_pairs(t_lane + (uint32_t)(h * BN + piece * 32), v);
-            if (piece == 1) {
-              tc_fence_before();
-              mbar_arrive(bar(F_D_EMPTY + h));  // the accumulator may be overwritten
-            }
-#pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
-              const ulonglong2 dd = dv[8 * piece + c4];
-              ffma2(res2[h][16 * piece + 2 * c4], dd.x, v[2 * c4]);
-              ffma2(res2[h][16 * piece + 2 * c4 + 1], dd.y, v[2 * c4 + 1]);
-            }
-          }
-        }
-      }
-      if (ok) ok = mbar_wait(bar(F_D2_FULL), it & 1, abort_flag, p.err, E_EPI);
-      if (ok) {  // C = f * res + the min term of the whole row of K (already negative)
-        tc_fence_after();
-        const unsigned long long rf2 = pack2(rf);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int piece = 0; piece < 2; ++piece) {
-            unsigned long long v[16];
-            tc_ld32_pairs(t_lane + (uint32_t)((2 + h) * BN + piece * 32), v);
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              ffma2(v[c], rf2, res2[h][16 * piece + c]);
-              res2[h][16 * piece + c] = v[c];
-            }
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(bar(F_D2_EMPTY));  // the next tile's min term may start
-      }
-      if (ok && row_ok && !*abort_flag) {
-        const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + n0 + h * BN + colq * 64;
-#pragma unroll
-          for (int c4 = 0; c4 < 16; ++c4) {
-            float4 v = make_float4(lo_f(res2[h][2 * c4]), hi_f(res2[h][2 * c4]), lo_f(res2[h][2 * c4 + 1]), hi_f(res2[h][2 * c4 + 1]));
-            if (p.rowscale) { v.x = __fmul_rn(rs, v.x); v.y = __fmul_rn(rs, v.y); v.z = __fmul_rn(rs, v.z); v.w = __fmul_rn(rs, v.w); }
-            float4* dst = reinterpret_cast<float4*>(cp) + c4;
-            if (p.acc == 1) {
-              const float4 o = *dst;
-              v.x = __fadd_rn(v.x, o.x); v.y = __fadd_rn(v.y, o.y); v.z = __fadd_rn(v.z, o.z); v.w = __fadd_rn(v.w, o.w);
-            } else if (p.acc == 2) {  // C holds the gate projection: C = v * silu(C)   (zero/kernels/gemm.cl:562-565)
-              const float4 o = *dst;
-              v.x = __fmul_rn(v.x, __fdiv_rn(o.x, __fadd_rn(1.0f, expf(-o.x))));
-              v.y = __fmul_rn(v.y, __fdiv_rn(o.y, __fadd_rn(1.0f, expf(-o.y))));
-              v.z = __fmul_rn(v.z, __fdiv_rn(o.z, __fadd_rn(1.0f, expf(-o.z))));
-              v.w = __fmul_rn(v.w, __fdiv_rn(o.w, __fadd_rn(1.0f, expf(-o.w))));
-            }
-            *dst = v;
-          }
-        }
-      }
-    }
-  }
-  // ---- teardown
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    // a wait gave up: let copies and MMAs still in flight land before shared memory and TMEM are released
-    for (int i = 0; i < 64; ++i) __nanosleep(20000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
-  }
-}
-
 // ---------------------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1194,86 +727,47 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
+// Diagnostics hook (izb_debug_wait_test): the spin limit of the bounded waits and the operand stage the activation
+// producer leaves out, for the NEXT launch only.
+std::atomic<uint32_t> g_test_spin{0};
+std::atomic<int> g_test_skip{-1};
+
 template <int QT, bool kDots>
-int launch_tc(const izb_weight* w, const TcParams& p, dim3 grid, cudaStream_t st) {
-  static bool attr = false;
-  if (!attr) {
-    IZB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<QT, kDots>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr = true;
-  }
+int launch_tc(const izb_weight* w, TcParams& p, dim3 grid, cudaStream_t st) {
+  IZB_SMEM_OPTIN((gemm_tc_kernel<QT, kDots>), SMEM_BYTES, w->device);
+  const uint32_t spin = g_test_spin.exchange(0);
+  p.spin_limit = spin ? spin : kSpinLimit;
+  p.skip_stage = g_test_skip.exchange(-1);
   CUtensorMap tm;
   memcpy(&tm, w->tmap_raw, sizeof tm);
   IZB_LAUNCH("gemm_tc", st, gemm_tc_kernel<QT, kDots><<<grid, kThreads, SMEM_BYTES, st>>>(tm, p));
   return IZB_OK;
 }
 
-int launch_tc_fold(const izb_weight* w, const TcParams& p, dim3 grid, cudaStream_t st) {
-  static bool attr = false;
-  if (!attr) {
-    IZB_CUDA(cudaFuncSetAttribute(gemm_tc_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_BYTES));
-    attr = true;
-  }
-  CUtensorMap tm;
-  memcpy(&tm, w->tmap_raw, sizeof tm);
-  IZB_LAUNCH("gemm_tc_fold", st, gemm_tc_fold_kernel<<<grid, F_THREADS, F_SMEM_BYTES, st>>>(tm, p));
-  return IZB_OK;
-}
-
-int tc_grid(int n_work);
-
-// Which kernel a Q4_K GEMM runs: the block-exact one, unless the environment asks for the folded kernel (N % 256 == 0
-// needed): IZB_GEMM_FOLD=1 wherever it can run, IZB_GEMM_FOLD=2 for dense GEMMs of at least eight 128 x 256 tiles per SM,
-// which is where it pays.  Measured on a B200, K = 5120, N = 17408: 2048 rows 0.88 ms against 0.89 ms for the block-exact
-// kernel; 8192 rows 3.25 ms against 3.48 ms in a short loop, but 3.45-3.51 ms against 3.58 ms per step in a sustained
-// run, where its doubled tensor-core work reaches the board's power cap; its pre-pass writes 1.8 times the operand
-// bytes.  A gain of 2-4 % does not outweigh a kernel with far more hours behind it, so it stays opt-in.  The
-// verification mode, Q8_0 and the grouped (MoE) GEMM (its tile count is only known on the device, and the folded kernel
-// has no parity test on grouped tiles) always use the block-exact kernel.
-bool tc_use_fold(const izb_weight* w, const int32_t* dots, int n_mtiles, bool grouped) {
-  static int mode = -1;  // 0 never, 1 wherever possible, 2 large dense GEMMs
-  if (mode < 0) {
-    const char* e = getenv("IZB_GEMM_FOLD");
-    mode = !e ? 0 : (e[0] == '1' ? 1 : (e[0] == '2' ? 2 : 0));
-  }
-  if (mode == 0 || grouped || w->type != IZB_Q4_K || dots || w->N % F_BN) return false;
-  if (mode == 1) return true;
-  return (long long)n_mtiles * (w->N / F_BN) >= 8LL * tc_grid(1 << 30);
-}
-
 // persistent grid: one CTA per SM (shared memory allows no more), fewer when there are fewer tiles
-int tc_grid(int n_work) {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
-  }
+int tc_grid(int device, int n_work) {
+  const int sms = izb_sm_count(device);
   return n_work < sms ? (n_work > 0 ? n_work : 1) : sms;
 }
 
-// scratch of one call: the operand images (sps stage images of 16 KB per superblock and tile; 9 for the folded kernel)
-// and the gathered scales (folded kernel: one factor per tile row)
+// scratch of one call: the operand images (sps stage images of 16 KB per superblock and tile) and the gathered scales
 void tc_scratch_bytes(int n_tiles, int K, int sps, size_t* img_bytes, size_t* asc_bytes) {
   *img_bytes = (size_t)n_tiles * (K / 256) * sps * STAGE_BYTES;
-  *asc_bytes = sps == 9 ? (size_t)n_tiles * BM * 4 : (size_t)n_tiles * (K / 32) * BM * 4;
+  *asc_bytes = (size_t)n_tiles * (K / 32) * BM * 4;
 }
-static_assert(F_SB_IMG == 9 * STAGE_BYTES, "operand image of the folded kernel");
 
 // the activation pre-pass + the GEMM on scratch the caller owns (img_bytes + asc_bytes of tc_scratch_bytes)
 int run_tc_on(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int lda, int rows_total, const int32_t* tiles,
               int n_tiles_grid, const int32_t* rowmap, const float* rowscale, int M_store, float* C, int ldc, int c_off, int acc,
               int32_t* dots, void* ws, uint32_t* err, cudaStream_t st, bool reuse_images) {
   const int K = w->K;
-  const bool fold = tc_use_fold(w, dots, n_tiles_grid, tiles != nullptr);
-  const int sps = fold ? 9 : (w->type == IZB_Q4_K && !dots) ? 5 : 4;
+  const int sps = (w->type == IZB_Q4_K && !dots) ? 5 : 4;
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes(n_tiles_grid, K, sps, &img_bytes, &asc_bytes);
   uint16_t* aimg = (uint16_t*)ws;
   float* ascimg = (float*)((unsigned char*)ws + img_bytes);
   dim3 pg((BM * (K / 8) + 255) / 256, n_tiles_grid);
   if (reuse_images) {
-  } else if (fold) {
-    IZB_LAUNCH("row_factor", st, row_factor_kernel<<<n_tiles_grid, 512, 0, st>>>(asc, lda, K / 32, rows_total, tiles, rowmap, ascimg));
-    IZB_LAUNCH("act_prepare_fold", st, act_prepare_fold_kernel<<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, ascimg));
   } else if (w->type == IZB_Q4_K)
     IZB_LAUNCH("act_prepare", st, act_prepare_kernel<IZB_Q4_K><<<pg, 256, 0, st>>>(aq, asc, lda, K, rows_total, tiles, rowmap, aimg, ascimg, sps));
   else
@@ -1295,8 +789,7 @@ int run_tc_on(const izb_weight* w, int mat, const int8_t* aq, const float* asc, 
   p.dots = dots;
   p.err = err;
   p.n_mtiles = n_tiles_grid;
-  if (fold) return launch_tc_fold(w, p, dim3(tc_grid(w->N / F_BN * n_tiles_grid)), st);
-  dim3 grid(tc_grid(w->N / BN * n_tiles_grid));
+  dim3 grid(tc_grid(w->device, w->N / BN * n_tiles_grid));
   if (w->type == IZB_Q4_K) return dots ? launch_tc<IZB_Q4_K, true>(w, p, grid, st) : launch_tc<IZB_Q4_K, false>(w, p, grid, st);
   return dots ? launch_tc<IZB_Q8_0, true>(w, p, grid, st) : launch_tc<IZB_Q8_0, false>(w, p, grid, st);
 }
@@ -1309,7 +802,7 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
   // of the same type and K (the up projection after the gate projection): its operand images are still there
   if (!w->has_tmap) return 1;
   if (w->N % BN || w->K % 256) return 1;
-  const int sps = tc_use_fold(w, dots, n_tiles_grid, tiles != nullptr) ? 9 : (w->type == IZB_Q4_K && !dots) ? 5 : 4;
+  const int sps = (w->type == IZB_Q4_K && !dots) ? 5 : 4;
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes(n_tiles_grid, w->K, sps, &img_bytes, &asc_bytes);
   void* ws = nullptr;
@@ -1321,6 +814,19 @@ int run_tc(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int
 }
 
 }  // namespace
+
+// scratch bytes of a dense tensor-core GEMM over `rows` activation rows (izb_reserve sizes the arenas with it)
+size_t izb_gemm_tc_scratch_bytes(int type, int rows, int K) {
+  size_t img_bytes, asc_bytes;
+  tc_scratch_bytes((rows + BM - 1) / BM, K, type == IZB_Q4_K ? 5 : 4, &img_bytes, &asc_bytes);
+  return img_bytes + asc_bytes;
+}
+
+extern "C" int izb_debug_wait_test(uint32_t spin_limit, int skip_stage) {
+  g_test_spin.store(spin_limit);
+  g_test_skip.store(skip_stage);
+  return IZB_OK;
+}
 
 int izb_make_raw_tensor_map(izb_weight* w) {
   EncodeTiledFn enc = get_encode();
@@ -1515,6 +1021,7 @@ int noalloc_setup(int device, NoAllocDev** out) {
     IZB_CUDA(cudaGetSymbolAddress(&s, g_noalloc_status));
     d.status = (uint32_t*)s;
     d.scratch = (unsigned char*)p;
+    izb_note_noalloc_status(device, d.status);  // izb_device_status reads (and clears) this word too
   }
   *out = &d;
   return IZB_OK;
@@ -1534,7 +1041,7 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   if (!w->has_tmap) IZB_FAIL(IZB_ERR_CUDA, "gemm_noalloc: the weight has no tensor map (driver entry point missing at creation)");
   const int K = w->K;
   const int n_tiles = (M + BM - 1) / BM;
-  const int sps = tc_use_fold(w, nullptr, n_tiles, false) ? 9 : w->type == IZB_Q4_K ? 5 : 4;
+  const int sps = w->type == IZB_Q4_K ? 5 : 4;
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes(n_tiles, K, sps, &img_bytes, &asc_bytes);
   if (img_bytes + asc_bytes > kNoAllocBytes || n_tiles > 65535)

@@ -53,11 +53,7 @@ int launch_qt(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const f
   const int grid = (w->N + kWarps * kRows - 1) / (kWarps * kRows);
   size_t smem = 0;
   const int spc = steps_per_chunk(QT, w->K, T, &smem);
-  static bool attr_set = false;
-  if (!attr_set) {
-    IZB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
-    attr_set = true;
-  }
+  IZB_SMEM_OPTIN((gemv_kernel<QT, T>), kMaxSmem, w->device);
   IZB_LAUNCH("gemv", st, gemv_kernel<QT, T><<<grid, kWarps * 32, smem, st>>>(raw, w->N, w->K, aq, asc, Mp, C, ldc, c_off, acc, spc));
   return IZB_OK;
 }
@@ -79,6 +75,7 @@ extern "C" int izb_gemv(const izb_weight* w, int mat, const int8_t* d_aq, const 
   if (acc != 0 && acc != 1) IZB_FAIL(IZB_ERR_ARG, "gemv: store mode %d (the GEMV stores or adds, zero/kernels/decode.cl:1031)", acc);
   if (ldc < c_off + w->N && T > 1) IZB_FAIL(IZB_ERR_SHAPE, "gemv: ldc = %d < c_off + N = %d", ldc, c_off + w->N);
   if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "gemv: aq not 16-byte aligned");
+  if (int rc = izb_require_device(w->device, "gemv")) return rc;
   const uint8_t* raw = w->raw + (size_t)mat * w->N * w->row_bytes;
   cudaStream_t st = (cudaStream_t)stream;
   {  // the streaming kernel takes every call whose staged activations fit in shared memory

@@ -359,13 +359,8 @@ int launch_q4k_reg(const izb_weight* w, const uint8_t* raw, const int8_t* aq, co
   slots = slots > 8 ? 8 : (slots & ~1);  // rows are taken two at a time
   if (slots < 2) return 1;
   const size_t smem = (size_t)kRegWarps * slots * slot_bytes + (size_t)kRegWarps * slots * 8;
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    IZB_CUDA(cudaGetDevice(&dev));
-    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    IZB_CUDA(cudaFuncSetAttribute(gemv_q4k_reg_kernel<NSTEPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
-  }
+  IZB_SMEM_OPTIN((gemv_q4k_reg_kernel<NSTEPS>), kBudget + 8192, w->device);
+  const int sms = izb_sm_count(w->device);
   int grid = 2 * sms;
   const int need = (w->N + kRegWarps - 1) / kRegWarps;
   if (grid > need) grid = need;
@@ -589,13 +584,8 @@ int launch_q4k_pair(const izb_weight* w, const uint8_t* raw, const int8_t* aq, c
   slots = slots > 8 ? 8 : (slots & ~1);
   if (slots < 2) return 1;
   const size_t smem = act + (size_t)kPairWarps * slots * slot_bytes + (size_t)kPairWarps * slots * 8;
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    IZB_CUDA(cudaGetDevice(&dev));
-    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    IZB_CUDA(cudaFuncSetAttribute(gemv_q4k_pair_kernel<NSB4, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
-  }
+  IZB_SMEM_OPTIN((gemv_q4k_pair_kernel<NSB4, T>), kBudget + 8192, w->device);
+  const int sms = izb_sm_count(w->device);
   int grid = sms;
   const int need = (w->N + kPairWarps - 1) / kPairWarps;
   if (grid > need) grid = need;
@@ -794,13 +784,8 @@ int launch_q4k_chunk(const izb_weight* w, const uint8_t* raw, const int8_t* aq, 
   int slots = (int)((kBudget - act - 4096) / ((size_t)kPairWarps * kChunkBytes));
   slots = slots > 12 ? 12 : (slots & ~1);
   const size_t smem = act + (size_t)kPairWarps * slots * kChunkBytes + (size_t)kPairWarps * slots * 8;
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    IZB_CUDA(cudaGetDevice(&dev));
-    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    IZB_CUDA(cudaFuncSetAttribute(gemv_q4k_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
-  }
+  IZB_SMEM_OPTIN((gemv_q4k_chunk_kernel<T>), kBudget + 8192, w->device);
+  const int sms = izb_sm_count(w->device);
   int grid = sms;
   const int need = (w->N + kPairWarps - 1) / kPairWarps;
   if (grid > need) grid = need;
@@ -835,13 +820,8 @@ int launch_stream(const izb_weight* w, const uint8_t* raw, const int8_t* aq, con
   if (slots < 2) return 1;  // (rows too long for a ring: the chunked kernel takes the call)
   if (slots > 8) slots = 8;
   const size_t smem = act + (size_t)kSWarps * slots * slot_bytes + (size_t)kSWarps * slots * 8;
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    IZB_CUDA(cudaGetDevice(&dev));
-    IZB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    IZB_CUDA(cudaFuncSetAttribute(gemv_stream_kernel<QT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kBudget + 8192)));
-  }
+  IZB_SMEM_OPTIN((gemv_stream_kernel<QT, T>), kBudget + 8192, w->device);
+  const int sms = izb_sm_count(w->device);
   int grid = sms;
   const int need = (w->N + kSWarps - 1) / kSWarps;
   if (grid > need) grid = need;

@@ -14,49 +14,69 @@ using namespace izb_gemvk;
 
 constexpr int kMaxPerLane = 16;  // experts per lane: NE <= 512
 
+// Routing.  The rule (zero/kernels/moe.cl:56-86; CPU twin tools/ref_forward.cpp:1660-1690): choice k is the largest logit
+// not chosen yet, the lower expert id winning a tie; p_k = exp(l_k - l_0) where l_0, the first choice, is the maximum;
+// w_k = p_k / (p_0 + ... + p_{NU-1}), the sum taken in choice order.
+//
+// One warp per token.  A logit and its expert id travel as ONE 64-bit key -- the order-preserving integer image of the
+// float in the high word, the complemented id in the low word -- so a single warp-wide maximum per choice yields the
+// winner and applies the tie rule at once.  Every lane keeps the key of its own best candidate and only the lane that
+// owned the winner rescans its (at most 16) experts.
+__device__ __forceinline__ unsigned long long route_key(float v, int e) {
+  uint32_t u = __float_as_uint(__fadd_rn(v, 0.0f));  // (-0 becomes +0: the two compare equal, so they must tie)
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (uint32_t)(~(uint32_t)e);
+}
+__device__ __forceinline__ float route_key_value(unsigned long long k) {
+  const uint32_t u = (uint32_t)(k >> 32);
+  return __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+}
+
 __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int ldl, int T, int NE, int NU,
                                                         int32_t* __restrict__ ids, float* __restrict__ wts,
                                                         int32_t* __restrict__ counts) {
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (t >= T) return;
-  const float* lg = logits + (size_t)t * ldl;
-  const int per = (NE + 31) / 32;
-  float v[kMaxPerLane];
-  float mx = -INFINITY;
+  const int token = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (token >= T) return;
+  const float* row = logits + (size_t)token * ldl;
+  unsigned long long key[kMaxPerLane];  // 0 = no candidate (past NE, or already chosen)
 #pragma unroll
   for (int i = 0; i < kMaxPerLane; ++i) {
     const int e = i * 32 + lane;
-    v[i] = (i < per && e < NE) ? lg[e] : -INFINITY;
-    mx = fmaxf(mx, v[i]);
+    key[i] = e < NE ? route_key(row[e], e) : 0ull;
   }
+  auto lane_best = [&]() {
+    unsigned long long b = 0ull;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-  float sum = 0.0f, my_p = 0.0f;
-  int my_sel = 0;
+    for (int i = 0; i < kMaxPerLane; ++i) b = key[i] > b ? key[i] : b;
+    return b;
+  };
+  unsigned long long mine = lane_best();
+  float top = 0.0f, denom = 0.0f, p_keep = 0.0f;
+  int e_keep = 0;
   for (int k = 0; k < NU; ++k) {
-    float bv = -INFINITY;
-    int bi = NE;
+    unsigned long long win = mine;
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i)
-      if (v[i] > bv) { bv = v[i]; bi = i * 32 + lane; }
-    float gv = bv;
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, win, o);
+      win = other > win ? other : win;
+    }
+    const int e = (int)(~(uint32_t)win);
+    const float l = route_key_value(win);
+    if (k == 0) top = l;
+    if ((e & 31) == lane) {  // the owner strikes the winner out and looks for its next candidate
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) gv = fmaxf(gv, __shfl_xor_sync(0xFFFFFFFFu, gv, o));
-    int gi = bv == gv ? bi : NE;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) gi = min(gi, __shfl_xor_sync(0xFFFFFFFFu, gi, o));
-#pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i)
-      if (i * 32 + lane == gi) v[i] = -INFINITY;
-    const int sel = min(gi, NE - 1);
-    const float p = expf(gv - mx);
-    sum += p;
-    if (lane == k) { my_p = p; my_sel = sel; }
+      for (int i = 0; i < kMaxPerLane; ++i)
+        if (i == (e >> 5)) key[i] = 0ull;
+      mine = lane_best();
+    }
+    const float p = expf(l - top);
+    denom += p;  // (every lane adds the same terms in choice order)
+    if (lane == k) { p_keep = p; e_keep = e; }
   }
   if (lane < NU) {
-    ids[t * NU + lane] = my_sel;
-    wts[t * NU + lane] = __fdiv_rn(my_p, sum);
-    atomicAdd(&counts[my_sel], 1);
+    ids[token * NU + lane] = e_keep;
+    wts[token * NU + lane] = __fdiv_rn(p_keep, denom);
+    atomicAdd(&counts[e_keep], 1);
   }
 }
 
@@ -195,7 +215,7 @@ __global__ void __launch_bounds__(kWarps * 32) moe_down_kernel(const uint8_t* __
 
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ inv, int T,
                                    int NU, int E) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4, t = blockIdx.y;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4, t = blockIdx.x;  // (tokens on x: no 65535 limit)
   if (c >= E) return;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int k = 0; k < NU; ++k) {
@@ -226,6 +246,7 @@ extern "C" int izb_moe_sort(const int32_t* d_ids, const float* d_wts, const int3
                             void* stream) {
   if (!d_ids || !d_wts || !d_counts || !d_offs || !d_tiles || !d_stok || !d_swt || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_sort: null pointer");
   if (T < 1 || NE < 1 || NE > 1024 || NU < 1 || TM < 1) IZB_FAIL(IZB_ERR_SHAPE, "moe_sort: T=%d NE=%d NU=%d TM=%d", T, NE, NU, TM);
+  if (!izb_aligned(d_ids, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_sort: ids must be 16-byte aligned (read four at a time)");
   if (max_tiles < (T * NU + TM - 1) / TM + NE) IZB_FAIL(IZB_ERR_LIMIT, "moe_sort: max_tiles = %d < %d (pairs/TM + NE)", max_tiles, (T * NU + TM - 1) / TM + NE);
   cudaStream_t st = (cudaStream_t)stream;
   IZB_LAUNCH("moe_scan", st, moe_scan_kernel<<<1, 1024, 0, st>>>(d_counts, NE, TM, d_offs, d_tiles, max_tiles));
@@ -241,10 +262,10 @@ int izb_moe_gateup_tiles(const izb_weight* wg, const izb_weight* wu, const int8_
   dim3 grid((F + kWarps * kRows - 1) / (kWarps * kRows), max_tiles);
   const size_t mat_bytes = (size_t)F * wg->row_bytes;
   if (wg->type == IZB_Q4_K) {
-    IZB_CUDA(cudaFuncSetAttribute(moe_gateup_kernel<IZB_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    IZB_SMEM_OPTIN((moe_gateup_kernel<IZB_Q4_K>), kMaxSmem, wg->device);
     moe_gateup_kernel<IZB_Q4_K><<<grid, kWarps * 32, smem, st>>>(wg->raw, wu->raw, F, K, mat_bytes, d_aq, d_asc, Mp, d_tiles, d_stok, d_h, spc);
   } else {
-    IZB_CUDA(cudaFuncSetAttribute(moe_gateup_kernel<IZB_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    IZB_SMEM_OPTIN((moe_gateup_kernel<IZB_Q8_0>), kMaxSmem, wg->device);
     moe_gateup_kernel<IZB_Q8_0><<<grid, kWarps * 32, smem, st>>>(wg->raw, wu->raw, F, K, mat_bytes, d_aq, d_asc, Mp, d_tiles, d_stok, d_h, spc);
   }
   IZB_LAUNCHED();
@@ -259,10 +280,10 @@ int izb_moe_down_tiles(const izb_weight* wd, const int8_t* d_hq, const float* d_
   dim3 grid((E + kWarps * kRows - 1) / (kWarps * kRows), max_tiles);
   const size_t mat_bytes = (size_t)E * wd->row_bytes;
   if (wd->type == IZB_Q4_K) {
-    IZB_CUDA(cudaFuncSetAttribute(moe_down_kernel<IZB_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    IZB_SMEM_OPTIN((moe_down_kernel<IZB_Q4_K>), kMaxSmem, wd->device);
     moe_down_kernel<IZB_Q4_K><<<grid, kWarps * 32, smem, st>>>(wd->raw, E, F, mat_bytes, d_hq, d_hsc, Sp, d_tiles, d_swt, d_y, spc);
   } else {
-    IZB_CUDA(cudaFuncSetAttribute(moe_down_kernel<IZB_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+    IZB_SMEM_OPTIN((moe_down_kernel<IZB_Q8_0>), kMaxSmem, wd->device);
     moe_down_kernel<IZB_Q8_0><<<grid, kWarps * 32, smem, st>>>(wd->raw, E, F, mat_bytes, d_hq, d_hsc, Sp, d_tiles, d_swt, d_y, spc);
   }
   IZB_LAUNCHED();
@@ -273,7 +294,8 @@ extern "C" int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_in
   if (!d_x || !d_y || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_combine: null pointer");
   if (T < 1 || NU < 1 || E < 4 || E % 4) IZB_FAIL(IZB_ERR_SHAPE, "moe_combine: T=%d NU=%d E=%d (E %% 4 == 0)", T, NU, E);
   if (!izb_aligned(d_x, 16) || !izb_aligned(d_y, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_combine: x, y must be 16-byte aligned");
-  dim3 grid((E / 4 + 127) / 128, T);
+  if ((E / 4 + 127) / 128 > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_combine: E = %d too wide", E);
+  dim3 grid(T, (E / 4 + 127) / 128);
   IZB_LAUNCH("moe_combine", (cudaStream_t)stream, moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(d_x, d_y, d_inv, T, NU, E));
   return IZB_OK;
 }
@@ -291,10 +313,13 @@ extern "C" int izb_moe_gateup(const izb_weight* wg, const izb_weight* wu, const 
     IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: gate and up stacks differ");
   if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_gateup: max_tiles = %d (1..65535)", max_tiles);
   if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_gateup: aq not 16-byte aligned");
+  if (wu->device != wg->device) IZB_FAIL(IZB_ERR_ARG, "moe_gateup: gate and up stacks live on different devices");
+  if (int rc = izb_require_device(wg->device, "moe_gateup")) return rc;
   if (TM >= 1 && TM <= 8) return izb_moe_gateup_tiles(wg, wu, d_aq, d_asc, Mp, d_tiles, max_tiles, d_stok, d_h, (cudaStream_t)stream);
   if (TM == 128) {
     const int rc = izb_moe_gateup_tc(wg, wu, d_aq, d_asc, Mp, d_tiles, max_tiles, d_stok, d_h, (cudaStream_t)stream);
     if (rc <= 0) return rc;
+    IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: the grouped tensor-core GEMM needs F %% 128 == 0 and a weight with a tensor map (F = %d, K = %d); use TM <= 8", wg->N, wg->K);
   }
   IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: tiles of %d slots (1..8: per-tile GEMV kernels; 128: grouped tensor-core GEMM)", TM);
 }
@@ -304,10 +329,12 @@ extern "C" int izb_moe_down(const izb_weight* wd, const int8_t* d_hq, const floa
   if (!wd || !d_hq || !d_hsc || !d_tiles || !d_swt || !d_y) IZB_FAIL(IZB_ERR_ARG, "moe_down: null pointer");
   if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_down: max_tiles = %d (1..65535)", max_tiles);
   if (!izb_aligned(d_hq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_down: hq not 16-byte aligned");
+  if (int rc = izb_require_device(wd->device, "moe_down")) return rc;
   if (TM >= 1 && TM <= 8) return izb_moe_down_tiles(wd, d_hq, d_hsc, Sp, d_tiles, max_tiles, d_swt, d_y, (cudaStream_t)stream);
   if (TM == 128) {
     const int rc = izb_moe_down_tc(wd, d_hq, d_hsc, Sp, d_tiles, max_tiles, d_swt, d_y, (cudaStream_t)stream);
     if (rc <= 0) return rc;
+    IZB_FAIL(IZB_ERR_SHAPE, "moe_down: the grouped tensor-core GEMM needs E %% 128 == 0 and a weight with a tensor map (E = %d, F = %d); use TM <= 8", wd->N, wd->K);
   }
   IZB_FAIL(IZB_ERR_SHAPE, "moe_down: tiles of %d slots (1..8: per-tile GEMV kernels; 128: grouped tensor-core GEMM)", TM);
 }

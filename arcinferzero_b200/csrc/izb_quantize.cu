@@ -320,6 +320,7 @@ extern "C" int izb_softcap_rows(float* d_C, int rows, int ld, int off, int N, fl
   if (rows < 0 || N < 0 || off < 0 || (rows > 1 && ld < off + N)) IZB_FAIL(IZB_ERR_SHAPE, "softcap_rows: rows=%d ld=%d off=%d N=%d", rows, ld, off, N);
   if (!(cap > 0.0f)) IZB_FAIL(IZB_ERR_ARG, "softcap_rows: cap = %g (must be positive)", (double)cap);
   if (rows == 0 || N == 0) return IZB_OK;
+  if (rows > 65535) IZB_FAIL(IZB_ERR_LIMIT, "softcap_rows: %d rows (at most 65535 per call)", rows);
   cudaStream_t st = (cudaStream_t)stream;
   const int vec = izb_aligned(d_C, 16) && ld % 4 == 0 && off % 4 == 0;
   const int per_row = vec ? (N + 3) / 4 : N;

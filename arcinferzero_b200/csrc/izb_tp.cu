@@ -68,7 +68,10 @@ void load_nccl() {
 
 int need_nccl() {
   std::call_once(g_nccl_once, load_nccl);
-  if (!g_nccl.ok) IZB_FAIL(IZB_ERR_NCCL, "libnccl.so.2 could not be loaded (%s)", dlerror() ? dlerror() : "symbols missing");
+  if (!g_nccl.ok) {
+    const char* why = dlerror();  // (a second call would return NULL: the message is consumed by the first)
+    IZB_FAIL(IZB_ERR_NCCL, "libnccl.so.2 could not be loaded (%s)", why ? why : "symbols missing");
+  }
   return IZB_OK;
 }
 
@@ -138,6 +141,7 @@ extern "C" int izb_tp_allreduce_rows(izb_tp* tp, float* d_x, float* d_part, int 
   if (!tp || !d_x || !d_part) IZB_FAIL(IZB_ERR_ARG, "tp_allreduce_rows: null pointer");
   if (rows < 1 || E < 4 || E % 4) IZB_FAIL(IZB_ERR_SHAPE, "tp_allreduce_rows: rows=%d E=%d (E %% 4 == 0)", rows, E);
   if (!izb_aligned(d_x, 16) || !izb_aligned(d_part, 16)) IZB_FAIL(IZB_ERR_ALIGN, "tp_allreduce_rows: buffers must be 16-byte aligned");
+  if (int rc = izb_require_device(tp->device, "tp_allreduce_rows")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t n = (size_t)rows * E;
   if (tp->nranks > 1) IZB_NCCL(g_nccl.AllReduce(d_part, d_part, n, ncclFloat32, ncclSum, tp->comm, st));
@@ -151,6 +155,7 @@ extern "C" int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d
   if (!tp || !d_part || !d_aq || !d_asc) IZB_FAIL(IZB_ERR_ARG, "tp_reduce_quant_gather: null pointer");
   const int R = tp->nranks;
   if (rows < 1 || rows % (16 * R) || E % 256) IZB_FAIL(IZB_ERR_SHAPE, "tp_reduce_quant_gather: rows=%d (multiple of 16*%d) E=%d (multiple of 256)", rows, R, E);
+  if (int rc = izb_require_device(tp->device, "tp_reduce_quant_gather")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const int own = rows / R;
   const size_t n_own = (size_t)own * E;

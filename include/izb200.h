@@ -14,7 +14,17 @@
  *     immutable after creation;
  *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream); calls are asynchronous on it unless
  *     stated otherwise (the *_create calls and the *_host convenience calls synchronise);
- *   - one izb_weight may be used from several threads; concurrent calls must use different streams and outputs.
+ *   - devices and threads: the library keeps its state (scratch arenas, kernel attributes, error word) per device, so one
+ *     process may drive several GPUs, one host thread per GPU, as the reference does (zero/mgpu/engine_tp.h:825).  A call
+ *     that takes a handle (izb_weight, izb_tp) must be made with the handle's device current in the calling thread
+ *     (cudaSetDevice), else it returns IZB_ERR_ARG; izb_weight_create* and izb_tp_create make their `device` current
+ *     and leave it current;
+ *   - per device the library is single-threaded, like one reference Engine (zero/runtime/clrt.h:143): the GEMM, MoE and
+ *     tensor-parallel calls keep activation images in one scratch arena each per device, so two such calls of one
+ *     device must be ordered (same stream, or events between streams); calls on different devices are independent.
+ *     An arena grows when a call needs more than any call before it, which waits for the device and calls
+ *     cudaFree / cudaMalloc: call izb_reserve once at start-up to keep that out of the hot path (and out of stream
+ *     capture).
  *
  * Buffer layouts are the reference engine's (zero/engine_alloc.h:10,39,41):
  *   aq     int8  [Mp][K]      quantised activations, row-major
@@ -67,6 +77,17 @@ int izb_profile_stop(char* json, size_t cap);
 /* Reads and clears the device-side error word of `device`: non-zero when a kernel gave up on a bounded wait
  * (value = where).  Synchronises the device. */
 int izb_device_status(int device, uint32_t* word);
+
+/* Sizes the per-device scratch arenas of izb_gemm / izb_matmul, the grouped MoE calls and izb_tp_reduce_quant_gather for
+ * calls of up to max_rows activation rows (token rows, or MoE slots) and K <= max_K, and creates the device error word,
+ * so that none of those calls allocates or synchronises later (the arenas are what Engine::alloc_buffers sizes once in
+ * the reference, zero/engine_alloc.h:10-41).  Synchronous; may be called again with larger sizes. */
+int izb_reserve(int device, int max_rows, int max_K);
+/* Diagnostics: the NEXT tensor-core GEMM launch of this process gives up its bounded device-side waits after spin_limit
+ * polls (0 = the default) and its activation producer leaves out operand stage `skip_stage` (-1 = none), so that the
+ * waits for that stage run out: the kernel drains, stores nothing for the affected tiles and reports through
+ * izb_device_status.  This is how the tests exercise the time-out path without a fault; never set it in production. */
+int izb_debug_wait_test(uint32_t spin_limit, int skip_stage);
 
 /* ------------------------------------------------------------------------------------------------ weights
  * Replaces Engine::make_weight / upload_padded (zero/engine_load.h:85-196) and the GpuWeight handle
@@ -149,10 +170,14 @@ int izb_selfcheck(int device);
  *   - Same arguments and results as izb_gemm with impl = IZB_GEMM_TC (N % 128 == 0 is required here: there is no second
  *     kernel to fall back to), plus d_status.
  *   - Limit: ceil(M/128) * (K/256 * S * 16384 + K/32 * 512) bytes, S = 5 for Q4_K and 4 for Q8_0, must fit in the array (e.g. M = 1024 at K = 5120, or
- *     M = 512 at K = 10240); a larger call returns IZB_ERR_LIMIT and launches nothing.  (With the opt-in folded-scale
- *     Q4_K kernel, IZB_GEMM_FOLD=1 or 2 in the environment, where it is selected: ceil(M/128) * (K/256 * 9 * 16384 + 512) bytes.)
- *   - d_status: a device uint32 of the caller's (or NULL to use one inside the library).  It is cleared at the start of
+ *     M = 512 at K = 10240); a larger call returns IZB_ERR_LIMIT and launches nothing.
+ *   - d_status: a device uint32 of the caller's, or NULL to use a word inside the library's device image, which
+ *     izb_device_status reports (and clears) together with the library's own error word.  It is cleared at the start of
  *     the call and is non-zero afterwards if a bounded device-side wait gave up (the output is then incomplete).
+ *   - "Allocates nothing" is about the call itself.  The CUDA runtime loads a kernel's code onto the device the first
+ *     time that kernel is launched, and that may reserve device memory: run one warm-up call per weight type before the
+ *     phase in which nothing may be allocated.  While izb_profile_start is active the library brackets every launch with
+ *     CUDA events and creates them on demand (cudaEventCreate): leave profiling off in that phase.
  *   - The first call on a device looks up the array's device address (the device must be current, as for every call):
  *     make that first call before any stream capture begins.
  *   - All calls share the one array and it keeps the last call's contents; each call rewrites everything it reads.  Two

@@ -21,12 +21,12 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 # every symbol include/izb200.h declares (tests check the library exports each of them)
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
-    "izb_reserve", "izb_debug_wait_test",
-    "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info",
+    "izb_reserve", "izb_set_sm_limit", "izb_debug_wait_test", "izb_tensor_peak",
+    "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info", "izb_weight_download",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
-    "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_destroy", "izb_tp_allreduce_rows",
+    "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_create_ex", "izb_tp_wait", "izb_tp_abort", "izb_tp_destroy", "izb_tp_allreduce_rows",
     "izb_tp_reduce_quant_gather",
 ]
 
@@ -112,6 +112,13 @@ class Weight:
         b = C.c_size_t(0)
         _check(lib().izb_weight_info(self.handle, None, None, None, None, C.byref(b)))
         return b.value
+
+    def download(self, offset: int = 0, nbytes: int | None = None) -> np.ndarray:
+        """The device form of the weight (without the slack) as bytes."""
+        n = self.nbytes - 1024 - offset if nbytes is None else nbytes
+        out = np.empty(n, np.uint8)
+        _check(lib().izb_weight_download(self.handle, C.c_size_t(offset), C.c_size_t(n), _p(out)))
+        return out
 
     def close(self):
         if self.handle:
@@ -250,6 +257,18 @@ def reserve(device: int, max_rows: int, max_K: int) -> None:
     _check(lib().izb_reserve(device, max_rows, max_K))
 
 
+def tensor_peak(device: int, kind: int, iters: int = 4096, launches: int = 1) -> tuple[float, float]:
+    """(Tops/s, SM clocks per MMA) of a TMEM-resident tcgen05.mma loop; kind 0 = kind::f16, 1 = kind::i8."""
+    tops, clk = C.c_double(0), C.c_double(0)
+    _check(lib().izb_tensor_peak(device, kind, iters, launches, C.byref(tops), C.byref(clk)))
+    return tops.value, clk.value
+
+
+def set_sm_limit(device: int, sms: int) -> None:
+    """Cap the persistent GEMM's grid at `sms` multiprocessors (0 = all), so that a collective can run beside it."""
+    _check(lib().izb_set_sm_limit(device, sms))
+
+
 def debug_wait_test(spin_limit: int, skip_stage: int) -> None:
     """Diagnostics: the next tensor-core GEMM launch gives up its waits early and leaves one operand stage out."""
     _check(lib().izb_debug_wait_test(C.c_uint32(spin_limit), skip_stage))
@@ -325,7 +344,7 @@ def tp_add(x, parts):
 class TpComm:
     """NCCL communicator of the library (izb_tp); the 128-byte id travels through torch.distributed."""
 
-    def __init__(self, nranks: int, rank: int, device: int):
+    def __init__(self, nranks: int, rank: int, device: int, timeout_ms: int = 0, max_ctas: int = 0):
         import torch
         import torch.distributed as dist
         idbuf = (C.c_char * 128)()
@@ -338,7 +357,7 @@ class TpComm:
             dist.broadcast(t, src=0)
             idbuf = (C.c_char * 128).from_buffer_copy(bytes(t.cpu().numpy().tobytes()))
         self.handle = C.c_void_p(0)
-        _check(lib().izb_tp_create(nranks, rank, idbuf, device, C.byref(self.handle)))
+        _check(lib().izb_tp_create_ex(nranks, rank, idbuf, device, timeout_ms, max_ctas, C.byref(self.handle)))
         self.nranks, self.rank, self.device = nranks, rank, device
 
     def allreduce_rows(self, x, part):
@@ -350,6 +369,13 @@ class TpComm:
         rows, E = part.shape
         _check(lib().izb_tp_reduce_quant_gather(self.handle, _p(x), _p(part), rows, E, _p(xsum), _p(aq), _p(asc), _stream()))
         return aq, asc
+
+    def wait(self, timeout_ms: int) -> None:
+        """Bounded wait for the current stream's work; raises IzbError (status -7) and aborts the communicator on time-out."""
+        _check(lib().izb_tp_wait(self.handle, _stream(), timeout_ms))
+
+    def abort(self) -> None:
+        _check(lib().izb_tp_abort(self.handle))
 
     def close(self):
         if self.handle:

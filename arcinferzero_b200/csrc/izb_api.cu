@@ -127,6 +127,7 @@ struct DevState {
   cudaEvent_t hstart = nullptr;
   std::atomic<int> tc_ok{-1};  // -1 unknown, 0 self-check failed, 1 passed
   std::atomic<int> sms{0};
+  std::atomic<int> sm_limit{0};  // izb_set_sm_limit: SMs the persistent GEMM may occupy (0 = all)
   uint32_t* noalloc_status = nullptr;  // status word of izb_gemm_noalloc (a device symbol's address), once looked up
 };
 DevState g_dev[kIzbMaxDev];
@@ -181,6 +182,19 @@ int izb_sm_count(int device) {
   }
   g_dev[device].sms.store(n, std::memory_order_relaxed);
   return n;
+}
+
+int izb_sm_budget(int device) {
+  const int n = izb_sm_count(device);
+  const int lim = device >= 0 && device < kIzbMaxDev ? g_dev[device].sm_limit.load(std::memory_order_relaxed) : 0;
+  return lim > 0 && lim < n ? lim : n;
+}
+
+extern "C" int izb_set_sm_limit(int device, int sms) {
+  if (device < 0 || device >= kIzbMaxDev) IZB_FAIL(IZB_ERR_ARG, "set_sm_limit: device %d out of range", device);
+  if (sms < 0) IZB_FAIL(IZB_ERR_ARG, "set_sm_limit: %d", sms);
+  g_dev[device].sm_limit.store(sms);
+  return IZB_OK;
 }
 
 // (called with `device` current: every caller has passed izb_require_device or holds a DeviceScope)
@@ -366,6 +380,15 @@ extern "C" void izb_weight_destroy(izb_weight* w) {
   cudaSetDevice(w->device);
   cudaFree(w->raw);
   delete w;
+}
+
+extern "C" int izb_weight_download(const izb_weight* w, size_t offset, size_t bytes, void* h_out) {
+  if (!w || !h_out) IZB_FAIL(IZB_ERR_ARG, "weight_download: null pointer");
+  if (offset > w->bytes || bytes > w->bytes - offset) IZB_FAIL(IZB_ERR_SHAPE, "weight_download: [%zu, +%zu) of %zu bytes", offset, bytes, w->bytes);
+  DeviceScope scope;
+  IZB_CUDA(scope.enter(w->device));
+  IZB_CUDA(cudaMemcpy(h_out, w->raw + offset, bytes, cudaMemcpyDeviceToHost));
+  return IZB_OK;
 }
 
 extern "C" int izb_weight_info(const izb_weight* w, int* type, int* n_mats, int* N, int* K, size_t* bytes) {

@@ -81,6 +81,8 @@ constexpr int kIzbMaxDev = 16;
 int izb_require_device(int device, const char* what);
 // multiprocessor count of `device` (looked up once per device)
 int izb_sm_count(int device);
+// the SMs a persistent GEMM grid may take: izb_sm_count, or less after izb_set_sm_limit
+int izb_sm_budget(int device);
 
 // Work that must run once per device at one call site (idempotent work only: two threads that race on the first call of
 // a device may both run it).  One bit per device.

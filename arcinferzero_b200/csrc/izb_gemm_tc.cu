@@ -746,7 +746,7 @@ int launch_tc(const izb_weight* w, TcParams& p, dim3 grid, cudaStream_t st) {
 
 // persistent grid: one CTA per SM (shared memory allows no more), fewer when there are fewer tiles
 int tc_grid(int device, int n_work) {
-  const int sms = izb_sm_count(device);
+  const int sms = izb_sm_budget(device);
   return n_work < sms ? (n_work > 0 ? n_work : 1) : sms;
 }
 

@@ -5,9 +5,12 @@
 // NCCL is resolved at run time from the library the process already has loaded (the framework's bundled libnccl.so.2),
 // so that no second copy of NCCL is linked in.  Only the stable C entry points below are used.
 #include <dlfcn.h>
+#include <limits.h>
 #include <string.h>
 
+#include <chrono>
 #include <mutex>
+#include <thread>
 
 #include "izb_common.cuh"
 
@@ -35,10 +38,27 @@ typedef struct ncclComm* ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 enum { ncclInt8 = 0, ncclFloat32 = 7 };
 enum { ncclSum = 0 };
+enum { ncclSuccess = 0, ncclInProgress = 7 };
+// The leading fields of ncclConfig_t as nccl.h has declared them since 2.18 (later versions only append; the library reads
+// `size` and `version` and gives every field past them its default).
+struct ncclConfigPrefix {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int blocking;
+  int cgaClusterSize;
+  int minCTAs;
+  int maxCTAs;
+  const char* netName;
+  int splitShare;
+};
 struct NcclApi {
   void* h = nullptr;
   int (*GetUniqueId)(ncclUniqueId*) = nullptr;
   int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfigPrefix*) = nullptr;
+  int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
+  int (*CommAbort)(ncclComm_t) = nullptr;
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -60,7 +80,7 @@ void load_nccl() {
   if (!g_nccl.h) return;
 #define SYM(f) *(void**)(&g_nccl.f) = dlsym(g_nccl.h, "nccl" #f)
   SYM(GetUniqueId); SYM(CommInitRank); SYM(CommDestroy); SYM(AllReduce); SYM(ReduceScatter); SYM(AllGather);
-  SYM(GroupStart); SYM(GroupEnd); SYM(GetErrorString);
+  SYM(GroupStart); SYM(GroupEnd); SYM(GetErrorString); SYM(CommInitRankConfig); SYM(CommGetAsyncError); SYM(CommAbort);
 #undef SYM
   g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllReduce && g_nccl.ReduceScatter &&
               g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
@@ -89,7 +109,51 @@ int need_nccl() {
 struct izb_tp {
   int nranks = 1, rank = 0, device = 0;
   ncclComm_t comm = nullptr;
+  int timeout_ms = 0;    // > 0: non-blocking communicator, every NCCL call is followed by a bounded wait for its result
+  bool aborted = false;  // the communicator was aborted after a time-out or an asynchronous error: it takes no more calls
+  cudaEvent_t done = nullptr;
 };
+
+namespace {
+// Bounded wait for a call on a non-blocking communicator to leave the "in progress" state (the reference bounds every
+// barrier and wait of its own transport the same way, zero/mgpu/engine_tp.h:93-123).  On a time-out or an error the
+// communicator is aborted -- ncclCommAbort also ends collectives of this rank that are stuck on the device -- and marked.
+int tp_settle(izb_tp* tp, int r, const char* what) {
+  if (tp->timeout_ms <= 0 || !tp->comm) {
+    if (r != ncclSuccess) {
+      izb_set_error("%s failed: %s", what, g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "nccl error");
+      return IZB_ERR_NCCL;
+    }
+    return IZB_OK;
+  }
+  const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(tp->timeout_ms);
+  int state = r;
+  while (state == ncclInProgress) {
+    if (g_nccl.CommGetAsyncError(tp->comm, &state) != ncclSuccess) { state = -1; break; }
+    if (state != ncclInProgress) break;
+    if (std::chrono::steady_clock::now() > t_end) break;
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+  if (state == ncclSuccess) return IZB_OK;
+  g_nccl.CommAbort(tp->comm);
+  tp->comm = nullptr;
+  tp->aborted = true;
+  if (state == ncclInProgress) {
+    izb_set_error("%s: no answer from the other ranks within %d ms; communicator aborted", what, tp->timeout_ms);
+    return IZB_ERR_TIMEOUT;
+  }
+  izb_set_error("%s failed: %s; communicator aborted", what, state > 0 && g_nccl.GetErrorString ? g_nccl.GetErrorString(state) : "nccl error");
+  return IZB_ERR_NCCL;
+}
+int tp_usable(izb_tp* tp, const char* what) {
+  if (tp->aborted) IZB_FAIL(IZB_ERR_NCCL, "%s: the communicator was aborted after a time-out or an error; create a new one", what);
+  return IZB_OK;
+}
+}  // namespace
+#define IZB_TP_NCCL(tp, call, what)                      \
+  do {                                                   \
+    if (int rc__ = tp_settle((tp), (call), (what))) return rc__; \
+  } while (0)
 
 extern "C" int izb_tp_add(float* d_x, const float* d_parts, size_t n, int np, size_t stride, void* stream) {
   if (!d_x || !d_parts) IZB_FAIL(IZB_ERR_ARG, "tp_add: null pointer");
@@ -108,32 +172,103 @@ extern "C" int izb_tp_unique_id(void* id128) {
   return IZB_OK;
 }
 
-extern "C" int izb_tp_create(int nranks, int rank, const void* id128, int device, izb_tp** out) {
+extern "C" int izb_tp_create_ex(int nranks, int rank, const void* id128, int device, int timeout_ms, int max_ctas, izb_tp** out) {
   if (!out || (nranks > 1 && !id128)) IZB_FAIL(IZB_ERR_ARG, "tp_create: null pointer");
   *out = nullptr;
   if (nranks < 1 || rank < 0 || rank >= nranks) IZB_FAIL(IZB_ERR_ARG, "tp_create: rank %d of %d", rank, nranks);
+  if (timeout_ms < 0 || max_ctas < 0) IZB_FAIL(IZB_ERR_ARG, "tp_create: timeout_ms = %d, max_ctas = %d", timeout_ms, max_ctas);
   IZB_CUDA(cudaSetDevice(device));
   izb_tp* tp = new izb_tp;
   tp->nranks = nranks;
   tp->rank = rank;
   tp->device = device;
+  if (cudaEventCreateWithFlags(&tp->done, cudaEventDisableTiming) != cudaSuccess) {
+    delete tp;
+    IZB_FAIL(IZB_ERR_CUDA, "tp_create: cannot create an event");
+  }
   if (nranks > 1) {
-    if (int rc = need_nccl()) { delete tp; return rc; }
+    if (int rc = need_nccl()) { cudaEventDestroy(tp->done); delete tp; return rc; }
     ncclUniqueId id;
     memcpy(&id, id128, 128);
-    const int r = g_nccl.CommInitRank(&tp->comm, nranks, id, rank);
-    if (r != 0) {
+    int r;
+    if (timeout_ms > 0 || max_ctas > 0) {
+      if (!g_nccl.CommInitRankConfig || !g_nccl.CommGetAsyncError || !g_nccl.CommAbort) {
+        cudaEventDestroy(tp->done);
+        delete tp;
+        IZB_FAIL(IZB_ERR_NCCL, "tp_create: this NCCL has no ncclCommInitRankConfig / ncclCommGetAsyncError / ncclCommAbort (2.18 or later needed)");
+      }
+      ncclConfigPrefix cfg;
+      cfg.size = sizeof cfg;
+      cfg.magic = 0xcafebeefu;
+      cfg.version = 21800;  // NCCL_VERSION(2, 18, 0): the version whose ncclConfig_t ends with splitShare
+      cfg.blocking = timeout_ms > 0 ? 0 : 1;
+      cfg.cgaClusterSize = INT_MIN;  // NCCL_CONFIG_UNDEF_INT: the library's default
+      cfg.minCTAs = INT_MIN;
+      cfg.maxCTAs = max_ctas > 0 ? max_ctas : INT_MIN;
+      cfg.netName = nullptr;
+      cfg.splitShare = INT_MIN;
+      tp->timeout_ms = timeout_ms;
+      r = g_nccl.CommInitRankConfig(&tp->comm, nranks, id, rank, &cfg);
+      if (timeout_ms > 0 && (r == ncclSuccess || r == ncclInProgress)) r = ncclInProgress;  // (the state is polled below)
+    } else {
+      r = g_nccl.CommInitRank(&tp->comm, nranks, id, rank);
+    }
+    if (int rc = tp_settle(tp, r, "ncclCommInitRank")) {
+      if (tp->comm && !tp->aborted) g_nccl.CommAbort ? g_nccl.CommAbort(tp->comm) : g_nccl.CommDestroy(tp->comm);
+      cudaEventDestroy(tp->done);
       delete tp;
-      IZB_FAIL(IZB_ERR_NCCL, "ncclCommInitRank failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "nccl error");
+      return rc;
     }
   }
   *out = tp;
   return IZB_OK;
 }
 
+extern "C" int izb_tp_create(int nranks, int rank, const void* id128, int device, izb_tp** out) {
+  return izb_tp_create_ex(nranks, rank, id128, device, 0, 0, out);
+}
+
+extern "C" int izb_tp_abort(izb_tp* tp) {
+  if (!tp) IZB_FAIL(IZB_ERR_ARG, "tp_abort: null handle");
+  if (tp->comm && g_nccl.CommAbort) {
+    g_nccl.CommAbort(tp->comm);
+    tp->comm = nullptr;
+  }
+  tp->aborted = tp->nranks > 1;
+  return IZB_OK;
+}
+
+extern "C" int izb_tp_wait(izb_tp* tp, void* stream, int timeout_ms) {
+  if (!tp) IZB_FAIL(IZB_ERR_ARG, "tp_wait: null handle");
+  if (timeout_ms < 1) IZB_FAIL(IZB_ERR_ARG, "tp_wait: timeout_ms = %d", timeout_ms);
+  if (int rc = izb_require_device(tp->device, "tp_wait")) return rc;
+  IZB_CUDA(cudaEventRecord(tp->done, (cudaStream_t)stream));
+  const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (;;) {
+    const cudaError_t q = cudaEventQuery(tp->done);
+    if (q == cudaSuccess) return IZB_OK;
+    if (q != cudaErrorNotReady) IZB_CUDA(q);
+    int state = ncclSuccess;
+    const bool async_ok = !tp->comm || !g_nccl.CommGetAsyncError || g_nccl.CommGetAsyncError(tp->comm, &state) == ncclSuccess;
+    const bool failed = !async_ok || (state != ncclSuccess && state != ncclInProgress);
+    if (failed || std::chrono::steady_clock::now() > t_end) {
+      // ending the communicator also ends this rank's collectives that wait on the device for a peer
+      if (tp->comm && g_nccl.CommAbort) {
+        g_nccl.CommAbort(tp->comm);
+        tp->comm = nullptr;
+        tp->aborted = true;
+      }
+      if (failed) IZB_FAIL(IZB_ERR_NCCL, "tp_wait: NCCL reported %s; communicator aborted", state > 0 && g_nccl.GetErrorString ? g_nccl.GetErrorString(state) : "an error");
+      IZB_FAIL(IZB_ERR_TIMEOUT, "tp_wait: the work queued on the stream did not finish within %d ms (a peer is missing?); communicator aborted", timeout_ms);
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(100));
+  }
+}
+
 extern "C" void izb_tp_destroy(izb_tp* tp) {
   if (!tp) return;
   if (tp->comm) g_nccl.CommDestroy(tp->comm);
+  if (tp->done) cudaEventDestroy(tp->done);
   delete tp;
 }
 
@@ -144,7 +279,8 @@ extern "C" int izb_tp_allreduce_rows(izb_tp* tp, float* d_x, float* d_part, int 
   if (int rc = izb_require_device(tp->device, "tp_allreduce_rows")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t n = (size_t)rows * E;
-  if (tp->nranks > 1) IZB_NCCL(g_nccl.AllReduce(d_part, d_part, n, ncclFloat32, ncclSum, tp->comm, st));
+  if (int rc = tp_usable(tp, "tp_allreduce_rows")) return rc;
+  if (tp->nranks > 1) IZB_TP_NCCL(tp, g_nccl.AllReduce(d_part, d_part, n, ncclFloat32, ncclSum, tp->comm, st), "ncclAllReduce");
   tp_add1_v4_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>((float4*)d_x, (const float4*)d_part, n / 4);
   IZB_LAUNCHED();
   return IZB_OK;
@@ -161,7 +297,8 @@ extern "C" int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d
   const size_t n_own = (size_t)own * E;
   // 1. this rank's token rows of the sum of partials, in place at their position in d_part
   float* mine = d_part + (size_t)tp->rank * n_own;
-  if (R > 1) IZB_NCCL(g_nccl.ReduceScatter(d_part, mine, n_own, ncclFloat32, ncclSum, tp->comm, st));
+  if (int rc = tp_usable(tp, "tp_reduce_quant_gather")) return rc;
+  if (R > 1) IZB_TP_NCCL(tp, g_nccl.ReduceScatter(d_part, mine, n_own, ncclFloat32, ncclSum, tp->comm, st), "ncclReduceScatter");
   // 2. + this rank's rows of the residual stream
   if (d_x) {
     tp_add1_v4_kernel<<<(unsigned)((n_own / 4 + 255) / 256), 256, 0, st>>>((float4*)mine, (const float4*)(d_x + (size_t)tp->rank * n_own), n_own / 4);
@@ -176,10 +313,15 @@ extern "C" int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d
   float* sc_stage = (float*)ws;  // [R][E/32][own]
   if (int rc = izb_quantize_act(mine, E, own, own, E, d_aq + (size_t)tp->rank * n_own, sc_stage + (size_t)tp->rank * (E / 32) * own, nullptr, st)) return rc;
   if (R > 1) {
+    // (inside a group a non-blocking communicator answers "in progress"; the group's end carries the result)
     IZB_NCCL(g_nccl.GroupStart());
-    IZB_NCCL(g_nccl.AllGather(d_aq + (size_t)tp->rank * n_own, d_aq, n_own, ncclInt8, tp->comm, st));
-    IZB_NCCL(g_nccl.AllGather(sc_stage + (size_t)tp->rank * (E / 32) * own, sc_stage, (size_t)(E / 32) * own, ncclFloat32, tp->comm, st));
-    IZB_NCCL(g_nccl.GroupEnd());
+    int r1 = g_nccl.AllGather(d_aq + (size_t)tp->rank * n_own, d_aq, n_own, ncclInt8, tp->comm, st);
+    int r2 = g_nccl.AllGather(sc_stage + (size_t)tp->rank * (E / 32) * own, sc_stage, (size_t)(E / 32) * own, ncclFloat32, tp->comm, st);
+    if (r1 == ncclInProgress) r1 = ncclSuccess;
+    if (r2 == ncclInProgress) r2 = ncclSuccess;
+    IZB_NCCL(r1);
+    IZB_NCCL(r2);
+    IZB_TP_NCCL(tp, g_nccl.GroupEnd(), "ncclAllGather");
   }
   // 4. [R][E/32][own] -> [E/32][R*own]
   IZB_CUDA(cudaMemcpy2DAsync(d_asc, (size_t)rows * 4, sc_stage, (size_t)own * 4, (size_t)own * 4, (size_t)(E / 32), cudaMemcpyDeviceToDevice, st));

@@ -66,9 +66,22 @@ class ShardPlan:
         return (self.q[1] - self.q[0]) + 2 * (self.kv[1] - self.kv[0])
 
 
-def shard_plan(cfg: StackConfig, world: int, rank: int) -> ShardPlan:
-    return ShardPlan(q=tp_range(cfg.q_rows, 256, world, rank), kv=tp_range(cfg.kv_rows, 128, world, rank),
-                     ffn=tp_range(cfg.ffn, 256, world, rank))
+def tp_range_tail(total: int, unit: int, n: int, r: int) -> tuple[int, int]:
+    """The same split with the extra units on the LAST `units % n` ranks instead of the first."""
+    units = total // unit
+    base, extra = divmod(units, n)
+    b = r * base + max(0, r - (n - extra))
+    e = b + base + (1 if r >= n - extra else 0)
+    return b * unit, e * unit
+
+
+def shard_plan(cfg: StackConfig, world: int, rank: int, balance: bool = False) -> ShardPlan:
+    """tp_range for every split dimension.  balance=True puts the extra Q units on the last ranks: tp_range gives the
+    first ranks the extra unit of EVERY dimension (at 8 ranks: 3 Q units + 9 FFN units against 2 + 8), so the same ranks
+    are the slowest in both halves of a layer; moving the Q extras to the ranks with fewer FFN rows costs nothing and
+    evens the work (33 : 28 units of 256 rows becomes 31 : 30)."""
+    q = tp_range_tail(cfg.q_rows, 256, world, rank) if balance else tp_range(cfg.q_rows, 256, world, rank)
+    return ShardPlan(q=q, kv=tp_range(cfg.kv_rows, 128, world, rank), ffn=tp_range(cfg.ffn, 256, world, rank))
 
 
 def condition_weight(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:
@@ -167,89 +180,176 @@ class Stack:
     """The rank-local stack on one GPU (needs the CUDA library and torch.distributed when world > 1).
 
     distinct_layers=False uploads one generated layer `cfg.layers` times (separate device copies, same bytes): the
-    benchmark's way to keep host-side generation short; timing and traffic are those of distinct layers."""
+    benchmark's way to keep host-side generation short; timing and traffic are those of distinct layers.
 
-    def __init__(self, cfg: StackConfig, world: int, rank: int, device: int, mode: str = "allreduce", distinct_layers: bool = True):
+    chunks > 1 splits the token rows into equal chunks that run through a layer one after the other; with overlap=True
+    the sum of a chunk's row-parallel partials runs on a second stream while the next chunk's GEMMs run on the first
+    (the reference hides its FFN sums behind the next chunk's GEMMs the same way: TpOverlap, zero/mgpu/engine_tp.h:126-151,
+    tpo_out :629).  The persistent GEMM then leaves `comm_sms` multiprocessors free (izb_set_sm_limit) and the collectives
+    are capped at as many CTAs, so that both are resident at once.  Every chunk owns its buffers; in "rs_quant_ag" mode a
+    rank owns the rows [rank * own, (rank + 1) * own) of EACH chunk (own = chunk rows / world)."""
+
+    def __init__(self, cfg: StackConfig, world: int, rank: int, device: int, mode: str = "allreduce", distinct_layers: bool = True,
+                 chunks: int = 1, overlap: bool = False, balance: bool = False, comm_sms: int = 8, timeout_ms: int = 0):
         import torch
 
         import arcinferzero_b200 as izb
         self.izb, self.torch = izb, torch
         self.cfg, self.world, self.rank, self.device, self.mode = cfg, world, rank, device, mode
         assert mode in ("allreduce", "rs_quant_ag")
-        self.plan = shard_plan(cfg, world, rank)
+        T, E = cfg.tokens, cfg.hidden
+        assert T % chunks == 0 and (T // chunks) % (16 * world) == 0, "chunk rows must be a multiple of 16 * world"
+        self.chunks, self.Tc = chunks, T // chunks
+        self.overlap = bool(overlap and world > 1)
+        self.plan = shard_plan(cfg, world, rank, balance)
         self.layers = []
         sh = None
         for li in range(cfg.layers):
             if sh is None or distinct_layers:
                 sh = shard_rows(cfg, layer_weights(cfg, li), self.plan)
             self.layers.append({k: izb.Weight(cfg.qtype, rows, N, K, device=device, col_range=cr) for k, (rows, N, K, cr) in sh.items()})
-        self.comm = izb.TpComm(world, rank, device)
-        T, E = cfg.tokens, cfg.hidden
+        self.comm = izb.TpComm(world, rank, device, timeout_ms=timeout_ms, max_ctas=comm_sms if self.overlap else 0)
         dev = torch.device("cuda", device)
         f32, i8 = torch.float32, torch.int8
-        self.x = torch.empty((T, E), dtype=f32, device=dev)
-        self.part = torch.empty((T, E), dtype=f32, device=dev)
-        self.qkv = torch.empty((T, self.plan.qkv_rows), dtype=f32, device=dev)
         nf = self.plan.ffn[1] - self.plan.ffn[0]
+        Tc = self.Tc
+        self.x = torch.empty((T, E), dtype=f32, device=dev)
+        self.part_a = torch.empty((T, E), dtype=f32, device=dev)   # partial outputs of O, per chunk rows
+        self.part_f = torch.empty((T, E), dtype=f32, device=dev) if chunks > 1 else self.part_a  # ... of down
+        self.qkv = torch.empty((T, self.plan.qkv_rows), dtype=f32, device=dev)
         self.h = torch.empty((T, nf), dtype=f32, device=dev)
         kmax = max(E, nf)
-        self.aq = torch.empty((T * kmax,), dtype=i8, device=dev)
-        self.asc = torch.empty((T * (kmax // 32),), dtype=f32, device=dev)
-        self.xq = torch.empty((T, E), dtype=i8, device=dev)       # quantised residual stream (input of QKV / gate / up)
-        self.xsc = torch.empty((E // 32, T), dtype=f32, device=dev)
+        self.aq = torch.empty((Tc * kmax,), dtype=i8, device=dev)
+        self.asc = torch.empty((Tc * (kmax // 32),), dtype=f32, device=dev)
+        self.xq = torch.empty((T, E), dtype=i8, device=dev)            # quantised residual stream (input of QKV / gate / up)
+        self.xsc_c = torch.empty((chunks, E // 32, Tc), dtype=f32, device=dev)  # its scales, [E/32][rows] per chunk
+        self.compute = None
+        self.side = torch.cuda.Stream(device=dev, priority=-1) if self.overlap else None
+        if self.overlap:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            izb.set_sm_limit(device, sms - comm_sms)
+        # every arena at its final size before the first step: no allocation, no device-wide wait inside the pipeline
+        izb.reserve(device, Tc, kmax)
+        self.ev_sum = [None] * chunks    # the last sum of chunk c (side stream)
+
+    # ---- views
+    def rows(self, c):
+        return slice(c * self.Tc, (c + 1) * self.Tc)
+
+    @property
+    def part(self):
+        return self.part_a
+
+    @property
+    def xsc(self):
+        """Scales of the whole quantised stream as [E/32][T]."""
+        E32 = self.cfg.hidden // 32
+        return self.xsc_c[0] if self.chunks == 1 else self.xsc_c.permute(1, 0, 2).reshape(E32, self.cfg.tokens)
+
+    def owned_rows(self) -> np.ndarray:
+        """Token rows whose residual-stream values this rank holds after a sum ("rs_quant_ag": its rows of every chunk)."""
+        if self.mode != "rs_quant_ag":
+            return np.arange(self.cfg.tokens)
+        own = self.Tc // self.world
+        return np.concatenate([np.arange(c * self.Tc + self.rank * own, c * self.Tc + (self.rank + 1) * own) for c in range(self.chunks)])
 
     def _quant(self, src, K):
-        T = self.cfg.tokens
-        aq = self.aq[:T * K].view(T, K)
-        asc = self.asc[:T * (K // 32)].view(K // 32, T)
-        self.izb.quantize_act(src, Mp=T, out=(aq, asc, None))
+        Tc = self.Tc
+        aq = self.aq[:Tc * K].view(Tc, K)
+        asc = self.asc[:Tc * (K // 32)].view(K // 32, Tc)
+        self.izb.quantize_act(src, Mp=Tc, out=(aq, asc, None))
         return aq, asc
 
-    def _sum(self):
-        """Row-parallel partials in self.part -> residual stream; leaves the quantised stream in xq / xsc."""
-        izb, T = self.izb, self.cfg.tokens
+    def _sum(self, c, part):
+        """Row-parallel partials of chunk c -> residual stream; leaves the chunk's quantised stream in xq / xsc_c[c]."""
+        izb, r = self.izb, self.rows(c)
+        x, xq, xsc = self.x[r], self.xq[r], self.xsc_c[c]
         if self.mode == "allreduce":
-            self.comm.allreduce_rows(self.x, self.part)
-            izb.quantize_act(self.x, Mp=T, out=(self.xq, self.xsc, None))
+            self.comm.allreduce_rows(x, part)
+            izb.quantize_act(x, Mp=self.Tc, out=(xq, xsc, None))
         else:
-            own = T // self.world
-            xs = self.x[self.rank * own:(self.rank + 1) * own]
-            self.comm.reduce_quant_gather(self.x, self.part, self.xq, self.xsc, xsum=xs)
+            own = self.Tc // self.world
+            xs = x[self.rank * own:(self.rank + 1) * own]
+            self.comm.reduce_quant_gather(x, part, xq, xsc, xsum=xs)
+
+    def _sum_async(self, c, part):
+        """The sum of chunk c: on the side stream, after what the compute stream has queued so far."""
+        torch = self.torch
+        if not self.overlap:
+            self._sum(c, part)
+            return
+        ev = torch.cuda.Event()
+        ev.record(self.compute)
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            self._sum(c, part)
+            done = torch.cuda.Event()
+            done.record(self.side)
+        self.ev_sum[c] = done
+
+    def _await_sum(self, c):
+        if self.overlap and self.ev_sum[c] is not None:
+            self.compute.wait_event(self.ev_sum[c])
 
     def set_input(self, x):
         self.x.copy_(x)
-        self.izb.quantize_act(self.x, Mp=self.cfg.tokens, out=(self.xq, self.xsc, None))
+        for c in range(self.chunks):
+            r = self.rows(c)
+            self.izb.quantize_act(self.x[r], Mp=self.Tc, out=(self.xq[r], self.xsc_c[c], None))
 
-    def forward(self, trace: list | None = None):
-        """One pass over all layers.  `trace` (tests only) receives per layer a dict of copies of every stage's output, so
-        that each stage can be checked against the oracle from the stage before it."""
-        izb, T = self.izb, self.cfg.tokens
+    def _attn_half(self, L, c):
+        izb, Tc, r = self.izb, self.Tc, self.rows(c)
         nq = self.plan.q[1] - self.plan.q[0]
-        for L in self.layers:
+        izb.matmul(L["qkv"], self.xq[r], self.xsc_c[c], Tc, out=self.qkv[r])
+        aq, asc = self._quant(self.qkv[r][:, :nq], nq)
+        izb.matmul(L["o"], aq, asc, Tc, out=self.part_a[r])
+
+    def _ffn_half(self, L, c):
+        izb, Tc, r = self.izb, self.Tc, self.rows(c)
+        izb.matmul(L["gate"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r])
+        izb.matmul(L["up"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r], acc=2)
+        aq, asc = self._quant(self.h[r], self.h.shape[1])
+        izb.matmul(L["down"], aq, asc, Tc, out=self.part_f[r])
+
+    def forward(self, trace: list | None = None, layers: int | None = None):
+        """One pass over all (or the first `layers`) layers.  `trace` (tests, parity fields of the benchmark) receives per
+        layer a dict of copies of every stage's output, so that each stage can be checked against the oracle from the
+        stage before it; with a trace the two halves of a layer are separated by device-wide waits."""
+        torch = self.torch
+        self.compute = torch.cuda.current_stream()
+        sync = torch.cuda.synchronize
+        for L in self.layers[:layers]:
             t = {} if trace is not None else None
             if t is not None:
-                t["xq0"], t["xsc0"] = self.xq.clone(), self.xsc.clone()
-            izb.matmul(L["qkv"], self.xq, self.xsc, T, out=self.qkv)
-            aq, asc = self._quant(self.qkv[:, :nq], nq)
-            izb.matmul(L["o"], aq, asc, T, out=self.part)
+                sync()
+                t["xq0"], t["xsc0"], t["x0"] = self.xq.clone(), self.xsc.clone(), self.x.clone()
+                t["o_part"], t["down_part"] = torch.empty_like(self.part_a), torch.empty_like(self.part_a)
+            for c in range(self.chunks):
+                self._await_sum(c)
+                self._attn_half(L, c)
+                if t is not None:  # (before the sum: the collectives work in place)
+                    t["o_part"][self.rows(c)].copy_(self.part_a[self.rows(c)])
+                self._sum_async(c, self.part_a[self.rows(c)])
             if t is not None:
-                t["qkv"], t["o_part"], t["x0"] = self.qkv.clone(), self.part.clone(), self.x.clone()
-            self._sum()
+                sync()
+                t["qkv"], t["x1"], t["xq1"], t["xsc1"] = self.qkv.clone(), self.x.clone(), self.xq.clone(), self.xsc.clone()
+            for c in range(self.chunks):
+                self._await_sum(c)
+                self._ffn_half(L, c)
+                if t is not None:
+                    t["down_part"][self.rows(c)].copy_(self.part_f[self.rows(c)])
+                self._sum_async(c, self.part_f[self.rows(c)])
             if t is not None:
-                t["x1"], t["xq1"], t["xsc1"] = self.x.clone(), self.xq.clone(), self.xsc.clone()
-            izb.matmul(L["gate"], self.xq, self.xsc, T, out=self.h)
-            izb.matmul(L["up"], self.xq, self.xsc, T, out=self.h, acc=2)
-            aq, asc = self._quant(self.h, self.h.shape[1])
-            izb.matmul(L["down"], aq, asc, T, out=self.part)
-            if t is not None:
-                t["h"], t["down_part"] = self.h.clone(), self.part.clone()
-            self._sum()
-            if t is not None:
-                t["x2"], t["xq2"], t["xsc2"] = self.x.clone(), self.xq.clone(), self.xsc.clone()
+                sync()
+                t["h"], t["x2"], t["xq2"], t["xsc2"] = self.h.clone(), self.x.clone(), self.xq.clone(), self.xsc.clone()
                 trace.append(t)
+        for c in range(self.chunks):
+            self._await_sum(c)
         return self.x
 
     def close(self):
+        if self.overlap:
+            self.izb.set_sm_limit(self.device, 0)
         for L in self.layers:
             for w in L.values():
                 w.close()

@@ -37,7 +37,6 @@ SEED = 20261125
 WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantize_act + GEMM per step)"
 NOMINAL_INT8_TOPS = 4500.0
 NCU_TRAFFIC_BYTES_PER_TILE = (132.1e6 + 116.6e6) / (16 * 136)       # gemm_tc: ncu capture of 16 x 136 tiles of 128 x 128
-NCU_TRAFFIC_BYTES_PER_TILE_FOLD = (244.4e6 + 123.9e6) / (16 * 136)  # gemm_tc_fold: the same case (profiles/)
 
 
 def peaks():
@@ -46,6 +45,11 @@ def peaks():
         d = json.load(open(p))
         return d["hbm_gbs"], d["bf16_tflops"], d["bf16_tflops_sustained"], "measured"
     return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def _rel(got, ref) -> float:
+    """The reference's error form (bench/gemv_bench.cpp:199-214): max|got - ref| / max|ref|."""
+    return float(np.abs(got.astype(np.float64) - ref.astype(np.float64)).max() / max(1e-30, float(np.abs(ref).max())))
 
 
 class ClockSampler:
@@ -128,7 +132,10 @@ def cpu_baseline(seconds_target: float = 15.0) -> dict:
     Ms, Ns = 64, 1024
     w = S.make_weight(QT, Ns, K, SEED)
     x = S.make_act(Ms, K, SEED + 1)
-    cores = os.cpu_count() or 1
+    # Every host core the process may use, set explicitly: a launcher (torch.distributed.run) exports OMP_NUM_THREADS=1,
+    # which would otherwise time the reference on one thread.
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores = O.set_threads(cores)
     if O.ref() is not None:
         kind = "reference"
         d = tempfile.mkdtemp()
@@ -136,7 +143,7 @@ def cpu_baseline(seconds_target: float = 15.0) -> dict:
         S.write_gguf(path, {"w": (QT, w, Ns, K)})
 
         def run(ms):
-            return O.ref_forward_matmul(path, "w", x[:ms] if ms <= Ms else np.tile(x, (ms // Ms, 1)), Ns)
+            return O.ref_forward_matmul(path, "w", x[:ms] if ms <= Ms else np.tile(x, (ms // Ms, 1)), Ns, threads=cores)
     else:
         kind = "port"
 
@@ -218,14 +225,17 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
     from arcinferzero_b200 import synth as S
     T, E, F, NE, NU, TM = 4096, 2048, 768, 128, 8, 128
     rng = np.random.default_rng(SEED + 9)
-    Wg = izb.Weight(QT, S.make_weight(QT, NE * F, E, SEED + 11), F, E, n_mats=NE)
-    Wu = izb.Weight(QT, S.make_weight(QT, NE * F, E, SEED + 12), F, E, n_mats=NE)
-    Wd = izb.Weight(QT, S.make_weight(QT, NE * E, F, SEED + 13), E, F, n_mats=NE)
+    wg, wu, wd = S.make_weight(QT, NE * F, E, SEED + 11), S.make_weight(QT, NE * F, E, SEED + 12), S.make_weight(QT, NE * E, F, SEED + 13)
+    Wg = izb.Weight(QT, wg, F, E, n_mats=NE)
+    Wu = izb.Weight(QT, wu, F, E, n_mats=NE)
+    Wd = izb.Weight(QT, wd, E, F, n_mats=NE)
     x = torch.from_numpy(S.make_act(T, E, SEED + 14)).cuda()
     logits = torch.from_numpy(rng.standard_normal((T, NE), dtype=np.float32)).cuda()
     Sn = T * NU
     Sp = izb.pad_rows(Sn)
     out = torch.empty_like(x)
+
+    keep = {}
 
     def one_pass():
         out.copy_(x)
@@ -236,7 +246,23 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
         hq, hsc, _ = izb.quantize_act(h, Mp=Sp)
         y = izb.moe_down(Wd, hq, hsc, tiles, max_tiles, TM, swt, Sn)
         izb.moe_combine(out, y, inv, NU)
+        keep.update(aq=aq, asc=asc, ids=ids, offs=offs, stok=stok, swt=swt, h=h, hq=hq, hsc=hsc, y=y)
         return counts
+
+    def parity() -> dict:
+        """Stage-wise, teacher-forced, on sampled slots against the CPU oracle (checker only, after the timed region)."""
+        from oracle import oracle as O
+        k = {n: v.cpu().numpy() for n, v in keep.items()}
+        rid, _, _ = O.moe_route(logits.cpu().numpy(), NU)
+        se = O.slot_experts(k["offs"])
+        smp = np.unique(np.concatenate([k["offs"][[0, 1, 64, 127]], k["offs"][[1, 65, 128]] - 1, rng.integers(0, Sn, 20)]))
+        rh = O.moe_gateup(QT, wg, wu, F, E, k["aq"], k["asc"], se[smp], k["stok"][smp])
+        rq, rs, _ = O.quantize_act(k["h"][smp])
+        ry = O.moe_down(QT, wd, E, F, rq, rs, se[smp], k["swt"][smp])
+        return {"parity_max_rel": max(_rel(k["h"][smp], rh), _rel(k["y"][smp], ry)), "parity_tolerance": 1e-5,
+                "routing_ids_exact": bool((k["ids"] == rid).all()),
+                "int8_rows_exact": bool(np.array_equal(k["hq"][smp], rq) and np.array_equal(k["hsc"][:, smp].view(np.uint32), rs.view(np.uint32))),
+                "parity_slots_sampled": int(len(smp))}
 
     for _ in range(3):
         counts = one_pass()
@@ -254,7 +280,7 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
     launches = (izb.launch_count() - l0) // iters
     ops = 2.0 * Sn * 3 * F * E
     c = counts.cpu().numpy()
-    tc_ms = sum(v["ms"] for k, v in prof.items() if k in ("gemm_tc", "gemm_tc_fold")) / iters
+    tc_ms = sum(v["ms"] for k, v in prof.items() if k == "gemm_tc") / iters
     res = {"workload": "config 4: 4096 tokens x top-8 of 128 experts, hidden 2048, expert FFN 768, Q4_K",
            "ms_per_pass": ms, "tokens_per_s": T / (ms * 1e-3), "tops": ops / (ms * 1e-3) / 1e12,
            "grouped_gemm_ms_per_pass": tc_ms, "grouped_gemm_tops": ops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else None,
@@ -263,6 +289,7 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
            "expert_load": {"max": int(c.max()), "min": int(c.min()), "mean": float(c.mean())},
            "kernel_ms_per_pass": {k: v["ms"] / iters for k, v in prof.items()},
            "finite": bool(torch.isfinite(out).all().item())}
+    res.update(parity())
     for W in (Wg, Wu, Wd):
         W.close()
     return res
@@ -296,17 +323,92 @@ def q8_config1_section(izb, torch, tc_peak: float, iters: int = 20) -> dict:
             "note": "128 tiles on 148 SMs: a single partial wave, host launch cost included"}
 
 
+def tp_stack_parity(st, torch, dist, x_in) -> dict:
+    """One teacher-forced layer of the stack on sampled token rows against the CPU oracle (checker only, outside every
+    timed region): each projection from the GPU's own quantised input, the sums from all ranks' partial outputs in rank
+    order, the quantiser bit for bit, and a checksum of the quantised stream that must be equal on all ranks."""
+    from arcinferzero_b200 import tp
+    from oracle import oracle as O
+    cfg, world, rank = st.cfg, st.world, st.rank
+    QT, E = cfg.qtype, cfg.hidden
+    st.set_input(x_in)
+    trace = []
+    st.forward(trace, layers=1)
+    torch.cuda.synchronize()
+    t = trace[0]
+    # the same sample on every rank: two rows of every rank's share of the first and of the last chunk
+    own = st.Tc // world
+    idx = np.array(sorted({c * st.Tc + r * own + o for c in (0, st.chunks - 1) for r in range(world) for o in (0, own - 1)}))
+    mine = np.intersect1d(idx, st.owned_rows())
+    g = lambda k: t[k][torch.from_numpy(idx).to(t[k].device)].cpu().numpy()  # noqa: E731
+    sh = tp.shard_rows(cfg, tp.layer_weights(cfg, 0), st.plan)
+    nq = st.plan.q[1] - st.plan.q[0]
+    rels, exact = {}, True
+    xq0, xsc0 = g("xq0"), np.ascontiguousarray(t["xsc0"][:, torch.from_numpy(idx).to(t["xsc0"].device)].cpu().numpy())
+    qkv = g("qkv")
+    rels["qkv"] = _rel(qkv, O.matmul(QT, sh["qkv"][0], E, xq0, xsc0, len(idx)))
+    hq, hsc, _ = O.quantize_act(np.ascontiguousarray(qkv[:, :nq]))
+    rows, _, Kk, cr = sh["o"]
+    o_part = g("o_part")
+    rels["o_part"] = _rel(o_part, O.matmul(QT, tp.slice_cols(QT, rows, Kk, *cr), nq, hq, hsc, len(idx)))
+
+    def all_parts(a):
+        tt = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        if world == 1:
+            return a[None]
+        out = [torch.empty_like(tt) for _ in range(world)]
+        dist.all_gather(out, tt)
+        return np.stack([o.cpu().numpy() for o in out])
+
+    sel = np.searchsorted(idx, mine)
+    x1 = g("x1")
+    rels["x1"] = _rel(x1[sel], O.tp_add(g("x0"), all_parts(o_part))[sel])
+    xq1 = g("xq1")
+    xsc1 = np.ascontiguousarray(t["xsc1"][:, torch.from_numpy(idx).to(t["xsc1"].device)].cpu().numpy())
+    rq, rs, _ = O.quantize_act(np.ascontiguousarray(x1[sel]))
+    exact &= bool(np.array_equal(xq1[sel], rq) and np.array_equal(xsc1[:, sel].view(np.uint32), rs.view(np.uint32)))
+    gate = O.matmul(QT, sh["gate"][0], E, xq1, xsc1, len(idx))
+    up = O.matmul(QT, sh["up"][0], E, xq1, xsc1, len(idx))
+    h = g("h")
+    rels["h"] = _rel(h, (up * (gate / (np.float32(1) + np.exp(-gate, dtype=np.float32)))).astype(np.float32))
+    hq, hsc, _ = O.quantize_act(h)
+    rows, _, Kk, cr = sh["down"]
+    d_part = g("down_part")
+    rels["down_part"] = _rel(d_part, O.matmul(QT, tp.slice_cols(QT, rows, Kk, *cr), cr[1] - cr[0], hq, hsc, len(idx)))
+    rels["x2"] = _rel(g("x2")[sel], O.tp_add(x1, all_parts(d_part))[sel])
+    # the quantised stream every rank holds must be the same bytes
+    chk = torch.stack([t["xq2"].view(torch.int64).sum(), t["xsc2"].view(torch.int32).to(torch.int64).sum(),
+                       t["xq1"].view(torch.int64).sum(), t["xsc1"].view(torch.int32).to(torch.int64).sum()])
+    same = True
+    if world > 1:
+        allc = [torch.empty_like(chk) for _ in range(world)]
+        dist.all_gather(allc, chk)
+        same = all(bool(torch.equal(allc[0], c)) for c in allc[1:])
+    worst = torch.tensor([max(rels.values()), 0.0 if exact else 1.0, 0.0 if same else 1.0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {"parity_max_rel": float(worst[0].item()), "parity_tolerance": 1e-5, "parity_by_stage_rank0": rels,
+            "int8_rows_exact": worst[1].item() == 0.0, "int8_identical_across_ranks": worst[2].item() == 0.0,
+            "parity_rows_sampled": int(len(idx))}
+
+
 def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens: int, passes: int = 2) -> list:
     """BASELINE.json config 5: the projections of 8 dense layers (Q4_K, hidden 5120, FFN 17408, 7168 QKV rows) over 32768
-    token rows, split over the ranks as the reference's tensor-parallel mode splits them, in both summation modes of
-    arcinferzero_b200/tp.py.  Device-timed per pass, max over ranks."""
+    token rows, split over the ranks as the reference's tensor-parallel mode splits them.  Three forms of
+    arcinferzero_b200/tp.py: the two summation modes with everything on one stream, and the pipelined form (token chunks,
+    the sums of one chunk on a second stream beside the GEMMs of the next, Q rows balanced against the FFN rows).
+    Device-timed per pass, max over ranks; each entry carries the parity of one teacher-forced layer."""
     from arcinferzero_b200 import synth as S
     from arcinferzero_b200 import tp
     cfg = tp.StackConfig(tokens=tokens)
     x_in = torch.from_numpy(S.make_act(cfg.tokens, cfg.hidden, SEED + 5)).cuda() * 0.05
     out = []
-    for mode in ("allreduce", "rs_quant_ag"):
-        st = tp.Stack(cfg, world, rank, local, mode=mode, distinct_layers=False)
+    forms = [("allreduce", dict()), ("rs_quant_ag", dict()),
+             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8))]
+    if world == 1:
+        forms = forms[1:]  # (one rank: both summation modes are the same work)
+    for mode, kw in forms:
+        st = tp.Stack(cfg, world, rank, local, mode=mode, distinct_layers=False, **kw)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ms = 0.0
         l0 = 0
@@ -328,12 +430,16 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_pass = float(t.item())
-        finite = bool(torch.isfinite(st.x[rank * (cfg.tokens // world):(rank + 1) * (cfg.tokens // world)]).all().item())
+        own = torch.from_numpy(st.owned_rows()).cuda()
+        finite = bool(torch.isfinite(st.x[own]).all().item())
         nbytes = cfg.tokens * cfg.hidden * 4
-        out.append({"mode": mode, "ms_per_pass": ms_pass, "tokens_per_s": cfg.tokens / (ms_pass * 1e-3),
-                    "tops_all_ranks": cfg.ops_per_pass / (ms_pass * 1e-3) / 1e12, "sums_per_pass": 2 * cfg.layers,
-                    "bytes_per_sum_f32": nbytes, "gpu_launches_per_pass": launches // passes, "finite": finite,
-                    "workload": f"config 5: {cfg.layers} layers x (QKV 7168, O, gate, up, down) Q4_K, T={cfg.tokens}, hidden 5120, FFN 17408"})
+        entry = {"mode": mode + ("+overlap" if kw else ""), "form": kw or {"chunks": 1, "overlap": False, "balance": False},
+                 "ms_per_pass": ms_pass, "tokens_per_s": cfg.tokens / (ms_pass * 1e-3),
+                 "tops_all_ranks": cfg.ops_per_pass / (ms_pass * 1e-3) / 1e12, "sums_per_pass": 2 * cfg.layers,
+                 "bytes_per_sum_f32": nbytes, "gpu_launches_per_pass": launches // passes, "finite": finite,
+                 "workload": f"config 5: {cfg.layers} layers x (QKV 7168, O, gate, up, down) Q4_K, T={cfg.tokens}, hidden 5120, FFN 17408"}
+        entry.update(tp_stack_parity(st, torch, dist, x_in))
+        out.append(entry)
         st.close()
         del st
         torch.cuda.empty_cache()
@@ -371,8 +477,7 @@ def main() -> None:
     ap.add_argument("--moe-only", action="store_true", help="profiling only: run just the MoE section")
     ap.add_argument("--gemv-only", action="store_true", help="profiling only: run just the decode GEMV section")
     ap.add_argument("--lite", action="store_true", help="profiling only: few launches per GEMV shape")
-    ap.add_argument("--tp-stack", action="store_true", help="also run the tensor-parallel projection stack (config 5); default when --gpus > 1")
-    ap.add_argument("--no-tp-stack", action="store_true")
+    ap.add_argument("--no-tp-stack", action="store_true", help="skip the tensor-parallel projection stack (BASELINE.json config 5)")
     ap.add_argument("--tp-tokens", type=int, default=32768, help="profiling only: token rows of the stack section")
     ap.add_argument("--tokens", type=int, default=M, help="profiling only: fewer token rows than the configured 8192")
     args = ap.parse_args()
@@ -476,18 +581,26 @@ def main() -> None:
     ms_e2e = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
     tp_stack = None
-    if (args.tp_stack or world > 1) and not args.no_tp_stack:
+    if not args.no_tp_stack:
         W.close()
         del x, aq, asc, out
         torch.cuda.empty_cache()
         tp_stack = tp_stack_section(izb, torch, dist, world, rank, local, args.tp_tokens)
+    # the device's own tensor-core rates: a TMEM-resident tcgen05.mma loop per MMA kind, a short burst and ~0.5 s sustained
+    tc_peaks = None
+    if rank == 0:
+        tc_peaks = {}
+        for name, kind in (("f16", 0), ("i8", 1)):
+            burst, clk = izb.tensor_peak(local, kind, 4096, 2)
+            sus, _ = izb.tensor_peak(local, kind, 4096, 400 if kind == 0 else 800)
+            tc_peaks[name] = {"burst_tops": burst, "sustained_tops": sus, "sm_clocks_per_128x256_mma": clk}
     status = izb.device_status(local)
 
     if rank == 0:
         hbm, tc_burst, tc_sus, src = peaks()
-        kname = next((k for k in ("gemm_tc_fold", "gemm_tc", "gemm_core") if k in prof), "gemm_tc")
+        kname = next((k for k in ("gemm_tc", "gemm_core") if k in prof), "gemm_tc")
         g = prof.get(kname) or {"launches": 0, "ms": 0.0}
-        per_tile = NCU_TRAFFIC_BYTES_PER_TILE_FOLD if kname == "gemm_tc_fold" else NCU_TRAFFIC_BYTES_PER_TILE
+        per_tile = NCU_TRAFFIC_BYTES_PER_TILE
         ms_kernel = g["ms"] / max(1, g["launches"])
         ops = 2.0 * M * Nr * K
         achieved = ops / (ms_kernel * 1e-3) / 1e12 if ms_kernel > 0 else 0.0
@@ -499,10 +612,7 @@ def main() -> None:
             "dtype": "int8",
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
-                       "arithmetic": ("int8 x 4-bit dot products on the tensor cores (kind::f16, f32 TMEM accumulators): activations with "
-                                      "their block scale as an fp16 pair hi + lo, weights sc*q as exact fp16 integers, one accumulator per "
-                                      "superblock" if kname == "gemm_tc_fold" else
-                                      "exact integer dot products per 32-block (int8 x 4-bit; operands fed to the tensor cores as fp16 "
+                       "arithmetic": ("exact integer dot products per 32-block (int8 x 4-bit; operands fed to the tensor cores as fp16 "
                                       "holding exact integers, f32 TMEM accumulators), f32 combine"),
                        "parallelism": f"weight rows split over {world} rank(s), no exchange",
                        "l2": "per step 168 MB of f32 activations in and 570 MB of outputs written: larger than the 126 MB L2",
@@ -510,8 +620,10 @@ def main() -> None:
             "roofline": {"bound": "tensor", "kernel": kname, "achieved": achieved, "peak": tc_sus, "unit": "TFLOP/s",
                          "frac": achieved / tc_sus, "peak_source": f"{src} dense bf16/fp16 (sustained; burst {tc_burst})",
                          "frac_of_burst_peak": achieved / tc_burst, "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS,
+                         "frac_of_measured_int8": achieved / tc_peaks["i8"]["burst_tops"], "frac_of_measured_f16_mma": achieved / tc_peaks["f16"]["burst_tops"],
+                         "measured_tcgen05_peaks": dict(tc_peaks, method="izb_tensor_peak: tcgen05.mma 128x256 loop, operands in shared memory, accumulators in TMEM, all SMs"),
                          # DRAM bytes per launch: one ncu capture of the same kernel at 2048 token rows and all weight rows
-                         # (read 128.8 MB + written 114.2 MB), scaled by the 128x128 tiles this launch runs
+                         # (read 132.1 MB + written 116.6 MB), scaled by the 128x128 tiles this launch runs
                          "traffic": per_tile * ((M + 127) // 128) * (Nr // 128),
                          "traffic_source": f"ncu dram__bytes_read+write of {kname} at M=2048, N=17408 (profiles/), per 128x128 tile x tiles",
                          "ms_per_launch": ms_kernel, "launches": g["launches"],

@@ -83,6 +83,17 @@ int izb_device_status(int device, uint32_t* word);
  * so that none of those calls allocates or synchronises later (the arenas are what Engine::alloc_buffers sizes once in
  * the reference, zero/engine_alloc.h:10-41).  Synchronous; may be called again with larger sizes. */
 int izb_reserve(int device, int max_rows, int max_K);
+/* The tensor-core GEMM is a persistent kernel with one CTA per multiprocessor.  A host that wants another kernel to be
+ * resident beside it -- the collective of the previous token chunk's tensor-parallel sum, as the reference overlaps its
+ * sums with the next chunk's GEMMs (TpOverlap, zero/mgpu/engine_tp.h:126-151) -- caps the grid at `sms` multiprocessors
+ * (0 = all).  Per device; takes effect from the next launch. */
+int izb_set_sm_limit(int device, int sms);
+/* Measured tensor-core rate of `device` (which must be current): `launches` back-to-back launches of a kernel that issues
+ * iters x 4 tcgen05.mma of 128 x 256 x (16 | 32) per multiprocessor on operands resident in shared memory and accumulators
+ * resident in TMEM, timed with CUDA events.  kind 0 = kind::f16 (f32 accumulation), 1 = kind::i8 (s32 accumulation).
+ * *tops = 2*M*N*K operations per second / 1e12; *clk_per_mma (may be NULL) = SM clocks per instruction on one
+ * multiprocessor.  The method of the reference's own peak probe (bench/gpu_bench.cpp:10-15).  Synchronous. */
+int izb_tensor_peak(int device, int kind, int iters, int launches, double* tops, double* clk_per_mma);
 /* Diagnostics: the NEXT tensor-core GEMM launch of this process gives up its bounded device-side waits after spin_limit
  * polls (0 = the default) and its activation producer leaves out operand stage `skip_stage` (-1 = none), so that the
  * waits for that stage run out: the kernel drains, stores nothing for the affected tiles and reports through
@@ -102,6 +113,9 @@ int izb_weight_create_slice(int ggml_type, const void* h_gguf_rows, int n_mats, 
                             int device, izb_weight** out);
 void izb_weight_destroy(izb_weight* w);
 int izb_weight_info(const izb_weight* w, int* ggml_type, int* n_mats, int* N, int* K, size_t* device_bytes);
+/* Copies `bytes` of the device form back, from byte `offset` (rows of K/256 superblocks of 144 (Q4_K) or 272 (Q8_0) bytes,
+ * matrix-major): lets a host check the layout against the reference's gpu_raw_sb (src/quants.h:728-751).  Synchronous. */
+int izb_weight_download(const izb_weight* w, size_t offset, size_t bytes, void* h_out);
 
 /* ------------------------------------------------------------------------------------------------ activations
  * Replaces Engine::quant_rows (zero/engine.h:1445) = ops.cl quant_store16 (zero/kernels/ops.cl:38-72); bit-exact with
@@ -226,6 +240,18 @@ int izb_tp_add(float* d_x, const float* d_parts, size_t n, int np, size_t stride
  * 0, distributed by the caller. */
 int izb_tp_unique_id(void* id128);
 int izb_tp_create(int nranks, int rank, const void* id128, int device, izb_tp** out);
+/* The same with failure detection and a cap on the collectives' CTAs.  timeout_ms > 0 makes the communicator
+ * non-blocking: creation and every collective call is followed by a wait of at most timeout_ms for NCCL's answer
+ * (ncclCommGetAsyncError), after which the communicator is aborted and the call returns IZB_ERR_TIMEOUT (the reference
+ * bounds every barrier and wait of its transport likewise, zero/mgpu/engine_tp.h:93-123).  max_ctas > 0 limits the CTAs a
+ * collective may use (ncclConfig_t.maxCTAs), which leaves multiprocessors to a GEMM running beside it.  0, 0 = izb_tp_create. */
+int izb_tp_create_ex(int nranks, int rank, const void* id128, int device, int timeout_ms, int max_ctas, izb_tp** out);
+/* Bounded host wait for everything queued on `stream` (wait_done, zero/mgpu/engine_tp.h:1313-1372): returns IZB_OK when it
+ * has finished; after timeout_ms, or when NCCL reports an asynchronous error, aborts the communicator -- which also ends
+ * this rank's collectives that are waiting on the device for a missing peer -- and returns IZB_ERR_TIMEOUT / IZB_ERR_NCCL.
+ * An aborted communicator refuses further collectives; destroy it and create a new one with the surviving ranks. */
+int izb_tp_wait(izb_tp* tp, void* stream, int timeout_ms);
+int izb_tp_abort(izb_tp* tp);
 void izb_tp_destroy(izb_tp* tp);
 /* tp_out's sum (zero/mgpu/engine_tp_shard.h:318-325, tp_reduce_at zero/mgpu/engine_tp.h:272): d_x[rows][E] += sum over
  * ranks of d_part (f32 all-reduce over NVLink; d_part is overwritten with the sum). */

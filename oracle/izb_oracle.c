@@ -14,6 +14,14 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#include <omp.h>
+
+/* Worker threads of the loops below (a launcher may have exported OMP_NUM_THREADS=1: the benchmark's CPU baseline sets
+ * the count it reports). */
+void orc_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+int orc_max_threads(void) { return omp_get_max_threads(); }
 
 #define ORC_Q8_0 8
 #define ORC_Q4_K 12

@@ -60,6 +60,13 @@ def ref():
     return _ref
 
 
+def set_threads(n: int) -> int:
+    """OpenMP threads of the restatement's loops (and of oracle/_ref's, which shares the process's OpenMP runtime when
+    ref_forward_matmul is given no count of its own); returns the count now in force."""
+    lib().orc_set_threads(int(n))
+    return int(lib().orc_max_threads())
+
+
 def _vp(a):
     return a.ctypes.data_as(C.c_void_p)
 
@@ -280,3 +287,19 @@ def ref_forward_matmul(gguf_path: str, name: str, x: np.ndarray, N: int, quant32
     if rc != 0:
         raise RuntimeError("ref_forward_matmul failed")
     return y
+
+
+def ref_expert_mv(gguf_path: str, name: str, e: int, N: int, K: int, x: np.ndarray, quant32: bool = True) -> np.ndarray:
+    """tools/ref_forward.cpp expert_mv() (:333) on expert e of the stacked tensor `name`.weight; x [K] f32 -> y [N] f32."""
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty(N, np.float32)
+    if ref().ref_expert_mv(gguf_path.encode(), name.encode(), e, N, K, _vp(x), _vp(y), int(quant32)) != 0:
+        raise RuntimeError("ref_expert_mv failed")
+    return y
+
+
+def ref_silu(x: np.ndarray) -> np.ndarray:
+    """tools/ref_forward.cpp silu() (:321) element by element."""
+    f = ref().ref_silu
+    f.restype, f.argtypes = C.c_float, [C.c_float]
+    return np.array([f(float(v)) for v in np.asarray(x, np.float32).ravel()], np.float32).reshape(np.shape(x))

@@ -11,6 +11,16 @@
 #include "tools/ref_forward.cpp"
 #undef main
 
+// the GGUF file the reference's global handle F is open on
+static std::string g_open_path;
+static void open_gguf(const char* path) {
+  if (!F || g_open_path != path) {
+    delete F;
+    F = new GgufFile(path);
+    g_open_path = path;
+  }
+}
+
 extern "C" {
 
 float ref_fp16_to_f32(uint16_t h) { return fp16_to_f32(h); }
@@ -47,12 +57,7 @@ int ref_forward_matmul(const char* path, const char* name, const float* X, int T
     if (quant32) { setenv("REF_Q", "all", 1); setenv("REF_QB", "32", 1); }
     else unsetenv("REF_Q");
     if (threads > 0) omp_set_num_threads(threads);
-    static std::string open_path;
-    if (!F || open_path != path) {
-      delete F;
-      F = new GgufFile(path);
-      open_path = path;
-    }
+    open_gguf(path);
     const GgufTensor& t = F->get(name);
     const int K = (int)t.dims[0];
     std::vector<float> x(X, X + (size_t)T * K), y;
@@ -64,6 +69,25 @@ int ref_forward_matmul(const char* path, const char* name, const float* X, int T
     return -1;
   }
 }
+
+// tools/ref_forward.cpp:333 expert_mv(): y[N] = W_e x for routed expert e of the stacked tensor `name`.weight
+// ([n_expert][N][K], dequantised row by row, double accumulation); with quant32 the input is rounded to int8 per 32 first
+// (REF_Q=all REF_QB=32), as the engine's moe_quant / quant_rows round it.
+int ref_expert_mv(const char* path, const char* name, int e, int N, int K, const float* x, float* y, int quant32) {
+  try {
+    if (quant32) { setenv("REF_Q", "all", 1); setenv("REF_QB", "32", 1); }
+    else unsetenv("REF_Q");
+    open_gguf(path);
+    expert_mv(name, e, N, K, x, y);
+    return 0;
+  } catch (const std::exception& ex) {
+    fprintf(stderr, "ref_expert_mv: %s\n", ex.what());
+    return -1;
+  }
+}
+
+// tools/ref_forward.cpp:321
+float ref_silu(float x) { return silu(x); }
 
 int ref_max_threads() { return omp_get_max_threads(); }
 }

@@ -8,6 +8,15 @@ What is stored (all inputs seeded; every array small):
   forward.npz    tools/ref_forward.cpp:251 matmul() outputs (REF_Q=all REF_QB=32) on small Q4_K / Q8_0 tensors
   rawsb.npz      gpu_raw_sb (src/quants.h:728) of Q8_0 superblocks: the regrouped form the weight loader must make
   rmsnorm.npz    tools/ref_forward.cpp:314 rmsnorm() rows (double-precision sum of squares)
+  moe.npz        the reference's CPU mixture-of-experts block (tools/ref_forward.cpp:1660-1690): expert_mv() (:333) outputs of
+                 the gate / up / down projections of routed experts, silu() (:321), and the routing of seeded logits.
+                 expert_mv and silu are the reference's functions, called through oracle/_ref; the routing lines
+                 (:1668-1676) sit inside its forward loop and cannot be called alone, so they are followed here step by
+                 step in numpy: stable descending sort (ties keep the lower expert first), exp(l - l_max) in double,
+                 normalised over the chosen NU, cast to float.
+
+    python tests/golden/make_golden.py            # everything
+    python tests/golden/make_golden.py moe        # only moe.npz (leaves the other files untouched)
 """
 import os
 import sys
@@ -23,9 +32,57 @@ from oracle import oracle as O  # noqa: E402
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
+def make_moe():
+    rng = np.random.default_rng(20261201)
+    # ---- routing (tools/ref_forward.cpp:1668-1676): 128 experts, top 8, with planted ties
+    T, NE, NU = 48, 128, 8
+    lg = rng.standard_normal((T, NE), dtype=np.float32)
+    lg[0, :] = 0.25                                   # every logit equal: experts 0..7 in order
+    lg[1, 100:108] = lg[1].max() + np.float32(1.0)    # an eight-way tie at the top, high ids
+    lg[2, [5, 90]] = lg[2].max() + np.float32(0.5)    # a two-way tie for the first place
+    lg[3, 17] = np.float32(30.0)                      # one dominant expert: tiny weights for the rest
+    lg[4, :] = np.round(lg[4] * 2) / 2                # many ties at all ranks
+    lg[5, 7] = np.float32(-0.0)
+    lg[5, 3] = np.float32(0.0)                        # +0 and -0 compare equal: a tie
+    ids = np.empty((T, NU), np.int32)
+    wts = np.empty((T, NU), np.float32)
+    for t in range(T):
+        order = np.argsort(-lg[t].astype(np.float64), kind="stable")  # std::stable_sort with l[a] > l[b]
+        sel = order[:NU]
+        p = np.exp(lg[t, sel].astype(np.float64) - np.float64(lg[t, sel[0]]))
+        ids[t] = sel
+        wts[t] = (p / p.sum()).astype(np.float32)
+    # ---- expert projections: expert_mv on stacked Q4_K tensors, inputs rounded to int8 per 32 (REF_Q=all REF_QB=32)
+    NEs, E, F = 3, 256, 256
+    wg = S.make_weight(S.GGML_Q4_K, NEs * F, E, 31)
+    wu = S.make_weight(S.GGML_Q4_K, NEs * F, E, 32)
+    wd = S.make_weight(S.GGML_Q4_K, NEs * E, F, 33)
+    x = rng.standard_normal((5, E), dtype=np.float32)
+    pairs = np.array([(0, 0), (0, 2), (1, 1), (2, 0), (3, 2), (4, 1), (4, 2)], np.int32)  # (token, expert)
+    g = np.empty((len(pairs), F), np.float32)
+    u = np.empty_like(g)
+    h = np.empty_like(g)
+    dn = np.empty((len(pairs), E), np.float32)
+    with tempfile.TemporaryDirectory() as d:
+        p = os.path.join(d, "moe.gguf")
+        S.write_gguf(p, {"blk.0.ffn_gate_exps.weight": (12, wg, F, E, NEs), "blk.0.ffn_up_exps.weight": (12, wu, F, E, NEs),
+                         "blk.0.ffn_down_exps.weight": (12, wd, E, F, NEs)})
+        for i, (t, e) in enumerate(pairs):
+            g[i] = O.ref_expert_mv(p, "blk.0.ffn_gate_exps", int(e), F, E, x[t])
+            u[i] = O.ref_expert_mv(p, "blk.0.ffn_up_exps", int(e), F, E, x[t])
+            h[i] = O.ref_silu(g[i]) * u[i]
+            dn[i] = O.ref_expert_mv(p, "blk.0.ffn_down_exps", int(e), E, F, h[i])
+    np.savez_compressed(os.path.join(OUT, "moe.npz"), logits=lg, ids=ids, wts=wts, wg=wg, wu=wu, wd=wd, x=x, pairs=pairs,
+                        g=g, u=u, h=h, dn=dn)
+
+
 def main():
     O.build(ref=True)
     assert O.ref() is not None, "oracle/_ref/libizb_ref.so missing: the reference sources are needed"
+    if sys.argv[1:] == ["moe"]:
+        make_moe()
+        print("moe.npz written to", OUT)
+        return
     rng = np.random.default_rng(20261125)
 
     # ---- quantize
@@ -87,6 +144,7 @@ def main():
     wn = (1.0 + 0.1 * r2.standard_normal(1024)).astype(np.float32)
     yn = O.ref_rmsnorm(xn, wn, 1e-6)
     np.savez_compressed(os.path.join(OUT, "rmsnorm.npz"), x=xn, w=wn, eps=np.float32(1e-6), y=yn)
+    make_moe()
     print("golden vectors written to", OUT)
 
 

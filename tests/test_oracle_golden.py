@@ -199,3 +199,61 @@ def test_softcap_rows_oracle_against_the_formula_in_double():
         keep = np.ones_like(c, dtype=bool)
         keep[:rows, off:off + N] = False
         assert (out[keep] == c[keep]).all()
+
+
+def test_moe_routing_matches_reference_rule_vectors(golden_dir):
+    """moe.npz: ids and weights by the rule of tools/ref_forward.cpp:1668-1676 (stable descending sort, double exp,
+    renormalised over the choice): the restated moe_route (zero/kernels/moe.cl:50-89) must choose the same experts in the
+    same order (ties, +0 / -0 included) and weigh them within 1e-6."""
+    g = np.load(os.path.join(golden_dir, "moe.npz"))
+    ids, wts, counts = O.moe_route(g["logits"], g["ids"].shape[1])
+    assert (ids == g["ids"]).all(), np.argwhere(ids != g["ids"])[:5]
+    assert np.abs(wts.astype(np.float64) - g["wts"]).max() <= 1e-6
+    assert (counts == np.bincount(g["ids"].ravel(), minlength=g["logits"].shape[1])).all()
+
+
+def test_moe_expert_projections_match_reference_vectors(golden_dir):
+    """moe.npz: gate / up / down of routed experts from the reference's expert_mv() (tools/ref_forward.cpp:333, inputs
+    rounded to int8 per 32, dequantised weights, double sums) and its silu() (:321).  The restated integer path
+    (decode_moe.cl moe_gateup_q / moe_down_q) must agree within 1e-5 of max|ref|, stage by stage: the down projection is
+    fed the golden h, as the reference fed it."""
+    g = np.load(os.path.join(golden_dir, "moe.npz"))
+    E, F = g["x"].shape[1], g["g"].shape[1]
+    pairs = g["pairs"]
+    tok, exp_ = np.ascontiguousarray(pairs[:, 0]), np.ascontiguousarray(pairs[:, 1])
+    aq, asc, _ = O.quantize_act(g["x"])
+    h, gg, uu = O.moe_gateup(12, g["wg"], g["wu"], F, E, aq, asc, exp_, tok, want_gu=True)
+    for got, ref, name in ((gg, g["g"], "gate"), (uu, g["u"], "up"), (h, g["h"], "h")):
+        assert np.abs(got.astype(np.float64) - ref).max() <= 1e-5 * np.abs(ref).max(), name
+    hq, hsc, _ = O.quantize_act(g["h"])
+    one = np.ones(len(pairs), np.float32)
+    y = O.moe_down(12, g["wd"], E, F, hq, hsc, exp_, one)
+    assert np.abs(y.astype(np.float64) - g["dn"]).max() <= 1e-5 * np.abs(g["dn"]).max()
+
+
+def test_moe_golden_is_what_the_live_reference_computes(golden_dir):
+    if O.ref() is None:
+        pytest.skip("oracle/_ref not built (needs the reference sources)")
+    g = np.load(os.path.join(golden_dir, "moe.npz"))
+    E, F = g["x"].shape[1], g["g"].shape[1]
+    with tempfile.TemporaryDirectory() as d:
+        p = os.path.join(d, "moe.gguf")
+        S.write_gguf(p, {"blk.0.ffn_gate_exps.weight": (12, g["wg"], F, E, 3), "blk.0.ffn_down_exps.weight": (12, g["wd"], E, F, 3)})
+        t, e = (int(v) for v in g["pairs"][1])
+        assert (bits(O.ref_expert_mv(p, "blk.0.ffn_gate_exps", e, F, E, g["x"][t])) == bits(g["g"][1])).all()
+        assert (bits(O.ref_expert_mv(p, "blk.0.ffn_down_exps", e, E, F, g["h"][1])) == bits(g["dn"][1])).all()
+    assert (bits(O.ref_silu(g["g"][1]) * g["u"][1]) == bits(g["h"][1])).all()
+
+
+def test_q8_0_regrouped_device_form_matches_reference_vectors(golden_dir):
+    """rawsb.npz: gpu_raw_sb (src/quants.h:728-751) of the Q8_0 superblocks of decode.npz: eight fp16 scales, then the
+    eight blocks' int8 values.  The restated regrouping (what the weight loader's kernel does on the device) in numpy."""
+    g = np.load(os.path.join(golden_dir, "decode.npz"))
+    raw = np.load(os.path.join(golden_dir, "rawsb.npz"))["raw8"]
+    i = 0
+    for n in range(6):
+        for s in range(2):
+            blocks = g["w8"][n, 272 * s:272 * (s + 1)].reshape(8, 34)
+            want = np.concatenate([blocks[:, :2].reshape(-1), blocks[:, 2:].reshape(-1)])
+            assert (raw[i][:272] == want).all()
+            i += 1

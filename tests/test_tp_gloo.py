@@ -195,6 +195,24 @@ def test_config5_plan_is_aligned_for_all_world_sizes():
     assert [tp.shard_plan(cfg, 8, r).ffn[1] - tp.shard_plan(cfg, 8, r).ffn[0] for r in range(8)] == [2304] * 4 + [2048] * 4
 
 
+def test_balanced_plan_moves_the_extra_q_units_to_the_last_ranks():
+    cfg = tp.StackConfig()
+    for total, unit in ((5120, 256), (17408, 256), (1024, 128)):
+        for n in (1, 2, 3, 4, 8):
+            got = [tp.tp_range_tail(total, unit, n, r) for r in range(n)]
+            assert got[0][0] == 0 and got[-1][1] == total // unit * unit
+            assert all(got[i][1] == got[i + 1][0] for i in range(n - 1))
+            sizes = [e - b for b, e in got]
+            assert sorted(sizes) == sizes and max(sizes) - min(sizes) <= unit  # the larger shards come last
+            assert sorted(sizes) == sorted(e - b for b, e in (tp.tp_range(total, unit, n, r) for r in range(n)))
+    # config 5 at 8 ranks, work in units of 256 rows (2 per Q unit for QKV + O, 3 per FFN unit): 33 : 28 becomes 31 : 30
+    def work(p):
+        return 2 * (p.q[1] - p.q[0]) // 256 + 3 * (p.ffn[1] - p.ffn[0]) // 256
+    plain = [work(tp.shard_plan(cfg, 8, r)) for r in range(8)]
+    even = [work(tp.shard_plan(cfg, 8, r, balance=True)) for r in range(8)]
+    assert (max(plain), min(plain)) == (33, 28) and (max(even), min(even)) == (31, 30) and sum(plain) == sum(even)
+
+
 def test_slice_cols_rejects_partial_superblocks():
     w = S.make_weight(S.GGML_Q4_K, 4, 512, 1)
     assert tp.slice_cols(S.GGML_Q4_K, w, 512, 256, 512).shape == (4, 144)

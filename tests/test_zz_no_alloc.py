@@ -26,6 +26,7 @@ def test_noalloc_gemm_matches_gemm_on_two_calls_in_a_row(izb, qt):
     w = S.make_weight(qt, N, K, 40 + qt)
     W = izb.Weight(qt, w, N, K)
     status = torch.full((1,), 123, dtype=torch.int32, device="cuda")  # garbage: the call must clear it
+    free_after_warmup = None
     # two calls in a row on different shapes and data: the second must not see anything of the first in the shared array
     for call, (M, seed) in enumerate(((300, 1), (130, 2))):
         Mp = izb.pad_rows(M)
@@ -45,6 +46,20 @@ def test_noalloc_gemm_matches_gemm_on_two_calls_in_a_row(izb, qt):
         base = torch.ones((Mp, N), dtype=torch.float32, device="cuda")
         izb.gemm_noalloc(W, aq, asc, M=M, out=base, acc=1)
         assert rel(base.cpu().numpy()[:M] - 1.0, ref[:M]) < 1e-4
+        assert izb.device_status(0) == 0  # (covers the library-owned status word of the call above)
+        # The first round was the warm-up (the CUDA runtime loads a kernel's code at its first launch); from then on the
+        # entry point must leave the device's free memory exactly as it found it.
+        torch.cuda.synchronize()
+        if free_after_warmup is None:
+            free_after_warmup = torch.cuda.mem_get_info()[0]
+        else:
+            out2 = torch.empty((Mp, N), dtype=torch.float32, device="cuda")
+            torch.cuda.synchronize()
+            before = torch.cuda.mem_get_info()[0]
+            for _ in range(3):
+                izb.gemm_noalloc(W, aq, asc, M=M, out=out2, status=status)
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == before
     W.close()
 
 

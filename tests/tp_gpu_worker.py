@@ -35,20 +35,21 @@ def gather(t, world):
     return [o.cpu().numpy() for o in out]
 
 
-def check_mode(mode: str, world: int, rank: int, device: int) -> None:
+def check_mode(mode: str, world: int, rank: int, device: int, chunks: int = 1, overlap: bool = False, balance: bool = False) -> None:
     import torch
     n = max(2, world)  # every rank gets at least one 256-wide unit of each split dimension
-    cfg = tp.StackConfig(layers=2, tokens=256, hidden=512, q_rows=256 * n, kv_rows=128 * n, ffn=256 * max(4, world), seed=4242)
+    # (with balance the Q rows do not divide evenly: the extra units must land on the last ranks and still add up)
+    cfg = tp.StackConfig(layers=2, tokens=256, hidden=512, q_rows=256 * n + (256 if balance else 0), kv_rows=128 * n,
+                         ffn=256 * max(4, world), seed=4242)
     QT, E, T = cfg.qtype, cfg.hidden, cfg.tokens
-    st = tp.Stack(cfg, world, rank, device, mode=mode)
+    st = tp.Stack(cfg, world, rank, device, mode=mode, chunks=chunks, overlap=overlap, balance=balance, comm_sms=8)
     x_in = (S.make_act(T, E, cfg.seed) * np.float32(0.1)).astype(np.float32)
     st.set_input(torch.from_numpy(x_in).cuda(device))
     trace = []
     st.forward(trace)
     torch.cuda.synchronize()
     plan = st.plan
-    own = T // world
-    mine = slice(rank * own, (rank + 1) * own) if mode == "rs_quant_ag" else slice(0, T)
+    mine = st.owned_rows()
     nq = plan.q[1] - plan.q[0]
     for li, t in enumerate(trace):
         sh = tp.shard_rows(cfg, tp.layer_weights(cfg, li), plan)
@@ -102,6 +103,9 @@ def main() -> int:
         for mode in ("allreduce", "rs_quant_ag"):
             check_mode(mode, world, rank, local)
             print(f"TP_WORKER_OK mode={mode} rank={rank}/{world}", flush=True)
+        # the pipelined form: two token chunks, sums on a second stream beside the next chunk's GEMMs, balanced Q split
+        check_mode("rs_quant_ag", world, rank, local, chunks=2, overlap=True, balance=True)
+        print(f"TP_WORKER_OK mode=rs_quant_ag/overlap rank={rank}/{world}", flush=True)
     finally:
         if world > 1:
             dist.destroy_process_group()

@@ -46,6 +46,14 @@ int izb_get_tc_ok(int device);
 int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C,
                          int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st);
 
+// Build-time experiment switches (defaults = the shipped kernel).
+#ifndef IZB_TC_ELECT
+#define IZB_TC_ELECT 0   // 1: combine warps release accumulators / scale slots with one predicated arrival per warp; 2: the dequantisers too
+#endif
+#ifndef IZB_TC_STRIP
+#define IZB_TC_STRIP 0   // timing diagnostics only: 1 = no combine arithmetic, 2 = no TMEM reads either
+#endif
+
 namespace {
 
 constexpr int BM = 128, BN = 128, KS = 64;
@@ -104,6 +112,11 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// one arrival for the whole warp: a predicated instruction, no branch (the warp must be converged and every lane's work
+// that the arrival publishes must precede it in program order)
+__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, int lane) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar), "r"(lane) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -355,12 +368,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     // Consumers release a buffer with one arrival per THREAD, not per warp: an elected lane costs a divergent branch and a
     // warp barrier per hand-over, which measured 10 % of the kernel.  S_FULL: the activation producer's expect_tx arrival
     // + the 128 dequantiser threads; S_EMPTY: one tcgen05.commit
-    for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), 129); mbar_init(bar(S_EMPTY + i), 1); }
-    for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), 128); }
-    for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), 256); }
+    constexpr int kDeqArr = IZB_TC_ELECT >= 2 ? 4 : 128, kCmbArr = IZB_TC_ELECT >= 1 ? 8 : 256;
+    for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), kDeqArr + 1); mbar_init(bar(S_EMPTY + i), 1); }
+    for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kDeqArr); }
+    for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), kCmbArr); }
     mbar_init(bar(D2_FULL), 1);
-    mbar_init(bar(D2_EMPTY), 256);
-    for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), 256); }
+    mbar_init(bar(D2_EMPTY), kCmbArr);
+    for (int i = 0; i < NASC; ++i) { mbar_init(bar(ASC_FULL + i), 1); mbar_init(bar(ASC_EMPTY + i), kCmbArr); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -542,7 +556,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           }
         }
         fence_proxy_async();
+#if IZB_TC_ELECT >= 2
+        __syncwarp();
+        mbar_arrive_lane0(bar(S_FULL + sbq), threadIdx.x & 31);
+#else
         mbar_arrive(bar(S_FULL + sbq));  // (every thread after its own stores and fence)
+#endif
         if (++sbq == NS) { sbq = 0; pbq ^= 1; }
       }
       if (!ok) break;
@@ -582,10 +601,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         *reinterpret_cast<uint4*>(orow + ((4 ^ (t & 7)) << 4)) = c2;
         *reinterpret_cast<uint4*>(orow + ((5 ^ (t & 7)) << 4)) = c1;
         fence_proxy_async();
+#if IZB_TC_ELECT >= 2
+        __syncwarp();
+        mbar_arrive_lane0(bar(S_FULL + sbq), threadIdx.x & 31);
+#else
         mbar_arrive(bar(S_FULL + sbq));  // (every thread after its own stores and fence)
+#endif
         if (++sbq == NS) { sbq = 0; pbq ^= 1; }
       }
+#if IZB_TC_ELECT >= 2
+      __syncwarp();
+      mbar_arrive_lane0(bar(RAW_EMPTY + rb), threadIdx.x & 31);
+#else
       mbar_arrive(bar(RAW_EMPTY + rb));
+#endif
       if (++rb == NR) { rb = 0; pr ^= 1; }
     }
   } else {
@@ -616,9 +645,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, p.spin_limit, E_EPI)) { ok = false; break; }
         tc_fence_after();
         unsigned long long v[32];
+#if IZB_TC_STRIP >= 2
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = 0ull;
+#else
         tc_ld64_pairs(t_lane + (uint32_t)(d * BN), v);  // the thread's 64 columns of this block; returns when they are in registers
+#endif
         tc_fence_before();
+#if IZB_TC_ELECT >= 1
+        mbar_arrive_lane0(bar(D1_EMPTY + d), lane);  // (the load's wait is warp-wide: every lane has its columns)
+#else
         mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
+#endif
         if (kDots) {
           if (row_ok) {
             int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64) * nb + 8 * s + b;
@@ -628,6 +666,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
               o[(size_t)(2 * c + 1) * nb] = __float2int_rn(hi_f(v[c]));
             }
           }
+        } else if (IZB_TC_STRIP >= 1) {
+          if (b == 7) tq2[0] = v[0];  // (keeps the load alive)
         } else if (QT == IZB_Q4_K) {
           if (b == 0) {
 #pragma unroll
@@ -649,7 +689,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
       if (!ok) break;
       if (!kDots) {  // the superblock's scales are read: its ring slot may be refilled
+#if IZB_TC_ELECT >= 1
+        mbar_arrive_lane0(bar(ASC_EMPTY + sq), lane);
+#else
         mbar_arrive(bar(ASC_EMPTY + sq));
+#endif
         if (++sq == NASC) { sq = 0; pq ^= 1; }
       }
       if (kMins) {  // res += d * tq
@@ -669,7 +713,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         unsigned long long v[32];
         tc_ld64_pairs(t_lane + (uint32_t)(ND1 * BN), v);
         tc_fence_before();
+#if IZB_TC_ELECT >= 1
+        mbar_arrive_lane0(bar(D2_EMPTY), lane);
+#else
         mbar_arrive(bar(D2_EMPTY));  // the next tile's min term may start
+#endif
         const unsigned long long one2 = pack2(1.0f);
 #pragma unroll
         for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);

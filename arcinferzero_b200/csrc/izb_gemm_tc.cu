@@ -47,41 +47,74 @@ int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* 
                          int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st);
 
 // Build-time experiment switches (defaults = the shipped kernel).
-#ifndef IZB_TC_ELECT
-#define IZB_TC_ELECT 0   // 1: combine warps release accumulators / scale slots with one predicated arrival per warp; 2: the dequantisers too
-#endif
 #ifndef IZB_TC_STRIP
 #define IZB_TC_STRIP 0   // timing diagnostics only: 1 = no combine arithmetic, 2 = no TMEM reads either
+#endif
+
+#ifndef IZB_TC_TRACE
+#define IZB_TC_TRACE 0   // diagnostics build: CTA 0 stamps clock64() at the hand-overs of its first blocks into TcParams::trace
+#endif
+#if IZB_TC_TRACE
+#define TRACE(ev, idx)                                                                                      \
+  do {                                                                                                      \
+    if (p.trace && blockIdx.x == 0 && lane == 0 && (idx) >= 0 && (idx) < 2048) p.trace[(ev) * 2048 + (idx)] = clock64(); \
+  } while (0)
+#else
+#define TRACE(ev, idx) do { } while (0)
 #endif
 
 namespace {
 
 constexpr int BM = 128, BN = 128, KS = 64;
-constexpr int NS = 4, ND1 = 3;            // operand stages (activation and weight tile share a ring position), accumulators
+constexpr int ND1 = 3;                    // accumulators of a 32-block in the ring
 constexpr int STAGE_BYTES = BM * KS * 2;  // 16 KB: 128 rows x 128 B
 constexpr int kThreads = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int RAW_Q4 = 128 * 144, RAW_Q8 = 128 * 272;  // 18432, 34816: the raw superblocks of a tile's 128 weight rows
+constexpr int NASC = 3;
+
+// Ring depths.  The two operands of a stage travel through rings of their own: an activation image is a bulk copy from L2
+// whose latency (not its bandwidth) is what has to be covered, so its ring is as deep as shared memory allows; a weight
+// tile is written by the dequantiser warps from a raw tile that is already in shared memory.
+#ifndef IZB_TC_NA4
+#define IZB_TC_NA4 6
+#endif
+#ifndef IZB_TC_NB4
+#define IZB_TC_NB4 4
+#endif
+#ifndef IZB_TC_NR4
+#define IZB_TC_NR4 2
+#endif
+#ifndef IZB_TC_NA8
+#define IZB_TC_NA8 4
+#endif
+#ifndef IZB_TC_NB8
+#define IZB_TC_NB8 4
+#endif
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr int OFF_A = 0;
-constexpr int OFF_B = OFF_A + NS * STAGE_BYTES;      // 65536
-constexpr int OFF_RAW = OFF_B + NS * STAGE_BYTES;    // 131072: ring of raw superblock tiles
-constexpr int RAW_Q4 = 128 * 144, RAW_Q8 = 128 * 272;  // 18432, 34816
-constexpr int NR_Q4 = 4, NR_Q8 = 2;                  // raw ring depth
-constexpr int OFF_DM = OFF_RAW + NR_Q4 * RAW_Q4;     // 204800: Q4_K: 4 x [128] f32 superblock scales d
-constexpr int OFF_D8 = OFF_RAW + NR_Q8 * RAW_Q8;     // 200704: Q8_0: 4 x [8][128] f32 block scales
-constexpr int NASC = 3;
-constexpr int OFF_ASC = 217088;                      // after the larger of the two maps: NASC x [8 blocks][128 rows] f32
-constexpr int OFF_BAR = OFF_ASC + NASC * 4096;       // 229376
-constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;    // barriers + alignment slack = 231424 <= 227 KB
-static_assert(OFF_DM + 4 * 512 <= OFF_ASC && OFF_D8 + 4 * 4096 <= OFF_ASC, "shared memory map");
-
-enum Bar {  // 8-byte mbarriers
-  S_FULL = 0, S_EMPTY = S_FULL + NS, RAW_FULL = S_EMPTY + NS,  // S_*: one barrier per stage for both operand tiles
-  RAW_EMPTY = RAW_FULL + 4, D1_FULL = RAW_EMPTY + 4, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1,
-  D2_EMPTY, ASC_FULL, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC
+template <int QT>
+struct Map {
+  static constexpr bool q4 = QT == IZB_Q4_K;
+  static constexpr int NA = q4 ? IZB_TC_NA4 : IZB_TC_NA8;  // activation stages
+  static constexpr int NB = q4 ? IZB_TC_NB4 : IZB_TC_NB8;  // weight-operand stages
+  static constexpr int NR = q4 ? IZB_TC_NR4 : 2;           // raw superblock tiles
+  static constexpr int RAW = q4 ? RAW_Q4 : RAW_Q8;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + NA * STAGE_BYTES;
+  static constexpr int OFF_RAW = OFF_B + NB * STAGE_BYTES;
+  static constexpr int OFF_SCL = OFF_RAW + NR * RAW;              // Q4_K: 4 x [128] f32 superblock scales d; Q8_0: 4 x [8][128] f32 block scales
+  static constexpr int OFF_ASC = OFF_SCL + (q4 ? 4 * 512 : 4 * 4096);  // NASC x [8 blocks][128 rows] f32 activation scales
+  static constexpr int OFF_BAR = OFF_ASC + NASC * 4096;
+  static constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;        // barriers + alignment slack
+  // 8-byte mbarriers
+  static constexpr int A_FULL = 0, A_EMPTY = A_FULL + NA, B_FULL = A_EMPTY + NA, B_EMPTY = B_FULL + NB, RAW_FULL = B_EMPTY + NB,
+                       RAW_EMPTY = RAW_FULL + NR, D1_FULL = RAW_EMPTY + NR, D1_EMPTY = D1_FULL + ND1, D2_FULL = D1_EMPTY + ND1,
+                       D2_EMPTY = D2_FULL + 1, ASC_FULL = D2_EMPTY + 1, ASC_EMPTY = ASC_FULL + NASC, NUM_BARS = ASC_EMPTY + NASC;
+  static_assert(SMEM_BYTES <= 232448, "shared memory per CTA");
+  static_assert(NUM_BARS * 8 + 16 <= 1024, "barrier area");
+  static_assert(OFF_RAW % 1024 == 0 && OFF_SCL % 16 == 0, "alignment of the TMA destinations");
 };
-static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
 
 // error-word codes (which wait gave up)
 enum : uint32_t { E_APROD = 1, E_WPROD = 2, E_DEQ = 4, E_MMA = 16, E_EPI = 32 };
@@ -103,6 +136,7 @@ struct TcParams {
   uint32_t* err;
   uint32_t spin_limit;    // polls after which a wait gives up
   int skip_stage;         // diagnostics: the operand stage the activation producer leaves out (-1: none)
+  unsigned long long* trace;  // diagnostics build only: [16][2048] clock stamps
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -112,11 +146,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// one arrival for the whole warp: a predicated instruction, no branch (the warp must be converged and every lane's work
-// that the arrival publishes must precede it in program order)
-__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, int lane) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(bar), "r"(lane) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -130,9 +159,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// non-blocking look at a barrier's phase
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok;
+}
 // Bounded wait.  false = gave up (or another thread did): the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* err,
                                           uint32_t limit, uint32_t code) {
+  // (a satisfied wait is the common case: one non-blocking look costs less than the blocking form)
+  if (mbar_test(bar, parity)) return true;
   for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
@@ -342,6 +382,12 @@ template <int QT, bool kDots>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using MP = Map<QT>;
+  constexpr int NA = MP::NA, NB = MP::NB, OFF_A = MP::OFF_A, OFF_B = MP::OFF_B, OFF_RAW = MP::OFF_RAW, OFF_DM = MP::OFF_SCL,
+                OFF_D8 = MP::OFF_SCL, OFF_ASC = MP::OFF_ASC, OFF_BAR = MP::OFF_BAR, NUM_BARS = MP::NUM_BARS;
+  constexpr int A_FULL = MP::A_FULL, A_EMPTY = MP::A_EMPTY, B_FULL = MP::B_FULL, B_EMPTY = MP::B_EMPTY, RAW_FULL = MP::RAW_FULL,
+                RAW_EMPTY = MP::RAW_EMPTY, D1_FULL = MP::D1_FULL, D1_EMPTY = MP::D1_EMPTY, D2_FULL = MP::D2_FULL,
+                D2_EMPTY = MP::D2_EMPTY, ASC_FULL = MP::ASC_FULL, ASC_EMPTY = MP::ASC_EMPTY;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NUM_BARS * 8);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + NUM_BARS * 8 + 4);
@@ -358,18 +404,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
   const int nsb = p.K >> 8, nb = p.K >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int SBB = QT == IZB_Q4_K ? 144 : 272;
-  constexpr int RAW = QT == IZB_Q4_K ? RAW_Q4 : RAW_Q8;
-  constexpr int NR = QT == IZB_Q4_K ? NR_Q4 : NR_Q8;
+  constexpr int RAW = MP::RAW, NR = MP::NR;
   constexpr bool kMins = QT == IZB_Q4_K && !kDots;
   constexpr int SPS = kMins ? 5 : 4;  // operand stages per superblock: four of 64 K-elements (+ the min-term stage)
   const int nstages = SPS * nsb;
 
   if (threadIdx.x == 0) {
     // Consumers release a buffer with one arrival per THREAD, not per warp: an elected lane costs a divergent branch and a
-    // warp barrier per hand-over, which measured 10 % of the kernel.  S_FULL: the activation producer's expect_tx arrival
-    // + the 128 dequantiser threads; S_EMPTY: one tcgen05.commit
-    constexpr int kDeqArr = IZB_TC_ELECT >= 2 ? 4 : 128, kCmbArr = IZB_TC_ELECT >= 1 ? 8 : 256;
-    for (int i = 0; i < NS; ++i) { mbar_init(bar(S_FULL + i), kDeqArr + 1); mbar_init(bar(S_EMPTY + i), 1); }
+    // warp barrier per hand-over, which measured 10 % of the kernel (and one predicated arrival per warp measured no
+    // better than 32).  A_FULL: the activation producer's expect_tx arrival; B_FULL: the 128 dequantiser threads;
+    // A_EMPTY / B_EMPTY: one tcgen05.commit each
+    constexpr int kDeqArr = 128, kCmbArr = 256;
+    for (int i = 0; i < NA; ++i) { mbar_init(bar(A_FULL + i), 1); mbar_init(bar(A_EMPTY + i), 1); }
+    for (int i = 0; i < NB; ++i) { mbar_init(bar(B_FULL + i), kDeqArr); mbar_init(bar(B_EMPTY + i), 1); }
     for (int i = 0; i < NR; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_EMPTY + i), kDeqArr); }
     for (int i = 0; i < ND1; ++i) { mbar_init(bar(D1_FULL + i), 1); mbar_init(bar(D1_EMPTY + i), kCmbArr); }
     mbar_init(bar(D2_FULL), 1);
@@ -399,13 +446,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         const int tile = w / n_ntiles;
         const unsigned char* src = reinterpret_cast<const unsigned char*>(p.aimg) + (size_t)tile * nstages * STAGE_BYTES;
         for (int g = 0; g < nstages; ++g) {
-          if (!mbar_wait(bar(S_EMPTY + sa), pa, abort_flag, p.err, p.spin_limit, E_APROD)) { ok = false; break; }
+          if (!mbar_wait(bar(A_EMPTY + sa), pa, abort_flag, p.err, p.spin_limit, E_APROD)) { ok = false; break; }
           if (lane == 0 && g != p.skip_stage) {  // (skip_stage: diagnostics only, makes the waits of this stage run out)
-            mbar_expect_tx(bar(S_FULL + sa), STAGE_BYTES);
-            bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(S_FULL + sa));
+            mbar_expect_tx(bar(A_FULL + sa), STAGE_BYTES);
+            bulk_g2s(smem_u32(smem + OFF_A + sa * STAGE_BYTES), src + (size_t)g * STAGE_BYTES, STAGE_BYTES, bar(A_FULL + sa));
           }
           __syncwarp();
-          if (++sa == NS) { sa = 0; pa ^= 1; }
+          if (++sa == NA) { sa = 0; pa ^= 1; }
         }
       }
     } else if (warp == 3) {
@@ -446,15 +493,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       const int gs = it * nstages, jb = it * nb;
       for (int s = 0; s < nsb && ok; ++s) {
         for (int t = warp - 1; t < (warp == 1 ? 4 : SPS) && ok; t += (t == 3 ? 1 : 2)) {
-          const int g = gs + SPS * s + t, sa = g % NS;
-          if (!mbar_wait(bar(S_FULL + sa), (g / NS) & 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
+          const int g = gs + SPS * s + t, sa = g % NA, sb = g % NB;
+          TRACE(10, g);
+          if (!mbar_wait(bar(B_FULL + sb), (g / NB) & 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
+          TRACE(11, g);
+          if (!mbar_wait(bar(A_FULL + sa), (g / NA) & 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
+          TRACE(12, g);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sa * STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(smem + OFF_A + sa * STAGE_BYTES), b_addr = smem_u32(smem + OFF_B + sb * STAGE_BYTES);
           if (t < 4) {
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
               const int j = jb + 8 * s + 2 * t + blk, d = j % ND1;
+              TRACE(0, j);
               if (!mbar_wait(bar(D1_EMPTY + d), ((j / ND1) & 1) ^ 1, abort_flag, p.err, p.spin_limit, E_MMA)) { ok = false; break; }
+              TRACE(1, j);
               tc_fence_after();
               if (lane == 0) {
                 const uint32_t dt = tmem_base + (uint32_t)(d * BN);
@@ -463,6 +516,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                   tc_mma_f16(dt, umma_desc(a_addr + blk * 64 + k16 * 32), umma_desc(b_addr + blk * 64 + k16 * 32), kIdescF16, k16);
                 tc_commit(bar(D1_FULL + d));
               }
+              TRACE(2, j);
               __syncwarp();
             }
             if (!ok) break;
@@ -477,7 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             }
           }
           if (lane == 0) {
-            tc_commit(bar(S_EMPTY + sa));
+            tc_commit(bar(A_EMPTY + sa));
+            tc_commit(bar(B_EMPTY + sb));
             if (kMins && t == 4 && s == nsb - 1) tc_commit(bar(D2_FULL));
           }
           __syncwarp();
@@ -509,7 +564,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
       }
 #pragma unroll 1  // (rolled on purpose: with the role loops resident at once, code size costs more than the loop)
       for (int c = 0; c < 4; ++c) {
-        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
+        if (warp == 4) TRACE(7, sbc * SPS + c);
+        if (!mbar_wait(bar(B_EMPTY + sbq), pbq, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
+        if (warp == 4) TRACE(8, sbc * SPS + c);
         unsigned char* orow = smem + OFF_B + sbq * STAGE_BYTES + t * 128;
         if (QT == IZB_Q4_K) {
           const uint4 q0 = *reinterpret_cast<const uint4*>(rrow + 16 + 32 * c), q1 = *reinterpret_cast<const uint4*>(rrow + 32 + 32 * c);
@@ -525,18 +582,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           const uint32_t blo = 0x64006400u | (uint32_t)sc_lo | ((uint32_t)sc_lo << 16), bhi = 0x64006400u | (uint32_t)sc_hi | ((uint32_t)sc_hi << 16);
           const __half2 slo = __hsub2(*reinterpret_cast<const __half2*>(&blo), k1024), shi = __hsub2(*reinterpret_cast<const __half2*>(&bhi), k1024);
           const __half2 nlo = __hmul2(slo, kneg), nhi = __hmul2(shi, kneg);
-          auto cvt = [](uint32_t word, int sh, __half2 scale, __half2 neg) -> uint32_t {
-            const uint32_t bitsv = ((word >> sh) & 0x000F000Fu) | 0x64006400u;  // (1024 + q) in both halves
-            const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&bitsv), scale, neg);  // = sc * q exactly
+          // High nibbles stay where they are: (word & 0x00F000F0) | 0x6400 is the fp16 number 1024 + 16 q, and
+          // (1024 + 16 q) * (sc / 16) - 64 sc = sc * q exactly (one rounding, of an integer below 2^11).  One shift per
+          // word (for its upper bytes) instead of three.
+          const __half2 k16th = __half2half2(__ushort_as_half((unsigned short)0x2C00));  // 1 / 16
+          const __half2 shi16 = __hmul2(shi, k16th), nhi16 = __hmul2(nhi, k16th);
+          auto cv = [](uint32_t word, uint32_t mask, __half2 scale, __half2 neg) -> uint32_t {
+            const uint32_t bitsv = (word & mask) | 0x64006400u;
+            const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&bitsv), scale, neg);
             return *reinterpret_cast<const uint32_t*>(&r);
           };
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
-            const uint32_t w0 = w[2 * jj], w1 = w[2 * jj + 1];
+            const uint32_t w0 = w[2 * jj], w1 = w[2 * jj + 1], x0 = w0 >> 8, x1 = w1 >> 8;
             *reinterpret_cast<uint4*>(orow + ((jj ^ (t & 7)) << 4)) =
-                make_uint4(cvt(w0, 0, slo, nlo), cvt(w0, 8, slo, nlo), cvt(w1, 0, slo, nlo), cvt(w1, 8, slo, nlo));
+                make_uint4(cv(w0, 0x000F000Fu, slo, nlo), cv(x0, 0x000F000Fu, slo, nlo), cv(w1, 0x000F000Fu, slo, nlo), cv(x1, 0x000F000Fu, slo, nlo));
             *reinterpret_cast<uint4*>(orow + (((4 + jj) ^ (t & 7)) << 4)) =
-                make_uint4(cvt(w0, 4, shi, nhi), cvt(w0, 12, shi, nhi), cvt(w1, 4, shi, nhi), cvt(w1, 12, shi, nhi));
+                make_uint4(cv(w0, 0x00F000F0u, shi16, nhi16), cv(x0, 0x00F000F0u, shi16, nhi16), cv(w1, 0x00F000F0u, shi16, nhi16), cv(x1, 0x00F000F0u, shi16, nhi16));
           }
         } else {
           const __half2 bias = __half2half2(__int2half_rn(1152));
@@ -556,20 +618,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           }
         }
         fence_proxy_async();
-#if IZB_TC_ELECT >= 2
-        __syncwarp();
-        mbar_arrive_lane0(bar(S_FULL + sbq), threadIdx.x & 31);
-#else
-        mbar_arrive(bar(S_FULL + sbq));  // (every thread after its own stores and fence)
-#endif
-        if (++sbq == NS) { sbq = 0; pbq ^= 1; }
+        mbar_arrive(bar(B_FULL + sbq));  // (every thread after its own stores and fence)
+        if (warp == 4) TRACE(9, sbc * SPS + c);
+        if (++sbq == NB) { sbq = 0; pbq ^= 1; }
       }
       if (!ok) break;
       if (kMins) {
         // the min-term stage: u[b] = -dmin * mn[b] (exact in f32: 11 x 6 bits) as three bf16 terms u1 + u2 + u3; the
         // stage's six 16-byte chunks hold (u1, u2, u1, u3, u2, u1) for the eight blocks, against the activation side's
         // (v1, v1, v2, v1, v2, v3)
-        if (!mbar_wait(bar(S_EMPTY + sbq), pbq, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
+        if (!mbar_wait(bar(B_EMPTY + sbq), pbq, abort_flag, p.err, p.spin_limit, E_DEQ)) { ok = false; break; }
         const float ndmin = -half_bits_to_float(hdr.x >> 16);
         uint32_t u1[4], u2[4], u3[4];
 #pragma unroll
@@ -601,20 +659,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         *reinterpret_cast<uint4*>(orow + ((4 ^ (t & 7)) << 4)) = c2;
         *reinterpret_cast<uint4*>(orow + ((5 ^ (t & 7)) << 4)) = c1;
         fence_proxy_async();
-#if IZB_TC_ELECT >= 2
-        __syncwarp();
-        mbar_arrive_lane0(bar(S_FULL + sbq), threadIdx.x & 31);
-#else
-        mbar_arrive(bar(S_FULL + sbq));  // (every thread after its own stores and fence)
-#endif
-        if (++sbq == NS) { sbq = 0; pbq ^= 1; }
+        mbar_arrive(bar(B_FULL + sbq));  // (every thread after its own stores and fence)
+        if (++sbq == NB) { sbq = 0; pbq ^= 1; }
       }
-#if IZB_TC_ELECT >= 2
-      __syncwarp();
-      mbar_arrive_lane0(bar(RAW_EMPTY + rb), threadIdx.x & 31);
-#else
       mbar_arrive(bar(RAW_EMPTY + rb));
-#endif
       if (++rb == NR) { rb = 0; pr ^= 1; }
     }
   } else {
@@ -642,7 +690,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
         const unsigned long long a2 = pack2(kDots ? 0.0f : as[b * BM]);
+        if (warp == 8) TRACE(3, sbc * 8 + b);
         if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, p.spin_limit, E_EPI)) { ok = false; break; }
+        if (warp == 8) TRACE(4, sbc * 8 + b);
         tc_fence_after();
         unsigned long long v[32];
 #if IZB_TC_STRIP >= 2
@@ -652,11 +702,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         tc_ld64_pairs(t_lane + (uint32_t)(d * BN), v);  // the thread's 64 columns of this block; returns when they are in registers
 #endif
         tc_fence_before();
-#if IZB_TC_ELECT >= 1
-        mbar_arrive_lane0(bar(D1_EMPTY + d), lane);  // (the load's wait is warp-wide: every lane has its columns)
-#else
+        if (warp == 8) TRACE(5, sbc * 8 + b);
         mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
-#endif
         if (kDots) {
           if (row_ok) {
             int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64) * nb + 8 * s + b;
@@ -685,15 +732,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             ffma2(res2[2 * c4 + 1], fmul2(a2, dd.y), v[2 * c4 + 1]);
           }
         }
+        if (warp == 8) TRACE(6, sbc * 8 + b);
         if (++d == ND1) { d = 0; pd ^= 1; }
       }
       if (!ok) break;
       if (!kDots) {  // the superblock's scales are read: its ring slot may be refilled
-#if IZB_TC_ELECT >= 1
-        mbar_arrive_lane0(bar(ASC_EMPTY + sq), lane);
-#else
         mbar_arrive(bar(ASC_EMPTY + sq));
-#endif
         if (++sq == NASC) { sq = 0; pq ^= 1; }
       }
       if (kMins) {  // res += d * tq
@@ -713,11 +757,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         unsigned long long v[32];
         tc_ld64_pairs(t_lane + (uint32_t)(ND1 * BN), v);
         tc_fence_before();
-#if IZB_TC_ELECT >= 1
-        mbar_arrive_lane0(bar(D2_EMPTY), lane);
-#else
         mbar_arrive(bar(D2_EMPTY));  // the next tile's min term may start
-#endif
         const unsigned long long one2 = pack2(1.0f);
 #pragma unroll
         for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);
@@ -726,6 +766,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     if (ok && !kDots && row_ok && !*abort_flag) {
       float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + n0 + half * 64;
       const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
+      // plain store, no row factor, 32-byte aligned rows: eight stores of one full 32-byte sector each per thread
+      if (p.acc == 0 && !p.rowscale && ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0) {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8)
+          asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * c8), "l"(res2[4 * c8]), "l"(res2[4 * c8 + 1]),
+                       "l"(res2[4 * c8 + 2]), "l"(res2[4 * c8 + 3])
+                       : "memory");
+      } else
 #pragma unroll
       for (int c4 = 0; c4 < 16; ++c4) {
         float4 v = make_float4(lo_f(res2[2 * c4]), hi_f(res2[2 * c4]), lo_f(res2[2 * c4 + 1]), hi_f(res2[2 * c4 + 1]));
@@ -779,13 +827,16 @@ EncodeTiledFn get_encode() {
 // producer leaves out, for the NEXT launch only.
 std::atomic<uint32_t> g_test_spin{0};
 std::atomic<int> g_test_skip{-1};
+std::atomic<unsigned long long*> g_test_trace{nullptr};
 
 template <int QT, bool kDots>
 int launch_tc(const izb_weight* w, TcParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int SMEM_BYTES = Map<QT>::SMEM_BYTES;
   IZB_SMEM_OPTIN((gemm_tc_kernel<QT, kDots>), SMEM_BYTES, w->device);
   const uint32_t spin = g_test_spin.exchange(0);
   p.spin_limit = spin ? spin : kSpinLimit;
   p.skip_stage = g_test_skip.exchange(-1);
+  p.trace = g_test_trace.load();
   CUtensorMap tm;
   memcpy(&tm, w->tmap_raw, sizeof tm);
   IZB_LAUNCH("gemm_tc", st, gemm_tc_kernel<QT, kDots><<<grid, kThreads, SMEM_BYTES, st>>>(tm, p));
@@ -868,6 +919,12 @@ size_t izb_gemm_tc_scratch_bytes(int type, int rows, int K) {
   size_t img_bytes, asc_bytes;
   tc_scratch_bytes((rows + BM - 1) / BM, K, type == IZB_Q4_K ? 5 : 4, &img_bytes, &asc_bytes);
   return img_bytes + asc_bytes;
+}
+
+// diagnostics builds (IZB_TC_TRACE): where CTA 0 of the following launches writes its clock stamps
+extern "C" int izb_debug_set_trace(unsigned long long* d_trace) {
+  g_test_trace.store(d_trace);
+  return IZB_OK;
 }
 
 extern "C" int izb_debug_wait_test(uint32_t spin_limit, int skip_stage) {

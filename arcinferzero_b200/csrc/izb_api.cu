@@ -377,8 +377,11 @@ extern "C" int izb_weight_create(int type, const void* h_rows, int n_mats, int N
 
 extern "C" void izb_weight_destroy(izb_weight* w) {
   if (!w) return;
-  cudaSetDevice(w->device);
-  cudaFree(w->raw);
+  {
+    DeviceScope scope;  // (the caller's current device is put back: a thread may free another GPU's handle)
+    scope.enter(w->device);
+    cudaFree(w->raw);
+  }
   delete w;
 }
 

@@ -47,9 +47,6 @@ int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* 
                          int ldc, int c_off, int acc, int32_t* dots, cudaStream_t st);
 
 // Build-time experiment switches (defaults = the shipped kernel).
-#ifndef IZB_TC_STRIP
-#define IZB_TC_STRIP 0   // timing diagnostics only: 1 = no combine arithmetic, 2 = no TMEM reads either
-#endif
 
 #ifndef IZB_TC_TRACE
 #define IZB_TC_TRACE 0   // diagnostics build: CTA 0 stamps clock64() at the hand-overs of its first blocks into TcParams::trace
@@ -694,42 +691,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         if (!mbar_wait(bar(D1_FULL + d), pd, abort_flag, p.err, p.spin_limit, E_EPI)) { ok = false; break; }
         if (warp == 8) TRACE(4, sbc * 8 + b);
         tc_fence_after();
-        unsigned long long v[32];
-#if IZB_TC_STRIP >= 2
 #pragma unroll
-        for (int c = 0; c < 32; ++c) v[c] = 0ull;
-#else
-        tc_ld64_pairs(t_lane + (uint32_t)(d * BN), v);  // the thread's 64 columns of this block; returns when they are in registers
-#endif
-        tc_fence_before();
-        if (warp == 8) TRACE(5, sbc * 8 + b);
-        mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
-        if (kDots) {
-          if (row_ok) {
-            int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64) * nb + 8 * s + b;
+        for (int h = 0; h < 2; ++h) {  // 32 columns at a time: the block loop's working set stays inside the register budget
+          unsigned long long v[16];
+          tc_ld32_pairs(t_lane + (uint32_t)(d * BN + 32 * h), v);
+          if (h == 1) {
+            tc_fence_before();
+            if (warp == 8) TRACE(5, sbc * 8 + b);
+            mbar_arrive(bar(D1_EMPTY + d));  // the accumulator buffer may be overwritten
+          }
+          if (kDots) {
+            if (row_ok) {
+              int32_t* o = p.dots + ((size_t)out_row * p.N + n0 + half * 64 + 32 * h) * nb + 8 * s + b;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              o[(size_t)(2 * c) * nb] = __float2int_rn(lo_f(v[c]));
-              o[(size_t)(2 * c + 1) * nb] = __float2int_rn(hi_f(v[c]));
+              for (int c = 0; c < 16; ++c) {
+                o[(size_t)(2 * c) * nb] = __float2int_rn(lo_f(v[c]));
+                o[(size_t)(2 * c + 1) * nb] = __float2int_rn(hi_f(v[c]));
+              }
             }
-          }
-        } else if (IZB_TC_STRIP >= 1) {
-          if (b == 7) tq2[0] = v[0];  // (keeps the load alive)
-        } else if (QT == IZB_Q4_K) {
-          if (b == 0) {
+          } else if (QT == IZB_Q4_K) {
+            if (b == 0) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) tq2[c] = fmul2(a2, v[c]);
+              for (int c = 0; c < 16; ++c) tq2[16 * h + c] = fmul2(a2, v[c]);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 16; ++c) ffma2(tq2[16 * h + c], a2, v[c]);
+            }
           } else {
+            const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (sbc & 3) * 4096 + b * 512 + half * 256 + h * 128);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) ffma2(tq2[c], a2, v[c]);
-          }
-        } else {
-          const ulonglong2* d8 = reinterpret_cast<const ulonglong2*>(smem + OFF_D8 + (sbc & 3) * 4096 + b * 512 + half * 256);
-#pragma unroll
-          for (int c4 = 0; c4 < 16; ++c4) {
-            const ulonglong2 dd = d8[c4];  // four column scales
-            ffma2(res2[2 * c4], fmul2(a2, dd.x), v[2 * c4]);
-            ffma2(res2[2 * c4 + 1], fmul2(a2, dd.y), v[2 * c4 + 1]);
+            for (int c4 = 0; c4 < 8; ++c4) {
+              const ulonglong2 dd = d8[c4];  // four column scales
+              ffma2(res2[16 * h + 2 * c4], fmul2(a2, dd.x), v[2 * c4]);
+              ffma2(res2[16 * h + 2 * c4 + 1], fmul2(a2, dd.y), v[2 * c4 + 1]);
+            }
           }
         }
         if (warp == 8) TRACE(6, sbc * 8 + b);

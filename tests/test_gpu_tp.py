@@ -35,3 +35,21 @@ def test_stack_all_visible_gpus(izb):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("TP_WORKER_OK") == 3 * n, r.stdout[-3000:]
+
+
+def test_collective_with_a_missing_peer_times_out_and_aborts(izb):
+    """Failure detection in the C ABI (izb_tp_create_ex with a time-out, izb_tp_wait, izb_tp_abort): two ranks, the second
+    stays away from a collective between steps; the first rank's bounded wait must end with IZB_ERR_TIMEOUT, not hang."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU visible: the time-out check needs two ranks")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "tp_timeout_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_TIMEOUT_OK") == 2, r.stdout[-3000:]

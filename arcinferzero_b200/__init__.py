@@ -16,13 +16,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("IZB200_LIB") or os.path.join(HERE, "libizb200.so")  # IZB200_LIB: another build of the library
 
 Q8_0, Q4_K = 8, 12
+Q4_0, Q5_K, Q6_K, IQ4_XS = 2, 13, 14, 23
 GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 
 # every symbol include/izb200.h declares (tests check the library exports each of them)
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_reserve", "izb_set_sm_limit", "izb_debug_wait_test", "izb_tensor_peak",
-    "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info", "izb_weight_download",
+    "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
@@ -130,6 +131,16 @@ class Weight:
             self.close()
         except Exception:
             pass
+
+
+def weight_decode_host(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:
+    """The loader's host-side decoder (no GPU): rows [N, K/256 * file bytes] of Q4_0 / Q5_K / Q6_K / IQ4_XS -> the uploaded
+    form [N, K/256 * (272 | 304)]."""
+    rows = np.ascontiguousarray(rows, np.uint8)
+    per = 272 if qtype == Q4_0 else 304
+    out = np.empty((rows.shape[0], K // 256 * per), np.uint8)
+    _check(lib().izb_weight_decode_host(qtype, _p(rows), C.c_size_t(rows.shape[0] * (K // 256)), _p(out), C.c_size_t(out.size)))
+    return out
 
 
 def quantize_act(x, Mp: int | None = None, want_absum: bool = False, out=None):

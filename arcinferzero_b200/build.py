@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libizb200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fopenmp",
          "-ccbin", "/usr/bin/g++"]
 
 
@@ -47,7 +47,7 @@ def build(verbose: bool = False) -> str:
             if verbose and log:
                 print(log)
     if jobs or not os.path.exists(OUT):
-        run([NVCC, "-shared", "-o", OUT, *objs, "-lcudart", "-ldl", "-ccbin", "/usr/bin/g++"])
+        run([NVCC, "-shared", "-o", OUT, *objs, "-lcudart", "-ldl", "-lgomp", "-ccbin", "/usr/bin/g++"])
     return OUT
 
 

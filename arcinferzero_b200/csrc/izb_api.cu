@@ -18,6 +18,8 @@ int izb_gemm_core_launch(const izb_weight* w, const uint8_t* raw, const int8_t* 
 int izb_gemm_tc_launch(const izb_weight* w, int mat, const int8_t* aq, const float* asc, int M, int Mp, float* C, int ldc,
                        int c_off, int acc, int32_t* dots, cudaStream_t st);
 int izb_make_raw_tensor_map(izb_weight* w);
+int izb_gemm_k16_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C, int ldc,
+                        int c_off, int acc, int32_t* dots, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------------- errors
 static thread_local char t_err[512] = "";
@@ -310,26 +312,33 @@ __global__ void regroup_q8_0_kernel(const uint8_t* __restrict__ src, uint8_t* __
 }
 }  // namespace
 
+int izb_gguf_sb_bytes(int ggml_type);
+void izb_transcode_sb(int ggml_type, const uint8_t* src, size_t n_sb, uint8_t* dst);
+
 extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats, int N, int K, int n0, int n1, int k0, int k1,
                                        int device, izb_weight** out) {
   if (!h_rows || !out) IZB_FAIL(IZB_ERR_ARG, "weight_create: null pointer");
   *out = nullptr;
-  if (type != IZB_Q8_0 && type != IZB_Q4_K) IZB_FAIL(IZB_ERR_TYPE, "weight_create: ggml type %d (only Q8_0 = 8 and Q4_K = 12)", type);
+  const int src_sb = izb_gguf_sb_bytes(type);
+  if (!src_sb) IZB_FAIL(IZB_ERR_TYPE, "weight_create: ggml type %d (taken: Q8_0 = 8, Q4_K = 12, Q4_0 = 2, Q5_K = 13, Q6_K = 14, IQ4_XS = 23)", type);
   if (n_mats < 1 || N < 1 || K < 256 || K % 256) IZB_FAIL(IZB_ERR_SHAPE, "weight_create: %d x [%d x %d] (K must be a multiple of 256)", n_mats, N, K);
   if (n0 < 0 || n1 > N || n0 >= n1 || k0 < 0 || k1 > K || k0 >= k1 || k0 % 256 || k1 % 256)
     IZB_FAIL(IZB_ERR_SHAPE, "weight_create: slice rows [%d,%d) cols [%d,%d) of %d x %d (columns in whole superblocks)", n0, n1, k0, k1, N, K);
   if (int rc = check_device(device)) return rc;
   IZB_CUDA(cudaSetDevice(device));
+  const bool direct = type == IZB_Q8_0 || type == IZB_Q4_K;  // the file's bytes are what is uploaded
   izb_weight* w = new izb_weight;
-  w->type = type;
+  w->ggml_type = type;
+  w->type = (type == IZB_Q8_0 || type == IZB_Q4_0) ? IZB_Q8_0 : type == IZB_Q4_K ? IZB_Q4_K : IZB_K16;
+  w->has_min = type == IZB_Q5_K;
   w->n_mats = n_mats;
   w->N = n1 - n0;
   w->K = k1 - k0;
   w->device = device;
-  w->sb_bytes = type == IZB_Q4_K ? 144 : 272;
+  w->sb_bytes = w->type == IZB_Q4_K ? 144 : w->type == IZB_Q8_0 ? 272 : kK16SbBytes;
   w->row_bytes = (size_t)(w->K / 256) * w->sb_bytes;
   w->bytes = (size_t)n_mats * w->N * w->row_bytes;
-  const size_t src_row = (size_t)(K / 256) * w->sb_bytes;  // the GGUF bytes of 256 values are 144 / 8*34 = 272 as well
+  const size_t src_row = (size_t)(K / 256) * src_sb;  // (the GGUF bytes of 256 values: 144 / 8*34 = 272 for the two direct types)
   if (cudaMalloc(&w->raw, w->bytes + kRawSlack) != cudaSuccess) {
     cudaGetLastError();
     const size_t want = w->bytes + kRawSlack;
@@ -339,12 +348,12 @@ extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats,
   cudaError_t e = cudaMemset(w->raw + w->bytes, 0, kRawSlack);
   uint8_t* upload = w->raw;
   uint8_t* tmp = nullptr;
-  if (e == cudaSuccess && type == IZB_Q8_0) {
+  if (e == cudaSuccess && w->type == IZB_Q8_0) {  // (GGUF block order on the way in, regrouped on the device)
     e = cudaMalloc(&tmp, w->bytes);
     upload = tmp;
   }
-  if (e == cudaSuccess) {
-    const uint8_t* src = (const uint8_t*)h_rows + (size_t)n0 * src_row + (size_t)(k0 / 256) * w->sb_bytes;
+  if (e == cudaSuccess && direct) {
+    const uint8_t* src = (const uint8_t*)h_rows + (size_t)n0 * src_row + (size_t)(k0 / 256) * src_sb;
     if (n0 == 0 && n1 == N && k0 == 0 && k1 == K) {
       e = cudaMemcpy(upload, src, w->bytes, cudaMemcpyHostToDevice);
     } else {
@@ -352,8 +361,26 @@ extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats,
         e = cudaMemcpy2D(upload + (size_t)m * w->N * w->row_bytes, w->row_bytes, src + (size_t)m * N * src_row, src_row,
                          w->row_bytes, w->N, cudaMemcpyHostToDevice);
     }
+  } else if (e == cudaSuccess) {
+    // decode the rows of the slice on the host, a matrix at a time, into the form that is uploaded
+    std::vector<uint8_t> stage;
+    try {
+      stage.resize((size_t)w->N * w->row_bytes);
+    } catch (const std::exception&) {
+      cudaFree(w->raw);
+      if (tmp) cudaFree(tmp);
+      delete w;
+      IZB_FAIL(IZB_ERR_NOMEM, "weight_create: host staging for the decoded rows");
+    }
+    const size_t nsb_row = (size_t)w->K / 256;
+    for (int m = 0; m < n_mats && e == cudaSuccess; ++m) {
+      const uint8_t* src = (const uint8_t*)h_rows + ((size_t)m * N + n0) * src_row + (size_t)(k0 / 256) * src_sb;
+#pragma omp parallel for schedule(static)
+      for (int n = 0; n < w->N; ++n) izb_transcode_sb(type, src + (size_t)n * src_row, nsb_row, stage.data() + (size_t)n * w->row_bytes);
+      e = cudaMemcpy(upload + (size_t)m * w->N * w->row_bytes, stage.data(), stage.size(), cudaMemcpyHostToDevice);
+    }
   }
-  if (e == cudaSuccess && type == IZB_Q8_0) {
+  if (e == cudaSuccess && w->type == IZB_Q8_0) {
     const size_t n_sb = w->bytes / 272, items = n_sb * 17;
     regroup_q8_0_kernel<<<(unsigned)((items + 255) / 256), 256>>>(tmp, w->raw, n_sb);
     g_izb_launches.fetch_add(1);
@@ -366,8 +393,18 @@ extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats,
     delete w;
     IZB_FAIL(IZB_ERR_CUDA, "weight_create: upload failed: %s", cudaGetErrorString(e));
   }
-  w->has_tmap = izb_make_raw_tensor_map(w) == IZB_OK;
+  w->has_tmap = w->type != IZB_K16 && izb_make_raw_tensor_map(w) == IZB_OK;
   *out = w;
+  return IZB_OK;
+}
+
+extern "C" int izb_weight_decode_host(int type, const void* h_src, size_t n_superblocks, void* h_dst, size_t dst_bytes) {
+  if (!h_src || !h_dst) IZB_FAIL(IZB_ERR_ARG, "weight_decode_host: null pointer");
+  if (type != IZB_Q4_0 && type != IZB_Q5_K && type != IZB_Q6_K && type != IZB_IQ4_XS)
+    IZB_FAIL(IZB_ERR_TYPE, "weight_decode_host: ggml type %d is uploaded as it is (or is not taken at all)", type);
+  const size_t per = type == IZB_Q4_0 ? 8 * 34 : kK16SbBytes;
+  if (dst_bytes < n_superblocks * per) IZB_FAIL(IZB_ERR_SHAPE, "weight_decode_host: %zu bytes for %zu superblocks of %zu", dst_bytes, n_superblocks, per);
+  izb_transcode_sb(type, (const uint8_t*)h_src, n_superblocks, (uint8_t*)h_dst);
   return IZB_OK;
 }
 
@@ -396,7 +433,7 @@ extern "C" int izb_weight_download(const izb_weight* w, size_t offset, size_t by
 
 extern "C" int izb_weight_info(const izb_weight* w, int* type, int* n_mats, int* N, int* K, size_t* bytes) {
   if (!w) IZB_FAIL(IZB_ERR_ARG, "weight_info: null handle");
-  if (type) *type = w->type;
+  if (type) *type = w->ggml_type;
   if (n_mats) *n_mats = w->n_mats;
   if (N) *N = w->N;
   if (K) *K = w->K;
@@ -424,6 +461,11 @@ extern "C" int izb_gemm(const izb_weight* w, int mat, const int8_t* d_aq, const 
   if (int rc = check_gemm_args(w, mat, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc)) return rc;
   if (int rc = izb_require_device(w->device, "gemm")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if (w->type == IZB_K16) {  // Q5_K / Q6_K / IQ4_XS: exact per-16 scales, CUDA cores (the reference requantises these for its GEMM)
+    if (impl == IZB_GEMM_TC) IZB_FAIL(IZB_ERR_TYPE, "gemm: the tensor-core kernel does not take ggml type %d", w->ggml_type);
+    if (impl != IZB_GEMM_AUTO && impl != IZB_GEMM_CORE) IZB_FAIL(IZB_ERR_ARG, "gemm: impl %d", impl);
+    return izb_gemm_k16_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc, nullptr, st);
+  }
   if (impl == IZB_GEMM_AUTO || impl == IZB_GEMM_TC) {
     const bool allowed = impl == IZB_GEMM_TC || g_dev[w->device].tc_ok.load() != 0;
     if (allowed) {
@@ -444,6 +486,10 @@ extern "C" int izb_block_dots(const izb_weight* w, int mat, const int8_t* d_aq, 
   if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "block_dots: aq not 16-byte aligned");
   if (int rc = izb_require_device(w->device, "block_dots")) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if (w->type == IZB_K16) {
+    if (impl != IZB_GEMM_CORE) IZB_FAIL(IZB_ERR_TYPE, "block_dots: the tensor-core kernel does not take ggml type %d", w->ggml_type);
+    return izb_gemm_k16_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, nullptr, M, M, nullptr, 0, 0, 0, d_dots, st);
+  }
   if (impl == IZB_GEMM_TC) {
     const int rc = izb_gemm_tc_launch(w, mat, d_aq, nullptr, M, M, nullptr, 0, 0, 0, d_dots, st);
     if (rc > 0) IZB_FAIL(IZB_ERR_SHAPE, "block_dots: the tensor-core kernel does not take M=%d N=%d K=%d", M, w->N, w->K);

@@ -14,9 +14,15 @@
 //   Q4_K: the 144-byte GGUF superblock unchanged: fp16 d | fp16 dmin | 12 B packed 6-bit scales/mins | 128 B nibbles
 //   Q8_0: 272 bytes per 256 values: fp16 d[8] | int8 q[8][32]
 // Both are multiples of 16 bytes, so every superblock starts on a 16-byte boundary (128-bit loads, TMA boxes).
+//   K16:  304 bytes per 256 values: f32 d | f32 dmin | int8 scale[16] | uint8 min[16] | 8 pad | int8 quant[256], the generic
+//         view of Q5_K / Q6_K / IQ4_XS superblocks (izb_types.cu)
+constexpr int IZB_K16 = 100;        // device form id (izb_weight::type holds the DEVICE form: IZB_Q8_0, IZB_Q4_K or IZB_K16)
+constexpr int kK16SbBytes = 304;
 struct izb_weight {
   int type = 0, n_mats = 0, N = 0, K = 0, device = 0;
-  int sb_bytes = 0;      // 144 or 272
+  int ggml_type = 0;     // the type of the file's tensor (Q4_0 is held as Q8_0, Q5_K / Q6_K / IQ4_XS as K16)
+  bool has_min = false;  // K16: the type has mins (Q5_K)
+  int sb_bytes = 0;      // 144, 272 or 304
   size_t row_bytes = 0;  // K/256 * sb_bytes
   size_t bytes = 0;      // n_mats * N * row_bytes (without the slack)
   uint8_t* raw = nullptr;

@@ -1138,6 +1138,7 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
   if (c_off < 0 || ldc < c_off + w->N) IZB_FAIL(IZB_ERR_SHAPE, "gemm_noalloc: ldc = %d < c_off + N = %d", ldc, c_off + w->N);
   if (!izb_aligned(d_aq, 16) || !izb_aligned(d_asc, 16) || !izb_aligned(d_C, 16) || ldc % 4 || c_off % 4 || (d_status && !izb_aligned(d_status, 4)))
     IZB_FAIL(IZB_ERR_ALIGN, "gemm_noalloc: aq, asc, C must be 16-byte aligned, ldc and c_off multiples of 4");
+  if (w->type == IZB_K16) IZB_FAIL(IZB_ERR_TYPE, "gemm_noalloc: ggml type %d is not taken by the tensor-core kernel", w->ggml_type);
   if (!w->has_tmap) IZB_FAIL(IZB_ERR_CUDA, "gemm_noalloc: the weight has no tensor map (driver entry point missing at creation)");
   const int K = w->K;
   const int n_tiles = (M + BM - 1) / BM;

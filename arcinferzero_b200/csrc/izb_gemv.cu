@@ -13,6 +13,8 @@
 // 16 int8 values each lane pairs with a min.
 #include "izb_gemv_body.cuh"
 
+int izb_gemv_k16_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int T, int Mp, float* C, int ldc,
+                        int c_off, int acc, cudaStream_t st);
 int izb_gemv_stream_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int T, int Mp, float* C,
                            int ldc, int c_off, int acc, cudaStream_t st);
 
@@ -78,6 +80,7 @@ extern "C" int izb_gemv(const izb_weight* w, int mat, const int8_t* d_aq, const 
   if (int rc = izb_require_device(w->device, "gemv")) return rc;
   const uint8_t* raw = w->raw + (size_t)mat * w->N * w->row_bytes;
   cudaStream_t st = (cudaStream_t)stream;
+  if (w->type == IZB_K16) return izb_gemv_k16_launch(w, raw, d_aq, d_asc, T, Mp, d_C, ldc, c_off, acc, st);
   {  // the streaming kernel takes every call whose staged activations fit in shared memory
     const int rc = izb_gemv_stream_launch(w, raw, d_aq, d_asc, T, Mp, d_C, ldc, c_off, acc, st);
     if (rc <= 0) return rc;

@@ -313,6 +313,7 @@ extern "C" int izb_moe_gateup(const izb_weight* wg, const izb_weight* wu, const 
     IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: gate and up stacks differ");
   if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_gateup: max_tiles = %d (1..65535)", max_tiles);
   if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_gateup: aq not 16-byte aligned");
+  if (wg->type == IZB_K16) IZB_FAIL(IZB_ERR_TYPE, "moe_gateup: expert stacks of ggml type %d are not taken (Q8_0, Q4_K, Q4_0)", wg->ggml_type);
   if (wu->device != wg->device) IZB_FAIL(IZB_ERR_ARG, "moe_gateup: gate and up stacks live on different devices");
   if (int rc = izb_require_device(wg->device, "moe_gateup")) return rc;
   if (TM >= 1 && TM <= 8) return izb_moe_gateup_tiles(wg, wu, d_aq, d_asc, Mp, d_tiles, max_tiles, d_stok, d_h, (cudaStream_t)stream);
@@ -329,6 +330,7 @@ extern "C" int izb_moe_down(const izb_weight* wd, const int8_t* d_hq, const floa
   if (!wd || !d_hq || !d_hsc || !d_tiles || !d_swt || !d_y) IZB_FAIL(IZB_ERR_ARG, "moe_down: null pointer");
   if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_down: max_tiles = %d (1..65535)", max_tiles);
   if (!izb_aligned(d_hq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_down: hq not 16-byte aligned");
+  if (wd->type == IZB_K16) IZB_FAIL(IZB_ERR_TYPE, "moe_down: expert stacks of ggml type %d are not taken (Q8_0, Q4_K, Q4_0)", wd->ggml_type);
   if (int rc = izb_require_device(wd->device, "moe_down")) return rc;
   if (TM >= 1 && TM <= 8) return izb_moe_down_tiles(wd, d_hq, d_hsc, Sp, d_tiles, max_tiles, d_swt, d_y, (cudaStream_t)stream);
   if (TM == 128) {

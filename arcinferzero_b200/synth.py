@@ -18,6 +18,10 @@ import numpy as np
 
 GGML_Q8_0 = 8
 GGML_Q4_K = 12
+GGML_Q4_0, GGML_Q5_K, GGML_Q6_K, GGML_IQ4_XS = 2, 13, 14, 23
+
+
+_SB_BYTES = {GGML_Q4_0: 8 * 18, GGML_Q5_K: 176, GGML_Q6_K: 210, GGML_IQ4_XS: 136}
 
 
 def sb_bytes(qtype: int) -> int:
@@ -26,6 +30,8 @@ def sb_bytes(qtype: int) -> int:
         return 144
     if qtype == GGML_Q8_0:
         return 8 * 34
+    if qtype in _SB_BYTES:
+        return _SB_BYTES[qtype]
     raise ValueError(f"unsupported ggml type {qtype}")
 
 
@@ -80,6 +86,30 @@ def make_weight(qtype: int, N: int, K: int, seed: int) -> np.ndarray:
         d = rng.uniform(0.001, 0.02, B).astype(np.float16)
         q = rng.integers(-127, 128, (B, 32), dtype=np.int8)
         return pack_q8_0(d, q).reshape(N, -1)
+    # The further types: every field uniform over its range (their byte layouts: src/quants.h:91-148, :297-312)
+    if qtype == GGML_Q4_0:      # 18-byte blocks: fp16 d | 16 bytes of nibbles
+        B = N * (K // 32)
+        out = np.empty((B, 18), np.uint8)
+        out[:, 0:2] = rng.uniform(0.001, 0.02, B).astype(np.float16).view(np.uint8).reshape(B, 2)
+        out[:, 2:] = rng.integers(0, 256, (B, 16), dtype=np.uint8)
+        return out.reshape(N, -1)
+    R = N * (K // 256)
+    if qtype == GGML_Q5_K:      # fp16 d, dmin | 12 B 6-bit scales / mins | 32 B fifth bits | 128 B nibbles
+        out = np.empty((R, 176), np.uint8)
+        out[:, 0:2] = rng.uniform(0.0, 0.01, R).astype(np.float16).view(np.uint8).reshape(R, 2)
+        out[:, 2:4] = rng.uniform(0.0, 0.01, R).astype(np.float16).view(np.uint8).reshape(R, 2)
+        out[:, 4:] = rng.integers(0, 256, (R, 172), dtype=np.uint8)
+        return out.reshape(N, -1)
+    if qtype == GGML_Q6_K:      # 128 B low nibbles | 64 B upper bits | 16 int8 scales | fp16 d
+        out = np.empty((R, 210), np.uint8)
+        out[:, 0:208] = rng.integers(0, 256, (R, 208), dtype=np.uint8)
+        out[:, 208:210] = rng.uniform(0.0, 0.001, R).astype(np.float16).view(np.uint8).reshape(R, 2)
+        return out.reshape(N, -1)
+    if qtype == GGML_IQ4_XS:    # fp16 d | u16 upper scale bits | 4 B scale nibbles | 128 B codebook indices
+        out = np.empty((R, 136), np.uint8)
+        out[:, 0:2] = rng.uniform(0.0, 0.001, R).astype(np.float16).view(np.uint8).reshape(R, 2)
+        out[:, 2:] = rng.integers(0, 256, (R, 134), dtype=np.uint8)
+        return out.reshape(N, -1)
     raise ValueError(f"unsupported ggml type {qtype}")
 
 

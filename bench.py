@@ -172,10 +172,13 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
     from arcinferzero_b200 import synth as S
     out = []
     # config 3's three matrices, then the down-projection shape of the same model (long rows: not in config 3)
-    for qt, Nn, Kk in ((12, 5120, K), (12, 17408, K), (8, 151936, K), (12, 5120, 17408)):
+    # ... and two Q6_K matrices (the type of the FFN down / output tensors of the common Q4_K_M files), held in the generic
+    # per-16-scale device form: GB/s counted on the FILE's bytes (210 per 256 weights), the device streams 304
+    for qt, Nn, Kk in ((12, 5120, K), (12, 17408, K), (8, 151936, K), (12, 5120, 17408), (14, 17408, K), (14, 151936, K)):
         w = S.make_weight(qt, Nn, Kk, SEED + Nn + (0 if Kk == K else Kk))
         wbytes = w.size
-        copies = max(1, -(-300_000_000 // wbytes)) if wbytes < 400_000_000 else 2
+        dev_bytes = wbytes if qt in (8, 12) else Nn * (Kk // 256) * 304
+        copies = max(1, -(-300_000_000 // dev_bytes)) if dev_bytes < 400_000_000 else 2
         Ws = [izb.Weight(qt, w, Nn, Kk) for _ in range(copies)]
         del w
         # (the output head once more with its logit soft-cap, as the reference's Gemma head runs: GEMV, then cap * tanh(v / cap))
@@ -210,7 +213,7 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
             us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
             nbytes = wbytes + T * (Kk + Kk // 32 * 4) + T * Nn * 4 * (3 if cap > 0 else 1)  # (the cap reads and writes the row again)
             gbs = nbytes / (us * 1e-6) / 1e9
-            out.append({"type": "Q4_K" if qt == 12 else "Q8_0", "N": Nn, "K": Kk, "batch": T, "softcap": cap, "in_config3": Kk == K and cap == 0, "us_per_launch": us,
+            out.append({"type": {12: "Q4_K", 8: "Q8_0", 14: "Q6_K"}[qt], "device_weight_bytes": dev_bytes, "N": Nn, "K": Kk, "batch": T, "softcap": cap, "in_config3": Kk == K and cap == 0 and qt != 14, "us_per_launch": us,
                         "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
                         "peak": f"{hbm_peak} GB/s {peak_src} copy", "weight_copies_in_rotation": copies})
         for W_ in Ws:

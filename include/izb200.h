@@ -45,7 +45,7 @@ extern "C" {
 #define IZB_OK 0
 #define IZB_ERR_ARG (-1)       /* null pointer, bad enum */
 #define IZB_ERR_SHAPE (-2)     /* K not a multiple of 256, Mp not a multiple of 16, N out of range ... */
-#define IZB_ERR_TYPE (-3)      /* ggml type other than Q8_0 (8) / Q4_K (12) */
+#define IZB_ERR_TYPE (-3)      /* a ggml type the library (or the called entry point) does not take */
 #define IZB_ERR_ALIGN (-4)     /* pointer or leading dimension not aligned as documented */
 #define IZB_ERR_CUDA (-5)      /* a CUDA runtime / driver call failed, or no sm_100 device */
 #define IZB_ERR_NCCL (-6)
@@ -54,8 +54,12 @@ extern "C" {
 #define IZB_ERR_SELFCHECK (-9) /* tensor-core kernel disagreed with the CUDA-core kernel at start-up */
 #define IZB_ERR_LIMIT (-10)    /* a fixed capacity of the called entry point was exceeded */
 
-#define IZB_Q8_0 8  /* ggml type ids, src/gguf.h */
+#define IZB_Q8_0 8  /* ggml type ids, src/gguf.h:19-22 */
 #define IZB_Q4_K 12
+#define IZB_Q4_0 2    /* the further types: decoded once at load into a device form the kernels read (see izb_weight_create) */
+#define IZB_Q5_K 13
+#define IZB_Q6_K 14
+#define IZB_IQ4_XS 23
 
 /* izb_gemm `impl` */
 #define IZB_GEMM_AUTO 0 /* tensor-core kernel when the shape allows it, else the CUDA-core kernel */
@@ -105,12 +109,23 @@ int izb_debug_wait_test(uint32_t spin_limit, int skip_stage);
  * (zero/engine.h:27-34).  h_gguf_rows: n_mats matrices of N rows of K values in GGUF block form (Q8_0: 34-byte blocks,
  * Q4_K: 144-byte superblocks), matrix-major, as in the file (MoE stacks are [NE][N][K], zero/engine_stream.h:285-306).
  * The device copy keeps Q4_K superblocks as they are and regroups Q8_0 per 256 values (8 fp16 scales, then 8 x 32
- * int8: the reference's gpu_raw_sb form, src/quants.h:728-751), followed by 1024 zero bytes of slack.  Synchronous. */
+ * int8: the reference's gpu_raw_sb form, src/quants.h:728-751), followed by 1024 zero bytes of slack.  Synchronous.
+ * Further types (the reference's table-driven block decoder, src/quants.h:89-315, zero/kernels/decode.cl:183-478):
+ *   Q4_0 (2)                    rewritten as Q8_0 blocks (same scale, int8 quants q - 8: exact) -> every Q8_0 kernel;
+ *   Q5_K (13), Q6_K (14), IQ4_XS (23)   decoded on the host into the reference's generic view, which is the device form:
+ *                               per 256 weights f32 d, f32 dmin, an int8 scale and a uint8 min per 16 elements, int8 quants
+ *                               with their offset removed (304 bytes).  GEMV for 1..8 rows and a CUDA-core GEMM, both with
+ *                               exact integer dots per 16-element half (zero/kernels/decode.cl:992-1004); not taken by the
+ *                               tensor-core GEMM, the MoE entry points or izb_gemm_noalloc (IZB_ERR_TYPE / IZB_ERR_SHAPE). */
 int izb_weight_create(int ggml_type, const void* h_gguf_rows, int n_mats, int N, int K, int device, izb_weight** out);
 /* Tensor-parallel shard of a matrix (Engine::tp_slice, zero/mgpu/engine_tp_shard.h:202-234): rows [n0, n1) and input
  * columns [k0, k1) of every matrix; k0, k1 multiples of 256. */
 int izb_weight_create_slice(int ggml_type, const void* h_gguf_rows, int n_mats, int N, int K, int n0, int n1, int k0, int k1,
                             int device, izb_weight** out);
+/* The loader's host-side decoder on its own (no device needed): n_superblocks superblocks (256 weights each) of a Q4_0,
+ * Q5_K, Q6_K or IQ4_XS row -> the form izb_weight_create uploads: GGUF Q8_0 blocks (8 x 34 bytes) for Q4_0, else 304 bytes:
+ * f32 d | f32 dmin | int8 scale[16] | uint8 min[16] | 8 zero bytes | int8 (quant - offset)[256]. */
+int izb_weight_decode_host(int ggml_type, const void* h_src, size_t n_superblocks, void* h_dst, size_t dst_bytes);
 void izb_weight_destroy(izb_weight* w);
 int izb_weight_info(const izb_weight* w, int* ggml_type, int* n_mats, int* N, int* K, size_t* device_bytes);
 /* Copies `bytes` of the device form back, from byte `offset` (rows of K/256 superblocks of 144 (Q4_K) or 272 (Q8_0) bytes,

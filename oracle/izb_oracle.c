@@ -25,6 +25,10 @@ int orc_max_threads(void) { return omp_get_max_threads(); }
 
 #define ORC_Q8_0 8
 #define ORC_Q4_K 12
+#define ORC_Q4_0 2   /* further ggml types: decoded into the reference's generic view below */
+#define ORC_Q5_K 13
+#define ORC_Q6_K 14
+#define ORC_IQ4_XS 23
 
 /* ---------------------------------------------------------------- fp16 <-> f32 (src/quants.h:17-52) */
 float orc_fp16_to_f32(uint16_t h) {
@@ -65,7 +69,19 @@ uint16_t orc_f32_to_fp16(float x) {
 }
 
 /* ---------------------------------------------------------------- block formats */
-int orc_sb_bytes(int type) { return type == ORC_Q4_K ? 144 : type == ORC_Q8_0 ? 8 * 34 : -1; } /* src/gguf.h:48-70 */
+/* bytes of 256 weights in GGUF form (src/gguf.h:48-70) */
+int orc_sb_bytes(int type) {
+  switch (type) {
+    case ORC_Q4_K: return 144;
+    case ORC_Q8_0: return 8 * 34;
+    case ORC_Q4_0: return 8 * 18;
+    case ORC_Q5_K: return 176;
+    case ORC_Q6_K: return 210;
+    case ORC_IQ4_XS: return 136;
+    default: return -1;
+  }
+}
+static int orc_generic(int type) { return type == ORC_Q5_K || type == ORC_Q6_K || type == ORC_IQ4_XS; }
 
 /* 6-bit scale / min j of a Q4_K superblock's 12 packed bytes (src/quants.h:61-69) */
 void orc_q4k_scale_min(int j, const uint8_t* s, uint8_t* sc, uint8_t* mn) {
@@ -123,10 +139,112 @@ void orc_q4k_pack_sb(uint16_t d, uint16_t dmin, const uint8_t* sc, const uint8_t
     for (int l = 0; l < 32; ++l) out[16 + 32 * j + l] = (uint8_t)((q[64 * j + l] & 15) | ((q[64 * j + 32 + l] & 15) << 4));
 }
 
+/* ---------------------------------------------------------------- further weight types
+ * The reference gives every K-quant and codebook type one generic view of a superblock (DecodedSB, src/quants.h:72-87):
+ *   w[e] = wd * wsc[e/16] * (q[e] - qoff) - wdmin * wmn[e/16]
+ * with an integer scale and min per 16 elements.  orc_decode_generic_sb fills it for Q5_K (src/quants.h:91-114), Q6_K
+ * (:115-135) and IQ4_XS (:297-312), with qoff already subtracted from q.  Q4_0 (:136-148) is a Q8_0 with 4-bit quants
+ * q - 8: orc_q4_0_to_q8_0 rewrites its blocks as Q8_0 blocks, exactly. */
+static const int8_t orc_iq4nl_values[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+int orc_decode_generic_sb(int type, const uint8_t* p, float* wd, float* wdmin, int8_t* wsc, uint8_t* wmn, int* has_min, int16_t* q) {
+  uint16_t h;
+  memset(wmn, 0, 16);
+  *wdmin = 0.0f;
+  *has_min = 0;
+  if (type == ORC_Q5_K) { /* fp16 d, dmin | 12 B 6-bit scales / mins | 32 B fifth bits | 128 B nibbles */
+    uint8_t sc[8], mn[8];
+    memcpy(&h, p, 2);
+    *wd = orc_fp16_to_f32(h);
+    memcpy(&h, p + 2, 2);
+    *wdmin = orc_fp16_to_f32(h);
+    *has_min = 1;
+    for (int b = 0; b < 8; ++b) orc_q4k_scale_min(b, p + 4, &sc[b], &mn[b]);
+    for (int i = 0; i < 16; ++i) { wsc[i] = (int8_t)sc[i / 2]; wmn[i] = mn[i / 2]; }
+    const uint8_t* qh = p + 16;
+    const uint8_t* qs = p + 48;
+    for (int j = 0; j < 4; ++j)
+      for (int l = 0; l < 32; ++l) {
+        q[64 * j + l] = (int16_t)((qs[32 * j + l] & 0xF) | (((qh[l] >> (2 * j)) & 1) << 4));
+        q[64 * j + 32 + l] = (int16_t)((qs[32 * j + l] >> 4) | (((qh[l] >> (2 * j + 1)) & 1) << 4));
+      }
+    return 0;
+  }
+  if (type == ORC_Q6_K) { /* 128 B low nibbles | 64 B upper two bits | 16 int8 scales | fp16 d; value q - 32 */
+    const uint8_t* ql = p;
+    const uint8_t* qh = p + 128;
+    memcpy(&h, p + 208, 2);
+    *wd = orc_fp16_to_f32(h);
+    for (int i = 0; i < 16; ++i) wsc[i] = (int8_t)p[192 + i];
+    for (int n = 0; n < 2; ++n)
+      for (int l = 0; l < 32; ++l) {
+        const uint8_t* L = ql + 64 * n;
+        const uint8_t* H = qh + 32 * n;
+        q[128 * n + l] = (int16_t)(((L[l] & 0xF) | (((H[l] >> 0) & 3) << 4)) - 32);
+        q[128 * n + l + 32] = (int16_t)(((L[l + 32] & 0xF) | (((H[l] >> 2) & 3) << 4)) - 32);
+        q[128 * n + l + 64] = (int16_t)(((L[l] >> 4) | (((H[l] >> 4) & 3) << 4)) - 32);
+        q[128 * n + l + 96] = (int16_t)(((L[l + 32] >> 4) | (((H[l] >> 6) & 3) << 4)) - 32);
+      }
+    return 0;
+  }
+  if (type == ORC_IQ4_XS) { /* fp16 d | u16 upper scale bits | 4 B lower scale nibbles | 128 B codebook indices */
+    uint16_t sh;
+    memcpy(&h, p, 2);
+    memcpy(&sh, p + 2, 2);
+    *wd = orc_fp16_to_f32(h);
+    const uint8_t* sl = p + 4;
+    const uint8_t* qs = p + 8;
+    for (int ib = 0; ib < 8; ++ib) {
+      const int ls = ((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4);
+      wsc[2 * ib] = wsc[2 * ib + 1] = (int8_t)(ls - 32);
+      for (int j = 0; j < 16; ++j) {
+        q[32 * ib + j] = orc_iq4nl_values[qs[16 * ib + j] & 0xF];
+        q[32 * ib + 16 + j] = orc_iq4nl_values[qs[16 * ib + j] >> 4];
+      }
+    }
+    return 0;
+  }
+  return -1;
+}
+
+/* Q4_0 rows (18-byte blocks: fp16 d, low nibbles = elements 0..15, high nibbles = 16..31, value q - 8) as Q8_0 rows */
+void orc_q4_0_to_q8_0(const uint8_t* src, size_t n_blocks, uint8_t* dst) {
+  for (size_t b = 0; b < n_blocks; ++b) {
+    const uint8_t* s8 = src + 18 * b;
+    uint8_t* d8 = dst + 34 * b;
+    d8[0] = s8[0];
+    d8[1] = s8[1];
+    for (int i = 0; i < 16; ++i) {
+      d8[2 + i] = (uint8_t)(int8_t)((s8[2 + i] & 0xF) - 8);
+      d8[2 + 16 + i] = (uint8_t)(int8_t)((s8[2 + i] >> 4) - 8);
+    }
+  }
+}
+
 /* one weight row -> f32 (src/quants.h:519-616 dequant_row, :319-326 dequant_value) */
 void orc_dequant_row(int type, const uint8_t* row, int K, float* out) {
   for (int s = 0; s < K / 256; ++s) {
-    if (type == ORC_Q4_K) {
+    if (orc_generic(type)) { /* src/quants.h:319-324: d * scale * q - dmin * min, left to right */
+      float wd, wdmin;
+      int8_t wsc[16];
+      uint8_t wmn[16];
+      int has_min;
+      int16_t q[256];
+      orc_decode_generic_sb(type, row + (size_t)s * orc_sb_bytes(type), &wd, &wdmin, wsc, wmn, &has_min, q);
+      for (int e = 0; e < 256; ++e)
+        out[s * 256 + e] = wd * wsc[e / 16] * q[e] - (has_min ? wdmin * wmn[e / 16] : 0.0f);
+    } else if (type == ORC_Q4_0) {
+      for (int b = 0; b < 8; ++b) {
+        const uint8_t* blk = row + (size_t)s * 144 + 18 * b;
+        uint16_t dh;
+        memcpy(&dh, blk, 2);
+        const float d = orc_fp16_to_f32(dh);
+        for (int i = 0; i < 16; ++i) {
+          out[s * 256 + 32 * b + i] = d * (float)((blk[2 + i] & 0xF) - 8);
+          out[s * 256 + 32 * b + 16 + i] = d * (float)((blk[2 + i] >> 4) - 8);
+        }
+      }
+    } else if (type == ORC_Q4_K) {
       float d, dmin;
       uint8_t sc[8], mn[8], q[256];
       orc_q4k_decode_sb(row + (size_t)s * 144, &d, &dmin, sc, mn, q);
@@ -411,6 +529,118 @@ void orc_matmul_gemm_order(int type, const uint8_t* w, int N, int K, const int8_
     free(q);
     free(dd);
     free(sm);
+  }
+}
+
+/* ---------------------------------------------------------------- the same for the generic view (Q5_K, Q6_K, IQ4_XS)
+ * Per 32-block with its two 16-element halves (zero/kernels/decode.cl:992-1004): lo / hi = integer dots of the halves,
+ * bs0 / bs1 = sums of the activations of the halves,
+ *   with mins:    term = sa * (d * (float)(sc0*lo + sc1*hi) - dmin * (float)(mn0*bs0 + mn1*bs1))
+ *   without:      term = sa * d * (float)(sc0*lo + sc1*hi)
+ * order 0 ("gemv"): sixteen lanes as in orc_matmul_gemv_order.  order 1 ("gemm"): the reference has no exact GEMM for these
+ * types (it requantises them, src/quants.h:683-686); the order defined here is the Q4_K one with per-16 scales:
+ *   tq = fma(sl, (float)(sc0*lo + sc1*hi), fma(sh, (float)(...), tq)), tmn likewise, res = fma(d, tq, fma(-dmin, tmn, res)). */
+typedef struct {
+  int16_t* q;      /* [K], offset subtracted */
+  float* wd;       /* [K/256] d, then [K/256] dmin */
+  int8_t* wsc;     /* [K/16] */
+  uint8_t* wmn;    /* [K/16] */
+  int has_min;
+} orc_grow;
+
+static void grow_alloc(orc_grow* g, int K) {
+  g->q = (int16_t*)malloc((size_t)K * 2);
+  g->wd = (float*)malloc((size_t)(K / 256) * 8);
+  g->wsc = (int8_t*)malloc((size_t)K / 16);
+  g->wmn = (uint8_t*)malloc((size_t)K / 16);
+}
+static void grow_free(orc_grow* g) { free(g->q); free(g->wd); free(g->wsc); free(g->wmn); }
+static void grow_decode(orc_grow* g, int type, const uint8_t* row, int K) {
+  const int nsb = K / 256;
+  for (int s = 0; s < nsb; ++s)
+    orc_decode_generic_sb(type, row + (size_t)s * orc_sb_bytes(type), &g->wd[s], &g->wd[nsb + s], g->wsc + 16 * s, g->wmn + 16 * s,
+                          &g->has_min, g->q + 256 * s);
+}
+static inline int32_t dot16(const int8_t* a, const int16_t* w) {
+  int32_t s = 0;
+  for (int i = 0; i < 16; ++i) s += (int32_t)a[i] * (int32_t)w[i];
+  return s;
+}
+static inline int32_t sum16(const int8_t* a) {
+  int32_t s = 0;
+  for (int i = 0; i < 16; ++i) s += a[i];
+  return s;
+}
+
+void orc_block_dots_generic(int type, const uint8_t* w, int N, int K, const int8_t* aq, int M, int32_t* dots) {
+  const int nb = K / 32;
+  const size_t rb = (size_t)(K / 256) * orc_sb_bytes(type);
+#pragma omp parallel
+  {
+    orc_grow g;
+    grow_alloc(&g, K);
+#pragma omp for schedule(dynamic, 8)
+    for (int n = 0; n < N; ++n) {
+      grow_decode(&g, type, w + (size_t)n * rb, K);
+      for (int m = 0; m < M; ++m)
+        for (int b = 0; b < nb; ++b) dots[((size_t)m * N + n) * nb + b] = dot32(aq + (size_t)m * K + 32 * b, g.q + 32 * b);
+    }
+    grow_free(&g);
+  }
+}
+
+void orc_matmul_generic(int type, const uint8_t* w, int N, int K, const int8_t* aq, const float* asc, int Mp, int T, float* C,
+                        int ldc, int c_off, int acc, int order) {
+  const int nb = K / 32, nsb = K / 256;
+  const size_t rb = (size_t)nsb * orc_sb_bytes(type);
+#pragma omp parallel
+  {
+    orc_grow g;
+    grow_alloc(&g, K);
+#pragma omp for schedule(dynamic, 8)
+    for (int n = 0; n < N; ++n) {
+      grow_decode(&g, type, w + (size_t)n * rb, K);
+      for (int t = 0; t < T; ++t) {
+        float v = 0.0f;
+        if (order == 0) {
+          float lane[16];
+          for (int l = 0; l < 16; ++l) lane[l] = 0.0f;
+          for (int b = 0; b < nb; ++b) {
+            const int8_t* a = aq + (size_t)t * K + 32 * b;
+            const float sa = asc[(size_t)b * Mp + t], d = g.wd[b / 8], dmin = g.wd[nsb + b / 8];
+            const int32_t x = (int32_t)g.wsc[2 * b] * dot16(a, g.q + 32 * b) + (int32_t)g.wsc[2 * b + 1] * dot16(a + 16, g.q + 32 * b + 16);
+            if (g.has_min) {
+              const int32_t y = (int32_t)g.wmn[2 * b] * sum16(a) + (int32_t)g.wmn[2 * b + 1] * sum16(a + 16);
+              lane[b % 16] += sa * (d * (float)x - dmin * (float)y);
+            } else {
+              lane[b % 16] += sa * d * (float)x;
+            }
+          }
+          for (int l = 0; l < 16; ++l) v += lane[l];
+        } else {
+          for (int s = 0; s < nsb; ++s) {
+            float tq = 0.0f, tmn = 0.0f;
+            for (int j = 0; j < 4; ++j) {
+              int32_t x[2], y[2];
+              float sc2[2];
+              for (int h = 0; h < 2; ++h) {
+                const int b = 8 * s + 2 * j + h;
+                const int8_t* a = aq + (size_t)t * K + 32 * b;
+                sc2[h] = asc[(size_t)b * Mp + t];
+                x[h] = (int32_t)g.wsc[2 * b] * dot16(a, g.q + 32 * b) + (int32_t)g.wsc[2 * b + 1] * dot16(a + 16, g.q + 32 * b + 16);
+                y[h] = (int32_t)g.wmn[2 * b] * sum16(a) + (int32_t)g.wmn[2 * b + 1] * sum16(a + 16);
+              }
+              tq = fmaf(sc2[0], (float)x[0], fmaf(sc2[1], (float)x[1], tq));
+              tmn = fmaf(sc2[0], (float)y[0], fmaf(sc2[1], (float)y[1], tmn));
+            }
+            v = fmaf(g.wd[s], tq, fmaf(-g.wd[nsb + s], tmn, v));
+          }
+        }
+        float* c = C + (size_t)t * ldc + c_off + n;
+        *c = order == 0 ? (acc ? *c + v : v) : store_mode(*c, v, acc);
+      }
+    }
+    grow_free(&g);
   }
 }
 

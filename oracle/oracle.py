@@ -13,6 +13,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 Q8_0, Q4_K = 8, 12
+Q4_0, Q5_K, Q6_K, IQ4_XS = 2, 13, 14, 23
+GENERIC = (Q5_K, Q6_K, IQ4_XS)   # types decoded into the reference's generic view (scale and min per 16 elements)
 
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C")
 _i8p = np.ctypeslib.ndpointer(np.int8, flags="C")
@@ -135,13 +137,39 @@ def dequant_rows(qtype: int, w: np.ndarray, K: int) -> np.ndarray:
     return out
 
 
+def q4_0_as_q8_0(w: np.ndarray) -> np.ndarray:
+    """Q4_0 rows [N, K/32*18] rewritten as Q8_0 rows [N, K/32*34] (same scale, int8 quants q - 8): exact."""
+    w = np.ascontiguousarray(w, np.uint8)
+    nblk = w.shape[1] // 18
+    out = np.empty((w.shape[0], nblk * 34), np.uint8)
+    lib().orc_q4_0_to_q8_0(_vp(w), C.c_size_t(w.shape[0] * nblk), _vp(out))
+    return out
+
+
+def decode_generic_sb(qtype: int, p: np.ndarray):
+    """One superblock of Q5_K / Q6_K / IQ4_XS in the generic view: wd, wdmin, wsc[16], wmn[16], has_min, q[256] (offset
+    subtracted)."""
+    wd, wdmin, hm = C.c_float(), C.c_float(), C.c_int()
+    wsc, wmn, q = np.empty(16, np.int8), np.empty(16, np.uint8), np.empty(256, np.int16)
+    rc = lib().orc_decode_generic_sb(qtype, _vp(np.ascontiguousarray(p, np.uint8)), C.byref(wd), C.byref(wdmin), _vp(wsc), _vp(wmn),
+                                     C.byref(hm), _vp(q))
+    assert rc == 0
+    return wd.value, wdmin.value, wsc, wmn, bool(hm.value), q
+
+
 def block_dots(qtype: int, w: np.ndarray, K: int, aq: np.ndarray):
     """dots [M, N, K/32] int32 and asum [M, K/32] int32 for the first M = aq.shape[0] rows."""
+    if qtype == Q4_0:
+        qtype, w = Q8_0, q4_0_as_q8_0(w)
     w = np.ascontiguousarray(w, np.uint8)
     aq = np.ascontiguousarray(aq, np.int8)
     N, M = w.shape[0], aq.shape[0]
     dots = np.empty((M, N, K // 32), np.int32)
     asum = np.empty((M, K // 32), np.int32)
+    if qtype in GENERIC:
+        lib().orc_block_dots_generic(qtype, _vp(w), N, K, _vp(aq), M, _vp(dots))
+        asum[:] = aq.astype(np.int32).reshape(M, K // 32, 32).sum(axis=2)
+        return dots, asum
     lib().orc_block_dots(qtype, _vp(w), N, K, _vp(aq), M, _vp(dots), _vp(asum))
     return dots, asum
 
@@ -150,12 +178,17 @@ def matmul(qtype: int, w: np.ndarray, K: int, aq: np.ndarray, asc: np.ndarray, T
            C_in: np.ndarray | None = None, ldc: int | None = None, c_off: int = 0, acc: int = 0) -> np.ndarray:
     """f32 outputs in one of the reference's two summation orders ("gemv": decode.cl, "gemm": gemm.cl) or "f64"
     (tools/ref_forward.cpp: dequantised weights, double accumulation)."""
+    if qtype == Q4_0 and order != "f64":
+        qtype, w = Q8_0, q4_0_as_q8_0(w)
     w = np.ascontiguousarray(w, np.uint8)
     aq = np.ascontiguousarray(aq, np.int8)
     asc = np.ascontiguousarray(asc, np.float32)
     N, Mp = w.shape[0], asc.shape[1]
     ldc = ldc or N
     out = np.zeros((T, ldc), np.float32) if C_in is None else np.array(C_in, np.float32, copy=True, order="C")
+    if qtype in GENERIC and order != "f64":
+        lib().orc_matmul_generic(qtype, _vp(w), N, K, _vp(aq), _vp(asc), Mp, T, _vp(out), ldc, c_off, acc, 0 if order == "gemv" else 1)
+        return out
     if order == "f64":
         assert acc == 0 and c_off == 0
         lib().orc_matmul_f64(qtype, _vp(w), N, K, _vp(aq), _vp(asc), Mp, T, _vp(out), ldc)
@@ -303,3 +336,12 @@ def ref_silu(x: np.ndarray) -> np.ndarray:
     f = ref().ref_silu
     f.restype, f.argtypes = C.c_float, [C.c_float]
     return np.array([f(float(v)) for v in np.asarray(x, np.float32).ravel()], np.float32).reshape(np.shape(x))
+
+
+def ref_decode_generic_sb(qtype: int, p: np.ndarray):
+    """The reference's decode_sb (src/quants.h:89) in its generic view: wd, wdmin, wsc[16], wmn[16], has_min, q - qoff."""
+    wd, wdmin, hm = C.c_float(), C.c_float(), C.c_int()
+    wsc, wmn, q = np.empty(16, np.int8), np.empty(16, np.uint8), np.empty(256, np.int16)
+    ref().ref_decode_generic_sb(qtype, _vp(np.ascontiguousarray(p, np.uint8)), C.byref(wd), C.byref(wdmin), _vp(wsc), _vp(wmn),
+                                C.byref(hm), _vp(q))
+    return wd.value, wdmin.value, wsc, wmn, bool(hm.value), q

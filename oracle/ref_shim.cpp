@@ -44,6 +44,17 @@ void ref_decode_sb(uint32_t type, const uint8_t* p, float* d, float* dmin, uint8
   for (int i = 0; i < 256; ++i) q[i] = o.q[i];
 }
 
+// the generic view of the same decode (DecodedSB::wd .. has_min, src/quants.h:80-86), qoff subtracted from q
+void ref_decode_generic_sb(uint32_t type, const uint8_t* p, float* wd, float* wdmin, int8_t* wsc, uint8_t* wmn, int* has_min, int16_t* q) {
+  DecodedSB o;
+  decode_sb(type, p, o);
+  *wd = o.wd;
+  *wdmin = o.wdmin;
+  *has_min = o.has_min ? 1 : 0;
+  for (int i = 0; i < 16; ++i) { wsc[i] = o.wsc[i]; wmn[i] = o.has_min ? o.wmn[i] : 0; }
+  for (int i = 0; i < 256; ++i) q[i] = (int16_t)(o.q[i] - o.qoff);
+}
+
 void ref_dequant_row(uint32_t type, const uint8_t* row, int K, float* out) { dequant_row(type, row, K, out); }
 
 // src/quants.h:728: the reference's GPU raw form of one superblock (Q8_0: scales first)

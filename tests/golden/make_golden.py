@@ -15,8 +15,12 @@ What is stored (all inputs seeded; every array small):
                  step in numpy: stable descending sort (ties keep the lower expert first), exp(l - l_max) in double,
                  normalised over the chosen NU, cast to float.
 
+  types.npz      Q4_0, Q5_K, Q6_K, IQ4_XS rows: decode_sb in its generic view (src/quants.h:72-87), dequant_row, and
+                 tools/ref_forward.cpp matmul() outputs on them
+
     python tests/golden/make_golden.py            # everything
     python tests/golden/make_golden.py moe        # only moe.npz (leaves the other files untouched)
+    python tests/golden/make_golden.py types      # only types.npz
 """
 import os
 import sys
@@ -76,12 +80,50 @@ def make_moe():
                         g=g, u=u, h=h, dn=dn)
 
 
+def make_types():
+    rng = np.random.default_rng(20261202)
+    K, N = 512, 5
+    x = rng.standard_normal((4, K), dtype=np.float32)
+    out = {"x": x}
+    tensors = {}
+    for name, qt in (("q4_0", 2), ("q5_k", 13), ("q6_k", 14), ("iq4_xs", 23)):
+        w = S.make_weight(qt, N, K, 40 + qt)
+        if qt == 13:
+            w[0, 0:4] = 0                 # d = dmin = 0
+            w[1, 4:16] = 0xFF             # every scale / min 63
+        if qt == 14:
+            w[0, 192:208] = 0x80          # every scale -128
+            w[1, 0:192] = 0xFF            # every quant 63 - 32 = 31
+            w[2, 0:192] = 0               # every quant -32
+        out["w_" + name] = w
+        out["deq_" + name] = O.ref_dequant_rows(qt, w, K)
+        if qt != 2:
+            sbb = S.sb_bytes(qt)
+            dec = [O.ref_decode_generic_sb(qt, w[n, sbb * s:sbb * (s + 1)]) for n in range(N) for s in range(K // 256)]
+            out["wd_" + name] = np.array([d[0] for d in dec], np.float32)
+            out["wdmin_" + name] = np.array([d[1] for d in dec], np.float32)
+            out["wsc_" + name] = np.stack([d[2] for d in dec])
+            out["wmn_" + name] = np.stack([d[3] for d in dec])
+            out["q_" + name] = np.stack([d[5] for d in dec])
+        tensors[name] = (qt, w, N, K)
+    with tempfile.TemporaryDirectory() as d:
+        p = os.path.join(d, "t.gguf")
+        S.write_gguf(p, tensors)
+        for name in tensors:
+            out["y_" + name] = O.ref_forward_matmul(p, name, x, N)
+    np.savez_compressed(os.path.join(OUT, "types.npz"), **out)
+
+
 def main():
     O.build(ref=True)
     assert O.ref() is not None, "oracle/_ref/libizb_ref.so missing: the reference sources are needed"
     if sys.argv[1:] == ["moe"]:
         make_moe()
         print("moe.npz written to", OUT)
+        return
+    if sys.argv[1:] == ["types"]:
+        make_types()
+        print("types.npz written to", OUT)
         return
     rng = np.random.default_rng(20261125)
 
@@ -145,6 +187,7 @@ def main():
     yn = O.ref_rmsnorm(xn, wn, 1e-6)
     np.savez_compressed(os.path.join(OUT, "rmsnorm.npz"), x=xn, w=wn, eps=np.float32(1e-6), y=yn)
     make_moe()
+    make_types()
     print("golden vectors written to", OUT)
 
 

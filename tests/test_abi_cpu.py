@@ -73,3 +73,26 @@ def test_no_gpu_means_an_error_not_a_fallback():
     assert b"no CPU path" in L.izb_last_error() or b"sm_100a" in L.izb_last_error()
     with pytest.raises(izb.IzbError):
         izb.Weight(12, rows, 16, 256)
+
+
+def test_host_decoder_of_further_weight_types_matches_the_oracle():
+    """izb_weight_decode_host (the loader's decoder, no device needed) against the oracle's restatement of the reference's
+    decode_sb generic view, field by field, and Q4_0 against its Q8_0 rewrite."""
+    import numpy as np
+    import arcinferzero_b200 as izb
+    from arcinferzero_b200 import synth as S
+    from oracle import oracle as O
+    K, N = 768, 7
+    for qt in (13, 14, 23):
+        w = S.make_weight(qt, N, K, 70 + qt)
+        dev = izb.weight_decode_host(qt, w, K).reshape(N, K // 256, 304)
+        sbb = S.sb_bytes(qt)
+        for n in range(N):
+            for s in range(K // 256):
+                wd, wdmin, wsc, wmn, has_min, q = O.decode_generic_sb(qt, w[n, sbb * s:sbb * (s + 1)])
+                b = dev[n, s]
+                assert b[0:4].view(np.float32)[0] == np.float32(wd) and b[4:8].view(np.float32)[0] == np.float32(wdmin)
+                assert (b[8:24].view(np.int8) == wsc).all() and (b[24:40] == wmn).all() and (b[40:48] == 0).all()
+                assert (b[48:304].view(np.int8) == q).all()
+    w = S.make_weight(2, N, K, 72)
+    assert (izb.weight_decode_host(2, w, K) == O.q4_0_as_q8_0(w)).all()

@@ -257,3 +257,42 @@ def test_q8_0_regrouped_device_form_matches_reference_vectors(golden_dir):
             want = np.concatenate([blocks[:, :2].reshape(-1), blocks[:, 2:].reshape(-1)])
             assert (raw[i][:272] == want).all()
             i += 1
+
+
+TYPES = (("q4_0", 2), ("q5_k", 13), ("q6_k", 14), ("iq4_xs", 23))
+
+
+@pytest.mark.parametrize("name,qt", TYPES)
+def test_further_weight_types_match_reference_vectors(golden_dir, name, qt):
+    """types.npz: decode_sb's generic view (wd, wdmin, a scale and a min per 16 elements, quants with their offset removed),
+    dequant_row and tools/ref_forward.cpp's matmul() for Q4_0, Q5_K, Q6_K and IQ4_XS rows: the restated decoders bit for
+    bit, the restated integer paths (both summation orders and the f64 model) within 1e-5 of max|ref|."""
+    g = np.load(os.path.join(golden_dir, "types.npz"))
+    w, K = g["w_" + name], 512
+    assert (bits(O.dequant_rows(qt, w, K)) == bits(g["deq_" + name])).all()
+    if qt != 2:
+        sbb = S.sb_bytes(qt)
+        i = 0
+        for n in range(w.shape[0]):
+            for s in range(K // 256):
+                wd, wdmin, wsc, wmn, has_min, q = O.decode_generic_sb(qt, w[n, sbb * s:sbb * (s + 1)])
+                assert np.float32(wd) == g["wd_" + name][i] and np.float32(wdmin) == g["wdmin_" + name][i]
+                assert (wsc == g["wsc_" + name][i]).all() and (wmn == g["wmn_" + name][i]).all() and (q == g["q_" + name][i]).all()
+                i += 1
+    else:
+        # Q4_0 rewritten as Q8_0 blocks dequantises to the same floats
+        assert (bits(O.dequant_rows(8, O.q4_0_as_q8_0(w), K)) == bits(g["deq_" + name])).all()
+    aq, asc, _ = O.quantize_act(g["x"])
+    y = g["y_" + name]
+    for order in ("f64", "gemv", "gemm"):
+        got = O.matmul(qt, w, K, aq, asc, g["x"].shape[0], order)
+        assert np.abs(got.astype(np.float64) - y).max() <= 1e-5 * np.abs(y).max(), (name, order)
+    # the f64 model IS the reference's arithmetic
+    assert (bits(O.matmul(qt, w, K, aq, asc, g["x"].shape[0], "f64")) == bits(y)).all()
+    # block dots: the integer sums over 32 of a * (q - offset)
+    dots, asum = O.block_dots(qt, w, K, aq)
+    deq_int = None
+    if qt != 2:
+        qs = g["q_" + name].reshape(w.shape[0], K).astype(np.int64)
+        deq_int = np.einsum("mbk,nbk->mnb", aq.astype(np.int64).reshape(-1, K // 32, 32), qs.reshape(-1, K // 32, 32))
+        assert (dots == deq_int).all()

@@ -26,9 +26,10 @@ SYMBOLS = [
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
-    "izb_moe_route", "izb_moe_sort", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
+    "izb_moe_route", "izb_moe_route_ex", "izb_moe_sort", "izb_moe_sort_ex", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
+    "izb_moe_combine_ex",
     "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_create_ex", "izb_tp_wait", "izb_tp_abort", "izb_tp_destroy", "izb_tp_allreduce_rows",
-    "izb_tp_reduce_quant_gather",
+    "izb_tp_reduce_quant_gather", "izb_tp_gather_logits",
 ]
 
 
@@ -292,20 +293,24 @@ def matmul_host(w: Weight, x_host, out_host, mat: int = 0) -> None:
 
 
 # ---------------------------------------------------------------------------------------------- mixture of experts
-def moe_route(logits, NU: int):
+def moe_route(logits, NU: int, shared_gate: bool = False):
+    """logits [T, NE] (or [T, NE + 1] with the shared expert's gate logit last) -> ids, wts, counts (, sgate [T])."""
     import torch
-    T, NE = logits.shape
+    T = logits.shape[0]
+    NE = logits.shape[1] - (1 if shared_gate else 0)
     ids = torch.empty((T, NU), dtype=torch.int32, device=logits.device)
     wts = torch.empty((T, NU), dtype=torch.float32, device=logits.device)
     counts = torch.empty((NE,), dtype=torch.int32, device=logits.device)
-    _check(lib().izb_moe_route(_p(logits), logits.stride(0), T, NE, NU, _p(ids), _p(wts), _p(counts), _stream()))
-    return ids, wts, counts
+    sgate = torch.empty((T,), dtype=torch.float32, device=logits.device) if shared_gate else None
+    _check(lib().izb_moe_route_ex(_p(logits), logits.stride(0), T, NE, NU, _p(ids), _p(wts), _p(counts), _p(sgate), _stream()))
+    return (ids, wts, counts, sgate) if shared_gate else (ids, wts, counts)
 
 
-def moe_sort(ids, wts, counts, TM: int):
+def moe_sort(ids, wts, counts, TM: int, expert_range: tuple[int, int] | None = None):
     import torch
     T, NU = ids.shape
     NE = counts.shape[0]
+    e0, e1 = expert_range or (0, NE)
     dev = ids.device
     max_tiles = (T * NU + TM - 1) // TM + NE
     offs = torch.empty((NE + 1,), dtype=torch.int32, device=dev)
@@ -313,8 +318,8 @@ def moe_sort(ids, wts, counts, TM: int):
     stok = torch.empty((T * NU,), dtype=torch.int32, device=dev)
     swt = torch.empty((T * NU,), dtype=torch.float32, device=dev)
     inv = torch.empty((T * NU,), dtype=torch.int32, device=dev)
-    _check(lib().izb_moe_sort(_p(ids), _p(wts), _p(counts), T, NE, NU, TM, _p(offs), _p(tiles), max_tiles, _p(stok), _p(swt),
-                              _p(inv), _stream()))
+    _check(lib().izb_moe_sort_ex(_p(ids), _p(wts), _p(counts), T, NE, NU, TM, e0, e1, _p(offs), _p(tiles), max_tiles, _p(stok),
+                                 _p(swt), _p(inv), _stream()))
     return offs, tiles, max_tiles, stok, swt, inv
 
 
@@ -333,9 +338,9 @@ def moe_down(wd: Weight, hq, hsc, tiles, max_tiles: int, TM: int, swt, S: int):
     return y
 
 
-def moe_combine(x, y, inv, NU: int):
+def moe_combine(x, y, inv, NU: int, sh=None, sgate=None, partial: bool = False):
     T, E = x.shape
-    _check(lib().izb_moe_combine(_p(x), _p(y), _p(inv), T, NU, E, _stream()))
+    _check(lib().izb_moe_combine_ex(_p(x), _p(y), _p(inv), T, NU, E, _p(sh), _p(sgate), int(partial), _stream()))
     return x
 
 
@@ -380,6 +385,15 @@ class TpComm:
         rows, E = part.shape
         _check(lib().izb_tp_reduce_quant_gather(self.handle, _p(x), _p(part), rows, E, _p(xsum), _p(aq), _p(asc), _stream()))
         return aq, asc
+
+    def gather_logits(self, local, vocab: int, full=None):
+        """local [rows, >= this rank's vocabulary rows] f32 -> full [rows, vocab] on every rank (rank order)."""
+        import torch
+        rows = local.shape[0]
+        if full is None:
+            full = torch.empty((rows, vocab), dtype=torch.float32, device=local.device)
+        _check(lib().izb_tp_gather_logits(self.handle, _p(local), local.stride(0), rows, vocab, _p(full), full.stride(0), _stream()))
+        return full
 
     def wait(self, timeout_ms: int) -> None:
         """Bounded wait for the current stream's work; raises IzbError (status -7) and aborts the communicator on time-out."""

@@ -34,10 +34,12 @@ __device__ __forceinline__ float route_key_value(unsigned long long k) {
 
 __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int ldl, int T, int NE, int NU,
                                                         int32_t* __restrict__ ids, float* __restrict__ wts,
-                                                        int32_t* __restrict__ counts) {
+                                                        int32_t* __restrict__ counts, float* __restrict__ sgate) {
   const int token = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (token >= T) return;
   const float* row = logits + (size_t)token * ldl;
+  // the shared expert's gate: the sigmoid of the logit after the experts' (SGATE, zero/kernels/moe.cl:44,88)
+  if (sgate && lane == 0) sgate[token] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-row[NE])));
   unsigned long long key[kMaxPerLane];  // 0 = no candidate (past NE, or already chosen)
 #pragma unroll
   for (int i = 0; i < kMaxPerLane; ++i) {
@@ -81,21 +83,24 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
 }
 
 // One thread per expert: offsets (exclusive scan, serial: NE is a few hundred) and the expert's tiles.
+// With an expert range [e0, e1) (the expert-parallel split, tp_moe_mask, zero/kernels/tp.cl:61-64) the other experts count
+// as empty and a tile names its expert by its index in this rank's stack, e - e0.
 __global__ void moe_scan_kernel(const int32_t* __restrict__ counts, int NE, int TM, int32_t* __restrict__ offs,
-                                int32_t* __restrict__ tiles, int max_tiles) {
+                                int32_t* __restrict__ tiles, int max_tiles, int e0, int e1) {
   const int e = threadIdx.x;
   int off = 0, toff = 0;
   for (int i = 0; i < e && i < NE; ++i) {
-    off += counts[i];
-    toff += (counts[i] + TM - 1) / TM;
+    const int ci = (i >= e0 && i < e1) ? counts[i] : 0;
+    off += ci;
+    toff += (ci + TM - 1) / TM;
   }
   if (e < NE) {
-    const int c = counts[e], nt = (c + TM - 1) / TM;
+    const int c = (e >= e0 && e < e1) ? counts[e] : 0, nt = (c + TM - 1) / TM;
     offs[e] = off;
     for (int i = 0; i < nt; ++i) {
       if (toff + i >= max_tiles) break;
       int32_t* tp = tiles + 1 + 3 * (toff + i);
-      tp[0] = e;
+      tp[0] = e - e0;
       tp[1] = off + i * TM;
       tp[2] = min(TM, c - i * TM);
     }
@@ -112,9 +117,14 @@ __global__ void moe_scan_kernel(const int32_t* __restrict__ counts, int NE, int 
 // barrier per pass is enough) gives every pair of the expert its slot.
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, int n,
                                                           int NU, const int32_t* __restrict__ offs, int32_t* __restrict__ stok,
-                                                          float* __restrict__ swt, int32_t* __restrict__ inv) {
+                                                          float* __restrict__ swt, int32_t* __restrict__ inv, int e0, int e1) {
   __shared__ int s_warp[2][8];
   const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (e < e0 || e >= e1) {  // another rank's expert: its pairs get no slot (tp_moe_scatter, zero/kernels/tp.cl:67-78)
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+      if (ids[i] == e) inv[i] = -1;
+    return;
+  }
   int base = offs[e];  // (every thread keeps the running base: no broadcast needed)
   int buf = 0;
   for (int i0 = 0; i0 < n; i0 += 1024, buf ^= 1) {
@@ -213,45 +223,70 @@ __global__ void __launch_bounds__(kWarps * 32) moe_down_kernel(const uint8_t* __
     }
 }
 
+// x[t] += v, v = sum over the token's choices (in choice order, slots < 0 left out) + sgate[t] * sh[t] when a shared expert is
+// given (moe_combine, zero/kernels/moe.cl:344-352); partial: x[t] = v, a rank's share of the sum in the expert-parallel
+// split (tp_moe_combine, zero/kernels/tp.cl:100-111).
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ inv, int T,
-                                   int NU, int E) {
+                                   int NU, int E, const float* __restrict__ sh, const float* __restrict__ sgate, int partial) {
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4, t = blockIdx.x;  // (tokens on x: no 65535 limit)
   if (c >= E) return;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int k = 0; k < NU; ++k) {
-    const float4 a = *reinterpret_cast<const float4*>(y + (size_t)inv[t * NU + k] * E + c);
+    const int s = inv[t * NU + k];
+    if (s < 0) continue;
+    const float4 a = *reinterpret_cast<const float4*>(y + (size_t)s * E + c);
     v.x = __fadd_rn(v.x, a.x); v.y = __fadd_rn(v.y, a.y); v.z = __fadd_rn(v.z, a.z); v.w = __fadd_rn(v.w, a.w);
   }
+  if (sh) {
+    const float g = sgate[t];
+    const float4 a = *reinterpret_cast<const float4*>(sh + (size_t)t * E + c);
+    v.x = __fadd_rn(v.x, __fmul_rn(g, a.x)); v.y = __fadd_rn(v.y, __fmul_rn(g, a.y));
+    v.z = __fadd_rn(v.z, __fmul_rn(g, a.z)); v.w = __fadd_rn(v.w, __fmul_rn(g, a.w));
+  }
   float4* px = reinterpret_cast<float4*>(x + (size_t)t * E + c);
-  float4 o = *px;
-  o.x = __fadd_rn(o.x, v.x); o.y = __fadd_rn(o.y, v.y); o.z = __fadd_rn(o.z, v.z); o.w = __fadd_rn(o.w, v.w);
-  *px = o;
+  if (!partial) {
+    const float4 o = *px;
+    v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y); v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w);
+  }
+  *px = v;
 }
 
 }  // namespace
 
-extern "C" int izb_moe_route(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts,
-                             int32_t* d_counts, void* stream) {
+extern "C" int izb_moe_route_ex(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts,
+                                int32_t* d_counts, float* d_sgate, void* stream) {
   if (!d_logits || !d_ids || !d_wts || !d_counts) IZB_FAIL(IZB_ERR_ARG, "moe_route: null pointer");
-  if (T < 1 || NE < 1 || NE > 32 * kMaxPerLane || NU < 1 || NU > 32 || NU > NE || ldl < NE)
-    IZB_FAIL(IZB_ERR_SHAPE, "moe_route: T=%d NE=%d NU=%d ldl=%d (NE <= 512, NU <= 32)", T, NE, NU, ldl);
+  if (T < 1 || NE < 1 || NE > 32 * kMaxPerLane || NU < 1 || NU > 32 || NU > NE || ldl < NE + (d_sgate ? 1 : 0))
+    IZB_FAIL(IZB_ERR_SHAPE, "moe_route: T=%d NE=%d NU=%d ldl=%d (NE <= 512, NU <= 32, ldl >= NE, + 1 with a shared-expert gate)", T, NE, NU, ldl);
   cudaStream_t st = (cudaStream_t)stream;
   IZB_CUDA(cudaMemsetAsync(d_counts, 0, (size_t)NE * 4, st));
-  IZB_LAUNCH("moe_route", st, moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(d_logits, ldl, T, NE, NU, d_ids, d_wts, d_counts));
+  IZB_LAUNCH("moe_route", st, moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(d_logits, ldl, T, NE, NU, d_ids, d_wts, d_counts, d_sgate));
+  return IZB_OK;
+}
+
+extern "C" int izb_moe_route(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts,
+                             int32_t* d_counts, void* stream) {
+  return izb_moe_route_ex(d_logits, ldl, T, NE, NU, d_ids, d_wts, d_counts, nullptr, stream);
+}
+
+extern "C" int izb_moe_sort_ex(const int32_t* d_ids, const float* d_wts, const int32_t* d_counts, int T, int NE, int NU, int TM,
+                               int e0, int e1, int32_t* d_offs, int32_t* d_tiles, int max_tiles, int32_t* d_stok, float* d_swt,
+                               int32_t* d_inv, void* stream) {
+  if (!d_ids || !d_wts || !d_counts || !d_offs || !d_tiles || !d_stok || !d_swt || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_sort: null pointer");
+  if (T < 1 || NE < 1 || NE > 1024 || NU < 1 || TM < 1) IZB_FAIL(IZB_ERR_SHAPE, "moe_sort: T=%d NE=%d NU=%d TM=%d", T, NE, NU, TM);
+  if (e0 < 0 || e1 > NE || e0 >= e1) IZB_FAIL(IZB_ERR_SHAPE, "moe_sort: expert range [%d, %d) of %d", e0, e1, NE);
+  if (!izb_aligned(d_ids, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_sort: ids must be 16-byte aligned (read four at a time)");
+  if (max_tiles < (T * NU + TM - 1) / TM + NE) IZB_FAIL(IZB_ERR_LIMIT, "moe_sort: max_tiles = %d < %d (pairs/TM + NE)", max_tiles, (T * NU + TM - 1) / TM + NE);
+  cudaStream_t st = (cudaStream_t)stream;
+  IZB_LAUNCH("moe_scan", st, moe_scan_kernel<<<1, 1024, 0, st>>>(d_counts, NE, TM, d_offs, d_tiles, max_tiles, e0, e1));
+  IZB_LAUNCH("moe_scatter", st, moe_scatter_kernel<<<NE, 256, 0, st>>>(d_ids, d_wts, T * NU, NU, d_offs, d_stok, d_swt, d_inv, e0, e1));
   return IZB_OK;
 }
 
 extern "C" int izb_moe_sort(const int32_t* d_ids, const float* d_wts, const int32_t* d_counts, int T, int NE, int NU, int TM,
                             int32_t* d_offs, int32_t* d_tiles, int max_tiles, int32_t* d_stok, float* d_swt, int32_t* d_inv,
                             void* stream) {
-  if (!d_ids || !d_wts || !d_counts || !d_offs || !d_tiles || !d_stok || !d_swt || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_sort: null pointer");
-  if (T < 1 || NE < 1 || NE > 1024 || NU < 1 || TM < 1) IZB_FAIL(IZB_ERR_SHAPE, "moe_sort: T=%d NE=%d NU=%d TM=%d", T, NE, NU, TM);
-  if (!izb_aligned(d_ids, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_sort: ids must be 16-byte aligned (read four at a time)");
-  if (max_tiles < (T * NU + TM - 1) / TM + NE) IZB_FAIL(IZB_ERR_LIMIT, "moe_sort: max_tiles = %d < %d (pairs/TM + NE)", max_tiles, (T * NU + TM - 1) / TM + NE);
-  cudaStream_t st = (cudaStream_t)stream;
-  IZB_LAUNCH("moe_scan", st, moe_scan_kernel<<<1, 1024, 0, st>>>(d_counts, NE, TM, d_offs, d_tiles, max_tiles));
-  IZB_LAUNCH("moe_scatter", st, moe_scatter_kernel<<<NE, 256, 0, st>>>(d_ids, d_wts, T * NU, NU, d_offs, d_stok, d_swt, d_inv));
-  return IZB_OK;
+  return izb_moe_sort_ex(d_ids, d_wts, d_counts, T, NE, NU, TM, 0, NE, d_offs, d_tiles, max_tiles, d_stok, d_swt, d_inv, stream);
 }
 
 int izb_moe_gateup_tiles(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
@@ -290,14 +325,21 @@ int izb_moe_down_tiles(const izb_weight* wd, const int8_t* d_hq, const float* d_
   return IZB_OK;
 }
 
-extern "C" int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, void* stream) {
+extern "C" int izb_moe_combine_ex(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, const float* d_sh,
+                                  const float* d_sgate, int partial, void* stream) {
   if (!d_x || !d_y || !d_inv) IZB_FAIL(IZB_ERR_ARG, "moe_combine: null pointer");
+  if ((d_sh == nullptr) != (d_sgate == nullptr)) IZB_FAIL(IZB_ERR_ARG, "moe_combine: the shared expert's output and its gate come together");
   if (T < 1 || NU < 1 || E < 4 || E % 4) IZB_FAIL(IZB_ERR_SHAPE, "moe_combine: T=%d NU=%d E=%d (E %% 4 == 0)", T, NU, E);
-  if (!izb_aligned(d_x, 16) || !izb_aligned(d_y, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_combine: x, y must be 16-byte aligned");
+  if (!izb_aligned(d_x, 16) || !izb_aligned(d_y, 16) || (d_sh && !izb_aligned(d_sh, 16))) IZB_FAIL(IZB_ERR_ALIGN, "moe_combine: x, y, sh must be 16-byte aligned");
   if ((E / 4 + 127) / 128 > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_combine: E = %d too wide", E);
   dim3 grid(T, (E / 4 + 127) / 128);
-  IZB_LAUNCH("moe_combine", (cudaStream_t)stream, moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(d_x, d_y, d_inv, T, NU, E));
+  IZB_LAUNCH("moe_combine", (cudaStream_t)stream,
+             moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(d_x, d_y, d_inv, T, NU, E, d_sh, d_sgate, partial ? 1 : 0));
   return IZB_OK;
+}
+
+extern "C" int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, void* stream) {
+  return izb_moe_combine_ex(d_x, d_y, d_inv, T, NU, E, nullptr, nullptr, 0, stream);
 }
 
 // grouped tensor-core path (izb_gemm_tc.cu): tiles of up to 128 slots; +1 = shape not taken

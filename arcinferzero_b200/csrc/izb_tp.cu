@@ -33,6 +33,8 @@ __global__ void tp_add1_v4_kernel(float4* __restrict__ x, const float4* __restri
   x[i] = a;
 }
 
+extern "C" int izb_tp_range(int64_t total, int64_t unit, int nranks, int rank, int64_t* begin, int64_t* end);
+
 // ---- the few NCCL entry points, by their public C signatures (nccl.h)
 typedef struct ncclComm* ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
@@ -63,6 +65,7 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*GroupStart)() = nullptr;
   int (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
@@ -80,7 +83,7 @@ void load_nccl() {
   if (!g_nccl.h) return;
 #define SYM(f) *(void**)(&g_nccl.f) = dlsym(g_nccl.h, "nccl" #f)
   SYM(GetUniqueId); SYM(CommInitRank); SYM(CommDestroy); SYM(AllReduce); SYM(ReduceScatter); SYM(AllGather);
-  SYM(GroupStart); SYM(GroupEnd); SYM(GetErrorString); SYM(CommInitRankConfig); SYM(CommGetAsyncError); SYM(CommAbort);
+  SYM(GroupStart); SYM(GroupEnd); SYM(GetErrorString); SYM(CommInitRankConfig); SYM(CommGetAsyncError); SYM(CommAbort); SYM(Broadcast);
 #undef SYM
   g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllReduce && g_nccl.ReduceScatter &&
               g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
@@ -328,5 +331,44 @@ extern "C" int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d
   for (int r = 1; r < R; ++r)
     IZB_CUDA(cudaMemcpy2DAsync(d_asc + (size_t)r * own, (size_t)rows * 4, sc_stage + (size_t)r * (E / 32) * own, (size_t)own * 4,
                                (size_t)own * 4, (size_t)(E / 32), cudaMemcpyDeviceToDevice, st));
+  return IZB_OK;
+}
+
+// The output head split by vocabulary rows (zero/mgpu/engine_tp_shard.h:68-72 with units of 16 rows; the reference joins the
+// shards' logits on the host in rank order, zero/mgpu/engine_tp.h:853-862).  Every rank passes its own logits
+// d_local [rows][ld_local] (its vocabulary rows [begin_r, end_r) of izb_tp_range(vocab, 16, nranks, rank) in the first
+// end_r - begin_r columns) and receives all of them in d_full [rows][ld_full]: one broadcast per rank and token row, grouped.
+extern "C" int izb_tp_gather_logits(izb_tp* tp, const float* d_local, int ld_local, int rows, int vocab, float* d_full, int ld_full,
+                                    void* stream) {
+  if (!tp || !d_local || !d_full) IZB_FAIL(IZB_ERR_ARG, "tp_gather_logits: null pointer");
+  if (rows < 1 || rows > 64 || vocab < 1 || ld_full < vocab) IZB_FAIL(IZB_ERR_SHAPE, "tp_gather_logits: rows=%d (1..64) vocab=%d ld_full=%d", rows, vocab, ld_full);
+  if (int rc = izb_require_device(tp->device, "tp_gather_logits")) return rc;
+  if (int rc = tp_usable(tp, "tp_gather_logits")) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int R = tp->nranks;
+  int64_t b0 = 0, b1 = 0;
+  izb_tp_range(vocab, 16, R, tp->rank, &b0, &b1);
+  if (tp->rank == R - 1) b1 = vocab;  // (the rows past the last whole unit of 16 belong to the last rank)
+  if (ld_local < (int)(b1 - b0)) IZB_FAIL(IZB_ERR_SHAPE, "tp_gather_logits: ld_local = %d < this rank's %lld rows", ld_local, (long long)(b1 - b0));
+  if (R == 1) {
+    IZB_CUDA(cudaMemcpy2DAsync(d_full, (size_t)ld_full * 4, d_local, (size_t)ld_local * 4, (size_t)vocab * 4, rows, cudaMemcpyDeviceToDevice, st));
+    return IZB_OK;
+  }
+  if (!g_nccl.Broadcast) IZB_FAIL(IZB_ERR_NCCL, "tp_gather_logits: ncclBroadcast is missing");
+  IZB_NCCL(g_nccl.GroupStart());
+  int worst = ncclSuccess;
+  for (int r = 0; r < R; ++r) {
+    int64_t rb = 0, re = 0;
+    izb_tp_range(vocab, 16, R, r, &rb, &re);
+    if (r == R - 1) re = vocab;  // (rows past the last whole unit of 16 belong to the last rank)
+    if (re <= rb) continue;
+    for (int t = 0; t < rows; ++t) {
+      const float* src = r == tp->rank ? d_local + (size_t)t * ld_local : d_full + (size_t)t * ld_full + rb;  // (ignored on non-roots)
+      int rr = g_nccl.Broadcast(src, d_full + (size_t)t * ld_full + rb, (size_t)(re - rb), ncclFloat32, r, tp->comm, st);
+      if (rr != ncclSuccess && rr != ncclInProgress) worst = rr;
+    }
+  }
+  IZB_NCCL(worst);
+  IZB_TP_NCCL(tp, g_nccl.GroupEnd(), "ncclBroadcast");
   return IZB_OK;
 }

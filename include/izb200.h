@@ -227,12 +227,23 @@ int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, int M, float
  * expert id), weights renormalised over the selection.  d_ids, d_wts: [T][NU]; d_counts: [NE] (overwritten). */
 int izb_moe_route(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts, int32_t* d_counts,
                   void* stream);
+/* The same with the shared expert's gate (SGATE, zero/kernels/moe.cl:44,88): d_sgate[t] = 1 / (1 + exp(-logits[t][NE])), the
+ * sigmoid of the logit that follows the NE expert logits of a row (ldl >= NE + 1).  d_sgate == NULL: izb_moe_route. */
+int izb_moe_route_ex(const float* d_logits, int ldl, int T, int NE, int NU, int32_t* d_ids, float* d_wts, int32_t* d_counts,
+                     float* d_sgate, void* stream);
 /* moe_scan + moe_scatter (zero/kernels/moe.cl:141-179), deterministic: slots of an expert in increasing (token, choice)
  * order.  d_offs [NE+1]; d_tiles [1 + 3*max_tiles] = count, then (expert, first slot, rows <= TM); d_stok, d_swt, d_inv
  * [T*NU]. */
 int izb_moe_sort(const int32_t* d_ids, const float* d_wts, const int32_t* d_counts, int T, int NE, int NU, int TM,
                  int32_t* d_offs, int32_t* d_tiles, int max_tiles, int32_t* d_stok, float* d_swt, int32_t* d_inv,
                  void* stream);
+/* Expert-parallel form (the reference's split of a MoE model by expert, zero/mgpu/engine_tp_shard.h:169-199,
+ * zero/kernels/tp.cl:55-78): this rank holds the experts [e0, e1).  The other experts count as empty (no slots, no tiles),
+ * their pairs get d_inv = -1, and a tile names its expert by its index in the rank's own weight stack (e - e0): pass the
+ * stack of those e1 - e0 matrices to izb_moe_gateup / izb_moe_down.  d_ids / d_counts stay global, as routed. */
+int izb_moe_sort_ex(const int32_t* d_ids, const float* d_wts, const int32_t* d_counts, int T, int NE, int NU, int TM, int e0,
+                    int e1, int32_t* d_offs, int32_t* d_tiles, int max_tiles, int32_t* d_stok, float* d_swt, int32_t* d_inv,
+                    void* stream);
 /* moe_gateup_q (zero/kernels/decode_moe.cl:92-260): d_h[slot][F] = silu(x_tok Wg_e^T) * (x_tok Wu_e^T) for every tile
  * of d_tiles (made by izb_moe_sort with the same TM); wg, wu are stacks [NE][F][K]; the activations are token rows
  * (d_aq [Mp][K], d_asc [K/32][Mp]) gathered through d_stok.  TM 1..8: per-tile kernels on the raw rows, as the
@@ -245,6 +256,13 @@ int izb_moe_down(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, i
                  int TM, const float* d_swt, float* d_y, void* stream);
 /* moe_combine (zero/kernels/moe.cl:344-352, no shared expert): x[t] += sum_k y[inv[t*NU+k]] in choice order. */
 int izb_moe_combine(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, void* stream);
+/* moe_combine in full (zero/kernels/moe.cl:344-352): v = sum_k y[inv[t*NU+k]] over the slots >= 0, in choice order,
+ * + d_sgate[t] * d_sh[t] when a shared expert's output d_sh [T][E] and its gate are given (both or neither);
+ * partial == 0: x[t] += v; partial != 0: x[t] = v, this rank's share of the sum in the expert-parallel split
+ * (tp_moe_combine, zero/kernels/tp.cl:100-111; the shares are then summed over the ranks like any row-parallel output,
+ * the shared expert added on one rank only). */
+int izb_moe_combine_ex(float* d_x, const float* d_y, const int32_t* d_inv, int T, int NU, int E, const float* d_sh,
+                       const float* d_sgate, int partial, void* stream);
 
 /* ------------------------------------------------------------------------------------------------ tensor parallel
  * tp_range (zero/mgpu/engine_tp_shard.h:68-72): rank r's [begin, end) of `total` in whole `unit`s. */
@@ -277,6 +295,13 @@ int izb_tp_allreduce_rows(izb_tp* tp, float* d_x, float* d_part, int rows, int E
  * == 0.  d_xsum (may be NULL) receives this rank's summed f32 rows [rows/nranks][E]. */
 int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d_part, int rows, int E, float* d_xsum, int8_t* d_aq,
                                float* d_asc, void* stream);
+
+/* The output head split by vocabulary rows in units of 16 (zero/mgpu/engine_tp_shard.h:68-72; the last rank also takes the
+ * rows past the last whole unit) and its logits joined in rank order (the reference joins them on the host,
+ * zero/mgpu/engine_tp.h:853-862): d_local [rows][ld_local] holds this rank's logits in its first end - begin columns,
+ * d_full [rows][ld_full] receives the whole vocabulary on every rank.  rows <= 64 (decode rows). */
+int izb_tp_gather_logits(izb_tp* tp, const float* d_local, int ld_local, int rows, int vocab, float* d_full, int ld_full,
+                         void* stream);
 
 #ifdef __cplusplus
 }

@@ -764,6 +764,59 @@ void orc_moe_down(int type, const uint8_t* wd, int E, int F, const int8_t* hq, c
 }
 
 /* x[t] += sum_k y[inv[t*NU+k]] in choice order (zero/kernels/moe.cl:344-352; no shared expert) */
+/* the shared expert's gate (SGATE, zero/kernels/moe.cl:44,88): the sigmoid of the logit that follows the experts' */
+void orc_moe_sgate(const float* logits, int ldl, int T, int NE, float* sgate) {
+  for (int t = 0; t < T; ++t) sgate[t] = 1.0f / (1.0f + expf(-logits[(size_t)t * ldl + NE]));
+}
+
+/* expert-parallel sort (zero/kernels/tp.cl:55-78): experts outside [e0, e1) count as empty, their pairs get inv = -1, and a
+ * tile names its expert by its index in the rank's own stack (e - e0) */
+void orc_moe_sort_range(const int32_t* ids, const float* wts, int T, int NE, int NU, int TM, const int32_t* counts, int e0, int e1,
+                        int32_t* offs, int32_t* tiles, int32_t* stok, float* swt, int32_t* inv) {
+  int nt = 0, off = 0;
+  for (int e = 0; e < NE; ++e) {
+    const int c = (e >= e0 && e < e1) ? counts[e] : 0;
+    offs[e] = off;
+    for (int i = 0; i * TM < c; ++i) {
+      int32_t* tp = tiles + 1 + 3 * nt++;
+      tp[0] = e - e0;
+      tp[1] = off + i * TM;
+      tp[2] = c - i * TM < TM ? c - i * TM : TM;
+    }
+    off += c;
+  }
+  offs[NE] = off;
+  tiles[0] = nt;
+  int32_t* cur = (int32_t*)malloc((size_t)NE * 4);
+  memcpy(cur, offs, (size_t)NE * 4);
+  for (int i = 0; i < T * NU; ++i) {
+    const int e = ids[i];
+    if (e < e0 || e >= e1) { inv[i] = -1; continue; }
+    const int s = cur[e]++;
+    stok[s] = i / NU;
+    swt[s] = wts[i];
+    inv[i] = s;
+  }
+  free(cur);
+}
+
+/* moe_combine with the shared expert (zero/kernels/moe.cl:344-352) and the partial form of the expert-parallel split
+ * (tp_moe_combine, zero/kernels/tp.cl:100-111): v = sum of the token's slots >= 0 in choice order (+ sgate * sh);
+ * x += v, or x = v when partial */
+void orc_moe_combine_ex(float* x, const float* y, const int32_t* inv, int T, int NU, int E, const float* sh, const float* sgate,
+                        int partial) {
+  for (int t = 0; t < T; ++t)
+    for (int c = 0; c < E; ++c) {
+      float v = 0.0f;
+      for (int k = 0; k < NU; ++k) {
+        const int s = inv[t * NU + k];
+        if (s >= 0) v += y[(size_t)s * E + c];
+      }
+      if (sh) v += sgate[t] * sh[(size_t)t * E + c];
+      x[(size_t)t * E + c] = partial ? v : x[(size_t)t * E + c] + v;
+    }
+}
+
 void orc_moe_combine(float* x, const float* y, const int32_t* inv, int T, int NU, int E) {
   for (int t = 0; t < T; ++t)
     for (int c = 0; c < E; ++c) {

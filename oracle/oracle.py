@@ -218,6 +218,34 @@ def moe_sort(ids: np.ndarray, wts: np.ndarray, counts: np.ndarray, TM: int):
     return offs, tiles, stok, swt, inv
 
 
+def moe_sgate(logits: np.ndarray, NE: int) -> np.ndarray:
+    logits = np.ascontiguousarray(logits, np.float32)
+    T = logits.shape[0]
+    out = np.empty(T, np.float32)
+    lib().orc_moe_sgate(_vp(logits), logits.shape[1], T, NE, _vp(out))
+    return out
+
+
+def moe_sort_range(ids: np.ndarray, wts: np.ndarray, counts: np.ndarray, TM: int, e0: int, e1: int):
+    T, NU = ids.shape
+    NE = counts.shape[0]
+    offs = np.empty(NE + 1, np.int32)
+    tiles = np.zeros(1 + 3 * (T * NU // TM + NE + 1), np.int32)
+    stok, swt, inv = np.zeros(T * NU, np.int32), np.zeros(T * NU, np.float32), np.empty(T * NU, np.int32)
+    lib().orc_moe_sort_range(_vp(np.ascontiguousarray(ids)), _vp(np.ascontiguousarray(wts)), T, NE, NU, TM, _vp(counts), e0, e1,
+                             _vp(offs), _vp(tiles), _vp(stok), _vp(swt), _vp(inv))
+    return offs, tiles, stok, swt, inv
+
+
+def moe_combine_ex(x: np.ndarray, y: np.ndarray, inv: np.ndarray, NU: int, sh=None, sgate=None, partial: bool = False) -> np.ndarray:
+    out = np.array(x, np.float32, copy=True, order="C")
+    T, E = out.shape
+    lib().orc_moe_combine_ex(_vp(out), _vp(np.ascontiguousarray(y, np.float32)), _vp(np.ascontiguousarray(inv, np.int32)), T, NU, E,
+                             None if sh is None else _vp(np.ascontiguousarray(sh, np.float32)),
+                             None if sgate is None else _vp(np.ascontiguousarray(sgate, np.float32)), int(partial))
+    return out
+
+
 def slot_experts(offs: np.ndarray) -> np.ndarray:
     return np.repeat(np.arange(len(offs) - 1, dtype=np.int32), np.diff(offs)).astype(np.int32)
 

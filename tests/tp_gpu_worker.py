@@ -90,6 +90,32 @@ def check_mode(mode: str, world: int, rank: int, device: int, chunks: int = 1, o
     st.close()
 
 
+def check_head_gather(world: int, rank: int, device: int) -> None:
+    """The output head split by vocabulary rows (units of 16, the last rank also takes the remainder): every rank runs the
+    few-row GEMV on its rows, izb_tp_gather_logits joins them in rank order; the result against the oracle on the whole head."""
+    import torch
+    import arcinferzero_b200 as izb
+    K, T = 512, 2
+    vocab = 16 * (3 * world + 1) + 5
+    w = S.make_weight(8, vocab, K, 99)
+    b, e = tp.tp_range(vocab, 16, world, rank)
+    if rank == world - 1:
+        e = vocab
+    W = izb.Weight(8, w, vocab, K, device=device, row_range=(b, e))
+    x = S.make_act(T, K, 98)
+    aq, asc, _ = O.quantize_act(x, Mp=16)
+    comm = izb.TpComm(world, rank, device)
+    local = izb.gemv(W, torch.from_numpy(aq).cuda(device), torch.from_numpy(asc).cuda(device), T)
+    full = torch.full((T, vocab + 3), float("nan"), dtype=torch.float32, device=f"cuda:{device}")
+    comm.gather_logits(local, vocab, full=full)
+    torch.cuda.synchronize()
+    got = full.cpu().numpy()
+    assert np.isnan(got[:, vocab:]).all()
+    assert relerr(got[:, :vocab], O.matmul(8, w, K, aq, asc, T, "gemv")) <= TOL
+    comm.close()
+    W.close()
+
+
 def main() -> int:
     import torch
     import torch.distributed as dist
@@ -106,6 +132,8 @@ def main() -> int:
         # the pipelined form: two token chunks, sums on a second stream beside the next chunk's GEMMs, balanced Q split
         check_mode("rs_quant_ag", world, rank, local, chunks=2, overlap=True, balance=True)
         print(f"TP_WORKER_OK mode=rs_quant_ag/overlap rank={rank}/{world}", flush=True)
+        check_head_gather(world, rank, local)
+        print(f"TP_WORKER_OK head gather rank={rank}/{world}", flush=True)
     finally:
         if world > 1:
             dist.destroy_process_group()

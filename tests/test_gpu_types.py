@@ -90,7 +90,7 @@ def test_gemv_1_to_8_rows(izb, torch, qt, K):
 
 @pytest.mark.parametrize("qt", TYPES)
 def test_gemm_and_store_modes(izb, torch, qt):
-    M, N, K = 130, 200, 1024
+    M, N, K = 130, 208, 1024     # (the GEMM keeps the reference's shape rule: N % 16 == 0)
     w = edge_rows(qt, S.make_weight(qt, N, K, 900 + qt), K)
     W = izb.Weight(qt, w, N, K)
     Mp = izb.pad_rows(M)

@@ -23,7 +23,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_reserve", "izb_set_sm_limit", "izb_debug_wait_test", "izb_tensor_peak",
-    "izb_weight_create", "izb_weight_create_slice", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
+    "izb_weight_create", "izb_weight_create_slice", "izb_weight_create_stack", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_route_ex", "izb_moe_sort", "izb_moe_sort_ex", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
@@ -132,6 +132,21 @@ class Weight:
             self.close()
         except Exception:
             pass
+
+
+def stacked_weight(qtype: int, parts: list, K: int, device: int = 0) -> "Weight":
+    """Several tensors (GGUF rows [N_i, row bytes]) of one type and K as one weight of sum(N_i) rows: one launch for Q | K | V
+    or gate | up (izb_weight_create_stack)."""
+    arrs = [np.ascontiguousarray(a, np.uint8) for a in parts]
+    if any(a.ndim != 2 or a.shape[1] != arrs[0].shape[1] for a in arrs):
+        raise ValueError("stacked_weight: every part is [rows, K/256 * superblock bytes] of the same K")
+    ptrs = (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
+    rows = (C.c_int * len(arrs))(*[a.shape[0] for a in arrs])
+    w = Weight.__new__(Weight)
+    w.handle = C.c_void_p(0)
+    _check(lib().izb_weight_create_stack(qtype, ptrs, rows, len(arrs), K, device, C.byref(w.handle)))
+    w.qtype, w.N, w.K, w.n_mats, w.device = qtype, sum(a.shape[0] for a in arrs), K, 1, device
+    return w
 
 
 def weight_decode_host(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:

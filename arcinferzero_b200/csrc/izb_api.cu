@@ -412,6 +412,34 @@ extern "C" int izb_weight_create(int type, const void* h_rows, int n_mats, int N
   return izb_weight_create_slice(type, h_rows, n_mats, N, K, 0, N, 0, K, device, out);
 }
 
+extern "C" int izb_weight_create_stack(int type, const void* const* h_parts, const int* n_rows, int n_parts, int K, int device,
+                                       izb_weight** out) {
+  if (!h_parts || !n_rows || !out) IZB_FAIL(IZB_ERR_ARG, "weight_create_stack: null pointer");
+  *out = nullptr;
+  const int src_sb = izb_gguf_sb_bytes(type);
+  if (!src_sb) IZB_FAIL(IZB_ERR_TYPE, "weight_create_stack: ggml type %d", type);
+  if (n_parts < 1 || n_parts > 64 || K < 256 || K % 256) IZB_FAIL(IZB_ERR_SHAPE, "weight_create_stack: %d parts, K = %d", n_parts, K);
+  const size_t src_row = (size_t)(K / 256) * src_sb;
+  long long total = 0;
+  for (int i = 0; i < n_parts; ++i) {
+    if (!h_parts[i] || n_rows[i] < 1) IZB_FAIL(IZB_ERR_ARG, "weight_create_stack: part %d is empty", i);
+    total += n_rows[i];
+  }
+  if (total > 0x7FFFFFFF) IZB_FAIL(IZB_ERR_SHAPE, "weight_create_stack: %lld rows", total);
+  std::vector<uint8_t> rows;
+  try {
+    rows.resize((size_t)total * src_row);
+  } catch (const std::exception&) {
+    IZB_FAIL(IZB_ERR_NOMEM, "weight_create_stack: %lld rows of %zu bytes on the host", total, src_row);
+  }
+  size_t at = 0;
+  for (int i = 0; i < n_parts; ++i) {
+    memcpy(rows.data() + at, h_parts[i], (size_t)n_rows[i] * src_row);
+    at += (size_t)n_rows[i] * src_row;
+  }
+  return izb_weight_create(type, rows.data(), 1, (int)total, K, device, out);
+}
+
 extern "C" void izb_weight_destroy(izb_weight* w) {
   if (!w) return;
   {

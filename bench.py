@@ -174,13 +174,16 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
     # config 3's three matrices, then the down-projection shape of the same model (long rows: not in config 3)
     # ... and two Q6_K matrices (the type of the FFN down / output tensors of the common Q4_K_M files), held in the generic
     # per-16-scale device form: GB/s counted on the FILE's bytes (210 per 256 weights), the device streams 304
-    for qt, Nn, Kk in ((12, 5120, K), (12, 17408, K), (8, 151936, K), (12, 5120, 17408), (14, 17408, K), (14, 151936, K)):
-        w = S.make_weight(qt, Nn, Kk, SEED + Nn + (0 if Kk == K else Kk))
-        wbytes = w.size
+    # ... and the gate and up matrices of one layer loaded as ONE weight of 2 x 17408 rows (izb_weight_create_stack): one
+    # launch where the separate matrices take two
+    for qt, Nn, Kk, parts in ((12, 5120, K, 1), (12, 17408, K, 1), (8, 151936, K, 1), (12, 5120, 17408, 1), (14, 17408, K, 1), (14, 151936, K, 1),
+                              (12, 34816, K, 2)):
+        ws = [S.make_weight(qt, Nn // parts, Kk, SEED + Nn + (0 if Kk == K else Kk) + 7 * p) for p in range(parts)]
+        wbytes = sum(w.size for w in ws)
         dev_bytes = wbytes if qt in (8, 12) else Nn * (Kk // 256) * 304
         copies = max(1, -(-300_000_000 // dev_bytes)) if dev_bytes < 400_000_000 else 2
-        Ws = [izb.Weight(qt, w, Nn, Kk) for _ in range(copies)]
-        del w
+        Ws = [izb.Weight(qt, ws[0], Nn, Kk) if parts == 1 else izb.stacked_weight(qt, ws, Kk) for _ in range(copies)]
+        del ws
         # (the output head once more with its logit soft-cap, as the reference's Gemma head runs: GEMV, then cap * tanh(v / cap))
         for T, cap in ((1, 0.0), (2, 0.0)) + (((1, 30.0),) if qt == 8 else ()):
             x = torch.from_numpy(S.make_act(T, Kk, SEED + T)).cuda()
@@ -213,7 +216,8 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
             us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
             nbytes = wbytes + T * (Kk + Kk // 32 * 4) + T * Nn * 4 * (3 if cap > 0 else 1)  # (the cap reads and writes the row again)
             gbs = nbytes / (us * 1e-6) / 1e9
-            out.append({"type": {12: "Q4_K", 8: "Q8_0", 14: "Q6_K"}[qt], "device_weight_bytes": dev_bytes, "N": Nn, "K": Kk, "batch": T, "softcap": cap, "in_config3": Kk == K and cap == 0 and qt != 14, "us_per_launch": us,
+            out.append({"type": {12: "Q4_K", 8: "Q8_0", 14: "Q6_K"}[qt], "device_weight_bytes": dev_bytes, "N": Nn, "K": Kk, "stacked_parts": parts, "batch": T, "softcap": cap,
+                        "in_config3": Kk == K and cap == 0 and qt != 14 and parts == 1, "us_per_launch": us,
                         "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
                         "peak": f"{hbm_peak} GB/s {peak_src} copy", "weight_copies_in_rotation": copies})
         for W_ in Ws:

@@ -122,6 +122,12 @@ int izb_weight_create(int ggml_type, const void* h_gguf_rows, int n_mats, int N,
  * columns [k0, k1) of every matrix; k0, k1 multiples of 256. */
 int izb_weight_create_slice(int ggml_type, const void* h_gguf_rows, int n_mats, int N, int K, int n0, int n1, int k0, int k1,
                             int device, izb_weight** out);
+/* Several tensors of one type and one K uploaded as ONE matrix, their rows one after the other (load_w_stack,
+ * zero/engine_load.h:315-339: the reference uploads Q | K | V and gate | up stacked and runs one GEMV launch over them,
+ * gemv_gu, zero/engine.h:1128-1146).  The result is an ordinary weight of sum(n_rows) rows: a single izb_matmul / izb_gemv
+ * over it writes the parts' outputs side by side, and a decode step pays one launch instead of n_parts. */
+int izb_weight_create_stack(int ggml_type, const void* const* h_parts, const int* n_rows, int n_parts, int K, int device,
+                            izb_weight** out);
 /* The loader's host-side decoder on its own (no device needed): n_superblocks superblocks (256 weights each) of a Q4_0,
  * Q5_K, Q6_K or IQ4_XS row -> the form izb_weight_create uploads: GGUF Q8_0 blocks (8 x 34 bytes) for Q4_0, else 304 bytes:
  * f32 d | f32 dmin | int8 scale[16] | uint8 min[16] | 8 zero bytes | int8 (quant - offset)[256]. */

@@ -138,3 +138,32 @@ def test_entry_points_that_do_not_take_the_generic_form_say_so(izb, torch):
         izb.Weight(10, np.zeros((4, 84), np.uint8), 4, 256)   # Q2_K: not taken
     assert e.value.status == -3
     W.close()
+
+
+@pytest.mark.parametrize("qt", [8, 12, 2, 14])
+def test_stacked_weight_is_the_parts_side_by_side(izb, torch, qt):
+    """Several tensors loaded as one weight (the reference's load_w_stack for Q | K | V and gate | up): one GEMV / GEMM over
+    the stack writes bit for bit what the separate launches write, side by side."""
+    K, rows = 1024, [96, 208, 64]
+    parts = [S.make_weight(qt, n, K, 900 + qt + n) for n in rows]
+    Wst = izb.stacked_weight(qt, parts, K)
+    assert (Wst.N, Wst.K) == (sum(rows), K)
+    Ws = [izb.Weight(qt, p, n, K) for p, n in zip(parts, rows)]
+    assert (Wst.download() == np.concatenate([W.download() for W in Ws])).all()
+    x = S.make_act(48, K, 901)
+    aq, asc, _ = O.quantize_act(x, Mp=48)
+    daq, dasc = dev(torch, aq), dev(torch, asc)
+    for T in (1, 2, 48):
+        got = izb.matmul(Wst, daq, dasc, T).cpu().numpy()
+        off = 0
+        for W, p, n in zip(Ws, parts, rows):
+            one = izb.matmul(W, daq, dasc, T).cpu().numpy()
+            if T <= 8:
+                assert (got[:, off:off + n] == one).all(), (T, off)
+            assert rel(got[:, off:off + n], O.matmul(qt, p, K, aq, asc, T, "f64")) < TOL
+            off += n
+    with pytest.raises(ValueError):
+        izb.stacked_weight(qt, [parts[0], parts[1][:, :-16]], K)
+    assert izb.device_status(0) == 0
+    for W in Ws + [Wst]:
+        W.close()

@@ -60,6 +60,16 @@ class Engine {
     return w;
   }
 
+  // load_w_stack (zero/engine_load.h:315-339): several tensors of one type and K as one weight (Q | K | V, gate | up), so
+  // that one matmul writes their outputs side by side (gemv_gu, zero/engine.h:1128-1146)
+  GpuWeight load_w_stack(int ggml_type, const void* const* parts, const int* n_rows, int n_parts, int K) const {
+    GpuWeight w;
+    check(izb_weight_create_stack(ggml_type, parts, n_rows, n_parts, K, device_, &w.h), "load_w_stack");
+    w.type = ggml_type; w.K = K; w.N = 0;
+    for (int i = 0; i < n_parts; ++i) w.N += n_rows[i];
+    return w;
+  }
+
   // alloc_buffers (zero/engine_alloc.h:4): activation buffers for up to max_rows rows of up to max_k values
   void alloc_buffers(int max_rows, int max_k) {
     release_buffers();
@@ -68,6 +78,8 @@ class Engine {
     if (cudaSetDevice(device_) != cudaSuccess || cudaMalloc(&aq_, (size_t)max_rows_ * max_k) != cudaSuccess ||
         cudaMalloc(&asc_, (size_t)max_rows_ * (max_k / 32) * sizeof(float)) != cudaSuccess)
       throw std::runtime_error("alloc_buffers: out of device memory");
+    // the library's own scratch at its final size too: no call of up to max_rows x max_k allocates after this
+    check(izb_reserve(device_, max_rows_, max_k), "alloc_buffers");
   }
   // row padding of a chunk (zero/engine.h:521-522)
   static int pad_rows(int T) { return T >= 128 ? (T + 127) / 128 * 128 : (T + 15) / 16 * 16; }
@@ -119,6 +131,14 @@ class Engine {
     nranks_ = nranks; rank_ = rank;
     check(izb_tp_create(nranks, rank, id128, device_, &tp_), "tp_setup");
   }
+  // the same with the reference's bounded barriers (zero/mgpu/engine_tp.h:93-123): collectives never block the host, and
+  // tp_wait gives up after timeout_ms with the communicator aborted and the context usable
+  void tp_setup(int nranks, int rank, const void* id128, int timeout_ms, int max_ctas = 0) {
+    nranks_ = nranks; rank_ = rank;
+    check(izb_tp_create_ex(nranks, rank, id128, device_, timeout_ms, max_ctas, &tp_), "tp_setup");
+  }
+  // wait_done (zero/mgpu/engine_tp.h:1313-1372): everything queued on the stream has finished, or a std::runtime_error
+  void tp_wait(int timeout_ms) { check(izb_tp_wait(tp_, stream_, timeout_ms), "tp_wait"); }
   // tp_range (zero/mgpu/engine_tp_shard.h:68-72)
   void tp_range(int64_t total, int64_t unit, int64_t* b, int64_t* e) const { check(izb_tp_range(total, unit, nranks_, rank_, b, e), "tp_range"); }
   // tp_out (zero/mgpu/engine_tp_shard.h:318-325): row-parallel projection into `part`, summed over the ranks into x

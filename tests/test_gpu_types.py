@@ -154,10 +154,10 @@ def test_stacked_weight_is_the_parts_side_by_side(izb, torch, qt):
     aq, asc, _ = O.quantize_act(x, Mp=48)
     daq, dasc = dev(torch, aq), dev(torch, asc)
     for T in (1, 2, 48):
-        got = izb.matmul(Wst, daq, dasc, T).cpu().numpy()
+        got = izb.matmul(Wst, daq, dasc, T).cpu().numpy()[:T]
         off = 0
         for W, p, n in zip(Ws, parts, rows):
-            one = izb.matmul(W, daq, dasc, T).cpu().numpy()
+            one = izb.matmul(W, daq, dasc, T).cpu().numpy()[:T]
             if T <= 8:
                 assert (got[:, off:off + n] == one).all(), (T, off)
             assert rel(got[:, off:off + n], O.matmul(qt, p, K, aq, asc, T, "f64")) < TOL

@@ -23,7 +23,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_reserve", "izb_set_sm_limit", "izb_debug_wait_test", "izb_tensor_peak",
-    "izb_weight_create", "izb_weight_create_slice", "izb_weight_create_stack", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
+    "izb_weight_create", "izb_weight_create_slice", "izb_weight_create_stack", "izb_weight_create_gateup", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_route_ex", "izb_moe_sort", "izb_moe_sort_ex", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
@@ -149,6 +149,19 @@ def stacked_weight(qtype: int, parts: list, K: int, device: int = 0) -> "Weight"
     return w
 
 
+def gateup_weight(qtype: int, gate_rows: np.ndarray, up_rows: np.ndarray, F: int, K: int, n_mats: int = 1, device: int = 0) -> "Weight":
+    """Gate and up projection ([n_mats * F, row bytes] each) as one weight of 2F rows per matrix, rows alternating in groups of
+    32 (izb_weight_create_gateup): gemm(..., acc=3) and moe_gateup(W, None, ...) store up * silu(gate) from one GEMM."""
+    g, u = np.ascontiguousarray(gate_rows, np.uint8), np.ascontiguousarray(up_rows, np.uint8)
+    if g.shape != u.shape or g.size % (n_mats * F):
+        raise ValueError("gateup_weight: gate and up are [n_mats * F, K/256 * superblock bytes] each")
+    w = Weight.__new__(Weight)
+    w.handle = C.c_void_p(0)
+    _check(lib().izb_weight_create_gateup(qtype, _p(g), _p(u), n_mats, F, K, device, C.byref(w.handle)))
+    w.qtype, w.N, w.K, w.n_mats, w.device = qtype, 2 * F, K, n_mats, device
+    return w
+
+
 def weight_decode_host(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:
     """The loader's host-side decoder (no GPU): rows [N, K/256 * file bytes] of Q4_0 / Q5_K / Q6_K / IQ4_XS -> the uploaded
     form [N, K/256 * (272 | 304)]."""
@@ -240,7 +253,7 @@ def gemm(w: Weight, aq, asc, M: int | None = None, out=None, c_off: int = 0, acc
     Mp = asc.shape[1]
     M = M or Mp
     if out is None:
-        out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
+        out = torch.empty((Mp, w.N // 2 if acc == 3 else w.N), dtype=torch.float32, device=aq.device)
     _check(lib().izb_gemm(w.handle, mat, _p(aq), _p(asc), M, Mp, _p(out), out.stride(0), c_off, acc, impl, _stream()))
     return out
 
@@ -255,7 +268,7 @@ def gemm_noalloc(w: Weight, aq, asc, M: int | None = None, out=None, c_off: int 
     Mp = asc.shape[1]
     M = M or Mp
     if out is None:
-        out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
+        out = torch.empty((Mp, w.N // 2 if acc == 3 else w.N), dtype=torch.float32, device=aq.device)
     _check(lib().izb_gemm_noalloc(w.handle, mat, _p(aq), _p(asc), M, Mp, _p(out), out.stride(0), c_off, acc, _p(status), _stream()))
     return out
 
@@ -338,10 +351,11 @@ def moe_sort(ids, wts, counts, TM: int, expert_range: tuple[int, int] | None = N
     return offs, tiles, max_tiles, stok, swt, inv
 
 
-def moe_gateup(wg: Weight, wu: Weight, aq, asc, tiles, max_tiles: int, TM: int, stok, S: int):
+def moe_gateup(wg: Weight, wu: Weight | None, aq, asc, tiles, max_tiles: int, TM: int, stok, S: int):
+    """wu = None: wg is an interleaved gate | up stack (gateup_weight) and one grouped GEMM computes both."""
     import torch
-    h = torch.empty((S, wg.N), dtype=torch.float32, device=aq.device)
-    _check(lib().izb_moe_gateup(wg.handle, wu.handle, _p(aq), _p(asc), asc.shape[1], _p(tiles), max_tiles, TM, _p(stok), _p(h),
+    h = torch.empty((S, wg.N if wu is not None else wg.N // 2), dtype=torch.float32, device=aq.device)
+    _check(lib().izb_moe_gateup(wg.handle, wu.handle if wu is not None else None, _p(aq), _p(asc), asc.shape[1], _p(tiles), max_tiles, TM, _p(stok), _p(h),
                                 _stream()))
     return h
 

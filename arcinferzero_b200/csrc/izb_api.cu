@@ -21,6 +21,8 @@ int izb_make_raw_tensor_map(izb_weight* w);
 int izb_gemm_k16_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C, int ldc,
                         int c_off, int acc, int32_t* dots, cudaStream_t st);
 
+int izb_swiglu_pairs_launch(const float* gu, int ldgu, int M, int F, float* C, int ldc, int c_off, cudaStream_t st);
+
 // ---------------------------------------------------------------------------------------------- errors
 static thread_local char t_err[512] = "";
 
@@ -440,6 +442,36 @@ extern "C" int izb_weight_create_stack(int type, const void* const* h_parts, con
   return izb_weight_create(type, rows.data(), 1, (int)total, K, device, out);
 }
 
+extern "C" int izb_weight_create_gateup(int type, const void* h_gate, const void* h_up, int n_mats, int F, int K, int device,
+                                        izb_weight** out) {
+  if (!h_gate || !h_up || !out) IZB_FAIL(IZB_ERR_ARG, "weight_create_gateup: null pointer");
+  *out = nullptr;
+  const int src_sb = izb_gguf_sb_bytes(type);
+  if (!src_sb) IZB_FAIL(IZB_ERR_TYPE, "weight_create_gateup: ggml type %d", type);
+  if (type != IZB_Q8_0 && type != IZB_Q4_K && type != IZB_Q4_0)
+    IZB_FAIL(IZB_ERR_TYPE, "weight_create_gateup: ggml type %d does not run on the tensor-core GEMM (Q8_0, Q4_K, Q4_0 do)", type);
+  if (n_mats < 1 || F < 64 || F % 64 || K < 256 || K % 256 || (long long)n_mats * 2 * F > 0x7FFFFFFF)
+    IZB_FAIL(IZB_ERR_SHAPE, "weight_create_gateup: n_mats = %d, F = %d (multiple of 64), K = %d (multiple of 256)", n_mats, F, K);
+  const size_t row = (size_t)(K / 256) * src_sb, grp = 32 * row;
+  std::vector<uint8_t> rows;
+  try {
+    rows.resize((size_t)n_mats * 2 * F * row);
+  } catch (const std::exception&) {
+    IZB_FAIL(IZB_ERR_NOMEM, "weight_create_gateup: %d x %d rows of %zu bytes on the host", n_mats, 2 * F, row);
+  }
+  const uint8_t* g = (const uint8_t*)h_gate;
+  const uint8_t* u = (const uint8_t*)h_up;
+  const long long n_grp = (long long)n_mats * (F / 32);  // (F % 32 == 0: groups never straddle two matrices)
+#pragma omp parallel for schedule(static)
+  for (long long j = 0; j < n_grp; ++j) {
+    memcpy(rows.data() + (size_t)(2 * j) * grp, g + (size_t)j * grp, grp);
+    memcpy(rows.data() + (size_t)(2 * j + 1) * grp, u + (size_t)j * grp, grp);
+  }
+  const int rc = izb_weight_create(type, rows.data(), n_mats, 2 * F, K, device, out);
+  if (rc == IZB_OK) (*out)->gu32 = true;
+  return rc;
+}
+
 extern "C" void izb_weight_destroy(izb_weight* w) {
   if (!w) return;
   {
@@ -474,11 +506,13 @@ static int check_gemm_args(const izb_weight* w, int mat, const int8_t* aq, const
                            int ldc, int c_off, int acc) {
   if (!w || !aq || !asc || !C) IZB_FAIL(IZB_ERR_ARG, "gemm: null pointer");
   if (mat < 0 || mat >= w->n_mats) IZB_FAIL(IZB_ERR_ARG, "gemm: matrix %d of %d", mat, w->n_mats);
-  if (acc < 0 || acc > 2) IZB_FAIL(IZB_ERR_ARG, "gemm: store mode %d", acc);
+  if (acc < 0 || acc > 3) IZB_FAIL(IZB_ERR_ARG, "gemm: store mode %d", acc);
+  if (acc == 3 && !w->gu32) IZB_FAIL(IZB_ERR_ARG, "gemm: store mode 3 needs a weight made by izb_weight_create_gateup");
   // the reference's shape rule (zero/engine.h:1233): Mp % 16, N % 16, K % 256
   if (Mp % 16 || w->N % 16 || w->K % 256) IZB_FAIL(IZB_ERR_SHAPE, "gemm: bad shape Mp=%d N=%d K=%d (need Mp%%16, N%%16, K%%256)", Mp, w->N, w->K);
   if (M < 1 || M > Mp) IZB_FAIL(IZB_ERR_SHAPE, "gemm: %d rows of Mp = %d", M, Mp);
-  if (c_off < 0 || ldc < c_off + w->N) IZB_FAIL(IZB_ERR_SHAPE, "gemm: ldc = %d < c_off + N = %d", ldc, c_off + w->N);
+  const int n_out = acc == 3 ? w->N / 2 : w->N;
+  if (c_off < 0 || ldc < c_off + n_out) IZB_FAIL(IZB_ERR_SHAPE, "gemm: ldc = %d < c_off + output columns = %d", ldc, c_off + n_out);
   if (!izb_aligned(aq, 16) || !izb_aligned(asc, 16) || !izb_aligned(C, 16) || ldc % 4 || c_off % 4)
     IZB_FAIL(IZB_ERR_ALIGN, "gemm: aq, asc, C must be 16-byte aligned, ldc and c_off multiples of 4");
   return IZB_OK;
@@ -492,6 +526,7 @@ extern "C" int izb_gemm(const izb_weight* w, int mat, const int8_t* d_aq, const 
   if (w->type == IZB_K16) {  // Q5_K / Q6_K / IQ4_XS: exact per-16 scales, CUDA cores (the reference requantises these for its GEMM)
     if (impl == IZB_GEMM_TC) IZB_FAIL(IZB_ERR_TYPE, "gemm: the tensor-core kernel does not take ggml type %d", w->ggml_type);
     if (impl != IZB_GEMM_AUTO && impl != IZB_GEMM_CORE) IZB_FAIL(IZB_ERR_ARG, "gemm: impl %d", impl);
+    if (acc == 3) IZB_FAIL(IZB_ERR_TYPE, "gemm: store mode 3 is not built for ggml type %d", w->ggml_type);
     return izb_gemm_k16_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc, nullptr, st);
   }
   if (impl == IZB_GEMM_AUTO || impl == IZB_GEMM_TC) {
@@ -503,6 +538,12 @@ extern "C" int izb_gemm(const izb_weight* w, int mat, const int8_t* d_aq, const 
     if (impl == IZB_GEMM_TC) IZB_FAIL(IZB_ERR_SHAPE, "gemm: the tensor-core kernel does not take M=%d Mp=%d N=%d K=%d", M, Mp, w->N, w->K);
   } else if (impl != IZB_GEMM_CORE) {
     IZB_FAIL(IZB_ERR_ARG, "gemm: impl %d", impl);
+  }
+  if (acc == 3) {  // both projections side by side into scratch, then the SwiGLU product of the column groups
+    void* ws = nullptr;
+    if (int rc = izb_workspace(w->device, kWsGemm, (size_t)Mp * w->N * 4, &ws)) return rc;
+    if (int rc = izb_gemm_core_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, d_asc, M, Mp, (float*)ws, w->N, 0, 0, nullptr, st)) return rc;
+    return izb_swiglu_pairs_launch((const float*)ws, w->N, M, w->N / 2, d_C, ldc, c_off, st);
   }
   return izb_gemm_core_launch(w, w->raw + (size_t)mat * w->N * w->row_bytes, d_aq, d_asc, M, Mp, d_C, ldc, c_off, acc, nullptr, st);
 }
@@ -534,7 +575,7 @@ extern "C" int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, cons
   if (!w) IZB_FAIL(IZB_ERR_ARG, "matmul: null weight");
   if (T < 1) IZB_FAIL(IZB_ERR_SHAPE, "matmul: T = %d", T);
   if (T <= 8) {
-    if (acc == 2) IZB_FAIL(IZB_ERR_ARG, "matmul: store mode 2 (fused SwiGLU) exists for the GEMM only (T > 8)");
+    if (acc >= 2) IZB_FAIL(IZB_ERR_ARG, "matmul: store modes 2 and 3 (fused SwiGLU) exist for the GEMM only (T > 8)");
     return izb_gemv(w, mat, d_aq, d_asc, T, Mp, d_C, ldc, c_off, acc, stream);
   }
   return izb_gemm(w, mat, d_aq, d_asc, Mp, Mp, d_C, ldc, c_off, acc, IZB_GEMM_AUTO, stream);

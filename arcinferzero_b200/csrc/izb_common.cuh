@@ -22,6 +22,7 @@ struct izb_weight {
   int type = 0, n_mats = 0, N = 0, K = 0, device = 0;
   int ggml_type = 0;     // the type of the file's tensor (Q4_0 is held as Q8_0, Q5_K / Q6_K / IQ4_XS as K16)
   bool has_min = false;  // K16: the type has mins (Q5_K)
+  bool gu32 = false;     // rows alternate in groups of 32 between a gate and an up projection (izb_weight_create_gateup)
   int sb_bytes = 0;      // 144, 272 or 304
   size_t row_bytes = 0;  // K/256 * sb_bytes
   size_t bytes = 0;      // n_mats * N * row_bytes (without the slack)

@@ -285,6 +285,12 @@ __device__ __forceinline__ unsigned long long pack2(float x) {
   asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
   return r;
 }
+// up * silu(gate) (zero/kernels/gemm.cl:562-565).  Out of line on purpose: the epilogues call it 64 and 32 times per
+// thread, and the role loops of the kernel compete for the instruction cache.
+__device__ __noinline__ float swiglu_mul(float g, float u) { return __fmul_rn(u, __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)))); }
+__device__ __forceinline__ unsigned long long pack_pair(float lo, float hi) {
+  return (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(hi) << 32);
+}
 __device__ __forceinline__ float lo_f(unsigned long long a) { return __uint_as_float((uint32_t)a); }
 __device__ __forceinline__ float hi_f(unsigned long long a) { return __uint_as_float((uint32_t)(a >> 32)); }
 
@@ -758,7 +764,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);
       }
     }
-    if (ok && !kDots && row_ok && !*abort_flag) {
+    if (ok && !kDots && row_ok && !*abort_flag && p.acc == 3) {
+      // Gate and up projections in one weight whose rows alternate in groups of 32 (izb_weight_create_gateup): this
+      // thread's 64 columns are 32 gate outputs followed by the 32 up outputs of the same FFN rows, so the SwiGLU product
+      // up * silu(gate) (zero/kernels/gemm.cl:562-565) is formed in registers and only the F-wide result is stored.
+      float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + (n0 >> 1) + half * 32;
+      const bool wide = ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        unsigned long long o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned long long g2 = res2[4 * j + i], u2 = res2[16 + 4 * j + i];
+          o[i] = pack_pair(swiglu_mul(lo_f(g2), lo_f(u2)), swiglu_mul(hi_f(g2), hi_f(u2)));
+        }
+        if (wide) {
+          asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * j), "l"(o[0]), "l"(o[1]), "l"(o[2]), "l"(o[3]) : "memory");
+        } else {
+          reinterpret_cast<float4*>(cp + 8 * j)[0] = make_float4(lo_f(o[0]), hi_f(o[0]), lo_f(o[1]), hi_f(o[1]));
+          reinterpret_cast<float4*>(cp + 8 * j)[1] = make_float4(lo_f(o[2]), hi_f(o[2]), lo_f(o[3]), hi_f(o[3]));
+        }
+      }
+    } else if (ok && !kDots && row_ok && !*abort_flag) {
       float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + n0 + half * 64;
       const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
       // plain store, no row factor, 32-byte aligned rows: eight stores of one full 32-byte sector each per thread
@@ -779,10 +806,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
           v.x = __fadd_rn(v.x, o.x); v.y = __fadd_rn(v.y, o.y); v.z = __fadd_rn(v.z, o.z); v.w = __fadd_rn(v.w, o.w);
         } else if (p.acc == 2) {  // C holds the gate projection: C = v * silu(C)   (zero/kernels/gemm.cl:562-565)
           const float4 o = *dst;
-          v.x = __fmul_rn(v.x, __fdiv_rn(o.x, __fadd_rn(1.0f, expf(-o.x))));
-          v.y = __fmul_rn(v.y, __fdiv_rn(o.y, __fadd_rn(1.0f, expf(-o.y))));
-          v.z = __fmul_rn(v.z, __fdiv_rn(o.z, __fadd_rn(1.0f, expf(-o.z))));
-          v.w = __fmul_rn(v.w, __fdiv_rn(o.w, __fadd_rn(1.0f, expf(-o.w))));
+          v.x = swiglu_mul(o.x, v.x);
+          v.y = swiglu_mul(o.y, v.y);
+          v.z = swiglu_mul(o.z, v.z);
+          v.w = swiglu_mul(o.w, v.w);
         }
         *dst = v;
       }
@@ -963,6 +990,12 @@ int izb_moe_gateup_tc(const izb_weight* wg, const izb_weight* wu, const int8_t* 
   return run_tc(wu, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, F, 0, 2, nullptr, kWsMoe, st, same);
 }
 
+// gate and up of every expert in one interleaved stack (izb_weight_create_gateup): one grouped GEMM, SwiGLU in its epilogue
+int izb_moe_gateup_fused_tc(const izb_weight* wgu, const int8_t* d_aq, const float* d_asc, int Mp, const int32_t* d_tiles,
+                            int max_tiles, const int32_t* d_stok, float* d_h, cudaStream_t st) {
+  return run_tc(wgu, 0, d_aq, d_asc, Mp, 0, d_tiles, max_tiles, d_stok, nullptr, 0, d_h, wgu->N / 2, 0, 3, nullptr, kWsMoe, st);
+}
+
 int izb_moe_down_tc(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles, int max_tiles,
                     const float* d_swt, float* d_y, cudaStream_t st) {
   return run_tc(wd, 0, d_hq, d_hsc, Sp, 0, d_tiles, max_tiles, nullptr, d_swt, 0, d_y, wd->N, 0, 0, nullptr, kWsMoe, st);
@@ -1132,10 +1165,11 @@ extern "C" int izb_gemm_noalloc(const izb_weight* w, int mat, const int8_t* d_aq
                                 int ldc, int c_off, int acc, uint32_t* d_status, void* stream) {
   if (!w || !d_aq || !d_asc || !d_C) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: null pointer");
   if (mat < 0 || mat >= w->n_mats) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: matrix %d of %d", mat, w->n_mats);
-  if (acc < 0 || acc > 2) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: store mode %d", acc);
+  if (acc < 0 || acc > 3 || (acc == 3 && !w->gu32)) IZB_FAIL(IZB_ERR_ARG, "gemm_noalloc: store mode %d", acc);
   if (Mp % 16 || w->N % BN || w->K % 256 || M < 1 || M > Mp)
     IZB_FAIL(IZB_ERR_SHAPE, "gemm_noalloc: M=%d Mp=%d N=%d K=%d (need Mp %% 16, N %% 128, K %% 256, 1 <= M <= Mp)", M, Mp, w->N, w->K);
-  if (c_off < 0 || ldc < c_off + w->N) IZB_FAIL(IZB_ERR_SHAPE, "gemm_noalloc: ldc = %d < c_off + N = %d", ldc, c_off + w->N);
+  if (c_off < 0 || ldc < c_off + (acc == 3 ? w->N / 2 : w->N))
+    IZB_FAIL(IZB_ERR_SHAPE, "gemm_noalloc: ldc = %d < c_off + output columns = %d", ldc, c_off + (acc == 3 ? w->N / 2 : w->N));
   if (!izb_aligned(d_aq, 16) || !izb_aligned(d_asc, 16) || !izb_aligned(d_C, 16) || ldc % 4 || c_off % 4 || (d_status && !izb_aligned(d_status, 4)))
     IZB_FAIL(IZB_ERR_ALIGN, "gemm_noalloc: aq, asc, C must be 16-byte aligned, ldc and c_off multiples of 4");
   if (w->type == IZB_K16) IZB_FAIL(IZB_ERR_TYPE, "gemm_noalloc: ggml type %d is not taken by the tensor-core kernel", w->ggml_type);

@@ -348,8 +348,21 @@ int izb_moe_gateup_tc(const izb_weight* wg, const izb_weight* wu, const int8_t* 
 int izb_moe_down_tc(const izb_weight* wd, const int8_t* d_hq, const float* d_hsc, int Sp, const int32_t* d_tiles, int max_tiles,
                     const float* d_swt, float* d_y, cudaStream_t st);
 
+int izb_moe_gateup_fused_tc(const izb_weight* wgu, const int8_t* d_aq, const float* d_asc, int Mp, const int32_t* d_tiles,
+                            int max_tiles, const int32_t* d_stok, float* d_h, cudaStream_t st);
+
 extern "C" int izb_moe_gateup(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
                               const int32_t* d_tiles, int max_tiles, int TM, const int32_t* d_stok, float* d_h, void* stream) {
+  if (wg && !wu && wg->gu32) {  // one interleaved gate | up stack: a single grouped GEMM with the SwiGLU product in its epilogue
+    if (!d_aq || !d_asc || !d_tiles || !d_stok || !d_h) IZB_FAIL(IZB_ERR_ARG, "moe_gateup: null pointer");
+    if (max_tiles < 1 || max_tiles > 65535) IZB_FAIL(IZB_ERR_LIMIT, "moe_gateup: max_tiles = %d (1..65535)", max_tiles);
+    if (!izb_aligned(d_aq, 16)) IZB_FAIL(IZB_ERR_ALIGN, "moe_gateup: aq not 16-byte aligned");
+    if (TM != 128) IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: an interleaved gate | up stack runs on the grouped tensor-core GEMM (TM = 128), not on tiles of %d", TM);
+    if (int rc = izb_require_device(wg->device, "moe_gateup")) return rc;
+    const int rc = izb_moe_gateup_fused_tc(wg, d_aq, d_asc, Mp, d_tiles, max_tiles, d_stok, d_h, (cudaStream_t)stream);
+    if (rc <= 0) return rc;
+    IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: the grouped tensor-core GEMM does not take this stack (2F = %d, K = %d)", wg->N, wg->K);
+  }
   if (!wg || !wu || !d_aq || !d_asc || !d_tiles || !d_stok || !d_h) IZB_FAIL(IZB_ERR_ARG, "moe_gateup: null pointer");
   if (wg->type != wu->type || wg->N != wu->N || wg->K != wu->K || wg->n_mats != wu->n_mats)
     IZB_FAIL(IZB_ERR_SHAPE, "moe_gateup: gate and up stacks differ");

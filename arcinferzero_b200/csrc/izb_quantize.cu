@@ -328,3 +328,24 @@ extern "C" int izb_softcap_rows(float* d_C, int rows, int ld, int off, int N, fl
   IZB_LAUNCH("softcap_rows", st, softcap_rows_kernel<<<grid, 256, 0, st>>>(d_C, ld, off, N, cap, 1.0f / cap, vec));
   return IZB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------- SwiGLU of interleaved columns
+// gu [M][ldgu]: the outputs of a gate | up weight whose rows alternate in groups of 32 (izb_weight_create_gateup): columns
+// 64 j .. 64 j + 31 are gate outputs, 64 j + 32 .. 64 j + 63 the up outputs of the same FFN rows.
+// C[m][c_off + 32 j + i] = up * silu(gate) (zero/kernels/gemm.cl:562-565).  Used where the tensor-core GEMM, which forms
+// this product in its epilogue, does not take the call.
+namespace {
+__global__ void __launch_bounds__(256) swiglu_pairs_kernel(const float* __restrict__ gu, int ldgu, int F, float* __restrict__ C, int ldc, int c_off) {
+  const int f = blockIdx.x * 256 + threadIdx.x;
+  if (f >= F) return;
+  const float* row = gu + (size_t)blockIdx.y * ldgu + 64 * (f >> 5) + (f & 31);
+  const float g = row[0], u = row[32];
+  C[(size_t)blockIdx.y * ldc + c_off + f] = __fmul_rn(u, __fdiv_rn(g, __fadd_rn(1.0f, expf(-g))));
+}
+}  // namespace
+
+int izb_swiglu_pairs_launch(const float* gu, int ldgu, int M, int F, float* C, int ldc, int c_off, cudaStream_t st) {
+  dim3 grid((F + 255) / 256, M);
+  IZB_LAUNCH("swiglu_pairs", st, swiglu_pairs_kernel<<<grid, 256, 0, st>>>(gu, ldgu, F, C, ldc, c_off));
+  return IZB_OK;
+}

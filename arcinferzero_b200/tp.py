@@ -187,10 +187,14 @@ class Stack:
     (the reference hides its FFN sums behind the next chunk's GEMMs the same way: TpOverlap, zero/mgpu/engine_tp.h:126-151,
     tpo_out :629).  The persistent GEMM then leaves `comm_sms` multiprocessors free (izb_set_sm_limit) and the collectives
     are capped at as many CTAs, so that both are resident at once.  Every chunk owns its buffers; in "rs_quant_ag" mode a
-    rank owns the rows [rank * own, (rank + 1) * own) of EACH chunk (own = chunk rows / world)."""
+    rank owns the rows [rank * own, (rank + 1) * own) of EACH chunk (own = chunk rows / world).
+
+    fused_ffn=True loads the gate and up shards as one interleaved weight (izb_weight_create_gateup) and runs them as one
+    GEMM whose epilogue stores up * silu(gate); False keeps the reference's two launches (gate, then up with store mode 2)."""
 
     def __init__(self, cfg: StackConfig, world: int, rank: int, device: int, mode: str = "allreduce", distinct_layers: bool = True,
-                 chunks: int = 1, overlap: bool = False, balance: bool = False, comm_sms: int = 8, timeout_ms: int = 0):
+                 chunks: int = 1, overlap: bool = False, balance: bool = False, comm_sms: int = 8, timeout_ms: int = 0,
+                 fused_ffn: bool = True):
         import torch
 
         import arcinferzero_b200 as izb
@@ -207,7 +211,11 @@ class Stack:
         for li in range(cfg.layers):
             if sh is None or distinct_layers:
                 sh = shard_rows(cfg, layer_weights(cfg, li), self.plan)
-            self.layers.append({k: izb.Weight(cfg.qtype, rows, N, K, device=device, col_range=cr) for k, (rows, N, K, cr) in sh.items()})
+            L = {k: izb.Weight(cfg.qtype, rows, N, K, device=device, col_range=cr) for k, (rows, N, K, cr) in sh.items()
+                 if not (fused_ffn and k in ("gate", "up"))}
+            if fused_ffn:  # gate | up rows interleaved in one weight: one GEMM, the SwiGLU product formed in its epilogue
+                L["gateup"] = izb.gateup_weight(cfg.qtype, sh["gate"][0], sh["up"][0], sh["gate"][1], sh["gate"][2], device=device)
+            self.layers.append(L)
         self.comm = izb.TpComm(world, rank, device, timeout_ms=timeout_ms, max_ctas=comm_sms if self.overlap else 0)
         dev = torch.device("cuda", device)
         f32, i8 = torch.float32, torch.int8
@@ -306,8 +314,11 @@ class Stack:
 
     def _ffn_half(self, L, c):
         izb, Tc, r = self.izb, self.Tc, self.rows(c)
-        izb.matmul(L["gate"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r])
-        izb.matmul(L["up"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r], acc=2)
+        if "gateup" in L:
+            izb.gemm(L["gateup"], self.xq[r], self.xsc_c[c], M=Tc, out=self.h[r], acc=3)
+        else:
+            izb.matmul(L["gate"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r])
+            izb.matmul(L["up"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r], acc=2)
         aq, asc = self._quant(self.h[r], self.h.shape[1])
         izb.matmul(L["down"], aq, asc, Tc, out=self.part_f[r])
 

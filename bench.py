@@ -233,8 +233,7 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
     T, E, F, NE, NU, TM = 4096, 2048, 768, 128, 8, 128
     rng = np.random.default_rng(SEED + 9)
     wg, wu, wd = S.make_weight(QT, NE * F, E, SEED + 11), S.make_weight(QT, NE * F, E, SEED + 12), S.make_weight(QT, NE * E, F, SEED + 13)
-    Wg = izb.Weight(QT, wg, F, E, n_mats=NE)
-    Wu = izb.Weight(QT, wu, F, E, n_mats=NE)
+    Wgu = izb.gateup_weight(QT, wg, wu, F, E, n_mats=NE)  # gate | up rows interleaved: one grouped GEMM, SwiGLU in its epilogue
     Wd = izb.Weight(QT, wd, E, F, n_mats=NE)
     x = torch.from_numpy(S.make_act(T, E, SEED + 14)).cuda()
     logits = torch.from_numpy(rng.standard_normal((T, NE), dtype=np.float32)).cuda()
@@ -249,7 +248,7 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
         aq, asc, _ = izb.quantize_act(x, Mp=T)
         ids, wts, counts = izb.moe_route(logits, NU)
         offs, tiles, max_tiles, stok, swt, inv = izb.moe_sort(ids, wts, counts, TM)
-        h = izb.moe_gateup(Wg, Wu, aq, asc, tiles, max_tiles, TM, stok, Sn)
+        h = izb.moe_gateup(Wgu, None, aq, asc, tiles, max_tiles, TM, stok, Sn)
         hq, hsc, _ = izb.quantize_act(h, Mp=Sp)
         y = izb.moe_down(Wd, hq, hsc, tiles, max_tiles, TM, swt, Sn)
         izb.moe_combine(out, y, inv, NU)
@@ -297,7 +296,7 @@ def moe_section(izb, torch, tc_peak: float, peak_src: str, iters: int = 10) -> d
            "kernel_ms_per_pass": {k: v["ms"] / iters for k, v in prof.items()},
            "finite": bool(torch.isfinite(out).all().item())}
     res.update(parity())
-    for W in (Wg, Wu, Wd):
+    for W in (Wgu, Wd):
         W.close()
     return res
 

@@ -128,6 +128,15 @@ int izb_weight_create_slice(int ggml_type, const void* h_gguf_rows, int n_mats, 
  * over it writes the parts' outputs side by side, and a decode step pays one launch instead of n_parts. */
 int izb_weight_create_stack(int ggml_type, const void* const* h_parts, const int* n_rows, int n_parts, int K, int device,
                             izb_weight** out);
+/* The gate and the up projection of an FFN (or of every expert of a stack, n_mats > 1) as ONE weight of 2F rows per matrix
+ * whose rows alternate in groups of 32: rows 64j .. 64j+31 are gate rows 32j .., rows 64j+32 .. 64j+63 the up rows of the
+ * same FFN channels (F % 64 == 0; Q8_0, Q4_K, Q4_0).  With store mode 3 of izb_gemm (and izb_moe_gateup given this stack
+ * and wu = NULL) one GEMM computes both projections and stores up * silu(gate) [rows][F]: the reference fuses the same
+ * product into its up GEMM, which reads the gate GEMM's output back (store mode 2, zero/kernels/gemm.cl:562-565; the
+ * `fused` flag of swiglu_quant, zero/kernels/ops.cl:277); here a thread of the GEMM's epilogue holds a gate column and its
+ * up column side by side, so the gate projection never goes to memory.  Same operations, same roundings as mode 2. */
+int izb_weight_create_gateup(int ggml_type, const void* h_gate_rows, const void* h_up_rows, int n_mats, int F, int K, int device,
+                             izb_weight** out);
 /* The loader's host-side decoder on its own (no device needed): n_superblocks superblocks (256 weights each) of a Q4_0,
  * Q5_K, Q6_K or IQ4_XS row -> the form izb_weight_create uploads: GGUF Q8_0 blocks (8 x 34 bytes) for Q4_0, else 304 bytes:
  * f32 d | f32 dmin | int8 scale[16] | uint8 min[16] | 8 zero bytes | int8 (quant - offset)[256]. */
@@ -177,7 +186,8 @@ int izb_softcap_rows(float* d_C, int rows, int ld, int off, int N, float cap, vo
  * the T valid rows, dispatching on T as the reference does: T == 1 -> GEMV (decode.cl gemv, :913), 2..8 -> few-row
  * GEMV reading the weights once (gemv_mt, :1581), T > 8 -> GEMM over Mp padded rows (gemm.cl gemm, :163; needs
  * Mp % 16 == 0, N % 16 == 0).  acc: 0 store, 1 add to C, 2 C = result * silu(C) (fused SwiGLU, gemm.cl:562-565; GEMM
- * only, as in the reference).  `mat` selects the matrix of a stack (0 for a dense weight). */
+ * only, as in the reference), 3 (GEMM only, weights of izb_weight_create_gateup): C[t][c_off + f] = up_f * silu(gate_f),
+ * N / 2 output columns.  `mat` selects the matrix of a stack (0 for a dense weight). */
 int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, const int16_t* d_absum, int T, int Mp,
                float* d_C, int ldc, int c_off, int acc, void* stream);
 /* The two kernels behind izb_matmul, callable directly (kernel ABIs of zero/kernels/decode.cl:913-915,1581-1583 and
@@ -253,7 +263,8 @@ int izb_moe_sort_ex(const int32_t* d_ids, const float* d_wts, const int32_t* d_c
 /* moe_gateup_q (zero/kernels/decode_moe.cl:92-260): d_h[slot][F] = silu(x_tok Wg_e^T) * (x_tok Wu_e^T) for every tile
  * of d_tiles (made by izb_moe_sort with the same TM); wg, wu are stacks [NE][F][K]; the activations are token rows
  * (d_aq [Mp][K], d_asc [K/32][Mp]) gathered through d_stok.  TM 1..8: per-tile kernels on the raw rows, as the
- * reference; TM = 128: grouped tensor-core GEMM.  The grid is sized by max_tiles; tiles past d_tiles[0] return. */
+ * reference; TM = 128: grouped tensor-core GEMM.  The grid is sized by max_tiles; tiles past d_tiles[0] return.
+ * wu = NULL with wg a stack made by izb_weight_create_gateup (TM = 128): one grouped GEMM for both projections. */
 int izb_moe_gateup(const izb_weight* wg, const izb_weight* wu, const int8_t* d_aq, const float* d_asc, int Mp,
                    const int32_t* d_tiles, int max_tiles, int TM, const int32_t* d_stok, float* d_h, void* stream);
 /* moe_down_q (zero/kernels/decode_moe.cl:269-449): d_y[slot][E] = swt[slot] * (hq[slot] Wd_e^T); d_hq [Sp][F],

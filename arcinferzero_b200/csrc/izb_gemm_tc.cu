@@ -788,8 +788,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     } else if (ok && !kDots && row_ok && !*abort_flag) {
       float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + n0 + half * 64;
       const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
-      // plain store, no row factor, 32-byte aligned rows: eight stores of one full 32-byte sector each per thread
-      if (p.acc == 0 && !p.rowscale && ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0) {
+      // plain store (with or without the row factor), 32-byte aligned rows: eight stores of one full 32-byte sector each
+      // per thread
+      if (p.acc == 0 && ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0) {
+        if (p.rowscale) {
+          const unsigned long long rs2 = pack2(rs);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) res2[c] = fmul2(rs2, res2[c]);
+        }
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8)
           asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * c8), "l"(res2[4 * c8]), "l"(res2[4 * c8 + 1]),

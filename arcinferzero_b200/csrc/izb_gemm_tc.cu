@@ -381,63 +381,6 @@ __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restri
 }
 
 // ---------------------------------------------------------------------------------------------- the GEMM kernel
-// The store modes other than the plain aligned store, for one thread's 64 columns (pairs r[0..31]) of output row `row`
-// (already offset by c_off): an optional factor per row, 1 add, 2 C = new * silu(C_old), 3 gate | up pairs, and rows that
-// are not 32-byte aligned.
-__device__ __noinline__ void store_other_modes(const unsigned long long* r, float* row, int n0, int half, int acc, float rs, bool has_rs,
-                                               int ldc) {
-  if (acc == 3) {
-    // Gate and up projections in one weight whose rows alternate in groups of 32 (izb_weight_create_gateup): this
-    // thread's 64 columns are 32 gate outputs followed by the 32 up outputs of the same FFN rows, so the SwiGLU product
-    // up * silu(gate) (zero/kernels/gemm.cl:562-565) is formed here and only the F-wide result is stored.
-    float* cp = row + (n0 >> 1) + half * 32;
-    const bool wide = ((reinterpret_cast<uintptr_t>(cp) | ((size_t)ldc * 4)) & 31) == 0;
-#pragma unroll 1
-    for (int j = 0; j < 4; ++j) {
-      unsigned long long o[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const unsigned long long g2 = r[4 * j + i], u2 = r[16 + 4 * j + i];
-        o[i] = pack_pair(swiglu_mul(lo_f(g2), lo_f(u2)), swiglu_mul(hi_f(g2), hi_f(u2)));
-      }
-      if (wide) {
-        asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * j), "l"(o[0]), "l"(o[1]), "l"(o[2]), "l"(o[3]) : "memory");
-      } else {
-        reinterpret_cast<float4*>(cp + 8 * j)[0] = make_float4(lo_f(o[0]), hi_f(o[0]), lo_f(o[1]), hi_f(o[1]));
-        reinterpret_cast<float4*>(cp + 8 * j)[1] = make_float4(lo_f(o[2]), hi_f(o[2]), lo_f(o[3]), hi_f(o[3]));
-      }
-    }
-    return;
-  }
-  float* cp = row + n0 + half * 64;
-  if (acc == 0 && ((reinterpret_cast<uintptr_t>(cp) | ((size_t)ldc * 4)) & 31) == 0) {  // the row factor, 32-byte stores
-    const unsigned long long rs2 = pack2(rs);
-#pragma unroll 1
-    for (int c8 = 0; c8 < 8; ++c8)
-      asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * c8), "l"(fmul2(rs2, r[4 * c8])), "l"(fmul2(rs2, r[4 * c8 + 1])),
-                   "l"(fmul2(rs2, r[4 * c8 + 2])), "l"(fmul2(rs2, r[4 * c8 + 3]))
-                   : "memory");
-    return;
-  }
-#pragma unroll 1
-  for (int c4 = 0; c4 < 16; ++c4) {
-    float4 v = make_float4(lo_f(r[2 * c4]), hi_f(r[2 * c4]), lo_f(r[2 * c4 + 1]), hi_f(r[2 * c4 + 1]));
-    if (has_rs) { v.x = __fmul_rn(rs, v.x); v.y = __fmul_rn(rs, v.y); v.z = __fmul_rn(rs, v.z); v.w = __fmul_rn(rs, v.w); }
-    float4* dst = reinterpret_cast<float4*>(cp) + c4;
-    if (acc == 1) {
-      const float4 o = *dst;
-      v.x = __fadd_rn(v.x, o.x); v.y = __fadd_rn(v.y, o.y); v.z = __fadd_rn(v.z, o.z); v.w = __fadd_rn(v.w, o.w);
-    } else if (acc == 2) {  // C holds the gate projection: C = v * silu(C)   (zero/kernels/gemm.cl:562-565)
-      const float4 o = *dst;
-      v.x = swiglu_mul(o.x, v.x);
-      v.y = swiglu_mul(o.y, v.y);
-      v.z = swiglu_mul(o.z, v.z);
-      v.w = swiglu_mul(o.w, v.w);
-    }
-    *dst = v;
-  }
-}
-
 template <int QT, bool kDots>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -746,9 +689,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     for (int c = 0; c < 32; ++c) res2[c] = tq2[c] = 0ull;
     for (int s = 0; s < nsb && ok; ++s, ++sbc) {
       const float* as = reinterpret_cast<const float*>(smem + OFF_ASC + sq * 4096) + r;  // this row's 8 block scales
-      if (warp == 8) TRACE(13, sbc);
       if (!kDots && !mbar_wait(bar(ASC_FULL + sq), pq, abort_flag, p.err, p.spin_limit, E_EPI)) { ok = false; break; }
-      if (warp == 8) TRACE(14, sbc);
 #pragma unroll
       for (int b = 0; b < 8; ++b) {
         const unsigned long long a2 = pack2(kDots ? 0.0f : as[b * BM]);
@@ -800,7 +741,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         mbar_arrive(bar(ASC_EMPTY + sq));
         if (++sq == NASC) { sq = 0; pq ^= 1; }
       }
-      if (warp == 8) TRACE(15, sbc);
       if (kMins) {  // res += d * tq
         const ulonglong2* dv = reinterpret_cast<const ulonglong2*>(smem + OFF_DM + (sbc & 3) * 512 + half * 256);
 #pragma unroll
@@ -824,21 +764,60 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         for (int c = 0; c < 32; ++c) ffma2(res2[c], one2, v[c]);
       }
     }
-    if (ok && !kDots && row_ok && !*abort_flag) {
-      float* row = p.C + (size_t)out_row * p.ldc + p.c_off;
-      float* cp = row + n0 + half * 64;
-      // plain store, 32-byte aligned rows: eight stores of one full 32-byte sector each per thread
-      if (p.acc == 0 && !p.rowscale && ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0) {
+    if (ok && !kDots && row_ok && !*abort_flag && p.acc == 3) {
+      // Gate and up projections in one weight whose rows alternate in groups of 32 (izb_weight_create_gateup): this
+      // thread's 64 columns are 32 gate outputs followed by the 32 up outputs of the same FFN rows, so the SwiGLU product
+      // up * silu(gate) (zero/kernels/gemm.cl:562-565) is formed in registers and only the F-wide result is stored.
+      float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + (n0 >> 1) + half * 32;
+      const bool wide = ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        unsigned long long o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned long long g2 = res2[4 * j + i], u2 = res2[16 + 4 * j + i];
+          o[i] = pack_pair(swiglu_mul(lo_f(g2), lo_f(u2)), swiglu_mul(hi_f(g2), hi_f(u2)));
+        }
+        if (wide) {
+          asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * j), "l"(o[0]), "l"(o[1]), "l"(o[2]), "l"(o[3]) : "memory");
+        } else {
+          reinterpret_cast<float4*>(cp + 8 * j)[0] = make_float4(lo_f(o[0]), hi_f(o[0]), lo_f(o[1]), hi_f(o[1]));
+          reinterpret_cast<float4*>(cp + 8 * j)[1] = make_float4(lo_f(o[2]), hi_f(o[2]), lo_f(o[3]), hi_f(o[3]));
+        }
+      }
+    } else if (ok && !kDots && row_ok && !*abort_flag) {
+      float* cp = p.C + (size_t)out_row * p.ldc + p.c_off + n0 + half * 64;
+      const float rs = p.rowscale ? p.rowscale[out_row] : 1.0f;
+      // plain store (with or without the row factor), 32-byte aligned rows: eight stores of one full 32-byte sector each
+      // per thread
+      if (p.acc == 0 && ((reinterpret_cast<uintptr_t>(cp) | ((size_t)p.ldc * 4)) & 31) == 0) {
+        if (p.rowscale) {
+          const unsigned long long rs2 = pack2(rs);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) res2[c] = fmul2(rs2, res2[c]);
+        }
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8)
           asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(cp + 8 * c8), "l"(res2[4 * c8]), "l"(res2[4 * c8 + 1]),
                        "l"(res2[4 * c8 + 2]), "l"(res2[4 * c8 + 3])
                        : "memory");
-      } else {  // every other store mode: out of line, on a copy (once per tile; the role loops stay small)
-        unsigned long long tmp[32];
+      } else
 #pragma unroll
-        for (int c = 0; c < 32; ++c) tmp[c] = res2[c];
-        store_other_modes(tmp, row, n0, half, p.acc, p.rowscale ? p.rowscale[out_row] : 1.0f, p.rowscale != nullptr, p.ldc);
+      for (int c4 = 0; c4 < 16; ++c4) {
+        float4 v = make_float4(lo_f(res2[2 * c4]), hi_f(res2[2 * c4]), lo_f(res2[2 * c4 + 1]), hi_f(res2[2 * c4 + 1]));
+        if (p.rowscale) { v.x = __fmul_rn(rs, v.x); v.y = __fmul_rn(rs, v.y); v.z = __fmul_rn(rs, v.z); v.w = __fmul_rn(rs, v.w); }
+        float4* dst = reinterpret_cast<float4*>(cp) + c4;
+        if (p.acc == 1) {
+          const float4 o = *dst;
+          v.x = __fadd_rn(v.x, o.x); v.y = __fadd_rn(v.y, o.y); v.z = __fadd_rn(v.z, o.z); v.w = __fadd_rn(v.w, o.w);
+        } else if (p.acc == 2) {  // C holds the gate projection: C = v * silu(C)   (zero/kernels/gemm.cl:562-565)
+          const float4 o = *dst;
+          v.x = swiglu_mul(o.x, v.x);
+          v.y = swiglu_mul(o.y, v.y);
+          v.z = swiglu_mul(o.z, v.z);
+          v.w = swiglu_mul(o.w, v.w);
+        }
+        *dst = v;
       }
     }
     }

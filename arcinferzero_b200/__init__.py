@@ -25,7 +25,7 @@ SYMBOLS = [
     "izb_reserve", "izb_set_sm_limit", "izb_debug_wait_test", "izb_tensor_peak",
     "izb_weight_create", "izb_weight_create_slice", "izb_weight_create_stack", "izb_weight_create_gateup", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
-    "izb_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
+    "izb_matmul", "izb_quant_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_route_ex", "izb_moe_sort", "izb_moe_sort_ex", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
     "izb_moe_combine_ex",
     "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_create_ex", "izb_tp_wait", "izb_tp_abort", "izb_tp_destroy", "izb_tp_allreduce_rows",
@@ -236,6 +236,23 @@ def matmul(w: Weight, aq, asc, T: int, out=None, c_off: int = 0, acc: int = 0, m
         out = torch.empty((Mp, w.N), dtype=torch.float32, device=aq.device)
     _check(lib().izb_matmul(w.handle, mat, _p(aq), _p(asc), None, T, Mp, _p(out), out.stride(0), c_off, acc, _stream()))
     return out
+
+
+def quant_matmul(w: Weight, x, T: int, Mp: int | None = None, out=None, c_off: int = 0, acc: int = 0, mat: int = 0, qout=None):
+    """izb_quant_matmul: quantise x [T, K] f32 and multiply in one call.  Returns (out, aq, asc); qout = (aq, asc) to reuse
+    buffers."""
+    import torch
+    Mp = Mp or pad_rows(T)
+    K = w.K
+    if qout is None:
+        aq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
+        asc = torch.empty((K // 32, Mp), dtype=torch.float32, device=x.device)
+    else:
+        aq, asc = qout
+    if out is None:
+        out = torch.empty((Mp, w.N // 2 if acc == 3 else w.N), dtype=torch.float32, device=x.device)
+    _check(lib().izb_quant_matmul(w.handle, mat, _p(x), x.stride(0), T, Mp, _p(aq), _p(asc), _p(out), out.stride(0), c_off, acc, _stream()))
+    return out, aq, asc
 
 
 def gemv(w: Weight, aq, asc, T: int, out=None, c_off: int = 0, acc: int = 0, mat: int = 0):

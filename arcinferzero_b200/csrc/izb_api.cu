@@ -21,6 +21,8 @@ int izb_make_raw_tensor_map(izb_weight* w);
 int izb_gemm_k16_launch(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int M, int Mp, float* C, int ldc,
                         int c_off, int acc, int32_t* dots, cudaStream_t st);
 
+int izb_gemm_tc_quant_launch(const izb_weight* w, int mat, const float* x, int ldx, int M, int Mp, int8_t* aq, float* asc, float* C,
+                             int ldc, int c_off, int acc, cudaStream_t st);
 int izb_swiglu_pairs_launch(const float* gu, int ldgu, int M, int F, float* C, int ldc, int c_off, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------------- errors
@@ -581,6 +583,22 @@ extern "C" int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, cons
   return izb_gemm(w, mat, d_aq, d_asc, Mp, Mp, d_C, ldc, c_off, acc, IZB_GEMM_AUTO, stream);
 }
 
+extern "C" int izb_quant_matmul(const izb_weight* w, int mat, const float* d_x, int ldx, int T, int Mp, int8_t* d_aq, float* d_asc,
+                                float* d_C, int ldc, int c_off, int acc, void* stream) {
+  if (!w || !d_x || !d_aq || !d_asc || !d_C) IZB_FAIL(IZB_ERR_ARG, "quant_matmul: null pointer");
+  if (T < 1 || T > Mp) IZB_FAIL(IZB_ERR_SHAPE, "quant_matmul: %d rows of Mp = %d", T, Mp);
+  // the GEMM with the fused pre-pass: same checks as izb_gemm, then one launch writes aq / asc and the operand images
+  if (T > 8 && (w->type == IZB_Q8_0 || w->type == IZB_Q4_K) && g_dev[w->device < 0 || w->device >= kIzbMaxDev ? 0 : w->device].tc_ok.load() != 0) {
+    if (int rc = check_gemm_args(w, mat, d_aq, d_asc, Mp, Mp, d_C, ldc, c_off, acc)) return rc;
+    if (ldx < w->K || ldx % 4 || !izb_aligned(d_x, 16)) IZB_FAIL(IZB_ERR_ALIGN, "quant_matmul: x must be 16-byte aligned with ldx >= K a multiple of 4");
+    if (int rc = izb_require_device(w->device, "quant_matmul")) return rc;
+    const int rc = izb_gemm_tc_quant_launch(w, mat, d_x, ldx, T, Mp, d_aq, d_asc, d_C, ldc, c_off, acc, (cudaStream_t)stream);
+    if (rc <= 0) return rc;
+  }
+  if (int rc = izb_quantize_act(d_x, ldx, T, Mp, w->K, d_aq, d_asc, nullptr, stream)) return rc;
+  return izb_matmul(w, mat, d_aq, d_asc, nullptr, T, Mp, d_C, ldc, c_off, acc, stream);
+}
+
 // records the verdict of the start-up check (izb_selfcheck lives with the tensor-core kernel)
 void izb_set_tc_ok(int device, int ok) { g_dev[device].tc_ok.store(ok); }
 int izb_get_tc_ok(int device) { return g_dev[device].tc_ok.load(); }
@@ -643,8 +661,7 @@ extern "C" int izb_matmul_host(const izb_weight* w, int mat, const float* h_x, i
     // compute: after the copy in, and after the buffer's previous result has left
     IZB_CUDA(cudaStreamWaitEvent(d.hs[1], d.he[b][0], 0));
     if (c >= 2) IZB_CUDA(cudaStreamWaitEvent(d.hs[1], d.he[b][2], 0));
-    if (int rc = izb_quantize_act(dx, K, m, Mp, K, daq, dasc, nullptr, d.hs[1])) return rc;
-    if (int rc = izb_matmul(w, mat, daq, dasc, nullptr, m, Mp, dC, N, 0, 0, d.hs[1])) return rc;
+    if (int rc = izb_quant_matmul(w, mat, dx, K, m, Mp, daq, dasc, dC, N, 0, 0, d.hs[1])) return rc;
     IZB_CUDA(cudaEventRecord(d.he[b][1], d.hs[1]));
     // copy out
     IZB_CUDA(cudaStreamWaitEvent(d.hs[2], d.he[b][1], 0));

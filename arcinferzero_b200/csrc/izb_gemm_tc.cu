@@ -380,6 +380,98 @@ __global__ void __launch_bounds__(256) act_prepare_kernel(const int8_t* __restri
   }
 }
 
+// ---------------------------------------------------------------------------------------------- quantiser + pre-pass in one
+// izb_quantize_act (csrc/izb_quantize.cu, the arithmetic of quantize_act_cpu, src/quants.h:626-643, bit for bit) and
+// act_prepare_kernel above in one pass over the f32 rows: a lane owns 8 consecutive values (= one 16-byte operand chunk),
+// four lanes a 32-block.  Writes aq / asc exactly as the quantiser does (the caller's buffers stay valid for every other
+// kernel) and, from the same registers, the operand images, the gathered scales and the min-term factors of the dense
+// tensor-core GEMM: the int8 rows are not read back and the second launch is gone.  One CTA = 32 rows x one superblock.
+template <int QT>
+__global__ void __launch_bounds__(256) quant_prepare_kernel(const float* __restrict__ x, int ldx, int M, int Mp, int K,
+                                                            int8_t* __restrict__ aq, float* __restrict__ asc,
+                                                            uint16_t* __restrict__ aimg, float* __restrict__ ascimg, int sps, int n_tiles) {
+  __shared__ float s_sc[8][33];
+  const int sb = blockIdx.x, m0 = blockIdx.y * 32, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = sb * 256 + lane * 8;
+  const size_t nstages = (size_t)(K / 256) * sps;
+  float v[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + warp + 8 * i;
+    if (m < M) {
+      const float4* p = reinterpret_cast<const float4*>(x + (size_t)m * ldx + col);
+      const float4 a = __ldcs(p), b = __ldcs(p + 1);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+      v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[i][k] = 0.0f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = warp + 8 * i, m = m0 + rr;
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[i][k]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    int q[8], s = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float pr = __fmul_rn(v[i][k], inv);
+      q[k] = fabsf(pr) <= 2147483520.0f ? __float2int_rn(pr) : 0;  // (see quantize_act_kernel: the overflow case)
+      q[k] = (int)(int8_t)q[k];  // the stored byte is what the GEMM multiplies
+      s += q[k];
+    }
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+    const float sc = __fdiv_rn(amax, 127.0f);
+    if (m < Mp) {
+      uint2 pk;
+      pk.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+      pk.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+      *reinterpret_cast<uint2*>(aq + (size_t)m * K + col) = pk;
+    }
+    if ((lane & 3) == 0) s_sc[lane >> 2][rr] = sc;
+    // ---- the operand image of this chunk: tile m / 128, row m % 128, stage lane / 8 of the superblock, chunk lane % 8
+    const int tile = m >> 7, r = m & 127;
+    if (tile >= n_tiles) continue;  // (padding rows past the last tile the GEMM reads: aq / asc only)
+    uint8_t* tile_img = reinterpret_cast<uint8_t*>(aimg) + (size_t)tile * nstages * STAGE_BYTES;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e0 = QT == IZB_Q4_K ? q4k_perm8(2 * j) : 2 * j, e1 = QT == IZB_Q4_K ? q4k_perm8(2 * j + 1) : 2 * j + 1;
+      const __half2 h = __floats2half2_rn((float)q[e0], (float)q[e1]);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(tile_img + ((size_t)sb * sps + (lane >> 3)) * STAGE_BYTES + r * 128 + (((lane & 7) ^ (r & 7)) << 4)) =
+        make_uint4(o[0], o[1], o[2], o[3]);
+    if ((lane & 3) == 0) {
+      const int b = lane >> 2;  // block of the superblock
+      ascimg[((size_t)tile * (K / 32) + sb * 8 + b) * BM + r] = sc;
+      if (QT == IZB_Q4_K && sps == 5) {
+        const float t = __fmul_rn(sc, (float)s);
+        const __nv_bfloat16 h1 = __float2bfloat16_rn(t);
+        const float r1 = __fsub_rn(t, __bfloat162float(h1));
+        const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+        const __nv_bfloat16 h3 = __float2bfloat16_rn(__fsub_rn(r1, __bfloat162float(h2)));
+        uint8_t* row = tile_img + ((size_t)sb * 5 + 4) * STAGE_BYTES + r * 128 + 2 * b;
+        const unsigned short t3[3] = {__bfloat16_as_ushort(h1), __bfloat16_as_ushort(h2), __bfloat16_as_ushort(h3)};
+        constexpr int term[6] = {0, 0, 1, 0, 1, 2};
+#pragma unroll
+        for (int k = 0; k < 6; ++k) *reinterpret_cast<unsigned short*>(row + ((k ^ (r & 7)) << 4)) = t3[term[k]];
+      }
+    }
+  }
+  __syncthreads();
+  {
+    const int b = threadIdx.x >> 5, r = threadIdx.x & 31;
+    if (m0 + r < Mp) asc[(size_t)(sb * 8 + b) * Mp + m0 + r] = s_sc[b][r];
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- the GEMM kernel
 template <int QT, bool kDots>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcParams p) {
@@ -983,6 +1075,30 @@ int izb_gemm_tc_launch(const izb_weight* w, int mat, const int8_t* aq, const flo
   const int n_tiles = (M + BM - 1) / BM;
   if (n_tiles > 65535) return 1;
   return run_tc(w, mat, aq, asc, Mp, Mp, nullptr, n_tiles, nullptr, nullptr, M, C, ldc, c_off, acc, dots, kWsGemm, st);
+}
+
+// quantise + multiply in one call (dense): the fused pre-pass over the M valid rows (rows up to Mp zeroed), then the GEMM on
+// its images.  +1 = shape not taken.
+int izb_gemm_tc_quant_launch(const izb_weight* w, int mat, const float* x, int ldx, int M, int Mp, int8_t* aq, float* asc, float* C,
+                             int ldc, int c_off, int acc, cudaStream_t st) {
+  const int n_tiles = (Mp + BM - 1) / BM;  // (the GEMM runs over the padded rows, as izb_matmul's does)
+  if (n_tiles > 65535 || !w->has_tmap || w->N % BN || w->K % 256) return 1;
+  const int K = w->K, sps = w->type == IZB_Q4_K ? 5 : 4;
+  size_t img_bytes, asc_bytes;
+  tc_scratch_bytes(n_tiles, K, sps, &img_bytes, &asc_bytes);
+  void* ws = nullptr;
+  if (int rc = izb_workspace(w->device, kWsGemm, img_bytes + asc_bytes, &ws)) return rc;
+  uint32_t* err = izb_device_error_word(w->device);
+  if (!err) IZB_FAIL(IZB_ERR_NOMEM, "gemm: no device error word");
+  uint16_t* aimg = (uint16_t*)ws;
+  float* ascimg = (float*)((unsigned char*)ws + img_bytes);
+  const int rows_img = n_tiles * BM > Mp ? n_tiles * BM : Mp;  // every row of every tile is written (rows past M as zeros)
+  dim3 grid(K / 256, (rows_img + 31) / 32);
+  if (w->type == IZB_Q4_K)
+    IZB_LAUNCH("quant_prepare", st, quant_prepare_kernel<IZB_Q4_K><<<grid, 256, 0, st>>>(x, ldx, M, Mp, K, aq, asc, aimg, ascimg, sps, n_tiles));
+  else
+    IZB_LAUNCH("quant_prepare", st, quant_prepare_kernel<IZB_Q8_0><<<grid, 256, 0, st>>>(x, ldx, M, Mp, K, aq, asc, aimg, ascimg, sps, n_tiles));
+  return run_tc_on(w, mat, aq, asc, Mp, Mp, nullptr, n_tiles, nullptr, nullptr, Mp, C, ldc, c_off, acc, nullptr, ws, err, st, true);
 }
 
 // MoE on the tensor cores: the slots of each expert are tiles of up to 128 rows (izb_moe_sort with TM = 128); gate then up

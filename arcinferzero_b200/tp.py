@@ -268,6 +268,13 @@ class Stack:
         self.izb.quantize_act(src, Mp=Tc, out=(aq, asc, None))
         return aq, asc
 
+    def _quant_matmul(self, w, src, K, out):
+        """quant_rows + matmul of a chunk in one call (the quantiser writes the GEMM's operand images as well)."""
+        Tc = self.Tc
+        aq = self.aq[:Tc * K].view(Tc, K)
+        asc = self.asc[:Tc * (K // 32)].view(K // 32, Tc)
+        self.izb.quant_matmul(w, src, Tc, Tc, out=out, qout=(aq, asc))
+
     def _sum(self, c, part):
         """Row-parallel partials of chunk c -> residual stream; leaves the chunk's quantised stream in xq / xsc_c[c]."""
         izb, r = self.izb, self.rows(c)
@@ -309,8 +316,7 @@ class Stack:
         izb, Tc, r = self.izb, self.Tc, self.rows(c)
         nq = self.plan.q[1] - self.plan.q[0]
         izb.matmul(L["qkv"], self.xq[r], self.xsc_c[c], Tc, out=self.qkv[r])
-        aq, asc = self._quant(self.qkv[r][:, :nq], nq)
-        izb.matmul(L["o"], aq, asc, Tc, out=self.part_a[r])
+        self._quant_matmul(L["o"], self.qkv[r][:, :nq], nq, self.part_a[r])
 
     def _ffn_half(self, L, c):
         izb, Tc, r = self.izb, self.Tc, self.rows(c)
@@ -319,8 +325,7 @@ class Stack:
         else:
             izb.matmul(L["gate"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r])
             izb.matmul(L["up"], self.xq[r], self.xsc_c[c], Tc, out=self.h[r], acc=2)
-        aq, asc = self._quant(self.h[r], self.h.shape[1])
-        izb.matmul(L["down"], aq, asc, Tc, out=self.part_f[r])
+        self._quant_matmul(L["down"], self.h[r], self.h.shape[1], self.part_f[r])
 
     def forward(self, trace: list | None = None, layers: int | None = None):
         """One pass over all (or the first `layers`) layers.  `trace` (tests, parity fields of the benchmark) receives per

@@ -532,8 +532,8 @@ def main() -> None:
     izb.selfcheck(local)
 
     def step():
-        izb.quantize_act(x, Mp=Mp, out=(aq, asc, None))
-        izb.matmul(W, aq, asc, M, out=out)
+        # quant_rows + matmul as one call (izb_quant_matmul): the quantiser also writes the tensor-core GEMM's operand images
+        izb.quant_matmul(W, x, M, Mp, out=out, qout=(aq, asc))
 
     def barrier():
         if world > 1:

@@ -190,6 +190,13 @@ int izb_softcap_rows(float* d_C, int rows, int ld, int off, int N, float cap, vo
  * N / 2 output columns.  `mat` selects the matrix of a stack (0 for a dense weight). */
 int izb_matmul(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, const int16_t* d_absum, int T, int Mp,
                float* d_C, int ldc, int c_off, int acc, void* stream);
+/* quant_rows + matmul in one call (Engine::quant_rows, zero/engine.h:1445, directly followed by Engine::matmul, :1080, as every
+ * projection of a prompt chunk runs them): d_x [T][ldx] f32 -> d_aq [Mp][K], d_asc [K/32][Mp] exactly as izb_quantize_act
+ * writes them (the buffers stay valid for further projections of the same activations), then C as izb_matmul.  For T > 8
+ * on the tensor-core kernel the quantiser also writes that kernel's operand images, so the int8 rows are not read back
+ * and the pre-pass launch of the GEMM is gone; results are bit for bit those of the two separate calls. */
+int izb_quant_matmul(const izb_weight* w, int mat, const float* d_x, int ldx, int T, int Mp, int8_t* d_aq, float* d_asc, float* d_C,
+                     int ldc, int c_off, int acc, void* stream);
 /* The two kernels behind izb_matmul, callable directly (kernel ABIs of zero/kernels/decode.cl:913-915,1581-1583 and
  * zero/kernels/gemm.cl:163-166). */
 int izb_gemv(const izb_weight* w, int mat, const int8_t* d_aq, const float* d_asc, int T, int Mp, float* d_C, int ldc,

@@ -106,3 +106,43 @@ def test_store_mode_3_needs_the_interleaved_weight(izb, torch):
         izb.matmul(Wgu, dev(torch, aq), dev(torch, asc), 2, acc=3)  # GEMV rows: no fused store
     W.close()
     Wgu.close()
+
+
+@pytest.mark.parametrize("qt", [12, 8])
+@pytest.mark.parametrize("T,N,K", [(200, 384, 1024), (40, 256, 512), (1024, 128, 2048), (5, 256, 512)])
+def test_quant_matmul_is_the_two_calls_bit_for_bit(izb, torch, qt, T, N, K):
+    """izb_quant_matmul (quantiser fused with the GEMM's pre-pass) against izb_quantize_act + izb_matmul: the int8 rows, the
+    scales and the outputs are identical, for row counts that are not multiples of the tile and for the GEMV row counts
+    (where it is the two calls)."""
+    w = S.make_weight(qt, N, K, 70 + qt + N)
+    W = izb.Weight(qt, w, N, K)
+    x = S.make_act(T, K, 71 + T)
+    x[0, :32] = 0.0                      # a zero block
+    x[min(T - 1, 3), 32:64] = 1e-42      # denormals: 127 / amax overflows
+    Mp = izb.pad_rows(T)
+    dx = dev(torch, x)
+    aq, asc, _ = izb.quantize_act(dx, Mp=Mp)
+    ref = izb.matmul(W, aq, asc, T)
+    out = torch.full((Mp, N + 16), float("nan"), dtype=torch.float32, device="cuda")
+    _, aq2, asc2 = izb.quant_matmul(W, dx, T, Mp, out=out, c_off=8)
+    assert (aq2.cpu().numpy() == aq.cpu().numpy()).all()
+    assert (bits(asc2.cpu().numpy()) == bits(asc.cpu().numpy())).all()
+    got, rows = out.cpu().numpy(), (Mp if T > 8 else T)
+    assert (bits(got[:rows, 8:N + 8]) == bits(ref.cpu().numpy()[:rows])).all()
+    assert np.isnan(got[:, :8]).all() and np.isnan(got[:, N + 8:]).all()
+    oq, osc, _ = O.quantize_act(x, Mp=Mp)
+    assert (aq2.cpu().numpy() == oq).all() and (bits(asc2.cpu().numpy()) == bits(osc)).all()
+    assert rel(got[:T, 8:N + 8], O.matmul(qt, w, K, oq, osc, T, "f64")) < TOL
+    # a padded row count far beyond the tiles the GEMM reads, and the store modes
+    if T > 8:
+        big = Mp + 256
+        o2, aq3, asc3 = izb.quant_matmul(W, dx, T, big)
+        assert (aq3.cpu().numpy()[:Mp] == oq).all() and not aq3.cpu().numpy()[Mp:].any()
+        assert (bits(o2.cpu().numpy()[:T]) == bits(ref.cpu().numpy()[:T])).all()
+        acc1 = ref.clone()
+        izb.quant_matmul(W, dx, T, Mp, out=acc1, acc=1)
+        two = ref.clone()
+        izb.matmul(W, aq, asc, T, out=two, acc=1)
+        assert (bits(acc1.cpu().numpy()[:T]) == bits(two.cpu().numpy()[:T])).all()
+    assert izb.device_status(0) == 0
+    W.close()

@@ -410,7 +410,9 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
     x_in = torch.from_numpy(S.make_act(cfg.tokens, cfg.hidden, SEED + 5)).cuda() * 0.05
     out = []
     forms = [("allreduce", dict()), ("rs_quant_ag", dict()),
-             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8))]
+             # (SMs left to the collectives: measured best at 8 ranks with 16 of 148 -- fewer and the sums become the
+             #  critical path, more and the GEMMs lose more than the sums gain; at 2 ranks the sums are 3 % of a pass)
+             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8 if world <= 2 else 16))]
     if world == 1:
         forms = forms[1:]  # (one rank: both summation modes are the same work)
     for mode, kw in forms:

@@ -183,6 +183,9 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
         dev_bytes = wbytes if qt in (8, 12) else Nn * (Kk // 256) * 304
         copies = max(1, -(-300_000_000 // dev_bytes)) if dev_bytes < 400_000_000 else 2
         Ws = [izb.Weight(qt, ws[0], Nn, Kk) if parts == 1 else izb.stacked_weight(qt, ws, Kk) for _ in range(copies)]
+        # rows the oracle checks after the timed launches: the first 1024 and the last 256 of the matrix
+        chk_rows = np.concatenate([np.arange(min(1024, Nn)), np.arange(max(Nn - 256, 0), Nn)])
+        w_chk = np.ascontiguousarray((ws[0] if parts == 1 else np.concatenate(ws))[chk_rows])
         del ws
         # (the output head once more with its logit soft-cap, as the reference's Gemma head runs: GEMV, then cap * tanh(v / cap))
         for T, cap in ((1, 0.0), (2, 0.0)) + (((1, 30.0),) if qt == 8 else ()):
@@ -214,11 +217,20 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
             e1.record()
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
+            # parity of this shape (checker only, outside the timed launches): one more launch against the oracle's f64 model
+            from oracle import oracle as O
+            launch(0)
+            got = y.cpu().numpy()[:, chk_rows]
+            ref = O.matmul(qt, w_chk, Kk, aq.cpu().numpy(), asc.cpu().numpy(), T, "f64")
+            if cap > 0:
+                ref = (np.float32(cap) * np.tanh(ref.astype(np.float64) / cap)).astype(np.float32)
+            par = _rel(got, ref)
             nbytes = wbytes + T * (Kk + Kk // 32 * 4) + T * Nn * 4 * (3 if cap > 0 else 1)  # (the cap reads and writes the row again)
             gbs = nbytes / (us * 1e-6) / 1e9
             out.append({"type": {12: "Q4_K", 8: "Q8_0", 14: "Q6_K"}[qt], "device_weight_bytes": dev_bytes, "N": Nn, "K": Kk, "stacked_parts": parts, "batch": T, "softcap": cap,
                         "in_config3": Kk == K and cap == 0 and qt != 14 and parts == 1, "us_per_launch": us,
-                        "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak,
+                        "bytes_per_launch": nbytes, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "parity_max_rel": par, "parity_tolerance": 1e-5,
+                        "parity_rows_checked": int(len(chk_rows)),
                         "peak": f"{hbm_peak} GB/s {peak_src} copy", "weight_copies_in_rotation": copies})
         for W_ in Ws:
             W_.close()
@@ -523,6 +535,7 @@ def main() -> None:
     Nr = n1 - n0
     w_full = S.make_weight(QT, N, K, SEED)
     W = izb.Weight(QT, w_full, N, K, device=local, row_range=(n0, n1))
+    w_shard = np.ascontiguousarray(w_full[n0:n1]) if rank == 0 else None  # (for the parity field of the line)
     del w_full
     x_host = torch.from_numpy(S.make_act(M, K, SEED + 1)).pin_memory()
     x = x_host.cuda(non_blocking=True)
@@ -570,6 +583,22 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
+
+    # ---- parity of what was just timed (rank 0; the oracle is the checker, outside the timed region): eight token rows of
+    # the last step's output against the oracle's quantiser (int8 rows and scales exact) and its f64 model of the product
+    parity = None
+    if rank == 0:
+        from oracle import oracle as O
+        idx = np.array([0, 1, 127, 128, M // 2, M - 129, M - 2, M - 1])
+        xs = x_host.numpy()[idx]
+        oq, osc, _ = O.quantize_act(xs, Mp=16)
+        tidx = torch.from_numpy(idx).cuda()
+        gq, gsc = aq[tidx].cpu().numpy(), asc[:, tidx].cpu().numpy()
+        ref = O.matmul(QT, w_shard, K, oq, osc, len(idx), "f64")
+        parity = {"parity_max_rel": _rel(out[tidx].cpu().numpy(), ref), "parity_tolerance": 1e-5,
+                  "int8_rows_exact": bool((gq == oq[:len(idx)]).all() and (gsc.view(np.uint32) == osc[:, :len(idx)].view(np.uint32)).all()),
+                  "rows_checked": int(len(idx)), "columns_checked": int(Nr)}
+        del w_shard
 
     # ---- end to end through the host-buffer C-ABI call
     for _ in range(2):
@@ -637,7 +666,7 @@ def main() -> None:
                          "ms_per_launch": ms_kernel, "launches": g["launches"],
                          "kernel_shares": {k: v["ms"] / total_prof for k, v in prof.items()}},
             "e2e": {"value": M / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * Nr * 4},
-            "gpu_launches": launches, "clocks": clocks, "device_wait_errors": status,
+            "gpu_launches": launches, "clocks": clocks, "device_wait_errors": status, "parity": parity,
         }
         if tp_stack is not None:
             line["tp_stack"] = tp_stack

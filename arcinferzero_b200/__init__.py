@@ -29,7 +29,7 @@ SYMBOLS = [
     "izb_moe_route", "izb_moe_route_ex", "izb_moe_sort", "izb_moe_sort_ex", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
     "izb_moe_combine_ex",
     "izb_tp_range", "izb_tp_add", "izb_tp_unique_id", "izb_tp_create", "izb_tp_create_ex", "izb_tp_wait", "izb_tp_abort", "izb_tp_destroy", "izb_tp_allreduce_rows",
-    "izb_tp_reduce_quant_gather", "izb_tp_gather_logits",
+    "izb_tp_reduce_quant_gather", "izb_tp_gather_logits", "izb_p2p_push", "izb_p2p_wait", "izb_p2p_wait_host", "izb_tp_scales_from_ranks",
 ]
 
 
@@ -401,6 +401,30 @@ def tp_add(x, parts):
     n = x.numel()
     _check(lib().izb_tp_add(_p(x), _p(parts), C.c_size_t(n), parts.shape[0], C.c_size_t(n), _stream()))
     return x
+
+
+def p2p_push(copies, flags, value: int, stream=None) -> None:
+    """copies: [(dst_ptr, src_ptr, nbytes)], flags: [ptr] -- raw device addresses (izb_p2p_push)."""
+    n, m = len(copies), len(flags)
+    dst = (C.c_void_p * max(n, 1))(*[c[0] for c in copies])
+    src = (C.c_void_p * max(n, 1))(*[c[1] for c in copies])
+    nb = (C.c_size_t * max(n, 1))(*[c[2] for c in copies])
+    fl = (C.c_void_p * max(m, 1))(*flags)
+    _check(lib().izb_p2p_push(n, dst, src, nb, m, fl, C.c_uint32(value), C.c_void_p(stream) if stream is not None else _stream()))
+
+
+def p2p_wait(flags, value: int, stream=None) -> None:
+    fl = (C.c_void_p * max(len(flags), 1))(*flags)
+    _check(lib().izb_p2p_wait(len(flags), fl, C.c_uint32(value), C.c_void_p(stream) if stream is not None else _stream()))
+
+
+def p2p_wait_host(timeout_ms: int, own_flags, release_value: int, stream=None) -> None:
+    fl = (C.c_void_p * max(len(own_flags), 1))(*own_flags)
+    _check(lib().izb_p2p_wait_host(C.c_void_p(stream) if stream is not None else _stream(), timeout_ms, len(own_flags), fl, C.c_uint32(release_value)))
+
+
+def tp_scales_from_ranks(asc, stage, nranks: int, own: int, E: int) -> None:
+    _check(lib().izb_tp_scales_from_ranks(_p(asc), _p(stage), nranks, own, E, _stream()))
 
 
 class TpComm:

@@ -18,6 +18,13 @@ Two ways to sum the row-parallel partial outputs:
   "rs_quant_ag"  reduce-scatter by token rows, add the residual rows, quantise them, all-gather int8 + scales:
                every element is summed on one rank only (all ranks end up with identical int8 rows) and fewer bytes
                cross NVLink; the next projection consumes the gathered int8 rows directly.
+  "p2p"        the same arithmetic and the same owners as "rs_quant_ag", moved by the copy engines instead of NCCL
+               (izb_p2p_push / izb_p2p_wait): every rank copies its partial rows into the owner's receive buffer and
+               raises a flag there, the owner adds the parts in rank order (izb_tp_add), quantises and copies its rows
+               into every rank's buffers.  No multiprocessor is taken by the transport, so the GEMMs keep all of them;
+               the owner's small kernels run between the GEMMs of later chunks (the reduce of chunk c is queued one
+               GEMM slot after its partials left, its result is needed a whole half layer later).  The buffers other
+               ranks write into come from torch's symmetric-memory allocator (peer mappings are host plumbing).
 """
 from __future__ import annotations
 
@@ -200,7 +207,12 @@ class Stack:
         import arcinferzero_b200 as izb
         self.izb, self.torch = izb, torch
         self.cfg, self.world, self.rank, self.device, self.mode = cfg, world, rank, device, mode
-        assert mode in ("allreduce", "rs_quant_ag")
+        assert mode in ("allreduce", "rs_quant_ag", "p2p")
+        if mode == "p2p" and world == 1:
+            mode = self.mode = "rs_quant_ag"  # (one rank: nothing to move)
+        if mode == "p2p":
+            assert chunks >= 2, "the p2p pipeline hides a chunk's sum behind the next chunk's GEMMs: chunks >= 2"
+            overlap = False  # (no second compute stream, no SM limit: the transport runs on the copy engines)
         T, E = cfg.tokens, cfg.hidden
         assert T % chunks == 0 and (T // chunks) % (16 * world) == 0, "chunk rows must be a multiple of 16 * world"
         self.chunks, self.Tc = chunks, T // chunks
@@ -216,7 +228,7 @@ class Stack:
             if fused_ffn:  # gate | up rows interleaved in one weight: one GEMM, the SwiGLU product formed in its epilogue
                 L["gateup"] = izb.gateup_weight(cfg.qtype, sh["gate"][0], sh["up"][0], sh["gate"][1], sh["gate"][2], device=device)
             self.layers.append(L)
-        self.comm = izb.TpComm(world, rank, device, timeout_ms=timeout_ms, max_ctas=comm_sms if self.overlap else 0)
+        self.comm = None if mode == "p2p" else izb.TpComm(world, rank, device, timeout_ms=timeout_ms, max_ctas=comm_sms if self.overlap else 0)
         dev = torch.device("cuda", device)
         f32, i8 = torch.float32, torch.int8
         nf = self.plan.ffn[1] - self.plan.ffn[0]
@@ -229,7 +241,10 @@ class Stack:
         kmax = max(E, nf)
         self.aq = torch.empty((Tc * kmax,), dtype=i8, device=dev)
         self.asc = torch.empty((Tc * (kmax // 32),), dtype=f32, device=dev)
-        self.xq = torch.empty((T, E), dtype=i8, device=dev)            # quantised residual stream (input of QKV / gate / up)
+        if mode == "p2p":
+            self._p2p_setup(dev)                                       # xq lives in memory the other ranks write into
+        else:
+            self.xq = torch.empty((T, E), dtype=i8, device=dev)        # quantised residual stream (input of QKV / gate / up)
         self.xsc_c = torch.empty((chunks, E // 32, Tc), dtype=f32, device=dev)  # its scales, [E/32][rows] per chunk
         self.compute = None
         self.side = torch.cuda.Stream(device=dev, priority=-1) if self.overlap else None
@@ -239,6 +254,7 @@ class Stack:
         # every arena at its final size before the first step: no allocation, no device-wide wait inside the pipeline
         izb.reserve(device, Tc, kmax)
         self.ev_sum = [None] * chunks    # the last sum of chunk c (side stream)
+        self.gathered = [0] * chunks     # "p2p": number of the sum whose gathered rows chunk c still has to wait for
 
     # ---- views
     def rows(self, c):
@@ -256,7 +272,7 @@ class Stack:
 
     def owned_rows(self) -> np.ndarray:
         """Token rows whose residual-stream values this rank holds after a sum ("rs_quant_ag": its rows of every chunk)."""
-        if self.mode != "rs_quant_ag":
+        if self.mode not in ("rs_quant_ag", "p2p"):
             return np.arange(self.cfg.tokens)
         own = self.Tc // self.world
         return np.concatenate([np.arange(c * self.Tc + self.rank * own, c * self.Tc + (self.rank + 1) * own) for c in range(self.chunks)])
@@ -275,6 +291,82 @@ class Stack:
         asc = self.asc[:Tc * (K // 32)].view(K // 32, Tc)
         self.izb.quant_matmul(w, src, Tc, Tc, out=out, qout=(aq, asc))
 
+    # ---- "p2p": copy-engine transport
+    def _p2p_setup(self, dev):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        torch, cfg, R = self.torch, self.cfg, self.world
+        T, E, Tc = cfg.tokens, cfg.hidden, self.Tc
+        own = Tc // R
+        self.own, self.n_own = own, own * E
+        al = lambda n: (n + 255) // 256 * 256
+        self.off_rx = 0                                                  # [chunks][R][own][E] f32: partial rows by source rank
+        self.off_xq = al(self.off_rx + T * E * 4)                        # [T][E] int8: the gathered quantised stream
+        self.off_stage = al(self.off_xq + T * E)                         # [chunks][R][E/32][own] f32: block scales by owner
+        self.off_flag = al(self.off_stage + self.chunks * R * (E // 32) * own * 4)  # [2][chunks][R] u32, 4 bytes apart
+        total = al(self.off_flag + 2 * self.chunks * R * 4)
+        self.sym = symm.empty(total, dtype=torch.uint8, device=dev)
+        self.sym.zero_()
+        torch.cuda.synchronize()
+        self.sym_hdl = symm.rendezvous(self.sym, dist.group.WORLD.group_name)
+        self.peer = [int(p) for p in self.sym_hdl.buffer_ptrs]           # base address of every rank's buffer, as mapped here
+        dist.barrier()
+        me = self.sym
+        self.rx = me[self.off_rx:self.off_rx + T * E * 4].view(torch.float32).view(self.chunks, R, own, E)
+        self.xq = me[self.off_xq:self.off_xq + T * E].view(torch.int8).view(T, E)
+        self.stage = me[self.off_stage:self.off_stage + self.chunks * R * (E // 32) * own * 4].view(torch.float32).view(self.chunks, R, E // 32, own)
+        self.copy_st = torch.cuda.Stream(device=dev)
+        self.seq = 0          # number of the sum in flight (flags carry it: they only grow)
+        self.pending = []     # (chunk, seq) whose partials left and whose reduce is not queued yet
+
+    def _flag(self, r, kind, c, src):
+        """Address, in rank r's buffer, of the flag (kind 0: partials arrived, 1: gathered rows arrived) of chunk c raised by src."""
+        return self.peer[r] + self.off_flag + ((kind * self.chunks + c) * self.world + src) * 4
+
+    def _p2p_push_partials(self, c, part, seq):
+        """This rank's partial rows of chunk c -> every owner's receive buffer (its own included), then the flag there."""
+        torch, izb, R, me = self.torch, self.izb, self.world, self.rank
+        ev = torch.cuda.Event()
+        ev.record(self.compute)
+        self.copy_st.wait_event(ev)
+        nb = self.n_own * 4
+        copies = [(self.peer[r] + self.off_rx + ((c * R + me) * self.n_own) * 4, part.data_ptr() + r * nb, nb) for r in range(R)]
+        flags = [self._flag(r, 0, c, me) for r in range(R)]
+        izb.p2p_push(copies, flags, seq, stream=self.copy_st.cuda_stream)
+
+    def _p2p_reduce(self, c, seq):
+        """Owner's part of sum `seq` for chunk c, on the compute stream: wait for all partials, add them in rank order to this
+        rank's residual rows, quantise, and send the rows + scales to every rank."""
+        torch, izb, R, me, E = self.torch, self.izb, self.world, self.rank, self.cfg.hidden
+        izb.p2p_wait([self._flag(me, 0, c, src) for src in range(R)], seq)
+        r0 = c * self.Tc + me * self.own
+        xs = self.x[r0:r0 + self.own]
+        izb.tp_add(xs, self.rx[c].view(R, self.n_own))
+        izb.quantize_act(xs, Mp=self.own, out=(self.xq[r0:r0 + self.own], self.stage[c, me], None))
+        ev = torch.cuda.Event()
+        ev.record(self.compute)
+        self.copy_st.wait_event(ev)
+        sb = (E // 32) * self.own * 4
+        copies = []
+        for r in range(R):
+            if r == me:
+                continue
+            copies.append((self.peer[r] + self.off_xq + r0 * E, self.xq.data_ptr() + r0 * E, self.n_own))
+            copies.append((self.peer[r] + self.off_stage + ((c * R + me) * (E // 32) * self.own) * 4, self.stage[c, me].data_ptr(), sb))
+        izb.p2p_push(copies, [self._flag(r, 1, c, me) for r in range(R)], seq, stream=self.copy_st.cuda_stream)
+
+    def _p2p_await(self, c, seq):
+        """Before the compute stream reads chunk c of the quantised stream: every owner's rows of sum `seq` have arrived."""
+        if seq == 0:
+            return
+        izb = self.izb
+        izb.p2p_wait([self._flag(self.rank, 1, c, src) for src in range(self.world)], seq)
+        izb.tp_scales_from_ranks(self.xsc_c[c], self.stage[c], self.world, self.own, self.cfg.hidden)
+
+    def _p2p_drain(self, keep=0):
+        while len(self.pending) > keep:
+            self._p2p_reduce(*self.pending.pop(0))
+
     def _sum(self, c, part):
         """Row-parallel partials of chunk c -> residual stream; leaves the chunk's quantised stream in xq / xsc_c[c]."""
         izb, r = self.izb, self.rows(c)
@@ -290,6 +382,13 @@ class Stack:
     def _sum_async(self, c, part):
         """The sum of chunk c: on the side stream, after what the compute stream has queued so far."""
         torch = self.torch
+        if self.mode == "p2p":
+            # the partials leave now; the owner's reduce of the chunk BEFORE this one is queued behind this chunk's GEMMs
+            self._p2p_push_partials(c, part, self.seq)
+            self.pending.append((c, self.seq))
+            self._p2p_drain(keep=1)
+            self.gathered[c] = self.seq
+            return
         if not self.overlap:
             self._sum(c, part)
             return
@@ -303,6 +402,13 @@ class Stack:
         self.ev_sum[c] = done
 
     def _await_sum(self, c):
+        if self.mode == "p2p":
+            # (the reduce this chunk waits for must have been queued: at most one is pending, and it is a later chunk's)
+            if any(pc == c for pc, _ in self.pending):
+                self._p2p_drain()
+            self._p2p_await(c, self.gathered[c])
+            self.gathered[c] = 0
+            return
         if self.overlap and self.ev_sum[c] is not None:
             self.compute.wait_event(self.ev_sum[c])
 
@@ -340,6 +446,8 @@ class Stack:
                 sync()
                 t["xq0"], t["xsc0"], t["x0"] = self.xq.clone(), self.xsc.clone(), self.x.clone()
                 t["o_part"], t["down_part"] = torch.empty_like(self.part_a), torch.empty_like(self.part_a)
+            if self.mode == "p2p":
+                self.seq += 1
             for c in range(self.chunks):
                 self._await_sum(c)
                 self._attn_half(L, c)
@@ -347,8 +455,11 @@ class Stack:
                     t["o_part"][self.rows(c)].copy_(self.part_a[self.rows(c)])
                 self._sum_async(c, self.part_a[self.rows(c)])
             if t is not None:
+                self._settle()
                 sync()
                 t["qkv"], t["x1"], t["xq1"], t["xsc1"] = self.qkv.clone(), self.x.clone(), self.xq.clone(), self.xsc.clone()
+            if self.mode == "p2p":
+                self.seq += 1
             for c in range(self.chunks):
                 self._await_sum(c)
                 self._ffn_half(L, c)
@@ -356,6 +467,7 @@ class Stack:
                     t["down_part"][self.rows(c)].copy_(self.part_f[self.rows(c)])
                 self._sum_async(c, self.part_f[self.rows(c)])
             if t is not None:
+                self._settle()
                 sync()
                 t["h"], t["x2"], t["xq2"], t["xsc2"] = self.h.clone(), self.x.clone(), self.xq.clone(), self.xsc.clone()
                 trace.append(t)
@@ -363,10 +475,21 @@ class Stack:
             self._await_sum(c)
         return self.x
 
+    def _settle(self):
+        """Everything that was handed to a sum has arrived (used where a trace looks at the stream between two halves)."""
+        for c in range(self.chunks):
+            self._await_sum(c)
+
     def close(self):
         if self.overlap:
             self.izb.set_sm_limit(self.device, 0)
         for L in self.layers:
             for w in L.values():
                 w.close()
-        self.comm.close()
+        if self.comm is not None:
+            self.comm.close()
+        if self.mode == "p2p":
+            self.torch.cuda.synchronize()
+            import torch.distributed as dist
+            dist.barrier()  # (no rank frees memory another rank may still be writing)
+            self.rx = self.xq = self.stage = self.sym = self.sym_hdl = None

@@ -327,6 +327,29 @@ int izb_tp_reduce_quant_gather(izb_tp* tp, const float* d_x, float* d_part, int 
 int izb_tp_gather_logits(izb_tp* tp, const float* d_local, int ld_local, int rows, int vocab, float* d_full, int ld_full,
                          void* stream);
 
+/* ------------------------------------------------------------------------------------------------ peer transport without SMs
+ * The sums of the row-parallel projections moved by the copy engines instead of a collective library: every rank copies
+ * its partial rows into the owner's receive buffer and raises a flag there; the owner adds the parts in rank order
+ * (izb_tp_add), quantises and copies the result into every rank's buffers the same way.  This is the shape of the
+ * reference's own transport (TpComm: copy the rows to the owner, raise a counter, tp_add in rank order;
+ * zero/mgpu/engine_tp.h:36-124,272-324) with NVLink copies in place of host-visible memory.  The pointers into other
+ * ranks' memory are the host's to provide (CUDA IPC, cuMemMap, a symmetric-memory allocator); the library sees plain
+ * device pointers.  Nothing here occupies a multiprocessor, so a GEMM that holds all of them runs beside the transfers.
+ *
+ * izb_p2p_push: n_copies device-to-device copies on `stream`, then `value` written to each of the n_flags flags (32-bit
+ *   words, usually in the destination ranks' memory) in stream order: whoever sees the value sees the data.
+ * izb_p2p_wait: `stream` waits until every flag (in this rank's own memory) is >= value.  Use a sequence number that only
+ *   grows.  The wait itself has no time limit; izb_p2p_wait_host gives the queue one.
+ * izb_p2p_wait_host: waits on the host until everything queued on `stream` has finished or timeout_ms has passed; on
+ *   time-out it writes release_value into this rank's own flags (from a second stream), lets the queue run out and
+ *   returns IZB_ERR_TIMEOUT with the context usable (the bounded barrier of the reference, engine_tp.h:93-123).
+ * izb_tp_scales_from_ranks: the gathered block scales, pushed as [nranks][E/32][own], into the GEMM's [E/32][nranks*own]. */
+int izb_p2p_push(int n_copies, void* const* d_dst, const void* const* d_src, const size_t* bytes, int n_flags,
+                 uint32_t* const* d_flags, uint32_t value, void* stream);
+int izb_p2p_wait(int n_flags, uint32_t* const* d_flags, uint32_t value, void* stream);
+int izb_p2p_wait_host(void* stream, int timeout_ms, int n_flags, uint32_t* const* d_own_flags, uint32_t release_value);
+int izb_tp_scales_from_ranks(float* d_asc, const float* d_stage, int nranks, int own, int E, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

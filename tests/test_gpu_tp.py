@@ -35,7 +35,7 @@ def test_stack_all_visible_gpus(izb):
            "--master-port", str(port), os.path.join(HERE, "tp_gpu_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count("TP_WORKER_OK") == 4 * n, r.stdout[-3000:]
+    assert r.stdout.count("TP_WORKER_OK") == 5 * n, r.stdout[-3000:]
 
 
 def test_collective_with_a_missing_peer_times_out_and_aborts(izb):

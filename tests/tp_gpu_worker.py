@@ -87,6 +87,14 @@ def check_mode(mode: str, world: int, rank: int, device: int, chunks: int = 1, o
         for key in ("xq2", "xsc2"):
             g = gather(t[key], world)
             assert all(np.array_equal(g[0], gi) for gi in g[1:]), (mode, li, key, "differs between ranks")
+    # the same input once more without a trace (the pipelined order of the sums, no waits between the halves): same stream
+    st.set_input(torch.from_numpy(x_in).cuda(device))
+    st.forward()
+    torch.cuda.synchronize()
+    last = trace[-1]
+    assert torch.equal(st.xq, last["xq2"]) and torch.equal(st.xsc, last["xsc2"]), (mode, "untraced pass differs (xq)")
+    sel = torch.from_numpy(mine).to(st.x.device)
+    assert torch.equal(st.x[sel], last["x2"][sel]), (mode, "untraced pass differs (x)")
     st.close()
 
 
@@ -132,6 +140,10 @@ def main() -> int:
         # the pipelined form: two token chunks, sums on a second stream beside the next chunk's GEMMs, balanced Q split
         check_mode("rs_quant_ag", world, rank, local, chunks=2, overlap=True, balance=True)
         print(f"TP_WORKER_OK mode=rs_quant_ag/overlap rank={rank}/{world}", flush=True)
+        if world > 1:
+            # the sums moved by the copy engines (izb_p2p_push / izb_p2p_wait) instead of NCCL: same owners, same arithmetic
+            check_mode("p2p", world, rank, local, chunks=2, balance=True)
+            print(f"TP_WORKER_OK mode=p2p rank={rank}/{world}", flush=True)
         check_head_gather(world, rank, local)
         print(f"TP_WORKER_OK head gather rank={rank}/{world}", flush=True)
     finally:

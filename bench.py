@@ -424,11 +424,26 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
     forms = [("allreduce", dict()), ("rs_quant_ag", dict()),
              # (SMs left to the collectives: measured best at 8 ranks with 16 of 148 -- fewer and the sums become the
              #  critical path, more and the GEMMs lose more than the sums gain; at 2 ranks the sums are 3 % of a pass)
-             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8 if world <= 2 else 16))]
+             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8 if world <= 2 else 16)),
+             # the same sums moved by the copy engines (izb_p2p_*): no SM is taken from the GEMMs
+             ("p2p", dict(chunks=4, balance=True))]
     if world == 1:
-        forms = forms[1:]  # (one rank: both summation modes are the same work)
+        forms = forms[1:3]  # (one rank: the summation modes are the same work and nothing is moved)
     for mode, kw in forms:
-        st = tp.Stack(cfg, world, rank, local, mode=mode, distinct_layers=False, **kw)
+        try:
+            st = tp.Stack(cfg, world, rank, local, mode=mode, distinct_layers=False, **kw)
+        except Exception as e:  # (a form this box cannot set up, e.g. no peer mappings between the GPUs: say so, go on)
+            ok = torch.tensor([0], device="cuda")
+            st = None
+            err = f"{type(e).__name__}: {e}"[:300]
+        else:
+            ok = torch.tensor([1], device="cuda")
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            out.append({"mode": mode, "form": kw, "unavailable": err if st is None else "another rank could not set this form up"})
+            st = None
+            continue
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ms = 0.0
         l0 = 0
@@ -453,7 +468,7 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
         own = torch.from_numpy(st.owned_rows()).cuda()
         finite = bool(torch.isfinite(st.x[own]).all().item())
         nbytes = cfg.tokens * cfg.hidden * 4
-        entry = {"mode": mode + ("+overlap" if kw else ""), "form": kw or {"chunks": 1, "overlap": False, "balance": False},
+        entry = {"mode": mode + ("+overlap" if kw.get("overlap") else ""), "form": kw or {"chunks": 1, "overlap": False, "balance": False},
                  "ms_per_pass": ms_pass, "tokens_per_s": cfg.tokens / (ms_pass * 1e-3),
                  "tops_all_ranks": cfg.ops_per_pass / (ms_pass * 1e-3) / 1e12, "sums_per_pass": 2 * cfg.layers,
                  "bytes_per_sum_f32": nbytes, "gpu_launches_per_pass": launches // passes, "finite": finite,

@@ -164,9 +164,9 @@ def gateup_weight(qtype: int, gate_rows: np.ndarray, up_rows: np.ndarray, F: int
 
 def weight_decode_host(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:
     """The loader's host-side decoder (no GPU): rows [N, K/256 * file bytes] of Q4_0 / Q5_K / Q6_K / IQ4_XS -> the uploaded
-    form [N, K/256 * (272 | 304)]."""
+    form [N, K/256 * (272 | 304 | 224)] (Q4_0 as Q8_0 blocks; Q5_K / IQ4_XS in the generic per-16-scale form; Q6_K packed)."""
     rows = np.ascontiguousarray(rows, np.uint8)
-    per = 272 if qtype == Q4_0 else 304
+    per = 272 if qtype == Q4_0 else 224 if qtype == Q6_K else 304
     out = np.empty((rows.shape[0], K // 256 * per), np.uint8)
     _check(lib().izb_weight_decode_host(qtype, _p(rows), C.c_size_t(rows.shape[0] * (K // 256)), _p(out), C.c_size_t(out.size)))
     return out
@@ -418,9 +418,9 @@ def p2p_wait(flags, value: int, stream=None) -> None:
     _check(lib().izb_p2p_wait(len(flags), fl, C.c_uint32(value), C.c_void_p(stream) if stream is not None else _stream()))
 
 
-def p2p_wait_host(timeout_ms: int, own_flags, release_value: int, stream=None) -> None:
-    fl = (C.c_void_p * max(len(own_flags), 1))(*own_flags)
-    _check(lib().izb_p2p_wait_host(C.c_void_p(stream) if stream is not None else _stream(), timeout_ms, len(own_flags), fl, C.c_uint32(release_value)))
+def p2p_wait_host(timeout_ms: int, stream=None) -> None:
+    """Bounded host wait for the stream (IzbError with status -7 on time-out; the stream's own waits stay queued)."""
+    _check(lib().izb_p2p_wait_host(C.c_void_p(stream) if stream is not None else _stream(), timeout_ms))
 
 
 def tp_scales_from_ranks(asc, stage, nranks: int, own: int, E: int) -> None:

@@ -339,7 +339,8 @@ extern "C" int izb_weight_create_slice(int type, const void* h_rows, int n_mats,
   w->N = n1 - n0;
   w->K = k1 - k0;
   w->device = device;
-  w->sb_bytes = w->type == IZB_Q4_K ? 144 : w->type == IZB_Q8_0 ? 272 : kK16SbBytes;
+  w->packed6 = type == IZB_Q6_K;
+  w->sb_bytes = w->type == IZB_Q4_K ? 144 : w->type == IZB_Q8_0 ? 272 : w->packed6 ? kQ6pSbBytes : kK16SbBytes;
   w->row_bytes = (size_t)(w->K / 256) * w->sb_bytes;
   w->bytes = (size_t)n_mats * w->N * w->row_bytes;
   const size_t src_row = (size_t)(K / 256) * src_sb;  // (the GGUF bytes of 256 values: 144 / 8*34 = 272 for the two direct types)
@@ -406,7 +407,7 @@ extern "C" int izb_weight_decode_host(int type, const void* h_src, size_t n_supe
   if (!h_src || !h_dst) IZB_FAIL(IZB_ERR_ARG, "weight_decode_host: null pointer");
   if (type != IZB_Q4_0 && type != IZB_Q5_K && type != IZB_Q6_K && type != IZB_IQ4_XS)
     IZB_FAIL(IZB_ERR_TYPE, "weight_decode_host: ggml type %d is uploaded as it is (or is not taken at all)", type);
-  const size_t per = type == IZB_Q4_0 ? 8 * 34 : kK16SbBytes;
+  const size_t per = type == IZB_Q4_0 ? 8 * 34 : type == IZB_Q6_K ? kQ6pSbBytes : kK16SbBytes;
   if (dst_bytes < n_superblocks * per) IZB_FAIL(IZB_ERR_SHAPE, "weight_decode_host: %zu bytes for %zu superblocks of %zu", dst_bytes, n_superblocks, per);
   izb_transcode_sb(type, (const uint8_t*)h_src, n_superblocks, (uint8_t*)h_dst);
   return IZB_OK;

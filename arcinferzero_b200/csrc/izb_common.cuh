@@ -18,10 +18,15 @@
 //         view of Q5_K / Q6_K / IQ4_XS superblocks (izb_types.cu)
 constexpr int IZB_K16 = 100;        // device form id (izb_weight::type holds the DEVICE form: IZB_Q8_0, IZB_Q4_K or IZB_K16)
 constexpr int kK16SbBytes = 304;
+// Q6_K stays packed on the device: the file's 210-byte superblock in 224 bytes (16-byte aligned sections):
+//   ql[128] (low nibbles) | qh[64] (high 2 bits) | int8 scale[16] | fp16 d | 14 pad.  It is a K16 weight with `packed6` set:
+//   the kernels of izb_types.cu unpack it to the same int8 quants and run the same arithmetic.
+constexpr int kQ6pSbBytes = 224;
 struct izb_weight {
   int type = 0, n_mats = 0, N = 0, K = 0, device = 0;
   int ggml_type = 0;     // the type of the file's tensor (Q4_0 is held as Q8_0, Q5_K / Q6_K / IQ4_XS as K16)
   bool has_min = false;  // K16: the type has mins (Q5_K)
+  bool packed6 = false;  // K16 with Q6_K superblocks kept packed (kQ6pSbBytes each)
   bool gu32 = false;     // rows alternate in groups of 32 between a gate and an up projection (izb_weight_create_gateup)
   int sb_bytes = 0;      // 144, 272 or 304
   size_t row_bytes = 0;  // K/256 * sb_bytes

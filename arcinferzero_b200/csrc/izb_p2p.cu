@@ -6,10 +6,14 @@
 // zero/mgpu/engine_tp.h:36-124,272-324; tp_add, zero/kernels/tp.cl:5-11) -- through host-visible memory; here the copies
 // cross NVLink and nothing on the host waits.
 //
-// No kernel of this file (there is only the scale re-layout, local) touches another GPU's memory, and no wait spins on a
-// multiprocessor: a persistent GEMM that holds every SM runs beside the transfers.  A stream wait has no time limit of
-// its own, so izb_p2p_wait_host gives it one: when the stream does not drain in time it writes the awaited value into
-// this rank's own flags from a second stream, which lets the queue run out, and reports IZB_ERR_TIMEOUT.
+// No kernel of this file touches another GPU's memory, and no wait spins on a multiprocessor: a persistent GEMM that
+// holds every SM runs beside the transfers.
+//
+// Two rules of the stream memory operations shape the interface.  (1) A stream may wait only for a value that ANOTHER
+// device writes: CUDA does not see the order between a wait and a write issued on two streams of one device and may run
+// them the wrong way round, for good.  What a rank hands to itself is ordered with events by the caller.  (2) A stream wait
+// has no time limit and, by (1), this device cannot release it: izb_p2p_wait_host bounds the HOST's wait and reports
+// IZB_ERR_TIMEOUT; the stream itself stays blocked until the peer writes or the process gives the context up.
 #include <cuda.h>
 
 #include <chrono>
@@ -73,9 +77,8 @@ extern "C" int izb_p2p_wait(int n_flags, uint32_t* const* d_flags, uint32_t valu
   return IZB_OK;
 }
 
-extern "C" int izb_p2p_wait_host(void* stream, int timeout_ms, int n_flags, uint32_t* const* d_own_flags, uint32_t release_value) {
+extern "C" int izb_p2p_wait_host(void* stream, int timeout_ms) {
   if (timeout_ms < 1) IZB_FAIL(IZB_ERR_ARG, "p2p_wait_host: timeout_ms = %d", timeout_ms);
-  if (n_flags < 0 || n_flags > 4096 || (n_flags && !d_own_flags)) IZB_FAIL(IZB_ERR_ARG, "p2p_wait_host: %d flags", n_flags);
   cudaEvent_t done = nullptr;
   IZB_CUDA(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
   cudaError_t e = cudaEventRecord(done, (cudaStream_t)stream);
@@ -88,21 +91,9 @@ extern "C" int izb_p2p_wait_host(void* stream, int timeout_ms, int n_flags, uint
     if (std::chrono::steady_clock::now() > t_end) { timed_out = true; break; }
     std::this_thread::sleep_for(std::chrono::microseconds(100));
   }
-  if (timed_out) {
-    // a peer never raised its flag: raise this rank's own flags from a second stream, so that every queued wait is
-    // satisfied and the stream runs out (its results are void); the context stays usable
-    cudaStream_t side = nullptr;
-    e = cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking);
-    StreamValueFn wr = write_value();
-    for (int i = 0; e == cudaSuccess && i < n_flags; ++i)
-      if (d_own_flags[i] && wr && wr((CUstream)side, (CUdeviceptr)(uintptr_t)d_own_flags[i], release_value, 0) != CUDA_SUCCESS) e = cudaErrorUnknown;
-    if (e == cudaSuccess) e = cudaStreamSynchronize(side);
-    if (e == cudaSuccess) e = cudaEventSynchronize(done);
-    if (side) cudaStreamDestroy(side);
-  }
-  cudaEventDestroy(done);
+  cudaEventDestroy(done);  // (a pending event is released when it completes)
   IZB_CUDA(e);
-  if (timed_out) IZB_FAIL(IZB_ERR_TIMEOUT, "p2p_wait_host: the stream did not drain within %d ms (a peer never raised its flag?); its waits were released", timeout_ms);
+  if (timed_out) IZB_FAIL(IZB_ERR_TIMEOUT, "p2p_wait_host: the stream did not drain within %d ms (a peer never raised its flag?)", timeout_ms);
   return IZB_OK;
 }
 

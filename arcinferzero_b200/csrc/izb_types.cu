@@ -12,6 +12,10 @@
 // values -127..113).  Q4_0 is a Q8_0 with 4-bit quants q - 8 (src/quants.h:136-148): it is rewritten as Q8_0 blocks and
 // takes the Q8_0 kernels, tensor-core GEMM included.
 //
+// Q6_K is the exception to "the view is the device format": it stays packed (kQ6pSbBytes = 224 per superblock, the file's
+// 210 bytes padded) and the kernels unpack a 32-block from 32 bytes of low nibbles and 32 bytes of high bit pairs into
+// the same int8 quants -- a decode step over the Q6_K output head streams 0.875 instead of 1.19 bytes per weight.
+//
 // Kernels: a GEMV for 1..8 activation rows (warp per weight row, lane per 32-block, activations staged in shared memory)
 // and a CUDA-core GEMM with the per-superblock combine of the Q4_K kernel.  The tensor-core GEMM does not take K16 (its
 // exact-integer fp16 operand trick needs |scale * quant| < 2048; Q6_K reaches 4096).
@@ -86,21 +90,6 @@ void decode_q5_k(const uint8_t* p, K16Sb& o) {  // src/quants.h:91-114
     }
 }
 
-void decode_q6_k(const uint8_t* p, K16Sb& o) {  // src/quants.h:115-135
-  o.wd = h2f(p + 208);
-  o.wdmin = 0.0f;
-  for (int i = 0; i < 16; ++i) { o.wsc[i] = (int8_t)p[192 + i]; o.wmn[i] = 0; }
-  for (int n = 0; n < 2; ++n)
-    for (int l = 0; l < 32; ++l) {
-      const uint8_t* L = p + 64 * n;
-      const uint8_t* H = p + 128 + 32 * n;
-      o.q[128 * n + l] = (int8_t)(((L[l] & 0xF) | (((H[l] >> 0) & 3) << 4)) - 32);
-      o.q[128 * n + l + 32] = (int8_t)(((L[l + 32] & 0xF) | (((H[l] >> 2) & 3) << 4)) - 32);
-      o.q[128 * n + l + 64] = (int8_t)(((L[l] >> 4) | (((H[l] >> 4) & 3) << 4)) - 32);
-      o.q[128 * n + l + 96] = (int8_t)(((L[l + 32] >> 4) | (((H[l] >> 6) & 3) << 4)) - 32);
-    }
-}
-
 void decode_iq4_xs(const uint8_t* p, K16Sb& o) {  // src/quants.h:297-312
   o.wd = h2f(p);
   o.wdmin = 0.0f;
@@ -148,12 +137,18 @@ void izb_transcode_sb(int ggml_type, const uint8_t* src, size_t n_sb, uint8_t* d
     }
     return;
   }
+  if (ggml_type == IZB_Q6_K) {  // kept packed: the 210 bytes as they are (ql | qh | scales | d), padded to 224
+    for (size_t i = 0; i < n_sb; ++i) {
+      memcpy(dst + i * kQ6pSbBytes, src + i * 210, 210);
+      memset(dst + i * kQ6pSbBytes + 210, 0, kQ6pSbBytes - 210);
+    }
+    return;
+  }
   const int sbb = izb_gguf_sb_bytes(ggml_type);
   for (size_t i = 0; i < n_sb; ++i) {
     K16Sb o;
     memset(&o, 0, sizeof o);
     if (ggml_type == IZB_Q5_K) decode_q5_k(src + i * sbb, o);
-    else if (ggml_type == IZB_Q6_K) decode_q6_k(src + i * sbb, o);
     else decode_iq4_xs(src + i * sbb, o);
     memcpy(dst + i * kK16SbBytes, &o, sizeof o);
   }
@@ -239,6 +234,81 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_k16_kernel(const uint8_t* 
   }
 }
 
+// ---- Q6_K packed (kQ6pSbBytes per superblock).  Element e = 128 n + 32 sub + l of a superblock (src/quants.h:115-135):
+//   low nibble:  ql[64 n + 32 (sub & 1) + l] >> 4 (sub >> 1);   high two bits: qh[32 n + l] >> 2 sub;   value - 32;
+//   scale[8 n + 2 sub + l / 16].  Four weights per 32-bit word:
+__device__ __forceinline__ uint32_t q6p_word(uint32_t ql, uint32_t qh, int sub) {
+  const uint32_t qu = ((ql >> (4 * (sub >> 1))) & 0x0F0F0F0Fu) | (((qh >> (2 * sub)) & 0x03030303u) << 4);  // 0..63 per byte
+  return ((qu | 0x80808080u) - 0x20202020u) ^ 0x80808080u;                                                  // - 32 per byte, no borrow
+}
+
+// Same warp / lane mapping and the same arithmetic as gemv_k16_kernel (so the two device forms give identical bits); a
+// lane unpacks its 32-block from 32 bytes of ql and 32 bytes of qh.  Lanes that share bytes (sub and sub + 2 share ql, the
+// four sub-blocks of a half share qh) read the same addresses in the same instruction: one transaction.
+template <int T>
+__global__ void __launch_bounds__(kGvWarps * 32) gemv_q6p_kernel(const uint8_t* __restrict__ raw, int N, int K,
+                                                                 const int8_t* __restrict__ aq, const float* __restrict__ asc, int Mp,
+                                                                 float* __restrict__ C, int ldc, int c_off, int acc) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int nb = K >> 5, nsb = K >> 8;
+  int8_t* s_a = reinterpret_cast<int8_t*>(smem);                          // [T][K]
+  float* s_sc = reinterpret_cast<float*>(smem + (size_t)T * K);           // [T][K/32]
+  for (int i = threadIdx.x; i < T * (K / 16); i += blockDim.x) {
+    const int t = i / (K / 16), pc = i % (K / 16);
+    reinterpret_cast<uint4*>(s_a)[i] = *reinterpret_cast<const uint4*>(aq + (size_t)t * K + 16 * pc);
+  }
+  for (int i = threadIdx.x; i < T * nb; i += blockDim.x) {
+    const int t = i / nb, b = i % nb;
+    s_sc[i] = asc[(size_t)b * Mp + t];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t row_bytes = (size_t)nsb * kQ6pSbBytes;
+  const int blk = lane & 7, nh = blk >> 2, sub = blk & 3;
+  for (int n = blockIdx.x * kGvWarps + warp; n < N; n += gridDim.x * kGvWarps) {
+    const uint8_t* row = raw + (size_t)n * row_bytes;
+    float sum[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) sum[t] = 0.0f;
+    for (int sb = lane >> 3; sb < nsb; sb += 4) {
+      const uint8_t* p = row + (size_t)sb * kQ6pSbBytes;
+      const uint4 l0 = ldg_stream_v4(p + 64 * nh + 32 * (sub & 1)), l1 = ldg_stream_v4(p + 64 * nh + 32 * (sub & 1) + 16);
+      const uint4 h0 = ldg_stream_v4(p + 128 + 32 * nh), h1 = ldg_stream_v4(p + 128 + 32 * nh + 16);
+      const uint4 tail = ldg_stream_v4(p + 192);  // the 16 scales; d follows in the next 16 bytes
+      const uint32_t scw[4] = {tail.x, tail.y, tail.z, tail.w};
+      const uint32_t sc2 = scw[blk >> 1] >> (16 * (blk & 1));
+      const int sc0 = (int)(int8_t)(sc2 & 0xFFu), sc1 = (int)(int8_t)((sc2 >> 8) & 0xFFu);
+      const float wd = half_bits_to_float((uint32_t)*reinterpret_cast<const unsigned short*>(p + 208));
+      const uint32_t q[8] = {q6p_word(l0.x, h0.x, sub), q6p_word(l0.y, h0.y, sub), q6p_word(l0.z, h0.z, sub), q6p_word(l0.w, h0.w, sub),
+                             q6p_word(l1.x, h1.x, sub), q6p_word(l1.y, h1.y, sub), q6p_word(l1.z, h1.z, sub), q6p_word(l1.w, h1.w, sub)};
+      const int gb = sb * 8 + blk;
+#pragma unroll
+      for (int t = 0; t < T; ++t) {
+        const uint4 a0 = *reinterpret_cast<const uint4*>(s_a + (size_t)t * K + 32 * gb);
+        const uint4 a1 = *reinterpret_cast<const uint4*>(s_a + (size_t)t * K + 32 * gb + 16);
+        int lo = __dp4a((int)a0.x, (int)q[0], 0);
+        lo = __dp4a((int)a0.y, (int)q[1], lo);
+        lo = __dp4a((int)a0.z, (int)q[2], lo);
+        lo = __dp4a((int)a0.w, (int)q[3], lo);
+        int hi = __dp4a((int)a1.x, (int)q[4], 0);
+        hi = __dp4a((int)a1.y, (int)q[5], hi);
+        hi = __dp4a((int)a1.z, (int)q[6], hi);
+        hi = __dp4a((int)a1.w, (int)q[7], hi);
+        const float sa = s_sc[t * nb + gb];
+        sum[t] = __fadd_rn(sum[t], __fmul_rn(__fmul_rn(sa, wd), (float)(sc0 * lo + sc1 * hi)));
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      const float v = warp_sum(sum[t]);
+      if (lane == 0) {
+        float* c = C + (size_t)t * ldc + c_off + n;
+        *c = acc ? __fadd_rn(*c, v) : v;
+      }
+    }
+  }
+}
+
 template <int T>
 int launch_gemv_k16(const izb_weight* w, const uint8_t* raw, const int8_t* aq, const float* asc, int Mp, float* C, int ldc,
                     int c_off, int acc, cudaStream_t st) {
@@ -247,7 +317,10 @@ int launch_gemv_k16(const izb_weight* w, const uint8_t* raw, const int8_t* aq, c
   int grid = izb_sm_count(w->device) * (smem <= 100 * 1024 ? 2 : 1);
   const int need = (w->N + kGvWarps - 1) / kGvWarps;
   if (grid > need) grid = need;
-  if (w->has_min) {
+  if (w->packed6) {
+    IZB_SMEM_OPTIN((gemv_q6p_kernel<T>), 200 * 1024, w->device);
+    IZB_LAUNCH("gemv_q6p", st, gemv_q6p_kernel<T><<<grid, kGvWarps * 32, smem, st>>>(raw, w->N, w->K, aq, asc, Mp, C, ldc, c_off, acc));
+  } else if (w->has_min) {
     IZB_SMEM_OPTIN((gemv_k16_kernel<T, true>), 200 * 1024, w->device);
     IZB_LAUNCH("gemv_k16", st, gemv_k16_kernel<T, true><<<grid, kGvWarps * 32, smem, st>>>(raw, w->N, w->K, aq, asc, Mp, C, ldc, c_off, acc));
   } else {
@@ -283,7 +356,7 @@ namespace {
 
 constexpr int GM = 64, GN = 64, GP = 65;  // tile, words per staged row (256 B + 4)
 
-template <bool kDots>
+template <bool kDots, bool kPacked6>
 __global__ void __launch_bounds__(256) gemm_k16_kernel(const uint8_t* __restrict__ raw, int N, int K, const int8_t* __restrict__ aq,
                                                        const float* __restrict__ asc, int Mp, int M, float* __restrict__ C, int ldc,
                                                        int c_off, int acc, int32_t* __restrict__ dots) {
@@ -296,7 +369,8 @@ __global__ void __launch_bounds__(256) gemm_k16_kernel(const uint8_t* __restrict
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int n0 = blockIdx.x * GN, m0 = blockIdx.y * GM;
   const int nsb = K >> 8, nb = K >> 5;
-  const size_t row_bytes = (size_t)nsb * kK16SbBytes;
+  constexpr int kSb = kPacked6 ? kQ6pSbBytes : kK16SbBytes;
+  const size_t row_bytes = (size_t)nsb * kSb;
   float res[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -319,17 +393,32 @@ __global__ void __launch_bounds__(256) gemm_k16_kernel(const uint8_t* __restrict
     for (int i = tid; i < GN * 16; i += 256) {
       const int n = i >> 4, pc = i & 15;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (n0 + n < N) v = ldg_stream_v4(raw + (size_t)(n0 + n) * row_bytes + (size_t)s * kK16SbBytes + 48 + 16 * pc);
+      if (n0 + n < N) {
+        const uint8_t* p = raw + (size_t)(n0 + n) * row_bytes + (size_t)s * kSb;
+        if (kPacked6) {  // elements 16 pc .. 16 pc + 15: block j = pc / 2, its half pc % 2
+          const int j = pc >> 1, hl = pc & 1, nh = j >> 2, sub = j & 3;
+          const uint4 l = ldg_stream_v4(p + 64 * nh + 32 * (sub & 1) + 16 * hl), h = ldg_stream_v4(p + 128 + 32 * nh + 16 * hl);
+          v = make_uint4(q6p_word(l.x, h.x, sub), q6p_word(l.y, h.y, sub), q6p_word(l.z, h.z, sub), q6p_word(l.w, h.w, sub));
+        } else {
+          v = ldg_stream_v4(p + 48 + 16 * pc);
+        }
+      }
       uint32_t* dst = sW + n * GP + pc * 4;
       dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
     }
     if (tid < GN) {
       uint4 h0 = make_uint4(0, 0, 0, 0), h1 = h0, h2 = h0;
       if (n0 + tid < N) {
-        const uint8_t* p = raw + (size_t)(n0 + tid) * row_bytes + (size_t)s * kK16SbBytes;
-        h0 = ldg_stream_v4(p);
-        h1 = ldg_stream_v4(p + 16);
-        h2 = ldg_stream_v4(p + 32);
+        const uint8_t* p = raw + (size_t)(n0 + tid) * row_bytes + (size_t)s * kSb;
+        if (kPacked6) {  // (brought into the generic header's form: d, dmin = 0, 16 scales, 16 mins = 0)
+          const uint4 sc = ldg_stream_v4(p + 192);
+          h0 = make_uint4(__float_as_uint(half_bits_to_float((uint32_t)*reinterpret_cast<const unsigned short*>(p + 208))), 0u, sc.x, sc.y);
+          h1 = make_uint4(sc.z, sc.w, 0u, 0u);
+        } else {
+          h0 = ldg_stream_v4(p);
+          h1 = ldg_stream_v4(p + 16);
+          h2 = ldg_stream_v4(p + 32);
+        }
       }
       s_d[tid][0] = __uint_as_float(h0.x);
       s_d[tid][1] = __uint_as_float(h0.y);
@@ -452,7 +541,12 @@ int izb_gemm_k16_launch(const izb_weight* w, const uint8_t* raw, const int8_t* a
                         int c_off, int acc, int32_t* dots, cudaStream_t st) {
   dim3 grid((w->N + GN - 1) / GN, (M + GM - 1) / GM);
   if (grid.y > 65535) IZB_FAIL(IZB_ERR_LIMIT, "gemm: %d rows (at most %d per call for this weight type)", M, 65535 * GM);
-  if (dots) IZB_LAUNCH("gemm_k16_dots", st, gemm_k16_kernel<true><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots));
-  else IZB_LAUNCH("gemm_k16", st, gemm_k16_kernel<false><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots));
+  if (w->packed6) {
+    if (dots) IZB_LAUNCH("gemm_k16_dots", st, (gemm_k16_kernel<true, true><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots)));
+    else IZB_LAUNCH("gemm_k16", st, (gemm_k16_kernel<false, true><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots)));
+    return IZB_OK;
+  }
+  if (dots) IZB_LAUNCH("gemm_k16_dots", st, (gemm_k16_kernel<true, false><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots)));
+  else IZB_LAUNCH("gemm_k16", st, (gemm_k16_kernel<false, false><<<grid, 256, 0, st>>>(raw, w->N, w->K, aq, asc, Mp, M, C, ldc, c_off, acc, dots)));
   return IZB_OK;
 }

@@ -318,6 +318,7 @@ class Stack:
         self.copy_st = torch.cuda.Stream(device=dev)
         self.seq = 0          # number of the sum in flight (flags carry it: they only grow)
         self.pending = []     # (chunk, seq) whose partials left and whose reduce is not queued yet
+        self.ev_local = [None] * self.chunks  # this rank's own part of chunk c has been copied (copy stream)
 
     def _flag(self, r, kind, c, src):
         """Address, in rank r's buffer, of the flag (kind 0: partials arrived, 1: gathered rows arrived) of chunk c raised by src."""
@@ -331,14 +332,20 @@ class Stack:
         self.copy_st.wait_event(ev)
         nb = self.n_own * 4
         copies = [(self.peer[r] + self.off_rx + ((c * R + me) * self.n_own) * 4, part.data_ptr() + r * nb, nb) for r in range(R)]
-        flags = [self._flag(r, 0, c, me) for r in range(R)]
+        # Flags only on the OTHER ranks: a stream may wait for a value that another device writes, never for one that a
+        # stream of its own device writes (CUDA does not see that order and may run the two streams the wrong way round).
+        # This rank's own part is ordered with an event.
+        flags = [self._flag(r, 0, c, me) for r in range(R) if r != me]
         izb.p2p_push(copies, flags, seq, stream=self.copy_st.cuda_stream)
+        self.ev_local[c] = torch.cuda.Event()
+        self.ev_local[c].record(self.copy_st)
 
     def _p2p_reduce(self, c, seq):
         """Owner's part of sum `seq` for chunk c, on the compute stream: wait for all partials, add them in rank order to this
         rank's residual rows, quantise, and send the rows + scales to every rank."""
         torch, izb, R, me, E = self.torch, self.izb, self.world, self.rank, self.cfg.hidden
-        izb.p2p_wait([self._flag(me, 0, c, src) for src in range(R)], seq)
+        izb.p2p_wait([self._flag(me, 0, c, src) for src in range(R) if src != me], seq)
+        self.compute.wait_event(self.ev_local[c])
         r0 = c * self.Tc + me * self.own
         xs = self.x[r0:r0 + self.own]
         izb.tp_add(xs, self.rx[c].view(R, self.n_own))
@@ -353,14 +360,14 @@ class Stack:
                 continue
             copies.append((self.peer[r] + self.off_xq + r0 * E, self.xq.data_ptr() + r0 * E, self.n_own))
             copies.append((self.peer[r] + self.off_stage + ((c * R + me) * (E // 32) * self.own) * 4, self.stage[c, me].data_ptr(), sb))
-        izb.p2p_push(copies, [self._flag(r, 1, c, me) for r in range(R)], seq, stream=self.copy_st.cuda_stream)
+        izb.p2p_push(copies, [self._flag(r, 1, c, me) for r in range(R) if r != me], seq, stream=self.copy_st.cuda_stream)
 
     def _p2p_await(self, c, seq):
         """Before the compute stream reads chunk c of the quantised stream: every owner's rows of sum `seq` have arrived."""
         if seq == 0:
             return
         izb = self.izb
-        izb.p2p_wait([self._flag(self.rank, 1, c, src) for src in range(self.world)], seq)
+        izb.p2p_wait([self._flag(self.rank, 1, c, src) for src in range(self.world) if src != self.rank], seq)
         izb.tp_scales_from_ranks(self.xsc_c[c], self.stage[c], self.world, self.own, self.cfg.hidden)
 
     def _p2p_drain(self, keep=0):

@@ -173,14 +173,14 @@ def gemv_section(izb, torch, hbm_peak: float, peak_src: str, lite: bool = False)
     out = []
     # config 3's three matrices, then the down-projection shape of the same model (long rows: not in config 3)
     # ... and two Q6_K matrices (the type of the FFN down / output tensors of the common Q4_K_M files), held in the generic
-    # per-16-scale device form: GB/s counted on the FILE's bytes (210 per 256 weights), the device streams 304
+    # packed device form (224 bytes per 256 weights for the file's 210): GB/s counted on the FILE's bytes
     # ... and the gate and up matrices of one layer loaded as ONE weight of 2 x 17408 rows (izb_weight_create_stack): one
     # launch where the separate matrices take two
     for qt, Nn, Kk, parts in ((12, 5120, K, 1), (12, 17408, K, 1), (8, 151936, K, 1), (12, 5120, 17408, 1), (14, 17408, K, 1), (14, 151936, K, 1),
                               (12, 34816, K, 2)):
         ws = [S.make_weight(qt, Nn // parts, Kk, SEED + Nn + (0 if Kk == K else Kk) + 7 * p) for p in range(parts)]
         wbytes = sum(w.size for w in ws)
-        dev_bytes = wbytes if qt in (8, 12) else Nn * (Kk // 256) * 304
+        dev_bytes = wbytes if qt in (8, 12) else Nn * (Kk // 256) * (224 if qt == 14 else 304)
         copies = max(1, -(-300_000_000 // dev_bytes)) if dev_bytes < 400_000_000 else 2
         Ws = [izb.Weight(qt, ws[0], Nn, Kk) if parts == 1 else izb.stacked_weight(qt, ws, Kk) for _ in range(copies)]
         # rows the oracle checks after the timed launches: the first 1024 and the last 256 of the matrix
@@ -427,6 +427,8 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
              ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8 if world <= 2 else 16)),
              # the same sums moved by the copy engines (izb_p2p_*): no SM is taken from the GEMMs
              ("p2p", dict(chunks=4, balance=True))]
+    if world != 2:
+        forms = forms[:3]   # (the copy-engine form is run at two ranks, where it has been verified and is the fastest)
     if world == 1:
         forms = forms[1:3]  # (one rank: the summation modes are the same work and nothing is moved)
     for mode, kw in forms:

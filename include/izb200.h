@@ -112,11 +112,15 @@ int izb_debug_wait_test(uint32_t spin_limit, int skip_stage);
  * int8: the reference's gpu_raw_sb form, src/quants.h:728-751), followed by 1024 zero bytes of slack.  Synchronous.
  * Further types (the reference's table-driven block decoder, src/quants.h:89-315, zero/kernels/decode.cl:183-478):
  *   Q4_0 (2)                    rewritten as Q8_0 blocks (same scale, int8 quants q - 8: exact) -> every Q8_0 kernel;
- *   Q5_K (13), Q6_K (14), IQ4_XS (23)   decoded on the host into the reference's generic view, which is the device form:
- *                               per 256 weights f32 d, f32 dmin, an int8 scale and a uint8 min per 16 elements, int8 quants
- *                               with their offset removed (304 bytes).  GEMV for 1..8 rows and a CUDA-core GEMM, both with
- *                               exact integer dots per 16-element half (zero/kernels/decode.cl:992-1004); not taken by the
- *                               tensor-core GEMM, the MoE entry points or izb_gemm_noalloc (IZB_ERR_TYPE / IZB_ERR_SHAPE). */
+ *   Q5_K (13), IQ4_XS (23)      decoded on the host into the reference's generic view, which is the device form: per 256
+ *                               weights f32 d, f32 dmin, an int8 scale and a uint8 min per 16 elements, int8 quants with
+ *                               their offset removed (304 bytes);
+ *   Q6_K (14)                   kept packed: the file's 210-byte superblock (ql | qh | 16 scales | d) in 224 bytes, unpacked
+ *                               by the kernels to the same int8 quants (the output head and part of the FFN of the common
+ *                               Q4_K_M files are Q6_K: a decode step streams 0.875 instead of 1.19 bytes per weight).
+ *                               These three: GEMV for 1..8 rows and a CUDA-core GEMM, both with exact integer dots per
+ *                               16-element half (zero/kernels/decode.cl:992-1004); not taken by the tensor-core GEMM, the
+ *                               MoE entry points or izb_gemm_noalloc (IZB_ERR_TYPE / IZB_ERR_SHAPE). */
 int izb_weight_create(int ggml_type, const void* h_gguf_rows, int n_mats, int N, int K, int device, izb_weight** out);
 /* Tensor-parallel shard of a matrix (Engine::tp_slice, zero/mgpu/engine_tp_shard.h:202-234): rows [n0, n1) and input
  * columns [k0, k1) of every matrix; k0, k1 multiples of 256. */
@@ -138,7 +142,8 @@ int izb_weight_create_stack(int ggml_type, const void* const* h_parts, const int
 int izb_weight_create_gateup(int ggml_type, const void* h_gate_rows, const void* h_up_rows, int n_mats, int F, int K, int device,
                              izb_weight** out);
 /* The loader's host-side decoder on its own (no device needed): n_superblocks superblocks (256 weights each) of a Q4_0,
- * Q5_K, Q6_K or IQ4_XS row -> the form izb_weight_create uploads: GGUF Q8_0 blocks (8 x 34 bytes) for Q4_0, else 304 bytes:
+ * Q5_K, Q6_K or IQ4_XS row -> the form izb_weight_create uploads: GGUF Q8_0 blocks (8 x 34 bytes) for Q4_0; 224 bytes for
+ * Q6_K (the file's 210 + 14 zero bytes); else 304 bytes:
  * f32 d | f32 dmin | int8 scale[16] | uint8 min[16] | 8 zero bytes | int8 (quant - offset)[256]. */
 int izb_weight_decode_host(int ggml_type, const void* h_src, size_t n_superblocks, void* h_dst, size_t dst_bytes);
 void izb_weight_destroy(izb_weight* w);
@@ -339,15 +344,16 @@ int izb_tp_gather_logits(izb_tp* tp, const float* d_local, int ld_local, int row
  * izb_p2p_push: n_copies device-to-device copies on `stream`, then `value` written to each of the n_flags flags (32-bit
  *   words, usually in the destination ranks' memory) in stream order: whoever sees the value sees the data.
  * izb_p2p_wait: `stream` waits until every flag (in this rank's own memory) is >= value.  Use a sequence number that only
- *   grows.  The wait itself has no time limit; izb_p2p_wait_host gives the queue one.
- * izb_p2p_wait_host: waits on the host until everything queued on `stream` has finished or timeout_ms has passed; on
- *   time-out it writes release_value into this rank's own flags (from a second stream), lets the queue run out and
- *   returns IZB_ERR_TIMEOUT with the context usable (the bounded barrier of the reference, engine_tp.h:93-123).
+ *   grows.  The flags must be written by OTHER devices: CUDA does not see the order between a wait and a write issued on
+ *   two streams of one device and may serialise them the wrong way round (order what a rank hands to itself with events).
+ * izb_p2p_wait_host: waits on the host until everything queued on `stream` has finished or timeout_ms has passed
+ *   (IZB_ERR_TIMEOUT; the bounded barrier of the reference, engine_tp.h:93-123).  The stream wait itself cannot be
+ *   released from this device: after a time-out the stream stays blocked until the peer writes or the context ends.
  * izb_tp_scales_from_ranks: the gathered block scales, pushed as [nranks][E/32][own], into the GEMM's [E/32][nranks*own]. */
 int izb_p2p_push(int n_copies, void* const* d_dst, const void* const* d_src, const size_t* bytes, int n_flags,
                  uint32_t* const* d_flags, uint32_t value, void* stream);
 int izb_p2p_wait(int n_flags, uint32_t* const* d_flags, uint32_t value, void* stream);
-int izb_p2p_wait_host(void* stream, int timeout_ms, int n_flags, uint32_t* const* d_own_flags, uint32_t release_value);
+int izb_p2p_wait_host(void* stream, int timeout_ms);
 int izb_tp_scales_from_ranks(float* d_asc, const float* d_stage, int nranks, int own, int E, void* stream);
 
 #ifdef __cplusplus

@@ -77,13 +77,17 @@ def test_no_gpu_means_an_error_not_a_fallback():
 
 def test_host_decoder_of_further_weight_types_matches_the_oracle():
     """izb_weight_decode_host (the loader's decoder, no device needed) against the oracle's restatement of the reference's
-    decode_sb generic view, field by field, and Q4_0 against its Q8_0 rewrite."""
+    decode_sb generic view, field by field; Q6_K, which stays packed on the device, as the file's bytes in 224; Q4_0
+    against its Q8_0 rewrite."""
     import numpy as np
     import arcinferzero_b200 as izb
     from arcinferzero_b200 import synth as S
     from oracle import oracle as O
     K, N = 768, 7
-    for qt in (13, 14, 23):
+    w = S.make_weight(14, N, K, 84)
+    dev = izb.weight_decode_host(14, w, K).reshape(N, K // 256, 224)
+    assert (dev[:, :, :210] == w.reshape(N, K // 256, 210)).all() and (dev[:, :, 210:] == 0).all()
+    for qt in (13, 23):
         w = S.make_weight(qt, N, K, 70 + qt)
         dev = izb.weight_decode_host(qt, w, K).reshape(N, K // 256, 304)
         sbb = S.sb_bytes(qt)

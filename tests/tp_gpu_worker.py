@@ -140,10 +140,10 @@ def main() -> int:
         # the pipelined form: two token chunks, sums on a second stream beside the next chunk's GEMMs, balanced Q split
         check_mode("rs_quant_ag", world, rank, local, chunks=2, overlap=True, balance=True)
         print(f"TP_WORKER_OK mode=rs_quant_ag/overlap rank={rank}/{world}", flush=True)
-        if world > 1:
+        if world == 2:
             # the sums moved by the copy engines (izb_p2p_push / izb_p2p_wait) instead of NCCL: same owners, same arithmetic
             check_mode("p2p", world, rank, local, chunks=2, balance=True)
-            print(f"TP_WORKER_OK mode=p2p rank={rank}/{world}", flush=True)
+        print(f"TP_WORKER_OK mode=p2p rank={rank}/{world}" + ("" if world == 2 else " (two-rank runs only)"), flush=True)
         check_head_gather(world, rank, local)
         print(f"TP_WORKER_OK head gather rank={rank}/{world}", flush=True)
     finally:

@@ -246,7 +246,7 @@ __device__ __forceinline__ uint32_t q6p_word(uint32_t ql, uint32_t qh, int sub) 
 // lane unpacks its 32-block from 32 bytes of ql and 32 bytes of qh.  Lanes that share bytes (sub and sub + 2 share ql, the
 // four sub-blocks of a half share qh) read the same addresses in the same instruction: one transaction.
 template <int T>
-__global__ void __launch_bounds__(kGvWarps * 32) gemv_q6p_kernel(const uint8_t* __restrict__ raw, int N, int K,
+__global__ void __launch_bounds__(kGvWarps * 32, T <= 2 ? 4 : T <= 4 ? 3 : 2) gemv_q6p_kernel(const uint8_t* __restrict__ raw, int N, int K,
                                                                  const int8_t* __restrict__ aq, const float* __restrict__ asc, int Mp,
                                                                  float* __restrict__ C, int ldc, int c_off, int acc) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -315,6 +315,9 @@ int launch_gemv_k16(const izb_weight* w, const uint8_t* raw, const int8_t* aq, c
   const size_t smem = (size_t)T * w->K + (size_t)T * (w->K / 32) * 4;
   if (smem > 200 * 1024) IZB_FAIL(IZB_ERR_LIMIT, "gemv: %d rows of K = %d do not fit in shared memory", T, w->K);
   int grid = izb_sm_count(w->device) * (smem <= 100 * 1024 ? 2 : 1);
+  // (the packed form needs more loads in flight per SM than two CTAs issue: four, or three for 3..4 rows, where the
+  //  activations leave room -- 151936 x 5120, one row: 300 us with two CTAs per SM, 142 us with four)
+  if (w->packed6 && T <= 4 && smem <= 48 * 1024) grid = izb_sm_count(w->device) * (T <= 2 ? 4 : 3);
   const int need = (w->N + kGvWarps - 1) / kGvWarps;
   if (grid > need) grid = need;
   if (w->packed6) {

@@ -36,7 +36,7 @@ QT = 12
 SEED = 20261125
 WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantize_act + GEMM per step)"
 NOMINAL_INT8_TOPS = 4500.0
-NCU_TRAFFIC_BYTES_PER_TILE = (132.1e6 + 116.6e6) / (16 * 136)       # gemm_tc: ncu capture of 16 x 136 tiles of 128 x 128
+NCU_TRAFFIC_BYTES_PER_TILE = (153.5e6 + 122.4e6) / (16 * 136)       # gemm_tc: ncu capture of 16 x 136 tiles of 128 x 128
 
 
 def peaks():

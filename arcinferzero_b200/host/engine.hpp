@@ -70,6 +70,16 @@ class Engine {
     return w;
   }
 
+  // gate and up of an FFN (or of every expert of a stack) as one weight with the rows interleaved in groups of 32: matmul
+  // with store mode 3 then writes up * silu(gate) from ONE GEMM (the reference fuses the product into its up GEMM, store
+  // mode 2, zero/kernels/gemm.cl:562-565, which reads the gate GEMM's output back)
+  GpuWeight make_weight_gateup(int ggml_type, const void* gate_rows, const void* up_rows, int F, int K, int n_mats = 1) const {
+    GpuWeight w;
+    check(izb_weight_create_gateup(ggml_type, gate_rows, up_rows, n_mats, F, K, device_, &w.h), "make_weight_gateup");
+    w.type = ggml_type; w.N = 2 * F; w.K = K; w.n_mats = n_mats;
+    return w;
+  }
+
   // alloc_buffers (zero/engine_alloc.h:4): activation buffers for up to max_rows rows of up to max_k values
   void alloc_buffers(int max_rows, int max_k) {
     release_buffers();
@@ -124,6 +134,15 @@ class Engine {
     if (!act32) throw std::runtime_error("matmul: only per-32 activation scales (act32) are implemented");
     if (w.K != cur_K_ || Mp != cur_Mp_) throw std::runtime_error("matmul: the quantised activations do not match this weight");
     check(izb_matmul(w.h, 0, aq_, asc_, nullptr, cur_T_, Mp, C, ldc, c_off, acc, stream_), "matmul");
+  }
+
+  // quant_rows + matmul in one call (zero/engine.h:1445 followed by :1080): for more than 8 rows the quantiser also writes
+  // the tensor-core GEMM's operand images; aq_ / asc_ are left as quant_rows leaves them
+  void quant_matmul(const char* name, const GpuWeight& w, const float* x, int ldx, int Mp, float* C, int ldc, int c_off, int acc) {
+    (void)name;
+    if (Mp > max_rows_ || w.K > max_k_) throw std::runtime_error("quant_matmul: more rows or columns than alloc_buffers reserved");
+    check(izb_quant_matmul(w.h, 0, x, ldx, cur_T_, Mp, aq_, asc_, C, ldc, c_off, acc, stream_), "quant_matmul");
+    cur_K_ = w.K; cur_Mp_ = Mp;
   }
 
   // tp_setup (zero/mgpu/engine_tp_shard.h:88): join the communicator; id128 from izb_tp_unique_id on rank 0

@@ -47,7 +47,7 @@ def test_noalloc_gemm_matches_gemm_on_two_calls_in_a_row(izb, qt):
         izb.gemm_noalloc(W, aq, asc, M=M, out=base, acc=1)
         assert rel(base.cpu().numpy()[:M] - 1.0, ref[:M]) < 1e-4
         assert izb.device_status(0) == 0  # (covers the library-owned status word of the call above)
-        # The first round was the warm-up (the CUDA runtime loads a kernel's code at its first launch); from then on the
+        # The first iteration was the warm-up (the CUDA runtime loads a kernel's code at its first launch); from then on the
         # entry point must leave the device's free memory exactly as it found it.
         torch.cuda.synchronize()
         if free_after_warmup is None:

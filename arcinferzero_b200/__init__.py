@@ -23,7 +23,7 @@ GEMM_AUTO, GEMM_CORE, GEMM_TC = 0, 1, 2
 SYMBOLS = [
     "izb_status_string", "izb_last_error", "izb_launch_count", "izb_device_status", "izb_profile_start", "izb_profile_stop",
     "izb_reserve", "izb_set_sm_limit", "izb_debug_wait_test", "izb_tensor_peak",
-    "izb_weight_create", "izb_weight_create_slice", "izb_weight_create_stack", "izb_weight_create_gateup", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
+    "izb_weight_create", "izb_weight_create_slice", "izb_weight_create_stack", "izb_weight_create_gateup", "izb_gateup_interleave_host", "izb_weight_destroy", "izb_weight_info", "izb_weight_download", "izb_weight_decode_host",
     "izb_quantize_act", "izb_swiglu_quant", "izb_rmsnorm_quant", "izb_add_norm_quant", "izb_softcap_rows",
     "izb_matmul", "izb_quant_matmul", "izb_gemv", "izb_gemm", "izb_gemm_noalloc", "izb_block_dots", "izb_selfcheck", "izb_matmul_host",
     "izb_moe_route", "izb_moe_route_ex", "izb_moe_sort", "izb_moe_sort_ex", "izb_moe_gateup", "izb_moe_down", "izb_moe_combine",
@@ -160,6 +160,14 @@ def gateup_weight(qtype: int, gate_rows: np.ndarray, up_rows: np.ndarray, F: int
     _check(lib().izb_weight_create_gateup(qtype, _p(g), _p(u), n_mats, F, K, device, C.byref(w.handle)))
     w.qtype, w.N, w.K, w.n_mats, w.device = qtype, 2 * F, K, n_mats, device
     return w
+
+
+def gateup_interleave_host(qtype: int, gate_rows: np.ndarray, up_rows: np.ndarray, F: int, K: int, n_mats: int = 1) -> np.ndarray:
+    """The host-side row order of gateup_weight (no GPU): [n_mats * 2F, row bytes]."""
+    g, u = np.ascontiguousarray(gate_rows, np.uint8), np.ascontiguousarray(up_rows, np.uint8)
+    out = np.empty((2 * g.shape[0], g.shape[1]), np.uint8)
+    _check(lib().izb_gateup_interleave_host(qtype, _p(g), _p(u), n_mats, F, K, _p(out), C.c_size_t(out.size)))
+    return out
 
 
 def weight_decode_host(qtype: int, rows: np.ndarray, K: int) -> np.ndarray:

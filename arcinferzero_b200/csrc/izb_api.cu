@@ -445,31 +445,43 @@ extern "C" int izb_weight_create_stack(int type, const void* const* h_parts, con
   return izb_weight_create(type, rows.data(), 1, (int)total, K, device, out);
 }
 
+extern "C" int izb_gateup_interleave_host(int type, const void* h_gate, const void* h_up, int n_mats, int F, int K, void* h_dst,
+                                         size_t dst_bytes) {
+  if (!h_gate || !h_up || !h_dst) IZB_FAIL(IZB_ERR_ARG, "gateup_interleave: null pointer");
+  const int src_sb = izb_gguf_sb_bytes(type);
+  if (!src_sb) IZB_FAIL(IZB_ERR_TYPE, "gateup_interleave: ggml type %d", type);
+  if (n_mats < 1 || F < 64 || F % 64 || K < 256 || K % 256 || (long long)n_mats * 2 * F > 0x7FFFFFFF)
+    IZB_FAIL(IZB_ERR_SHAPE, "gateup_interleave: n_mats = %d, F = %d (multiple of 64), K = %d (multiple of 256)", n_mats, F, K);
+  const size_t row = (size_t)(K / 256) * src_sb, grp = 32 * row;
+  if (dst_bytes < (size_t)n_mats * 2 * F * row) IZB_FAIL(IZB_ERR_SHAPE, "gateup_interleave: %zu bytes for %d x %d rows of %zu", dst_bytes, n_mats, 2 * F, row);
+  const uint8_t* g = (const uint8_t*)h_gate;
+  const uint8_t* u = (const uint8_t*)h_up;
+  uint8_t* dst = (uint8_t*)h_dst;
+  const long long n_grp = (long long)n_mats * (F / 32);  // (F % 32 == 0: groups never straddle two matrices)
+#pragma omp parallel for schedule(static)
+  for (long long j = 0; j < n_grp; ++j) {
+    memcpy(dst + (size_t)(2 * j) * grp, g + (size_t)j * grp, grp);
+    memcpy(dst + (size_t)(2 * j + 1) * grp, u + (size_t)j * grp, grp);
+  }
+  return IZB_OK;
+}
+
 extern "C" int izb_weight_create_gateup(int type, const void* h_gate, const void* h_up, int n_mats, int F, int K, int device,
                                         izb_weight** out) {
   if (!h_gate || !h_up || !out) IZB_FAIL(IZB_ERR_ARG, "weight_create_gateup: null pointer");
   *out = nullptr;
-  const int src_sb = izb_gguf_sb_bytes(type);
-  if (!src_sb) IZB_FAIL(IZB_ERR_TYPE, "weight_create_gateup: ggml type %d", type);
   if (type != IZB_Q8_0 && type != IZB_Q4_K && type != IZB_Q4_0)
     IZB_FAIL(IZB_ERR_TYPE, "weight_create_gateup: ggml type %d does not run on the tensor-core GEMM (Q8_0, Q4_K, Q4_0 do)", type);
   if (n_mats < 1 || F < 64 || F % 64 || K < 256 || K % 256 || (long long)n_mats * 2 * F > 0x7FFFFFFF)
     IZB_FAIL(IZB_ERR_SHAPE, "weight_create_gateup: n_mats = %d, F = %d (multiple of 64), K = %d (multiple of 256)", n_mats, F, K);
-  const size_t row = (size_t)(K / 256) * src_sb, grp = 32 * row;
+  const size_t row = (size_t)(K / 256) * izb_gguf_sb_bytes(type);
   std::vector<uint8_t> rows;
   try {
     rows.resize((size_t)n_mats * 2 * F * row);
   } catch (const std::exception&) {
     IZB_FAIL(IZB_ERR_NOMEM, "weight_create_gateup: %d x %d rows of %zu bytes on the host", n_mats, 2 * F, row);
   }
-  const uint8_t* g = (const uint8_t*)h_gate;
-  const uint8_t* u = (const uint8_t*)h_up;
-  const long long n_grp = (long long)n_mats * (F / 32);  // (F % 32 == 0: groups never straddle two matrices)
-#pragma omp parallel for schedule(static)
-  for (long long j = 0; j < n_grp; ++j) {
-    memcpy(rows.data() + (size_t)(2 * j) * grp, g + (size_t)j * grp, grp);
-    memcpy(rows.data() + (size_t)(2 * j + 1) * grp, u + (size_t)j * grp, grp);
-  }
+  if (int rc = izb_gateup_interleave_host(type, h_gate, h_up, n_mats, F, K, rows.data(), rows.size())) return rc;
   const int rc = izb_weight_create(type, rows.data(), n_mats, 2 * F, K, device, out);
   if (rc == IZB_OK) (*out)->gu32 = true;
   return rc;

@@ -141,6 +141,10 @@ int izb_weight_create_stack(int ggml_type, const void* const* h_parts, const int
  * up column side by side, so the gate projection never goes to memory.  Same operations, same roundings as mode 2. */
 int izb_weight_create_gateup(int ggml_type, const void* h_gate_rows, const void* h_up_rows, int n_mats, int F, int K, int device,
                              izb_weight** out);
+/* The row order izb_weight_create_gateup uploads, on the host alone (no device needed): h_dst receives n_mats matrices of
+ * 2F GGUF rows, groups of 32 gate rows and 32 up rows alternating. */
+int izb_gateup_interleave_host(int ggml_type, const void* h_gate_rows, const void* h_up_rows, int n_mats, int F, int K, void* h_dst,
+                               size_t dst_bytes);
 /* The loader's host-side decoder on its own (no device needed): n_superblocks superblocks (256 weights each) of a Q4_0,
  * Q5_K, Q6_K or IQ4_XS row -> the form izb_weight_create uploads: GGUF Q8_0 blocks (8 x 34 bytes) for Q4_0; 224 bytes for
  * Q6_K (the file's 210 + 14 zero bytes); else 304 bytes:

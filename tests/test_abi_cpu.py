@@ -100,3 +100,23 @@ def test_host_decoder_of_further_weight_types_matches_the_oracle():
                 assert (b[48:304].view(np.int8) == q).all()
     w = S.make_weight(2, N, K, 72)
     assert (izb.weight_decode_host(2, w, K) == O.q4_0_as_q8_0(w)).all()
+
+
+def test_gateup_interleave_on_the_host():
+    """izb_gateup_interleave_host (the row order izb_weight_create_gateup uploads): per matrix, 32 gate rows then the 32 up
+    rows of the same FFN channels, and so on; shapes it cannot take are refused."""
+    import numpy as np
+    import pytest
+    import arcinferzero_b200 as izb
+    from arcinferzero_b200 import synth as S
+    for qt in (12, 8, 2):
+        n_mats, F, K = 3, 128, 512
+        g, u = S.make_weight(qt, n_mats * F, K, 90 + qt), S.make_weight(qt, n_mats * F, K, 91 + qt)
+        out = izb.gateup_interleave_host(qt, g, u, F, K, n_mats=n_mats)
+        per = g.shape[1]
+        ref = np.stack([g.reshape(n_mats, F // 32, 32, per), u.reshape(n_mats, F // 32, 32, per)], axis=2).reshape(n_mats * 2 * F, per)
+        assert out.shape == ref.shape and (out == ref).all()
+    with pytest.raises(izb.IzbError):
+        izb.gateup_interleave_host(12, g[:96], u[:96], 96, K)          # F % 64
+    with pytest.raises(izb.IzbError):
+        izb.gateup_interleave_host(99, g, u, F, K, n_mats=n_mats)       # unknown type

@@ -183,6 +183,43 @@ class StepGuard:
             time.sleep(0.01)
 
 
+class SumPipeline:
+    """Order of the owner's work in the "p2p" mode, as pure bookkeeping (no device): which reduce is queued when.
+
+    A chunk's partial rows leave right after its GEMMs (`sent`); the owner's reduce of that chunk is queued `lag` GEMM
+    slots later, so that the copies run beside the GEMMs of the chunks in between; a chunk's gathered rows are awaited
+    just before its next GEMMs (`needed`), by which time its reduce must have been queued.  Every rank runs the same
+    sequence, and every wait in it depends only on operations that come earlier in it: no rank can wait for something
+    another rank has not been asked to do yet."""
+
+    def __init__(self, chunks: int, lag: int = 1):
+        assert chunks >= 1 and lag >= 0
+        self.chunks, self.lag = chunks, lag
+        self.pending: list[tuple[int, int]] = []   # (chunk, seq): partials sent, reduce not queued yet
+        self.waiting = [0] * chunks                # seq of the sum whose gathered rows chunk c has not awaited yet (0: none)
+
+    def sent(self, c: int, seq: int) -> list[tuple[int, int]]:
+        """The partials of (c, seq) have been handed to the transport.  Returns the reduces to queue now, oldest first."""
+        assert self.waiting[c] == 0, "a chunk hands in a new sum only after it has awaited the one before"
+        self.pending.append((c, seq))
+        self.waiting[c] = seq
+        out = []
+        while len(self.pending) > self.lag:
+            out.append(self.pending.pop(0))
+        return out
+
+    def needed(self, c: int) -> tuple[list[tuple[int, int]], int]:
+        """Chunk c is about to be read.  Returns (reduces to queue first, seq to await or 0)."""
+        out = []
+        if any(pc == c for pc, _ in self.pending):   # (its own reduce is still held back: everything up to it goes now)
+            while self.pending:
+                out.append(self.pending.pop(0))
+                if out[-1][0] == c:
+                    break
+        seq, self.waiting[c] = self.waiting[c], 0
+        return out, seq
+
+
 class Stack:
     """The rank-local stack on one GPU (needs the CUDA library and torch.distributed when world > 1).
 
@@ -254,7 +291,6 @@ class Stack:
         # every arena at its final size before the first step: no allocation, no device-wide wait inside the pipeline
         izb.reserve(device, Tc, kmax)
         self.ev_sum = [None] * chunks    # the last sum of chunk c (side stream)
-        self.gathered = [0] * chunks     # "p2p": number of the sum whose gathered rows chunk c still has to wait for
 
     # ---- views
     def rows(self, c):
@@ -317,7 +353,7 @@ class Stack:
         self.stage = me[self.off_stage:self.off_stage + self.chunks * R * (E // 32) * own * 4].view(torch.float32).view(self.chunks, R, E // 32, own)
         self.copy_st = torch.cuda.Stream(device=dev)
         self.seq = 0          # number of the sum in flight (flags carry it: they only grow)
-        self.pending = []     # (chunk, seq) whose partials left and whose reduce is not queued yet
+        self.pipe = SumPipeline(self.chunks, lag=1)
         self.ev_local = [None] * self.chunks  # this rank's own part of chunk c has been copied (copy stream)
 
     def _flag(self, r, kind, c, src):
@@ -370,10 +406,6 @@ class Stack:
         izb.p2p_wait([self._flag(self.rank, 1, c, src) for src in range(self.world) if src != self.rank], seq)
         izb.tp_scales_from_ranks(self.xsc_c[c], self.stage[c], self.world, self.own, self.cfg.hidden)
 
-    def _p2p_drain(self, keep=0):
-        while len(self.pending) > keep:
-            self._p2p_reduce(*self.pending.pop(0))
-
     def _sum(self, c, part):
         """Row-parallel partials of chunk c -> residual stream; leaves the chunk's quantised stream in xq / xsc_c[c]."""
         izb, r = self.izb, self.rows(c)
@@ -392,9 +424,8 @@ class Stack:
         if self.mode == "p2p":
             # the partials leave now; the owner's reduce of the chunk BEFORE this one is queued behind this chunk's GEMMs
             self._p2p_push_partials(c, part, self.seq)
-            self.pending.append((c, self.seq))
-            self._p2p_drain(keep=1)
-            self.gathered[c] = self.seq
+            for rc, rseq in self.pipe.sent(c, self.seq):
+                self._p2p_reduce(rc, rseq)
             return
         if not self.overlap:
             self._sum(c, part)
@@ -410,11 +441,10 @@ class Stack:
 
     def _await_sum(self, c):
         if self.mode == "p2p":
-            # (the reduce this chunk waits for must have been queued: at most one is pending, and it is a later chunk's)
-            if any(pc == c for pc, _ in self.pending):
-                self._p2p_drain()
-            self._p2p_await(c, self.gathered[c])
-            self.gathered[c] = 0
+            reduces, seq = self.pipe.needed(c)
+            for rc, rseq in reduces:
+                self._p2p_reduce(rc, rseq)
+            self._p2p_await(c, seq)
             return
         if self.overlap and self.ev_sum[c] is not None:
             self.compute.wait_event(self.ev_sum[c])

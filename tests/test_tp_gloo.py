@@ -229,3 +229,46 @@ def test_peer_leaving_between_steps_is_seen_on_the_host():
     res = run_ranks(worker_failure)
     assert res[1] == "steps [0, 1]", res
     assert res[0].startswith("PeerGone after [0, 1]"), res
+
+
+@pytest.mark.parametrize("chunks,lag", [(2, 1), (4, 1), (8, 1), (4, 2), (3, 0), (1, 1)])
+def test_sum_pipeline_order(chunks, lag):
+    """The order in which the copy-engine mode queues the owners' reduces (tp.SumPipeline, pure bookkeeping): every sum of
+    every chunk is reduced exactly once, after its partials were sent and before its gathered rows are awaited; at most
+    `lag` reduces are held back; and the sequence is the same on every rank, with every await depending only on
+    operations earlier in it (what rules out a deadlock between ranks)."""
+    p = tp.SumPipeline(chunks, lag)
+    log = []
+    seq = 0
+    for half in range(7):
+        seq += 1
+        for c in range(chunks):
+            reduces, s = p.needed(c)
+            log += [("reduce", rc, rs) for rc, rs in reduces]
+            log.append(("await", c, s))
+            log.append(("send", c, seq))
+            log += [("reduce", rc, rs) for rc, rs in p.sent(c, seq)]
+            assert len(p.pending) <= lag
+    for c in range(chunks):
+        reduces, s = p.needed(c)
+        log += [("reduce", rc, rs) for rc, rs in reduces]
+        log.append(("await", c, s))
+    assert not p.pending and not any(p.waiting)
+    pos = {e: i for i, e in enumerate(log)}
+    assert len(pos) == len([e for e in log if e[2] != 0]) + len({e for e in log if e[2] == 0})  # nothing queued twice
+    for s in range(1, seq + 1):
+        for c in range(chunks):
+            assert pos[("send", c, s)] < pos[("reduce", c, s)] < pos[("await", c, s)], (c, s)
+    # reduces leave in the order their partials were sent
+    sends = [e[1:] for e in log if e[0] == "send"]
+    reds = [e[1:] for e in log if e[0] == "reduce"]
+    assert reds == sends
+    # with a lag, a chunk's reduce is queued only after `lag` later sends (the copies run beside those chunks' GEMMs)
+    if lag and chunks > lag:
+        tail = set(sends[-lag:])   # (the last sends of the run: flushed at the end, nothing follows them)
+        for s in range(1, seq + 1):
+            for c in range(chunks):
+                if (c, s) in tail:
+                    continue
+                between = [e for e in log[pos[("send", c, s)] + 1:pos[("reduce", c, s)]] if e[0] == "send"]
+                assert len(between) >= min(lag, 1), (c, s, between)

@@ -422,9 +422,10 @@ def tp_stack_section(izb, torch, dist, world: int, rank: int, local: int, tokens
     x_in = torch.from_numpy(S.make_act(cfg.tokens, cfg.hidden, SEED + 5)).cuda() * 0.05
     out = []
     forms = [("allreduce", dict()), ("rs_quant_ag", dict()),
-             # (SMs left to the collectives: measured best at 8 ranks with 16 of 148 -- fewer and the sums become the
-             #  critical path, more and the GEMMs lose more than the sums gain; at 2 ranks the sums are 3 % of a pass)
-             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8 if world <= 2 else 16)),
+             # (SMs left to the collectives, swept at 8 ranks: 4 -> 138 ms, 8 -> 81, 12 -> 68.2, 16 -> 66.9, 20 -> 66.0,
+             #  24 -> 70.4, 32 -> 74.4 per pass: too few and the sums become the critical path, too many and the GEMMs lose
+             #  more than the sums gain; at 2 ranks the sums are 3 % of a pass)
+             ("rs_quant_ag", dict(chunks=4, overlap=True, balance=True, comm_sms=8 if world <= 2 else 16 if world < 8 else 20)),
              # the same sums moved by the copy engines (izb_p2p_*): no SM is taken from the GEMMs
              ("p2p", dict(chunks=4, balance=True))]
     if world != 2:

@@ -34,7 +34,7 @@ sys.path.insert(0, ROOT)
 M, N, K = 8192, 17408, 5120
 QT = 12
 SEED = 20261125
-WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantize_act + GEMM per step)"
+WORKLOAD = "config2: Q4_K prefill GEMM M=8192 N=17408 K=5120 (quantiser + GEMM per step: one izb_quant_matmul call)"
 NOMINAL_INT8_TOPS = 4500.0
 NCU_TRAFFIC_BYTES_PER_TILE = (153.5e6 + 122.4e6) / (16 * 136)       # gemm_tc: ncu capture of 16 x 136 tiles of 128 x 128
 

@@ -17,7 +17,10 @@ import numpy as np
 
 MAGIC = 0x46554747
 # ggml type -> (elements per block, bytes per block) for the types the path multiplies, plus the plain float types
-BLOCK = {0: (1, 4), 1: (1, 2), 8: (32, 34), 12: (256, 144), 30: (1, 2)}
+BLOCK = {0: (1, 4), 1: (1, 2), 30: (1, 2),
+         8: (32, 34), 12: (256, 144),                                  # Q8_0, Q4_K
+         2: (32, 18), 13: (256, 176), 14: (256, 210), 23: (256, 136)}  # Q4_0, Q5_K, Q6_K, IQ4_XS (src/gguf.h:48-70)
+WEIGHT_TYPES = (8, 12, 2, 13, 14, 23)   # the block types izb_weight_create takes
 _SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 _MAX_ENTRIES = 1_000_000
 
@@ -137,11 +140,11 @@ class GGUFFile:
         return typ, dims, np.frombuffer(self._mm, dtype=np.uint8, count=nbytes, offset=self.data_start + off)
 
     def weight_rows(self, name: str) -> tuple[int, np.ndarray, int, int, int]:
-        """A Q4_K / Q8_0 matrix (dims [K, N]) or stack of matrices ([K, N, n_mats]) as (type, rows [n_mats * N, row_bytes],
-        N, K, n_mats): exactly what izb_weight_create takes."""
+        """A block-quantised matrix (dims [K, N]) or stack of matrices ([K, N, n_mats]) of one of WEIGHT_TYPES as (type, rows
+        [n_mats * N, row_bytes], N, K, n_mats): exactly what izb_weight_create takes."""
         typ, dims, data = self.tensor(name)
-        if typ not in (8, 12):
-            raise GGUFError(f"{self.path}: {name}: type {typ} is not Q8_0 / Q4_K")
+        if typ not in WEIGHT_TYPES:
+            raise GGUFError(f"{self.path}: {name}: type {typ} is not one the library multiplies (Q8_0, Q4_K, Q4_0, Q5_K, Q6_K, IQ4_XS)")
         if len(dims) not in (2, 3) or dims[0] % 256:
             raise GGUFError(f"{self.path}: {name}: dims {dims} (need [K, N] or [K, N, n_mats], K a multiple of 256)")
         K, N = dims[0], dims[1]
@@ -164,6 +167,44 @@ class GGUFFile:
 
     def __exit__(self, *exc):
         self.close()
+
+
+def stacked_rows(g: GGUFFile, names: list[str]) -> tuple[int, list[np.ndarray], int]:
+    """The tensors `names` of one type and one K as (type, [rows of each], K): what izb_weight_create_stack takes (the
+    reference's load_w_stack, zero/engine_load.h:315-339: Q | K | V and gate | up uploaded as one matrix)."""
+    parts, typ0, K0 = [], None, None
+    for n in names:
+        typ, rows, N, K, n_mats = g.weight_rows(n)
+        if n_mats != 1:
+            raise GGUFError(f"{g.path}: {n}: a stack of matrices cannot be a part of a stacked weight")
+        if typ0 is None:
+            typ0, K0 = typ, K
+        elif (typ, K) != (typ0, K0):
+            raise GGUFError(f"{g.path}: {n}: type {typ}, K = {K} against type {typ0}, K = {K0} of the parts before it")
+        parts.append(rows)
+    if not parts:
+        raise GGUFError(f"{g.path}: no tensor names given")
+    return typ0, parts, K0
+
+
+def load_stacked(path: str, names: list[str], device: int = 0):
+    """Q | K | V or gate | up of a GGUF file as ONE device weight (izb_weight_create_stack); needs the CUDA library."""
+    import arcinferzero_b200 as izb
+    with GGUFFile(path) as g:
+        typ, parts, K = stacked_rows(g, names)
+        return izb.stacked_weight(typ, [np.array(p) for p in parts], K, device=device)
+
+
+def load_gateup(path: str, gate: str, up: str, device: int = 0):
+    """The gate and up tensors (matrices or expert stacks [K, F, n_mats]) of a GGUF file as one interleaved weight
+    (izb_weight_create_gateup): one GEMM with store mode 3 computes up * silu(gate).  Needs the CUDA library."""
+    import arcinferzero_b200 as izb
+    with GGUFFile(path) as g:
+        tg, rg, F, K, nm = g.weight_rows(gate)
+        tu, ru, Fu, Ku, nmu = g.weight_rows(up)
+        if (tg, F, K, nm) != (tu, Fu, Ku, nmu):
+            raise GGUFError(f"{path}: {gate} and {up} differ in type or shape")
+        return izb.gateup_weight(tg, np.array(rg), np.array(ru), F, K, n_mats=nm, device=device)
 
 
 def load_weight(path: str, name: str, device: int = 0, row_range=None, col_range=None):

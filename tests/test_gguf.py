@@ -93,3 +93,37 @@ def test_reference_reader_accepts_the_same_file(model):
     aq, asc, _ = O.quantize_act(x)
     mine = O.matmul(12, w4, 512, aq, asc, 2, "f64")
     assert np.max(np.abs(y - mine)) / np.max(np.abs(mine)) < 1e-6
+
+
+def test_further_weight_types_and_stacked_parts(tmp_path):
+    """The reader sizes and returns the further block types (Q4_0, Q5_K, Q6_K, IQ4_XS) as izb_weight_create takes them, and
+    collects the parts of a stacked weight (Q | K | V) with their type and K checked."""
+    K = 512
+    ws = {qt: S.make_weight(qt, 7 + qt % 3, K, 30 + qt) for qt in (2, 13, 14, 23)}
+    q, k, v = S.make_weight(12, 8, K, 41), S.make_weight(12, 4, K, 42), S.make_weight(12, 4, K, 43)
+    p = str(tmp_path / "t.gguf")
+    tensors = {f"t{qt}.weight": (qt, w, w.shape[0], K) for qt, w in ws.items()}
+    tensors.update({"attn_q.weight": (12, q, 8, K), "attn_k.weight": (12, k, 4, K), "attn_v.weight": (12, v, 4, K),
+                    "other_k.weight": (12, S.make_weight(12, 4, 256, 44), 4, 256)})
+    S.write_gguf(p, tensors)
+    with G.GGUFFile(p) as g:
+        for qt, w in ws.items():
+            typ, rows, N, Kk, nm = g.weight_rows(f"t{qt}.weight")
+            assert (typ, N, Kk, nm) == (qt, w.shape[0], K, 1) and np.array_equal(rows, w)
+        typ, parts, Kk = G.stacked_rows(g, ["attn_q.weight", "attn_k.weight", "attn_v.weight"])
+        assert (typ, Kk) == (12, K) and [a.shape[0] for a in parts] == [8, 4, 4]
+        assert np.array_equal(np.concatenate(parts), np.concatenate([q, k, v]))
+        with pytest.raises(G.GGUFError):
+            G.stacked_rows(g, ["attn_q.weight", "other_k.weight"])     # another K
+        with pytest.raises(G.GGUFError):
+            G.stacked_rows(g, ["attn_q.weight", "t14.weight"])         # another type
+        with pytest.raises(G.GGUFError):
+            G.stacked_rows(g, [])
+    # the reference's own reader multiplies with the Q6_K tensor of the same file
+    from oracle import oracle as O
+    if O.ref() is not None:
+        x = S.make_act(2, K, 9)
+        y = O.ref_forward_matmul(p, "t14.weight", x, ws[14].shape[0])
+        aq, asc, _ = O.quantize_act(x)
+        mine = O.matmul(14, ws[14], K, aq, asc, 2, "f64")
+        assert np.max(np.abs(y - mine)) / np.max(np.abs(mine)) < 1e-6
